@@ -1,0 +1,244 @@
+"""The cache manager: which pages and which state slot each live request holds.
+
+Host-side only; the tensors live in :mod:`kairyu_b200.cache.storage`.
+
+Cache slots (one per schedule call that writes a cache) with equal page
+geometry and window form a *group*; each group has its own page pool and its
+own block table per request, because a group that keeps every key and a group
+that keeps a window of them fill and empty at different rates.  A request's
+table for a group maps page index ``position // page_size`` to a physical page,
+or -1 once a windowed group has given the page back.
+
+The reference's dense pool is uniform (one table per request,
+kairyu/engine/core/radix_kv.py:144-149); groups generalise it the way its
+hybrid cache descriptors do (kairyu/engine/core/frontier_cache.py:19-75).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Hashable, Iterable, Mapping, Optional, Sequence
+
+from kairyu_b200.cache.page_pool import OutOfPages, PagePool
+from kairyu_b200.parts.base import PagedKVSpec, StateSpec
+
+
+@dataclass(frozen=True)
+class CacheGroup:
+    index: int
+    spec: PagedKVSpec
+    slots: tuple[int, ...]  # cache slots stored in this group, in storage order
+
+
+@dataclass(frozen=True)
+class StateBinding:
+    slot: int  # cache slot
+    index: int  # which of the slot's StateSpecs
+    spec: StateSpec
+
+
+@dataclass(frozen=True)
+class CacheLayout:
+    """Groups of paged slots and the list of per-request state tensors."""
+
+    groups: tuple[CacheGroup, ...]
+    states: tuple[StateBinding, ...]
+    group_of_slot: Mapping[int, int]
+
+    @classmethod
+    def from_slot_specs(cls, slot_specs: Mapping[int, Sequence[Any]]) -> "CacheLayout":
+        by_spec: dict[PagedKVSpec, list[int]] = {}
+        states: list[StateBinding] = []
+        for slot in sorted(slot_specs):
+            paged = [s for s in slot_specs[slot] if isinstance(s, PagedKVSpec)]
+            if len(paged) > 1:
+                raise ValueError(f"cache slot {slot} asks for more than one paged cache")
+            if paged:
+                by_spec.setdefault(paged[0], []).append(slot)
+            for index, spec in enumerate(s for s in slot_specs[slot] if isinstance(s, StateSpec)):
+                states.append(StateBinding(slot, index, spec))
+        groups = tuple(
+            CacheGroup(index, spec, tuple(slots)) for index, (spec, slots) in enumerate(by_spec.items())
+        )
+        group_of_slot = {slot: group.index for group in groups for slot in group.slots}
+        return cls(groups, tuple(states), group_of_slot)
+
+
+@dataclass
+class RequestCache:
+    request_id: Hashable
+    state_slot: int
+    tables: list[list[int]]  # per group: page index -> physical page or -1
+    first_live: list[int]  # per group: lowest page index still held
+    num_tokens: int = 0  # positions [0, num_tokens) have been computed
+
+
+class CacheManager:
+    def __init__(
+        self,
+        layout: CacheLayout,
+        *,
+        num_pages: int,
+        page_size: int,
+        max_requests: int,
+        reserved_pages: int = 1,
+    ) -> None:
+        if page_size < 1:
+            raise ValueError("page_size must be >= 1")
+        self.layout = layout
+        self.page_size = page_size
+        self.num_pages = num_pages
+        self.pools = [PagePool(num_pages, reserved=reserved_pages) for _ in layout.groups]
+        self.max_requests = max_requests
+        self._free_state_slots = list(range(max_requests - 1, -1, -1))
+        self._requests: dict[Hashable, RequestCache] = {}
+        self.fresh_state_slots: list[int] = []  # slots handed out since the storage last zeroed them
+
+    # ------------------------------------------------------------------ queries
+    def __contains__(self, request_id: Hashable) -> bool:
+        return request_id in self._requests
+
+    def get(self, request_id: Hashable) -> RequestCache:
+        return self._requests[request_id]
+
+    @property
+    def live_requests(self) -> int:
+        return len(self._requests)
+
+    def free_pages(self, group: int = 0) -> int:
+        return self.pools[group].num_free
+
+    def pages_for(self, num_tokens: int) -> int:
+        return -(-num_tokens // self.page_size)
+
+    def _first_needed_page(self, group: CacheGroup, query_start: int) -> int:
+        """Lowest page index a query at ``query_start`` (or later) can read."""
+        if group.spec.window is None:
+            return 0
+        return max(0, query_start - group.spec.window + 1) // self.page_size
+
+    def pages_needed(self, request_id: Optional[Hashable], upto: int, query_start: int) -> list[int]:
+        """New pages per group to cover positions [.., upto) for queries from ``query_start``."""
+        needed = []
+        record = self._requests.get(request_id) if request_id is not None else None
+        for group in self.layout.groups:
+            first = self._first_needed_page(group, query_start)
+            last = self.pages_for(upto)
+            if record is None:
+                needed.append(max(0, last - first))
+            else:
+                table = record.tables[group.index]
+                held = sum(1 for index in range(first, min(last, len(table))) if table[index] >= 0)
+                needed.append(max(0, last - first) - held)
+        return needed
+
+    def can_hold(self, num_tokens: int) -> bool:
+        """Whether an empty cache could ever hold a request of this many tokens."""
+        for group, pool in zip(self.layout.groups, self.pools):
+            if group.spec.window is None:
+                pages = self.pages_for(num_tokens)
+            else:
+                pages = min(self.pages_for(num_tokens), self.pages_for(group.spec.window) + 2)
+            if pages > pool.capacity:
+                return False
+        return True
+
+    # ------------------------------------------------------------------ lifecycle
+    def admit(self, request_id: Hashable) -> RequestCache:
+        if request_id in self._requests:
+            raise ValueError(f"request {request_id!r} is already live")
+        if not self._free_state_slots:
+            raise OutOfPages(f"all {self.max_requests} request slots are in use")
+        slot = self._free_state_slots.pop()
+        self.fresh_state_slots.append(slot)
+        record = RequestCache(
+            request_id,
+            slot,
+            tables=[[] for _ in self.layout.groups],
+            first_live=[0 for _ in self.layout.groups],
+        )
+        self._requests[request_id] = record
+        return record
+
+    def ensure_capacity(self, request_id: Hashable, upto: int, *, query_start: Optional[int] = None) -> bool:
+        """Hold pages for positions up to ``upto`` (exclusive) as seen by queries
+        from ``query_start`` (default: the request's computed length).  All
+        groups or nothing: returns False, changing nothing, if any pool is short."""
+        record = self._requests[request_id]
+        if query_start is None:
+            query_start = record.num_tokens
+        needed = self.pages_needed(request_id, upto, query_start)
+        if any(count > pool.num_free for count, pool in zip(needed, self.pools)):
+            return False
+        last = self.pages_for(upto)
+        for group, pool in zip(self.layout.groups, self.pools):
+            table = record.tables[group.index]
+            first = self._first_needed_page(group, query_start)
+            while len(table) < last:
+                table.append(-1)
+            for index in range(first, last):
+                if table[index] < 0:
+                    table[index] = pool.allocate(1)[0]
+        return True
+
+    def advance(self, request_id: Hashable, num_tokens: int) -> None:
+        """Record that positions [0, num_tokens) are computed and give back the
+        pages of windowed groups that no later query can read."""
+        record = self._requests[request_id]
+        if num_tokens < record.num_tokens:
+            raise ValueError("a request's computed length cannot shrink")
+        record.num_tokens = num_tokens
+        for group, pool in zip(self.layout.groups, self.pools):
+            if group.spec.window is None:
+                continue
+            table = record.tables[group.index]
+            keep_from = self._first_needed_page(group, num_tokens)
+            stale = []
+            for index in range(record.first_live[group.index], min(keep_from, len(table))):
+                if table[index] >= 0:
+                    stale.append(table[index])
+                    table[index] = -1
+            if stale:
+                pool.free(stale)
+            record.first_live[group.index] = max(record.first_live[group.index], min(keep_from, len(table)))
+
+    def release(self, request_id: Hashable) -> None:
+        """The request ended (finished, aborted or preempted): everything goes back."""
+        record = self._requests.pop(request_id)
+        for table, pool in zip(record.tables, self.pools):
+            pool.free([page for page in table if page >= 0])
+        self._free_state_slots.append(record.state_slot)
+
+    def block_table(self, request_id: Hashable, group: int) -> list[int]:
+        return self._requests[request_id].tables[group]
+
+    def take_fresh_state_slots(self) -> list[int]:
+        fresh, self.fresh_state_slots = self.fresh_state_slots, []
+        return fresh
+
+    # ------------------------------------------------------------------ invariants
+    def check(self) -> None:
+        """No page lost, held twice, or freed twice; no state slot shared."""
+        for group, pool in zip(self.layout.groups, self.pools):
+            pool.check()
+            seen: dict[int, Hashable] = {}
+            for record in self._requests.values():
+                for page in record.tables[group.index]:
+                    if page < 0:
+                        continue
+                    if page in seen:
+                        raise AssertionError(
+                            f"group {group.index}: page {page} held by {seen[page]!r} and {record.request_id!r}"
+                        )
+                    if page < pool.reserved:
+                        raise AssertionError(f"group {group.index}: reserved page {page} handed out")
+                    seen[page] = record.request_id
+            if len(seen) != pool.num_held:
+                raise AssertionError(
+                    f"group {group.index}: pool holds {pool.num_held} pages, requests hold {len(seen)}"
+                )
+        slots = [record.state_slot for record in self._requests.values()]
+        if len(set(slots)) != len(slots):
+            raise AssertionError("two requests share a state slot")
+        if sorted(slots + self._free_state_slots) != list(range(self.max_requests)):
+            raise AssertionError("a state slot was lost or duplicated")

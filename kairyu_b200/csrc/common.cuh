@@ -1,0 +1,79 @@
+// Shared helpers of the sm_100a kernels: element conversion, reductions with a
+// fixed order, the C export macro and launch checking.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define KB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Return codes of every exported entry point: 0 ok, >0 a cudaError_t from the
+// launch, <0 an argument this kernel refuses (the Python side turns the code
+// into a message).
+#define KB_ERR_BAD_ARG (-1)
+#define KB_ERR_UNSUPPORTED_SIZE (-2)
+#define KB_ERR_NULL (-3)
+
+static inline int kb_launch_result() { return (int)cudaGetLastError(); }
+
+// Bits of the device-side error word that indexing kernels set instead of
+// touching memory outside their tensors.
+#define KB_FLAG_BAD_PAGE 1
+#define KB_FLAG_BAD_TOKEN 2
+#define KB_FLAG_BAD_ROW 4
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+    return v;
+}
+
+// Sum over a block in a fixed order (warp butterflies, then warp 0 over the
+// per-warp partials): the result depends only on blockDim, never on the grid.
+// `scratch` holds at least 32 floats.  Every thread gets the sum.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = (lane < warps) ? scratch[lane] : 0.0f;
+    total = warp_sum(total);
+    return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = (lane < warps) ? scratch[lane] : -INFINITY;
+    total = warp_max(total);
+    return total;
+}

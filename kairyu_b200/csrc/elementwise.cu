@@ -1,0 +1,149 @@
+// Embedding gather, RMSNorm (with the residual sum fused in) and SiLU-gated
+// multiply.  Statistics and the residual sum are 32-bit in every variant.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// out[t, :] = table[ids[t], :] as fp32 (the residual stream is fp32 in both
+// modes).  An id outside [0, V) writes zeros and raises KB_FLAG_BAD_TOKEN.
+template <typename TT>
+__global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int H, int V, int* flag) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* dst = out + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_TOKEN);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.0f;
+        return;
+    }
+    const TT* src = table + (size_t)id * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = to_float(src[i]);
+}
+
+KB_EXPORT int kb_embedding(const void* table, int table_is_bf16, const int* ids, float* out, int T,
+                           int H, int V, int* flag, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!table || !ids || !out) return KB_ERR_NULL;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_is_bf16)
+        embedding_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V, flag);
+    else
+        embedding_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V, flag);
+    return kb_launch_result();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row r; source row s = rows ? rows[r] : r.
+//   v = x[s] (+ delta[s]);  if write_back: x[s] = v  (the fp32 residual sum)
+//   out[r] = v * rsqrt(mean(v^2) + eps) * w          (kairyu/models/layers.py:42-46,
+// without its intermediate rounding of the normalised value: one rounding at the end).
+template <typename TX, typename TA, typename TW>
+__global__ void rmsnorm_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
+                               const TW* __restrict__ w, TA* __restrict__ out,
+                               const int* __restrict__ rows, int H, float eps, int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    TX* xr = x + (size_t)s * H;
+    const TA* dr = delta ? delta + (size_t)s * H : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_float(xr[i]);
+        if (dr) {
+            v += to_float(dr[i]);
+            if (write_back) xr[i] = from_float<TX>(v);
+        }
+        ss += v * v;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    TA* orow = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_float(xr[i]);
+        if (dr && !write_back) v += to_float(dr[i]);
+        orow[i] = from_float<TA>(v * inv * to_float(w[i]));
+    }
+}
+
+template <typename TX, typename TA>
+static int rmsnorm_dispatch_w(void* x, const void* delta, const void* w, int w_bf16, void* out,
+                              const int* rows, int R, int H, float eps, int write_back,
+                              cudaStream_t stream) {
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (w_bf16)
+        rmsnorm_kernel<TX, TA, __nv_bfloat16><<<R, threads, 0, stream>>>(
+            (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back);
+    else
+        rmsnorm_kernel<TX, TA, float><<<R, threads, 0, stream>>>(
+            (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back);
+    return kb_launch_result();
+}
+
+// x: [*, H] fp32 or bf16 (x_bf16); delta/out: activation dtype (act_bf16); w: fp32 or bf16.
+KB_EXPORT int kb_rmsnorm(void* x, int x_bf16, const void* delta, const void* w, int w_bf16,
+                         void* out, int act_bf16, const int* rows, int R, int H, float eps,
+                         int write_back, cudaStream_t stream) {
+    if (R == 0) return 0;
+    if (!x || !w || !out) return KB_ERR_NULL;
+    if (H < 1) return KB_ERR_BAD_ARG;
+    if (rows) write_back = 0;
+    if (x_bf16) {
+        if (act_bf16)
+            return rmsnorm_dispatch_w<__nv_bfloat16, __nv_bfloat16>(x, delta, w, w_bf16, out, rows, R, H, eps, write_back, stream);
+        return KB_ERR_BAD_ARG;  // bf16 input with fp32 activations is not a mode of this engine
+    }
+    if (act_bf16)
+        return rmsnorm_dispatch_w<float, __nv_bfloat16>(x, delta, w, w_bf16, out, rows, R, H, eps, write_back, stream);
+    return rmsnorm_dispatch_w<float, float>(x, delta, w, w_bf16, out, rows, R, H, eps, write_back, stream);
+}
+
+// ------------------------------------------------------------------ SiLU(gate) * up
+// gate_up: [T, 2*I] with the gate in columns [0, I) and up in [I, 2I)
+// (kairyu/models/layers.py:244); out: [T, I].
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    const int t = blockIdx.y;
+    const T* g = gate_up + (size_t)t * 2 * I;
+    const T* u = g + I;
+    T* o = out + (size_t)t * I;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+        const float gv = to_float(g[i]);
+        const float uv = to_float(u[i]);
+        o[i] = from_float<T>(gv / (1.0f + expf(-gv)) * uv);
+    }
+}
+
+KB_EXPORT int kb_swiglu(const void* gate_up, void* out, int is_bf16, int T, int I, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!gate_up || !out) return KB_ERR_NULL;
+    if (T > 65535) return KB_ERR_UNSUPPORTED_SIZE;
+    const int threads = 256;
+    int bx = (I + threads - 1) / threads;
+    if (bx > 1024) bx = 1024;
+    dim3 grid(bx, T);
+    if (is_bf16)
+        swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
+    else
+        swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+    return kb_launch_result();
+}
+
+// ------------------------------------------------------------------ row gather (fp32 or bf16 rows)
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
+                                   T* __restrict__ out, int H) {
+    const T* s = src + (size_t)rows[blockIdx.x] * H;
+    T* o = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = s[i];
+}
+
+KB_EXPORT int kb_gather_rows(const void* src, const int* rows, void* out, int is_bf16, int R, int H,
+                             cudaStream_t stream) {
+    if (R == 0) return 0;
+    if (!src || !rows || !out) return KB_ERR_NULL;
+    if (is_bf16)
+        gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)src, rows, (__nv_bfloat16*)out, H);
+    else
+        gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)src, rows, (float*)out, H);
+    return kb_launch_result();
+}

@@ -1,0 +1,137 @@
+// Per-head RMSNorm of q and k (optional), rotary position encoding, and the
+// write of k and v into the paged cache: one pass over the packed qkv rows.
+//
+//   q, k <- RMSNorm_D(q, k) * w           (kairyu/models/attention.py:162-199, before RoPE)
+//   q, k <- u*cos + rotate_half(u)*sin    (kairyu/models/layers.py:165-190)
+//   K[slot], V[slot] <- k, v  where slot = table[row, pos / P] * P + pos % P and
+//   pos >= write_from[row]               (kairyu/engine/core/kv_pool.py:163-189)
+//
+// All arithmetic is fp32 with one rounding at the store (the reference's GPU
+// kernels round cos, sin and each product to bf16 first, kairyu/kernels/rope_gpu.py:74-112).
+#include "common.cuh"
+
+#define KB_FLAG_BAD_POS 8
+#define ROPE_WARPS 4
+#define ROPE_MAX_D 512
+
+template <typename T, typename TW>
+__global__ void __launch_bounds__(ROPE_WARPS * 32)
+qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hkv, int D,
+                             const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w,
+                             float eps, const float* __restrict__ cos_table,
+                             const float* __restrict__ sin_table, int rot_half, int max_pos,
+                             const int* __restrict__ positions, const int* __restrict__ row_ids,
+                             const int* __restrict__ block_table, int max_pages,
+                             const int* __restrict__ write_from, T* __restrict__ k_cache,
+                             T* __restrict__ v_cache, int page_size, int num_pages, int* flag) {
+    __shared__ float head_buf[ROPE_WARPS][ROPE_MAX_D];
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    const int row = row_ids[t];
+    T* token = qkv + (size_t)t * qkv_stride;
+
+    const bool rotate = cos_table != nullptr && rot_half > 0;
+    if (rotate && (pos < 0 || pos >= max_pos)) {
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+        return;
+    }
+    const float* cos_row = rotate ? cos_table + (size_t)pos * rot_half : nullptr;
+    const float* sin_row = rotate ? sin_table + (size_t)pos * rot_half : nullptr;
+
+    // Where this token's k and v go (or nowhere).
+    long long slot = -1;
+    if (k_cache != nullptr && pos >= write_from[row]) {
+        const int page_index = pos / page_size;
+        if (page_index >= max_pages) {
+            if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
+        } else {
+            const int page = block_table[(size_t)row * max_pages + page_index];
+            if (page < 0 || page >= num_pages) {
+                if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
+            } else {
+                slot = (long long)page * page_size + (pos % page_size);
+            }
+        }
+    }
+
+    float* buf = head_buf[warp];
+    // q heads [0, Hq), then k heads [Hq, Hq+Hkv): norm + rotation.
+    for (int head = warp; head < Hq + Hkv; head += ROPE_WARPS) {
+        const bool is_k = head >= Hq;
+        T* x = token + (size_t)head * D;
+        const TW* w = is_k ? k_norm_w : q_norm_w;
+        float ss = 0.0f;
+        for (int i = lane; i < D; i += 32) {
+            const float v = to_float(x[i]);
+            buf[i] = v;
+            ss += v * v;
+        }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)D + eps);
+            for (int i = lane; i < D; i += 32) buf[i] = buf[i] * inv * to_float(w[i]);
+        }
+        __syncwarp();
+        T* kdst = nullptr;
+        if (is_k && slot >= 0) kdst = k_cache + ((size_t)slot * Hkv + (head - Hq)) * D;
+        for (int i = lane; i < D; i += 32) {
+            float out;
+            if (rotate && i < 2 * rot_half) {
+                const int j = i < rot_half ? i : i - rot_half;
+                const float c = cos_row[j];
+                const float s = sin_row[j];
+                // rotate_half(u) = cat(-u[half:], u[:half])
+                out = i < rot_half ? buf[i] * c - buf[i + rot_half] * s
+                                   : buf[i] * c + buf[i - rot_half] * s;
+            } else {
+                out = buf[i];
+            }
+            const T rounded = from_float<T>(out);
+            x[i] = rounded;
+            if (kdst) kdst[i] = rounded;
+        }
+        __syncwarp();
+    }
+    // v heads: copy into the cache.
+    if (slot >= 0 && v_cache != nullptr) {
+        const T* v = token + (size_t)(Hq + Hkv) * D;
+        T* vdst = v_cache + (size_t)slot * Hkv * D;
+        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) vdst[i] = v[i];
+    }
+}
+
+// qkv: [T, qkv_stride] with q | k | v packed per token, head-major.
+// *_norm_w: [D] (both or neither), norm_w_bf16 says which type.
+// cos/sin: [max_pos, rot_half] fp32 or null.  caches: [num_pages, page_size, Hkv, D] or null.
+KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_stride, int Hq,
+                                       int Hkv, int D, const void* q_norm_w, const void* k_norm_w,
+                                       int norm_w_bf16, float eps, const float* cos_table,
+                                       const float* sin_table, int rot_half, int max_pos,
+                                       const int* positions, const int* row_ids,
+                                       const int* block_table, int max_pages,
+                                       const int* write_from, void* k_cache, void* v_cache,
+                                       int page_size, int num_pages, int* flag,
+                                       cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!qkv || !positions || !row_ids) return KB_ERR_NULL;
+    if (D < 1 || D > ROPE_MAX_D || 2 * rot_half > D) return KB_ERR_UNSUPPORTED_SIZE;
+    if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return KB_ERR_BAD_ARG;
+    if (k_cache && (!block_table || !write_from || !v_cache || page_size < 1)) return KB_ERR_NULL;
+    const int threads = ROPE_WARPS * 32;
+#define LAUNCH(T_, TW_)                                                                         \
+    qk_norm_rope_kv_write_kernel<T_, TW_><<<T, threads, 0, stream>>>(                           \
+        (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps,      \
+        cos_table, sin_table, rot_half, max_pos, positions, row_ids, block_table, max_pages,    \
+        write_from, (T_*)k_cache, (T_*)v_cache, page_size, num_pages, flag)
+    if (is_bf16) {
+        if (norm_w_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        else LAUNCH(__nv_bfloat16, float);
+    } else {
+        if (norm_w_bf16) LAUNCH(float, __nv_bfloat16);
+        else LAUNCH(float, float);
+    }
+#undef LAUNCH
+    return kb_launch_result();
+}

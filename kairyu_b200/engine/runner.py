@@ -1,0 +1,390 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step runs only the tokens it is given, against the cache earlier steps left,
+and returns fp32 logits at the wanted positions.  Rows may be portions of
+prompts of any length beside single decoded tokens; a row's tokens continue at
+the request's computed length (kairyu/engine/core/prefill.py:17-43 and
+kairyu/engine/core/model_runner.py:1833-1962 are the reference's equivalents).
+
+The step's metadata is packed into one pinned int32 buffer and copied to the
+device once.  Steps whose rows all carry one token can be replayed from a CUDA
+graph captured per (padded batch size, context-length bucket), as
+kairyu/engine/core/step_executor.py:591-934 does with its buckets.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Hashable, Optional, Sequence
+
+import torch
+
+from kairyu_b200.cache.manager import CacheManager
+from kairyu_b200.cache.page_pool import OutOfPages
+from kairyu_b200.cache.storage import CacheStorage
+from kairyu_b200.engine.workspace import Workspace
+from kairyu_b200.parts.base import CacheView, StepContext
+
+ATTENTION_TILE_M = 64  # queries per tile of the prefill attention kernel
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step."""
+
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()  # places among ``tokens`` whose logits are wanted
+
+
+class StepError(RuntimeError):
+    pass
+
+
+def decode_buckets(max_batch: int) -> list[int]:
+    """Padded batch sizes graphs are captured for: 1, 2, 4, 8, 16, 24, 32, then
+    every 8 (kairyu/engine/core/graph_buckets.py:9-28)."""
+    sizes = [size for size in (1, 2, 4, 8) if size <= max_batch]
+    sizes += list(range(16, max_batch + 1, 8))
+    if not sizes or sizes[-1] < max_batch:
+        sizes.append(max_batch)
+    return sizes
+
+
+@dataclass
+class _Graph:
+    graph: Any
+    meta: torch.Tensor  # static device int32 buffer the graph reads
+    logits: torch.Tensor
+    generation: int
+    layout: dict[str, tuple[int, int]]
+
+
+class ModelRunner:
+    def __init__(
+        self,
+        model: Any,
+        cache: CacheManager,
+        storage: CacheStorage,
+        *,
+        max_model_len: int,
+        decode_mode: str = "eager",
+        max_graph_batch: int = 256,
+        debug_poison: bool = False,
+    ) -> None:
+        self.model = model
+        self.cache = cache
+        self.storage = storage
+        self.device = model.device
+        self.max_model_len = max_model_len
+        self.max_pages_per_request = -(-max_model_len // cache.page_size)
+        self.decode_mode = decode_mode
+        self.max_graph_batch = max_graph_batch
+        self.debug_poison = debug_poison
+        self.workspace = Workspace(self.device)
+        self.graph_workspace = Workspace(self.device)
+        self._is_cuda = str(self.device).startswith("cuda")
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._views: dict[tuple[int, bool], CacheView] = {}
+        for call in model.schedule:
+            key = (call.cache_slot, call.writes_cache)
+            if key not in self._views:
+                self._views[key] = storage.view(call.cache_slot, writes=call.writes_cache)
+        self._graphs: dict[tuple[int, int], _Graph] = {}
+        self._graph_pool = None
+        self._buckets = decode_buckets(max_graph_batch)
+        self.counters = {"steps": 0, "graph_replays": 0, "graph_captures": 0, "eager_steps": 0, "tokens": 0}
+
+    # ------------------------------------------------------------------ host-side packing
+    def _prepare_rows(self, entries: Sequence[StepEntry]) -> list[tuple[StepEntry, int, int]]:
+        """Checks and page growth; returns (entry, start, seq_len) per row."""
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen: set[Hashable] = set()
+        rows = []
+        vocab = self.model.spec.vocab_size
+        for entry in entries:
+            if entry.request_id in seen:
+                raise StepError(f"request {entry.request_id!r} appears twice in one step")
+            seen.add(entry.request_id)
+            count = len(entry.tokens)
+            if count < 1:
+                raise StepError(f"request {entry.request_id!r} brings no tokens")
+            if min(entry.tokens) < 0 or max(entry.tokens) >= vocab:
+                raise StepError(f"request {entry.request_id!r} has a token id outside [0, {vocab})")
+            if any(not 0 <= place < count for place in entry.want):
+                raise StepError(f"request {entry.request_id!r} wants a place outside its tokens")
+            if entry.request_id not in self.cache:
+                self.cache.admit(entry.request_id)
+            start = self.cache.get(entry.request_id).num_tokens
+            seq_len = start + count
+            if seq_len > self.max_model_len:
+                raise StepError(
+                    f"request {entry.request_id!r} would reach {seq_len} tokens; max_model_len is {self.max_model_len}"
+                )
+            if not self.cache.ensure_capacity(entry.request_id, seq_len, query_start=start):
+                raise OutOfPages(
+                    f"no pages left for request {entry.request_id!r} to reach {seq_len} tokens"
+                )
+            rows.append((entry, start, seq_len))
+        return rows
+
+    def _pack(
+        self,
+        rows: Sequence[tuple[StepEntry, int, int]],
+        *,
+        pad_rows: Optional[int] = None,
+        max_pages: Optional[int] = None,
+        include_want: bool = True,
+    ) -> tuple[torch.Tensor, dict[str, tuple[int, int]], dict[str, Any]]:
+        """One int32 host tensor holding every index array of the step, the
+        (offset, length) of each array, and host-side facts."""
+        page_size = self.cache.page_size
+        groups = self.cache.layout.groups
+        num_rows = len(rows)
+        padded_rows = pad_rows if pad_rows is not None else num_rows
+        token_ids: list[int] = []
+        positions: list[int] = []
+        row_ids: list[int] = []
+        qo_indptr = [0]
+        seq_lens: list[int] = []
+        write_from: list[int] = []
+        state_slots: list[int] = []
+        want: list[int] = []
+        tile_rows: list[int] = []
+        tile_starts: list[int] = []
+        decode_rows: list[int] = []
+        decode_tokens: list[int] = []
+        for row, (entry, start, seq_len) in enumerate(rows):
+            count = len(entry.tokens)
+            base = len(token_ids)
+            token_ids.extend(entry.tokens)
+            positions.extend(range(start, seq_len))
+            row_ids.extend([row] * count)
+            qo_indptr.append(base + count)
+            seq_lens.append(seq_len)
+            write_from.append(0)
+            state_slots.append(self.cache.get(entry.request_id).state_slot)
+            if include_want:
+                want.extend(base + place for place in entry.want)
+            if count == 1:
+                decode_rows.append(row)
+                decode_tokens.append(base)
+            else:
+                for tile_start in range(0, count, ATTENTION_TILE_M):
+                    tile_rows.append(row)
+                    tile_starts.append(tile_start)
+        for row in range(num_rows, padded_rows):  # padding rows of a replayed graph
+            base = len(token_ids)
+            token_ids.append(0)
+            positions.append(0)
+            row_ids.append(row)
+            qo_indptr.append(base + 1)
+            seq_lens.append(1)
+            write_from.append(0)
+            state_slots.append(0)
+            decode_rows.append(row)
+            decode_tokens.append(base)
+        needed_pages = max(-(-seq_len // page_size) for _, _, seq_len in rows)
+        table_width = max_pages if max_pages is not None else needed_pages
+        tables: list[int] = []
+        for group in groups:
+            for entry, _, seq_len in rows:
+                table = self.cache.block_table(entry.request_id, group.index)
+                pages = table[: -(-seq_len // page_size)]
+                tables.extend(pages)
+                tables.extend([-1] * (table_width - len(pages)))
+            for _ in range(num_rows, padded_rows):
+                tables.extend([0] * table_width)  # the reserved page
+        arrays = {
+            "token_ids": token_ids,
+            "positions": positions,
+            "row_ids": row_ids,
+            "qo_indptr": qo_indptr,
+            "seq_lens": seq_lens,
+            "write_from": write_from,
+            "state_slots": state_slots,
+            "want": want,
+            "tile_rows": tile_rows,
+            "tile_starts": tile_starts,
+            "decode_rows": decode_rows,
+            "decode_tokens": decode_tokens,
+            "tables": tables,
+        }
+        layout: dict[str, tuple[int, int]] = {}
+        flat: list[int] = []
+        for name, values in arrays.items():
+            layout[name] = (len(flat), len(values))
+            flat.extend(values)
+        host = torch.tensor(flat, dtype=torch.int32)
+        if self._is_cuda:
+            host = host.pin_memory()
+        facts = {
+            "num_tokens": len(token_ids),
+            "num_rows": padded_rows,
+            "table_width": table_width,
+            "max_seq_len": max(seq_lens),
+            "host_qo_indptr": tuple(qo_indptr),
+            "host_seq_lens": tuple(seq_lens),
+        }
+        return host, layout, facts
+
+    def _context(
+        self,
+        meta: torch.Tensor,
+        layout: dict[str, tuple[int, int]],
+        facts: dict[str, Any],
+        workspace: Workspace,
+    ) -> tuple[StepContext, Optional[torch.Tensor]]:
+        def part(name: str) -> torch.Tensor:
+            offset, length = layout[name]
+            return meta[offset : offset + length]
+
+        num_rows = facts["num_rows"]
+        width = facts["table_width"]
+        tables = part("tables").view(len(self.cache.layout.groups), num_rows, width)
+        ctx = StepContext(
+            num_tokens=facts["num_tokens"],
+            num_rows=num_rows,
+            dtype=self.model.dtype,
+            token_ids=part("token_ids"),
+            positions=part("positions"),
+            row_ids=part("row_ids"),
+            qo_indptr=part("qo_indptr"),
+            seq_lens=part("seq_lens"),
+            write_from=part("write_from"),
+            state_slots=part("state_slots"),
+            block_tables={group.index: tables[group.index] for group in self.cache.layout.groups},
+            host_qo_indptr=facts["host_qo_indptr"],
+            host_seq_lens=facts["host_seq_lens"],
+            num_prefill_tiles=layout["tile_rows"][1],
+            tile_rows=part("tile_rows"),
+            tile_starts=part("tile_starts"),
+            num_decode_rows=layout["decode_rows"][1],
+            decode_rows=part("decode_rows"),
+            decode_tokens=part("decode_tokens"),
+            max_seq_len=facts["max_seq_len"],
+            workspace=workspace,
+            error_flag=self.error_flag,
+        )
+        want = part("want") if layout["want"][1] else None
+        return ctx, want
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run one batch; returns ``[wanted, vocab]`` fp32 logits on the device,
+        in the order of the entries and of their ``want`` lists, or None."""
+        rows = self._prepare_rows(entries)
+        self.storage.zero_state_slots(self.cache.take_fresh_state_slots())
+        self.counters["steps"] += 1
+        self.counters["tokens"] += sum(len(entry.tokens) for entry, _, _ in rows)
+        pure_decode = all(len(entry.tokens) == 1 for entry, _, _ in rows)
+        if (
+            pure_decode
+            and self.decode_mode == "cuda_graph"
+            and self._is_cuda
+            and len(rows) <= self.max_graph_batch
+        ):
+            logits = self._graph_step(rows)
+        else:
+            logits = self._eager_step(rows)
+        for entry, _, seq_len in rows:
+            self.cache.advance(entry.request_id, seq_len)
+        return logits
+
+    def _eager_step(self, rows: Sequence[tuple[StepEntry, int, int]]) -> Optional[torch.Tensor]:
+        host, layout, facts = self._pack(rows)
+        meta = self.workspace.flat("meta", host.numel(), torch.int32)
+        meta.copy_(host, non_blocking=True)
+        ctx, want = self._context(meta, layout, facts, self.workspace)
+        self.counters["eager_steps"] += 1
+        return self.model.forward(ctx, self._views, want)
+
+    # ------------------------------------------------------------------ graphs
+    def _graph_key(self, num_rows: int, max_seq_len: int) -> tuple[int, int]:
+        bucket = next(size for size in self._buckets if size >= num_rows)
+        context_bucket = 256
+        while context_bucket < max_seq_len:
+            context_bucket *= 2
+        return bucket, min(context_bucket, max(self.max_model_len, 256))
+
+    def _graph_step(self, rows: Sequence[tuple[StepEntry, int, int]]) -> Optional[torch.Tensor]:
+        num_rows = len(rows)
+        max_seq_len = max(seq_len for _, _, seq_len in rows)
+        key = self._graph_key(num_rows, max_seq_len)
+        bucket, context_bucket = key
+        host, layout, facts = self._pack(
+            rows, pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
+        )
+        # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
+        facts["max_seq_len"] = context_bucket
+        held = self._graphs.get(key)
+        if held is None or held.generation != self.graph_workspace.generation:
+            held = self._capture(key, host, layout, facts)
+        held.meta.copy_(host, non_blocking=True)
+        held.graph.replay()
+        self.counters["graph_replays"] += 1
+        wanted_rows = [row for row, (entry, _, _) in enumerate(rows) if entry.want]
+        if not wanted_rows:
+            return None
+        if wanted_rows == list(range(num_rows)):
+            return held.logits[:num_rows]
+        index = torch.tensor(wanted_rows, dtype=torch.long, device=self.device)
+        return held.logits.index_select(0, index)
+
+    def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict) -> _Graph:
+        bucket, _ = key
+        workspace = self.graph_workspace
+        meta = torch.zeros(host.numel(), dtype=torch.int32, device=self.device)
+        meta.copy_(host)
+        graph_layout = dict(layout)
+        # inside the graph every row's single token gives logits
+        want_all = torch.arange(bucket, dtype=torch.int32, device=self.device)
+        ctx, _ = self._context(meta, graph_layout, facts, workspace)
+
+        def run() -> torch.Tensor:
+            return self.model.forward(ctx, self._views, want_all)
+
+        # Warm up on a side stream: buffers reach their size, libraries initialise.
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                run()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        generation = workspace.generation
+        workspace.freeze(True)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = run()
+        finally:
+            workspace.freeze(False)
+        if generation != workspace.generation:
+            raise StepError("the graph workspace changed during capture")
+        # a grown workspace invalidates graphs captured against the old buffers
+        self._graphs = {k: g for k, g in self._graphs.items() if g.generation == generation}
+        held = _Graph(graph, meta, logits, generation, graph_layout)
+        self._graphs[key] = held
+        self.counters["graph_captures"] += 1
+        return held
+
+    # ------------------------------------------------------------------ errors
+    def check_errors(self) -> None:
+        """Raise if a kernel saw an index outside its tensors (synchronises)."""
+        flag = int(self.error_flag.item())
+        if flag:
+            self.error_flag.zero_()
+            reasons = []
+            if flag & 1:
+                reasons.append("a block table entry outside the page pool")
+            if flag & 2:
+                reasons.append("a token id outside the vocabulary")
+            if flag & 4:
+                reasons.append("a row index outside the batch")
+            if flag & 8:
+                reasons.append("a position outside the rotary table")
+            raise StepError("a kernel refused an index: " + "; ".join(reasons))

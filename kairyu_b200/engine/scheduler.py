@@ -1,0 +1,372 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token
+budget, decodes, finishes and frees.  Pure policy over the cache manager; it
+never touches a tensor (kairyu/engine/core/scheduler.py:404-1770 is the
+reference; priorities, scheduling classes, speculative reservations and prefix
+sharing are left out).
+
+A request's work is ``prompt + outputs``; ``computed`` counts how many of those
+tokens have been fed.  While more than one token is left to feed the request
+is in prefill (portions, cut anywhere); when exactly one is left the request
+decodes.  The step that feeds the last token samples the next one.  This view
+makes recompute-preemption uniform: a victim's ``computed`` goes back to 0 and
+its prompt *and* outputs are fed again.
+
+Order within a step (scheduler.py:1641-1657): decodes first (one token each),
+then running prefills, then admissions from the head of the queue.
+
+When pages run out:
+
+* at admission, the head waits (no skip-ahead) until the pages its whole
+  prompt needs are free; a prompt that could never fit, even in an empty
+  cache, is rejected: finished, reason ``"length"``, no output
+  (scheduler.py:1007-1019, 1479-1490);
+* for a decode, the youngest running request that has no outputs yet is
+  recompute-preempted (scheduler.py:1065-1110); if there is none, the youngest
+  other running request is, outputs included (the reference raises here); the
+  victim goes back to the front of the queue.  A request that is alone and
+  still cannot grow is finished with reason ``"length"``;
+* a prefill portion that cannot get pages is skipped this step;
+* if a step would be empty while requests are unfinished, the youngest running
+  request is preempted, or the stuck head is rejected
+  (kairyu/engine/core/engine_core.py:76-88).
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Hashable, Mapping, Optional, Sequence
+
+from kairyu_b200.cache.manager import CacheManager
+from kairyu_b200.cache.page_pool import OutOfPages
+from kairyu_b200.sampling.params import SamplingParams
+
+
+@dataclass(frozen=True)
+class EngineRequest:
+    """kairyu/engine/core/scheduler.py:31-57."""
+
+    request_id: str
+    prompt_token_ids: tuple[int, ...]
+    max_new_tokens: int = 16
+    eos_token_ids: tuple[int, ...] = ()
+    stop_token_ids: tuple[int, ...] = ()
+    min_tokens: int = 0
+    ignore_eos: bool = False
+    params: SamplingParams = field(default_factory=lambda: SamplingParams(temperature=0.0))
+
+
+class Status(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+class RequestState:
+    __slots__ = ("request", "status", "computed", "outputs", "finish_reason", "preemptions", "arrival")
+
+    def __init__(self, request: EngineRequest, arrival: int) -> None:
+        self.request = request
+        self.status = Status.WAITING
+        self.computed = 0
+        self.outputs: list[int] = []
+        self.finish_reason: Optional[str] = None
+        self.preemptions = 0
+        self.arrival = arrival
+
+    @property
+    def total_tokens(self) -> int:
+        return len(self.request.prompt_token_ids) + len(self.outputs)
+
+    @property
+    def remaining(self) -> int:
+        return self.total_tokens - self.computed
+
+    def tokens(self, start: int, count: int) -> list[int]:
+        prompt = self.request.prompt_token_ids
+        end = start + count
+        if end <= len(prompt):
+            return list(prompt[start:end])
+        if start >= len(prompt):
+            return self.outputs[start - len(prompt) : end - len(prompt)]
+        return list(prompt[start:]) + self.outputs[: end - len(prompt)]
+
+
+@dataclass(frozen=True)
+class ScheduledChunk:
+    request_id: str
+    start: int  # offset into prompt + outputs
+    num_tokens: int
+    is_prefill: bool
+    samples: bool  # the chunk feeds the last known token, so its last logits pick the next
+
+
+@dataclass(frozen=True)
+class SchedulerOutput:
+    scheduled: tuple[ScheduledChunk, ...]
+    preempted: tuple[str, ...] = ()
+    rejected: tuple[str, ...] = ()
+
+
+class Scheduler:
+    def __init__(
+        self,
+        cache: CacheManager,
+        *,
+        max_num_batched_tokens: int = 2048,
+        max_num_seqs: int = 256,
+        max_num_partial_prefills: int = 2,
+        max_model_len: Optional[int] = None,
+        prefill_chunk_size: Optional[int] = None,
+    ) -> None:
+        self.cache = cache
+        self.budget = max_num_batched_tokens
+        self.max_num_seqs = max_num_seqs
+        self.max_num_partial_prefills = max_num_partial_prefills
+        self.max_model_len = max_model_len
+        self.prefill_chunk_size = prefill_chunk_size
+        self._states: dict[str, RequestState] = {}
+        self._waiting: deque[str] = deque()
+        self._running: list[str] = []  # admission order; the last is the youngest
+        self._arrivals = 0
+        self.counters = {"preemptions": 0, "rejections": 0, "steps": 0}
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, request: EngineRequest) -> None:
+        if request.request_id in self._states:
+            raise ValueError(f"request id {request.request_id!r} is already known")
+        if not request.prompt_token_ids:
+            raise ValueError("a request needs at least one prompt token")
+        if request.max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be >= 1")
+        if self.max_model_len is not None and len(request.prompt_token_ids) + request.max_new_tokens > self.max_model_len:
+            # kairyu/engine/engine_loop.py:630-644
+            raise ValueError(
+                f"prompt ({len(request.prompt_token_ids)}) + max_tokens ({request.max_new_tokens}) "
+                f"exceeds max_model_len ({self.max_model_len})"
+            )
+        self._states[request.request_id] = RequestState(request, self._arrivals)
+        self._arrivals += 1
+        self._waiting.append(request.request_id)
+
+    def abort(self, request_id: str) -> None:
+        state = self._states.get(request_id)
+        if state is None or state.status is Status.FINISHED:
+            return
+        if state.status is Status.WAITING:
+            self._waiting.remove(request_id)
+        else:
+            self._running.remove(request_id)
+        self._finish(state, "abort", in_running=False)
+
+    def finish_early(self, request_id: str, reason: str) -> None:
+        """End a running request between steps (a stop string was produced)."""
+        state = self._states.get(request_id)
+        if state is not None and state.status is Status.RUNNING:
+            self._finish(state, reason)
+
+    def forget(self, request_id: str) -> None:
+        state = self._states.get(request_id)
+        if state is not None and state.status is Status.FINISHED:
+            del self._states[request_id]
+
+    # ------------------------------------------------------------------ queries
+    def has_unfinished(self) -> bool:
+        return bool(self._waiting or self._running)
+
+    def state(self, request_id: str) -> RequestState:
+        return self._states[request_id]
+
+    @property
+    def num_waiting(self) -> int:
+        return len(self._waiting)
+
+    @property
+    def num_running(self) -> int:
+        return len(self._running)
+
+    def output_tokens(self, request_id: str) -> tuple[int, ...]:
+        return tuple(self._states[request_id].outputs)
+
+    def finish_reason(self, request_id: str) -> Optional[str]:
+        return self._states[request_id].finish_reason
+
+    # ------------------------------------------------------------------ internals
+    def _finish(self, state: RequestState, reason: str, *, in_running: bool = True) -> None:
+        state.status = Status.FINISHED
+        state.finish_reason = reason
+        if in_running:
+            self._running.remove(state.request.request_id)
+        if state.request.request_id in self.cache:
+            self.cache.release(state.request.request_id)
+
+    def _preempt(self, request_id: str) -> None:
+        """Recompute-preemption: give everything back, start over from the front of the queue."""
+        state = self._states[request_id]
+        self._running.remove(request_id)
+        if request_id in self.cache:
+            self.cache.release(request_id)
+        state.computed = 0
+        state.status = Status.WAITING
+        state.preemptions += 1
+        self._waiting.appendleft(request_id)
+        self.counters["preemptions"] += 1
+
+    def _pick_victim(self, needy: str, taken: set[str]) -> Optional[str]:
+        fallback = None
+        for candidate in reversed(self._running):
+            if candidate == needy or candidate in taken:
+                continue
+            if not self._states[candidate].outputs:
+                return candidate
+            if fallback is None:
+                fallback = candidate
+        return fallback
+
+    def _grow(self, state: RequestState, count: int) -> bool:
+        return self.cache.ensure_capacity(
+            state.request.request_id, state.computed + count, query_start=state.computed
+        )
+
+    def _chunk_cap(self, budget: int, sharers: int) -> int:
+        cap = -(-budget // max(sharers, 1))
+        if self.prefill_chunk_size is not None:
+            cap = min(cap, self.prefill_chunk_size)
+        return cap
+
+    # ------------------------------------------------------------------ one plan
+    def schedule(self) -> SchedulerOutput:
+        self.counters["steps"] += 1
+        plan, preempted, rejected = self._plan()
+        if not plan and self.has_unfinished():
+            # Nothing can move.  Free something, or give up on the stuck head.
+            if self._running:
+                victim = self._running[-1]
+                self._preempt(victim)
+                preempted.append(victim)
+                more, more_preempted, more_rejected = self._plan()
+                plan, preempted, rejected = more, preempted + more_preempted, rejected + more_rejected
+            if not plan and self._waiting and not self._running:
+                head = self._waiting.popleft()
+                self._finish(self._states[head], "length", in_running=False)
+                self.counters["rejections"] += 1
+                rejected.append(head)
+        return SchedulerOutput(tuple(plan), tuple(preempted), tuple(rejected))
+
+    def _plan(self) -> tuple[list[ScheduledChunk], list[str], list[str]]:
+        plan: list[ScheduledChunk] = []
+        preempted: list[str] = []
+        rejected: list[str] = []
+        budget = self.budget
+        taken: set[str] = set()
+
+        # 1. decodes: one token each, oldest first
+        for request_id in list(self._running):
+            if budget < 1:
+                break
+            state = self._states.get(request_id)
+            if state is None or state.status is not Status.RUNNING or state.remaining != 1:
+                continue
+            while not self._grow(state, 1):
+                victim = self._pick_victim(request_id, taken)
+                if victim is None:
+                    break
+                self._preempt(victim)
+                preempted.append(victim)
+            else:
+                plan.append(ScheduledChunk(request_id, state.computed, 1, False, True))
+                state.computed += 1
+                taken.add(request_id)
+                budget -= 1
+                continue
+            if len(self._running) == 1:
+                # alone and the cache is exhausted: it cannot go on
+                self._finish(state, "length")
+                rejected.append(request_id)
+
+        # 2. running prefills share what is left of the budget
+        prefilling = [
+            request_id
+            for request_id in self._running
+            if self._states[request_id].remaining > 1 and request_id not in taken
+        ]
+        for index, request_id in enumerate(prefilling):
+            if budget < 1:
+                break
+            state = self._states[request_id]
+            count = min(state.remaining, budget, self._chunk_cap(budget, len(prefilling) - index))
+            if count < 1 or not self._grow(state, count):
+                continue
+            completes = count == state.remaining
+            plan.append(ScheduledChunk(request_id, state.computed, count, True, completes))
+            state.computed += count
+            taken.add(request_id)
+            budget -= count
+
+        # 3. admissions from the head of the queue
+        while self._waiting and budget >= 1:
+            if len(self._running) >= self.max_num_seqs:
+                break
+            partial = sum(1 for r in self._running if self._states[r].remaining > 1 and r not in taken) + sum(
+                1 for chunk in plan if chunk.is_prefill and not chunk.samples
+            )
+            if partial >= self.max_num_partial_prefills:
+                break
+            head = self._waiting[0]
+            state = self._states[head]
+            if not self.cache.can_hold(state.total_tokens):
+                self._waiting.popleft()
+                self._finish(state, "length", in_running=False)
+                self.counters["rejections"] += 1
+                rejected.append(head)
+                continue
+            needed = self.cache.pages_needed(None, state.total_tokens, 0)
+            if any(count > self.cache.free_pages(group) for group, count in enumerate(needed)):
+                break  # the head waits for pages
+            try:
+                self.cache.admit(head)
+            except OutOfPages:
+                break
+            count = min(state.remaining, budget, self._chunk_cap(budget, 1))
+            if not self._grow(state, count):
+                self.cache.release(head)
+                break
+            self._waiting.popleft()
+            state.status = Status.RUNNING
+            self._running.append(head)
+            completes = count == state.remaining
+            plan.append(ScheduledChunk(head, state.computed, count, count > 1 or not completes, completes))
+            state.computed += count
+            taken.add(head)
+            budget -= count
+        return plan, preempted, rejected
+
+    # ------------------------------------------------------------------ results
+    def update(self, sampled: Mapping[str, int]) -> tuple[str, ...]:
+        """Commit one sampled token per request; return the ids that finished
+        (kairyu/engine/core/scheduler.py:1688-1770)."""
+        finished: list[str] = []
+        for request_id, token in sampled.items():
+            if isinstance(token, bool) or not isinstance(token, int):
+                raise TypeError(f"request {request_id!r}: sampled tokens must be ints, got {token!r}")
+            state = self._states.get(request_id)
+            if state is None or state.status is not Status.RUNNING or state.remaining != 0:
+                raise ValueError(f"request {request_id!r} is not awaiting a sampled token")
+            state.outputs.append(token)
+            reason = self._terminal_reason(state, token)
+            if reason is not None:
+                self._finish(state, reason)
+                finished.append(request_id)
+        return tuple(finished)
+
+    @staticmethod
+    def _terminal_reason(state: RequestState, token: int) -> Optional[str]:
+        request = state.request
+        is_eos = not request.ignore_eos and token in request.eos_token_ids
+        is_stop = is_eos or token in request.stop_token_ids
+        if is_stop and len(state.outputs) >= request.min_tokens:
+            return "stop"
+        if len(state.outputs) >= request.max_new_tokens:
+            return "length"
+        return None

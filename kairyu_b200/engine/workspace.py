@@ -1,0 +1,53 @@
+"""Scratch tensors of a step, kept between steps so that a step allocates
+nothing and a captured graph sees fixed addresses."""
+
+from __future__ import annotations
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device: str) -> None:
+        self.device = device
+        self._buffers: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
+        self._frozen = False
+        self.generation = 0  # bumps whenever a buffer is (re)allocated
+
+    def buffer(self, tag: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        """A ``[rows, cols]`` view of the buffer named ``tag``; grows (by
+        reallocation) when more rows are asked for than ever before."""
+        key = (tag, cols, dtype)
+        held = self._buffers.get(key)
+        if held is None or held.shape[0] < rows:
+            if self._frozen:
+                raise RuntimeError(
+                    f"workspace buffer {tag!r} would have to grow to {rows} rows while a graph is being captured"
+                )
+            capacity = max(rows, 1)
+            if held is not None:
+                capacity = max(capacity, 2 * held.shape[0])
+            held = torch.empty((capacity, cols), dtype=dtype, device=self.device)
+            self._buffers[key] = held
+            self.generation += 1
+        return held[:rows]
+
+    def flat(self, tag: str, count: int, dtype: torch.dtype) -> torch.Tensor:
+        """A 1-D buffer of ``count`` elements named ``tag``."""
+        key = (tag, -1, dtype)
+        held = self._buffers.get(key)
+        if held is None or held.numel() < count:
+            if self._frozen:
+                raise RuntimeError(f"workspace buffer {tag!r} would have to grow while a graph is being captured")
+            capacity = max(count, 1)
+            if held is not None:
+                capacity = max(capacity, 2 * held.numel())
+            held = torch.empty((capacity,), dtype=dtype, device=self.device)
+            self._buffers[key] = held
+            self.generation += 1
+        return held[:count]
+
+    def freeze(self, frozen: bool = True) -> None:
+        self._frozen = frozen
+
+    def bytes_held(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._buffers.values())

@@ -1,0 +1,515 @@
+"""Python entry points of the hand-written sm_100a kernels.
+
+Every function takes CUDA tensors, checks what the kernel assumes, and launches
+on the current stream.  There is no other implementation behind them: a tensor
+that is not on a CUDA device, or a library that cannot be built or loaded, is
+an error.  Model parts call these as ``kernels.<name>(...)``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from kairyu_b200.kernels.build import KernelBuildError, load_library
+
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_void_p = ctypes.c_void_p
+
+FLAG_BAD_PAGE = 1
+FLAG_BAD_TOKEN = 2
+FLAG_BAD_ROW = 4
+FLAG_BAD_POS = 8
+
+_CODES = {
+    -1: "bad argument",
+    -2: "a size this kernel does not support",
+    -3: "a required pointer is null",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_CODES.get(code, f'error {code}')}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _need_cuda(what: str, *tensors: Optional[torch.Tensor]) -> None:
+    for tensor in tensors:
+        if tensor is not None and not tensor.is_cuda:
+            raise KernelError(
+                f"{what}: tensor on {tensor.device}; the kernels of kairyu_b200 run on CUDA "
+                "devices only and have no CPU implementation"
+            )
+
+
+def _is_bf16(tensor: torch.Tensor, what: str) -> int:
+    if tensor.dtype == torch.bfloat16:
+        return 1
+    if tensor.dtype == torch.float32:
+        return 0
+    raise KernelError(f"{what}: dtype {tensor.dtype} is not supported (float32 or bfloat16)")
+
+
+def _need_i32(what: str, *tensors: Optional[torch.Tensor]) -> None:
+    for tensor in tensors:
+        if tensor is not None and (tensor.dtype != torch.int32 or not tensor.is_contiguous()):
+            raise KernelError(f"{what}: index tensors must be contiguous int32")
+
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _fn(library: str, name: str, argtypes: list) -> ctypes._CFuncPtr:
+    function = _functions.get(name)
+    if function is None:
+        function = getattr(load_library(library), name)
+        function.argtypes = argtypes
+        function.restype = c_int
+        _functions[name] = function
+    return function
+
+
+# ----------------------------------------------------------------------------- elementwise
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, flag: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[ids[t]] as fp32."""
+    _need_cuda("embedding", table, ids, out, flag)
+    _need_i32("embedding", ids)
+    V, H = table.shape
+    if out.dtype != torch.float32 or out.shape != (ids.numel(), H) or not out.is_contiguous():
+        raise KernelError("embedding: out must be contiguous fp32 [tokens, hidden]")
+    if not table.is_contiguous():
+        raise KernelError("embedding: table must be contiguous")
+    fn = _fn("elementwise", "kb_embedding", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(table.data_ptr(), _is_bf16(table, "embedding"), ids.data_ptr(), out.data_ptr(), ids.numel(), H, V, _ptr(flag), _stream()), "embedding")
+
+
+def rmsnorm(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    out: torch.Tensor,
+    *,
+    delta: Optional[torch.Tensor] = None,
+    rows: Optional[torch.Tensor] = None,
+) -> None:
+    """``x += delta`` (if given and ``rows`` is None), ``out = rmsnorm(x) * weight``.
+
+    With ``rows`` only the listed rows of x (+delta) are normed, into
+    out[0..len(rows)), and x is not modified.
+    """
+    _need_cuda("rmsnorm", x, weight, out, delta, rows)
+    _need_i32("rmsnorm", rows)
+    H = x.shape[-1]
+    R = rows.numel() if rows is not None else x.shape[0]
+    if not x.is_contiguous() or not out.is_contiguous() or (delta is not None and not delta.is_contiguous()):
+        raise KernelError("rmsnorm: tensors must be contiguous")
+    if weight.numel() != H or out.shape[-1] != H or out.shape[0] < R:
+        raise KernelError("rmsnorm: shape mismatch")
+    if delta is not None and (delta.dtype != out.dtype or delta.shape != x.shape):
+        raise KernelError("rmsnorm: delta must have the activation dtype and x's shape")
+    fn = _fn("elementwise", "kb_rmsnorm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(
+        fn(x.data_ptr(), _is_bf16(x, "rmsnorm"), _ptr(delta), weight.data_ptr(), _is_bf16(weight, "rmsnorm"), out.data_ptr(), _is_bf16(out, "rmsnorm"), _ptr(rows), R, H, float(eps), 1, _stream()),
+        "rmsnorm",
+    )
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need_cuda("swiglu", gate_up, out)
+    T, two_i = gate_up.shape
+    if two_i % 2 or out.shape != (T, two_i // 2) or out.dtype != gate_up.dtype:
+        raise KernelError("swiglu: shape or dtype mismatch")
+    if not gate_up.is_contiguous() or not out.is_contiguous():
+        raise KernelError("swiglu: tensors must be contiguous")
+    fn = _fn("elementwise", "kb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(gate_up.data_ptr(), out.data_ptr(), _is_bf16(out, "swiglu"), T, two_i // 2, _stream()), "swiglu")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda("gather_rows", src, rows, out)
+    _need_i32("gather_rows", rows)
+    if src.dtype != out.dtype or out.shape != (rows.numel(), src.shape[1]):
+        raise KernelError("gather_rows: shape or dtype mismatch")
+    if not src.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gather_rows: tensors must be contiguous")
+    fn = _fn("elementwise", "kb_gather_rows", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(src.data_ptr(), rows.data_ptr(), out.data_ptr(), _is_bf16(src, "gather_rows"), rows.numel(), src.shape[1], _stream()), "gather_rows")
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+
+
+def qk_norm_rope_kv_write(
+    qkv: torch.Tensor,
+    num_q_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    *,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    q_norm_weight: Optional[torch.Tensor] = None,
+    k_norm_weight: Optional[torch.Tensor] = None,
+    eps: float = 0.0,
+    cos: Optional[torch.Tensor] = None,
+    sin: Optional[torch.Tensor] = None,
+    block_table: Optional[torch.Tensor] = None,
+    write_from: Optional[torch.Tensor] = None,
+    k_cache: Optional[torch.Tensor] = None,
+    v_cache: Optional[torch.Tensor] = None,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """In place on the packed ``qkv`` rows: per-head norm of q and k (if weights
+    are given), rotation (if tables are given), then k and v into the paged
+    cache (if caches are given)."""
+    _need_cuda("qk_norm_rope_kv_write", qkv, positions, row_ids, q_norm_weight, k_norm_weight, cos, sin, block_table, write_from, k_cache, v_cache, flag)
+    _need_i32("qk_norm_rope_kv_write", positions, row_ids, block_table, write_from)
+    T = qkv.shape[0]
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width or qkv.stride(1) != 1:
+        raise KernelError(f"qk_norm_rope_kv_write: qkv must be [tokens, {width}] with unit inner stride")
+    rot_half = 0
+    max_pos = 0
+    if cos is not None:
+        if sin is None or cos.shape != sin.shape or cos.dtype != torch.float32 or sin.dtype != torch.float32:
+            raise KernelError("qk_norm_rope_kv_write: cos and sin must be fp32 tables of one shape")
+        if not cos.is_contiguous() or not sin.is_contiguous():
+            raise KernelError("qk_norm_rope_kv_write: cos and sin must be contiguous")
+        max_pos, rot_half = cos.shape
+    norm_bf16 = 0
+    if q_norm_weight is not None:
+        if k_norm_weight is None or q_norm_weight.dtype != k_norm_weight.dtype:
+            raise KernelError("qk_norm_rope_kv_write: q and k norm weights come together, in one dtype")
+        norm_bf16 = _is_bf16(q_norm_weight, "qk_norm_rope_kv_write")
+    page_size = num_pages = max_pages = 0
+    if k_cache is not None:
+        if v_cache is None or k_cache.shape != v_cache.shape or k_cache.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope_kv_write: caches must match each other and the qkv dtype")
+        if not k_cache.is_contiguous() or not v_cache.is_contiguous():
+            raise KernelError("qk_norm_rope_kv_write: caches must be contiguous")
+        num_pages, page_size, kv_heads, dim = k_cache.shape
+        if kv_heads != num_kv_heads or dim != head_dim:
+            raise KernelError("qk_norm_rope_kv_write: cache geometry does not match the heads")
+        if block_table is None or write_from is None:
+            raise KernelError("qk_norm_rope_kv_write: a cache write needs block_table and write_from")
+        max_pages = block_table.shape[1]
+    fn = _fn(
+        "rope_kv",
+        "kb_qk_norm_rope_kv_write",
+        [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(
+            qkv.data_ptr(), _is_bf16(qkv, "qk_norm_rope_kv_write"), T, qkv.stride(0), num_q_heads, num_kv_heads, head_dim,
+            _ptr(q_norm_weight), _ptr(k_norm_weight), norm_bf16, float(eps), _ptr(cos), _ptr(sin), rot_half, max_pos,
+            positions.data_ptr(), row_ids.data_ptr(), _ptr(block_table), max_pages, _ptr(write_from),
+            _ptr(k_cache), _ptr(v_cache), page_size, num_pages, _ptr(flag), _stream(),
+        ),
+        "qk_norm_rope_kv_write",
+    )
+
+
+# ----------------------------------------------------------------------------- attention
+
+
+def paged_attention_generic(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    positions: torch.Tensor,
+    row_ids: torch.Tensor,
+    block_table: torch.Tensor,
+    num_q_heads: int,
+    scale: float,
+    window: int = 0,
+    flag: Optional[torch.Tensor] = None,
+) -> None:
+    """fp32-arithmetic attention of every token in ``q`` over its request's pages.
+
+    ``q``: [tokens, >= heads*dim] (a view into the packed qkv rows is fine);
+    ``out``: [tokens, heads*dim].
+    """
+    _need_cuda("paged_attention_generic", q, out, k_cache, v_cache, positions, row_ids, block_table, flag)
+    _need_i32("paged_attention_generic", positions, row_ids, block_table)
+    num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
+    if q.dtype != k_cache.dtype or out.dtype != q.dtype or v_cache.shape != k_cache.shape:
+        raise KernelError("paged_attention_generic: dtype or cache shape mismatch")
+    if q.stride(1) != 1 or out.stride(1) != 1 or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("paged_attention_generic: inner strides must be 1 and caches contiguous")
+    if head_dim > 256:
+        raise KernelError(f"paged_attention_generic: head_dim {head_dim} > 256 is not supported")
+    if num_q_heads % num_kv_heads:
+        raise KernelError("paged_attention_generic: query heads must be a multiple of KV heads")
+    T = q.shape[0]
+    fn = _fn(
+        "attention_generic",
+        "kb_paged_attention_generic",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    )
+    _check(
+        fn(
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            _is_bf16(q, "paged_attention_generic"), positions.data_ptr(), row_ids.data_ptr(), block_table.data_ptr(),
+            block_table.shape[1], T, num_q_heads, num_kv_heads, head_dim, page_size, num_pages, float(scale),
+            int(window), _ptr(flag), _stream(),
+        ),
+        "paged_attention_generic",
+    )
+
+
+DECODE_SPLIT = 256  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
+
+
+def attention_mma_supported(head_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
+    """Sizes the tensor-core attention kernels take; others use the generic kernel."""
+    return (
+        head_dim % 16 == 0
+        and 16 <= head_dim <= 256
+        and num_kv_heads >= 1
+        and num_q_heads % num_kv_heads == 0
+        and num_q_heads // num_kv_heads <= 16
+    )
+
+
+def _check_mma_common(what: str, q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
+        raise KernelError(f"{what}: bf16 only")
+    if k_cache.shape != v_cache.shape or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError(f"{what}: caches must be contiguous and of one shape")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"{what}: inner strides must be 1")
+    if q.data_ptr() % 16 or (q.stride(0) * 2) % 16 or k_cache.data_ptr() % 16 or v_cache.data_ptr() % 16:
+        raise KernelError(f"{what}: q rows and caches must be 16-byte aligned")
+
+
+def attention_prefill_mma(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    qo_indptr: torch.Tensor,
+    seq_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    tile_rows: torch.Tensor,
+    tile_starts: torch.Tensor,
+    num_tiles: int,
+    num_q_heads: int,
+    scale: float,
+    window: int = 0,
+) -> None:
+    """Flash attention over 64-query tiles of rows with several tokens (bf16)."""
+    what = "attention_prefill_mma"
+    _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
+    _need_i32(what, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
+    _check_mma_common(what, q, out, k_cache, v_cache)
+    num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
+    if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
+        raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
+    fn = _fn(
+        "attention_mma",
+        "kb_attention_prefill_mma",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    )
+    _check(
+        fn(
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+            tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
+            page_size, num_pages, float(scale), int(window), _stream(),
+        ),
+        what,
+    )
+
+
+def attention_decode_mma(
+    q: torch.Tensor,
+    out: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    *,
+    seq_lens: torch.Tensor,
+    block_table: torch.Tensor,
+    decode_rows: torch.Tensor,
+    decode_tokens: torch.Tensor,
+    num_rows: int,
+    max_seq_len: int,
+    num_q_heads: int,
+    scale: float,
+    window: int = 0,
+    workspace: object,
+) -> None:
+    """Split-KV attention of rows that carry one token (bf16), then the merge.
+
+    ``max_seq_len`` bounds every row's length; it sizes the grid and the scratch
+    (``workspace.flat`` gives persistent fp32 buffers).
+    """
+    what = "attention_decode_mma"
+    _need_cuda(what, q, out, k_cache, v_cache, seq_lens, block_table, decode_rows, decode_tokens)
+    _need_i32(what, seq_lens, block_table, decode_rows, decode_tokens)
+    _check_mma_common(what, q, out, k_cache, v_cache)
+    num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
+    if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
+        raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
+    num_splits = max(1, -(-int(max_seq_len) // DECODE_SPLIT))
+    part_o = workspace.flat("attn.part_o", num_rows * num_q_heads * num_splits * head_dim, torch.float32)
+    part_ml = workspace.flat("attn.part_ml", num_rows * num_q_heads * num_splits * 2, torch.float32)
+    fn = _fn(
+        "attention_mma",
+        "kb_attention_decode_mma",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    )
+    _check(
+        fn(
+            q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
+            decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
+            float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _stream(),
+        ),
+        what,
+    )
+
+
+# ----------------------------------------------------------------------------- matrix products
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out = x @ weight.T (+ bias).
+
+    float32: this package's own FMA kernel (true 32-bit, fixed summation order).
+    bfloat16: the library product (cuBLAS through torch), as the reference's
+    ``F.linear`` is (kairyu/models/packed_linear.py:217); accumulation is fp32,
+    ``out`` may be bfloat16 or float32.
+    """
+    _need_cuda("linear", x, weight, bias, out)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or out.shape != (M, N):
+        raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(weight.shape)} out{tuple(out.shape)} do not agree")
+    if x.dtype == torch.float32:
+        if weight.dtype != torch.float32 or out.dtype != torch.float32:
+            raise KernelError("linear: the 32-bit path needs fp32 weights and output")
+        if bias is not None and bias.dtype != torch.float32:
+            raise KernelError("linear: the 32-bit path needs an fp32 bias")
+        if x.stride(1) != 1 or weight.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear: inner strides must be 1")
+        fn = _fn("gemm_f32", "kb_gemm_f32", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+        _check(fn(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), M, N, K, _stream()), "linear")
+        return
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise KernelError(f"linear: dtypes {x.dtype} / {weight.dtype} are not supported")
+    if M == 0:
+        return
+    if out.dtype == torch.bfloat16:
+        if bias is not None:
+            torch.addmm(bias, x, weight.t(), out=out)
+        else:
+            torch.mm(x, weight.t(), out=out)
+    elif out.dtype == torch.float32:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+        if bias is not None:
+            out.add_(bias)
+    else:
+        raise KernelError(f"linear: output dtype {out.dtype} is not supported")
+
+
+# ----------------------------------------------------------------------------- sampling
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda("argmax", logits, out)
+    _need_i32("argmax", out)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be fp32 with unit inner stride")
+    n, V = logits.shape
+    fn = _fn("sampling", "kb_argmax", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), n, V, out.data_ptr(), _stream()), "argmax")
+
+
+def edit_logits(
+    logits: torch.Tensor,
+    rows: torch.Tensor,
+    tokens: torch.Tensor,
+    mul: torch.Tensor,
+    sub: torch.Tensor,
+    mask: torch.Tensor,
+) -> None:
+    _need_cuda("edit_logits", logits, rows, tokens, mul, sub, mask)
+    _need_i32("edit_logits", rows, tokens, mask)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("edit_logits: logits must be fp32 with unit inner stride")
+    E = rows.numel()
+    if not (tokens.numel() == mul.numel() == sub.numel() == mask.numel() == E):
+        raise KernelError("edit_logits: entry arrays must have one length")
+    if mul.dtype != torch.float32 or sub.dtype != torch.float32:
+        raise KernelError("edit_logits: mul and sub must be fp32")
+    fn = _fn("sampling", "kb_edit_logits", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(), tokens.data_ptr(), mul.data_ptr(), sub.data_ptr(), mask.data_ptr(), E, _stream()), "edit_logits")
+
+
+def sample(
+    logits: torch.Tensor,
+    work: torch.Tensor,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    min_p: torch.Tensor,
+    seeds: torch.Tensor,
+    out: torch.Tensor,
+) -> None:
+    """One draw per row; ``seeds`` are int64 bit patterns of the per-position seeds."""
+    _need_cuda("sample", logits, work, temperature, top_k, top_p, min_p, seeds, out)
+    _need_i32("sample", top_k, out)
+    n, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be fp32 with unit inner stride")
+    if work.dtype != torch.float32 or not work.is_contiguous() or work.numel() < n * V:
+        raise KernelError("sample: work must be contiguous fp32 with at least rows*vocab elements")
+    if seeds.dtype != torch.int64 or temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or min_p.dtype != torch.float32:
+        raise KernelError("sample: parameter dtypes are fp32 (temperature, top_p, min_p), int32 (top_k), int64 (seeds)")
+    fn = _fn("sampling", "kb_sample", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(
+        fn(logits.data_ptr(), logits.stride(0), work.data_ptr(), n, V, temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), seeds.data_ptr(), out.data_ptr(), _stream()),
+        "sample",
+    )
+
+
+__all__ = [
+    "KernelBuildError",
+    "KernelError",
+    "argmax",
+    "attention_decode_mma",
+    "attention_mma_supported",
+    "attention_prefill_mma",
+    "edit_logits",
+    "embedding",
+    "gather_rows",
+    "linear",
+    "paged_attention_generic",
+    "qk_norm_rope_kv_write",
+    "rmsnorm",
+    "sample",
+    "swiglu",
+]

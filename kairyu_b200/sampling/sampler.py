@@ -1,0 +1,121 @@
+"""Chooses the next token of each row from its logits, on the device.
+
+Order of operations (kairyu/engine/core/sampler.py:1-27): min-tokens mask,
+penalties, then argmax when temperature is 0, else temperature, min-p, top-k,
+top-p and a seeded Gumbel-max draw.  One kernel launch edits logits (only when
+some row needs it) and one selects tokens for all rows.
+"""
+
+from __future__ import annotations
+
+from collections import Counter
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from kairyu_b200 import kernels
+from kairyu_b200.sampling.params import SamplingParams
+from kairyu_b200.sampling.rng import as_signed64, mix_seed, stable_request_seed
+
+
+@dataclass
+class SamplingRow:
+    """What the sampler needs to know about one row of logits."""
+
+    request_id: str
+    params: SamplingParams
+    position: int  # index of the output token being chosen
+    prompt_token_ids: Sequence[int] = ()
+    output_token_ids: Sequence[int] = ()
+    eos_token_ids: Sequence[int] = ()
+
+    def base_seed(self) -> int:
+        if self.params.seed is not None:
+            return self.params.seed & ((1 << 64) - 1)
+        return stable_request_seed(self.request_id)
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, device: str) -> None:
+        self.vocab_size = vocab_size
+        self.device = device
+        self._work: Optional[torch.Tensor] = None
+        self._is_cuda = str(device).startswith("cuda")
+
+    def _host(self, values: list, dtype: torch.dtype) -> torch.Tensor:
+        tensor = torch.tensor(values, dtype=dtype)
+        if self._is_cuda:
+            tensor = tensor.pin_memory()
+        return tensor.to(self.device, non_blocking=True)
+
+    def _edits(self, rows: Sequence[SamplingRow]) -> Optional[tuple[list[int], list[int], list[float], list[float], list[int]]]:
+        e_row: list[int] = []
+        e_tok: list[int] = []
+        e_mul: list[float] = []
+        e_sub: list[float] = []
+        e_mask: list[int] = []
+        for index, row in enumerate(rows):
+            p = row.params
+            masked: set[int] = set()
+            if row.position < p.min_tokens:
+                # kairyu/engine/core/sampler.py:666-699: the whole stop set, EOS included
+                for token in (*p.stop_token_ids, *row.eos_token_ids):
+                    if 0 <= token < self.vocab_size and token not in masked:
+                        masked.add(token)
+                        e_row.append(index); e_tok.append(token); e_mul.append(1.0); e_sub.append(0.0); e_mask.append(1)
+            has_rep = p.repetition_penalty != 1.0
+            has_out = p.frequency_penalty != 0.0 or p.presence_penalty != 0.0
+            if not (has_rep or has_out):
+                continue
+            counts = Counter(row.output_token_ids)
+            seen = set(counts)
+            if has_rep:
+                seen |= set(row.prompt_token_ids)
+            for token in seen:
+                if token in masked or not 0 <= token < self.vocab_size:
+                    continue
+                count = counts.get(token, 0)
+                sub = p.frequency_penalty * count + (p.presence_penalty if count else 0.0)
+                e_row.append(index); e_tok.append(token)
+                e_mul.append(p.repetition_penalty if has_rep else 1.0)
+                e_sub.append(sub); e_mask.append(0)
+        if not e_row:
+            return None
+        return e_row, e_tok, e_mul, e_sub, e_mask
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[SamplingRow]) -> torch.Tensor:
+        """``logits``: [n, vocab] fp32 on the device (edited in place when a row
+        has penalties or a min-tokens mask).  Returns int32 token ids [n] on the device."""
+        n = logits.shape[0]
+        if n != len(rows):
+            raise ValueError(f"{n} rows of logits for {len(rows)} sampling rows")
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        edits = self._edits(rows)
+        if edits is not None:
+            e_row, e_tok, e_mul, e_sub, e_mask = edits
+            kernels.edit_logits(
+                logits,
+                self._host(e_row, torch.int32),
+                self._host(e_tok, torch.int32),
+                self._host(e_mul, torch.float32),
+                self._host(e_sub, torch.float32),
+                self._host(e_mask, torch.int32),
+            )
+        if all(row.params.temperature == 0.0 for row in rows):
+            kernels.argmax(logits, out)
+            return out
+        if self._work is None or self._work.numel() < n * self.vocab_size:
+            self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
+        seeds = [as_signed64(mix_seed(row.base_seed(), row.position)) for row in rows]
+        kernels.sample(
+            logits,
+            self._work,
+            self._host([float(row.params.temperature) for row in rows], torch.float32),
+            self._host([int(row.params.top_k) for row in rows], torch.int32),
+            self._host([float(row.params.top_p) for row in rows], torch.float32),
+            self._host([float(row.params.min_p) for row in rows], torch.float32),
+            self._host(seeds, torch.int64),
+            out,
+        )
+        return out

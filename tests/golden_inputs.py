@@ -1,0 +1,22 @@
+"""Seeded weights and prompts shared by the golden script and the tests."""
+
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from kairyu_b200.weights.random_init import _specs_without_building, random_tensors
+from kairyu_b200.registry import architecture_of
+
+
+def golden_weights(config: Mapping, seed: int) -> dict[str, torch.Tensor]:
+    """fp32 CPU tensors by HF name for a tiny config (the tied head is absent)."""
+    architecture = architecture_of(config)
+    spec = architecture.build_spec(architecture.parse_config(config))
+    return random_tensors(_specs_without_building(spec), seed, device="cpu")
+
+
+def golden_prompt(config: Mapping, seed: int, length: int = 90) -> list[int]:
+    generator = torch.Generator().manual_seed(1000 + seed)
+    return torch.randint(0, config["vocab_size"], (length,), generator=generator).tolist()
