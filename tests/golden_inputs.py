@@ -20,3 +20,13 @@ def golden_weights(config: Mapping, seed: int) -> dict[str, torch.Tensor]:
 def golden_prompt(config: Mapping, seed: int, length: int = 90) -> list[int]:
     generator = torch.Generator().manual_seed(1000 + seed)
     return torch.randint(0, config["vocab_size"], (length,), generator=generator).tolist()
+
+
+def as_held_in_bf16(weights: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+    """The values a bfloat16 engine computes with, as fp32 tensors: matrices and
+    biases rounded to bf16, norm weights (stored in 32-bit) left as they are."""
+    held = {}
+    for name, tensor in weights.items():
+        keep = tensor.ndim == 1 and name.endswith("norm.weight")
+        held[name] = tensor if keep else tensor.to(torch.bfloat16).float()
+    return held

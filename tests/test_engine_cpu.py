@@ -1,0 +1,87 @@
+"""The engine loop (scheduler + step function + sampler + entry point) on the
+CPU with the kernels replaced by their torch statements: host-side decisions
+only.  The same workloads run on the GPU with the real kernels."""
+
+import pytest
+import torch
+
+import plain_model
+import torch_kernels
+from test_engine_gpu import engine_weights, plain_generate, prompts_of
+from tiny_configs import TINY
+
+from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+
+@pytest.fixture(autouse=True)
+def cpu_kernels(monkeypatch):
+    torch_kernels.install(monkeypatch)
+
+
+def make_llm(name, **kwargs):
+    config, seed, page_size = TINY[name]
+    kwargs.setdefault("page_size", page_size)
+    return LLM.from_random(config, seed=seed, dtype="float32", device="cpu", **kwargs), config
+
+
+def test_greedy_generation_matches_plain():
+    llm, config = make_llm("llama", num_pages=32)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [1, 7, 33, 50], seed=100)
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], SamplingParams(temperature=0.0, max_tokens=8))
+    for prompt, output in zip(prompts, outputs):
+        assert list(output.outputs[0].token_ids) == plain_generate(config, weights, prompt, 8)
+        assert output.outputs[0].finish_reason == "length"
+        assert output.finished
+
+
+def test_sampled_generation_matches_plain_and_repeats():
+    llm, config = make_llm("qwen3", num_pages=64, prefill_chunk_size=24)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [3, 50, 27], seed=101)
+    params = [SamplingParams(temperature=0.8, top_p=0.9, seed=50 + i, max_tokens=6) for i in range(3)]
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    for index, (prompt, output) in enumerate(zip(prompts, outputs)):
+        expected = plain_generate(config, weights, prompt, 6, dict(temperature=0.8, top_p=0.9), request_seed=50 + index)
+        assert list(output.outputs[0].token_ids) == expected
+    again = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    assert [o.outputs[0].token_ids for o in again] == [o.outputs[0].token_ids for o in outputs]
+
+
+def test_small_budget_few_pages_preempts_and_still_matches():
+    llm, config = make_llm("odd", num_pages=9, max_num_batched_tokens=7, max_num_seqs=4)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [30, 14, 46, 31, 15, 47], seed=102)
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], SamplingParams(temperature=0.0, max_tokens=20))
+    assert llm.engine.scheduler.counters["preemptions"] > 0
+    llm.engine.cache.check()
+    assert llm.engine.cache.live_requests == 0
+    for prompt, output in zip(prompts, outputs):
+        assert list(output.outputs[0].token_ids) == plain_generate(config, weights, prompt, 20)
+
+
+def test_n_completions_and_param_lists():
+    llm, config = make_llm("llama", num_pages=32)
+    prompt = prompts_of(config, [6], seed=105)[0]
+    out = llm.generate(TokensPrompt(tuple(prompt)), SamplingParams(temperature=1.0, seed=3, n=3, max_tokens=5))[0]
+    assert len(out.outputs) == 3 and [c.index for c in out.outputs] == [0, 1, 2]
+    assert len({c.token_ids for c in out.outputs}) > 1
+    with pytest.raises(ValueError):
+        llm.generate([TokensPrompt((1,)), TokensPrompt((2,))], [SamplingParams()])
+    with pytest.raises(ValueError):
+        llm.generate("text needs a tokenizer")
+    with pytest.raises(ValueError):
+        llm.generate(TokensPrompt((1,)), SamplingParams(logprobs=1))
+    with pytest.raises(ValueError):
+        llm.generate(TokensPrompt((1,) * 10), SamplingParams(max_tokens=100000))
+    # vLLM-style dict prompts
+    out = llm.generate({"prompt_token_ids": prompt}, SamplingParams(temperature=0.0, max_tokens=2))[0]
+    assert len(out.outputs[0].token_ids) == 2
+
+
+def test_llm_rejects_unknown_options_and_parallel_sizes():
+    config, seed, _ = TINY["llama"]
+    with pytest.raises(TypeError):
+        LLM.from_random(config, seed=0, device="cpu", not_an_option=1)
+    with pytest.raises(ValueError):
+        LLM("/nonexistent", tensor_parallel_size=2)

@@ -1,0 +1,182 @@
+"""Generation through the Python entry point on the GPU, compared with the
+plain implementation: the two tiny workloads (greedy; temperature + top-p with
+seeds), portions under a token budget, preemption when pages run out."""
+
+import pytest
+import torch
+
+import plain_model
+from golden_inputs import golden_weights
+from tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_generate(config, weights, prompt, steps, params=None, request_seed=0):
+    tokens = list(prompt)
+    for position in range(steps):
+        logits = plain_model.forward_logits(config, weights, tokens)[-1]
+        if params is None:
+            token = int(logits.argmax())
+        else:
+            token = plain_model.sample_token(logits, base_seed=request_seed, position=position, **params)
+        tokens.append(token)
+    return tokens[len(prompt):]
+
+
+def prompts_of(config, lengths, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, config["vocab_size"], (n,), generator=g).tolist() for n in lengths]
+
+
+def test_greedy_workload_tiny_llama():
+    """4 prompts of 1, 7, 33 and 50 tokens, 16 greedy tokens each, page size 16, fp32."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["llama"]
+    llm = LLM.from_random(config, seed=seed, dtype="float32", page_size=page_size, num_pages=32)
+    weights = {spec.name: None for spec in llm.engine.model.tensor_specs()}
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [1, 7, 33, 50], seed=100)
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], SamplingParams(temperature=0.0, max_tokens=16))
+    for prompt, output in zip(prompts, outputs):
+        assert output.prompt_token_ids == tuple(prompt)
+        assert list(output.outputs[0].token_ids) == plain_generate(config, weights, prompt, 16)
+        assert output.outputs[0].finish_reason == "length"
+
+
+def engine_weights(llm):
+    """The engine's own (random, device-generated) weights by HF tensor name, as fp32 CPU tensors."""
+    model = llm.engine.model
+    out = {}
+    for index, block in enumerate(model.blocks):
+        p = f"model.layers.{index}"
+        mixer, ffn = block.mixer, block.ffn
+        q, kv = mixer.q_size, mixer.kv_size
+        out[f"{p}.self_attn.q_proj.weight"] = mixer.w_qkv[:q]
+        out[f"{p}.self_attn.k_proj.weight"] = mixer.w_qkv[q : q + kv]
+        out[f"{p}.self_attn.v_proj.weight"] = mixer.w_qkv[q + kv :]
+        out[f"{p}.self_attn.o_proj.weight"] = mixer.w_o
+        if mixer.b_qkv is not None:
+            out[f"{p}.self_attn.q_proj.bias"] = mixer.b_qkv[:q]
+            out[f"{p}.self_attn.k_proj.bias"] = mixer.b_qkv[q : q + kv]
+            out[f"{p}.self_attn.v_proj.bias"] = mixer.b_qkv[q + kv :]
+        if mixer.b_o is not None:
+            out[f"{p}.self_attn.o_proj.bias"] = mixer.b_o
+        if mixer.q_norm_weight is not None:
+            out[f"{p}.self_attn.q_norm.weight"] = mixer.q_norm_weight
+            out[f"{p}.self_attn.k_norm.weight"] = mixer.k_norm_weight
+        inter = ffn.intermediate_size
+        out[f"{p}.mlp.gate_proj.weight"] = ffn.w_gate_up[:inter]
+        out[f"{p}.mlp.up_proj.weight"] = ffn.w_gate_up[inter:]
+        out[f"{p}.mlp.down_proj.weight"] = ffn.w_down
+        out[f"{p}.input_layernorm.weight"] = block.mixer_norm.weight
+        out[f"{p}.post_attention_layernorm.weight"] = block.ffn_norm.weight
+    out["model.embed_tokens.weight"] = model.embedding.weight
+    out["model.norm.weight"] = model.final_norm.weight
+    out["lm_head.weight"] = model.head.weight
+    return {k: v.detach().float().cpu() for k, v in out.items()}
+
+
+def test_sampled_workload_tiny_qwen3():
+    """6 prompts of 1..120 tokens, portions of 24, temperature 0.8 / top-p 0.9 with seeds, 24 tokens, page size 8, fp32."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["qwen3"]
+    llm = LLM.from_random(config, seed=seed, dtype="float32", page_size=page_size, num_pages=128, prefill_chunk_size=24)
+    weights = engine_weights(llm)
+    g = torch.Generator().manual_seed(7)
+    lengths = torch.randint(1, 121, (6,), generator=g).tolist()
+    prompts = prompts_of(config, lengths, seed=101)
+    params = [SamplingParams(temperature=0.8, top_p=0.9, seed=1000 + i, max_tokens=24) for i in range(6)]
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    for index, (prompt, output) in enumerate(zip(prompts, outputs)):
+        expected = plain_generate(config, weights, prompt, 24, dict(temperature=0.8, top_p=0.9), request_seed=1000 + index)
+        assert list(output.outputs[0].token_ids) == expected
+    again = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    assert [o.outputs[0].token_ids for o in again] == [o.outputs[0].token_ids for o in outputs]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_under_a_small_budget_and_few_pages(dtype):
+    """A token budget of 7 cuts prompts into many portions beside decodes; so few
+    pages that requests wait and are preempted; the greedy tokens stay those of
+    the plain implementation (fp32) or agree with it almost everywhere (bf16)."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["odd"]
+    llm = LLM.from_random(config, seed=seed, dtype=dtype, page_size=page_size, num_pages=9, max_num_batched_tokens=7, max_num_seqs=4)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [30, 14, 46, 31, 15, 47], seed=102)
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], SamplingParams(temperature=0.0, max_tokens=20))
+    assert llm.engine.scheduler.counters["preemptions"] > 0
+    llm.engine.cache.check()
+    assert llm.engine.cache.live_requests == 0
+    agree = total = 0
+    for prompt, output in zip(prompts, outputs):
+        expected = plain_generate(config, weights, prompt, 20)
+        got = list(output.outputs[0].token_ids)
+        assert len(got) == 20
+        if dtype == "float32":
+            assert got == expected
+        # count agreement up to the first divergence (after it the contexts differ)
+        for a, b in zip(got, expected):
+            total += 1
+            if a != b:
+                break
+            agree += 1
+    if dtype == "bfloat16":
+        assert agree / total > 0.9
+
+
+def test_stop_token_and_eos():
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["llama"]
+    llm = LLM.from_random(config, seed=seed, dtype="float32", page_size=page_size, num_pages=32)
+    prompt = prompts_of(config, [9], seed=103)[0]
+    free = llm.generate(TokensPrompt(tuple(prompt)), SamplingParams(temperature=0.0, max_tokens=12))[0].outputs[0].token_ids
+    stop_at = free[4]
+    first = free.index(stop_at)
+    out = llm.generate(TokensPrompt(tuple(prompt)), SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[stop_at]))[0].outputs[0]
+    assert out.token_ids == free[: first + 1]
+    assert out.finish_reason == "stop" and out.stop_reason == stop_at
+    # min_tokens masks the stop token until enough tokens exist
+    out = llm.generate(
+        TokensPrompt(tuple(prompt)), SamplingParams(temperature=0.0, max_tokens=12, stop_token_ids=[stop_at], min_tokens=first + 2)
+    )[0].outputs[0]
+    assert len(out.token_ids) >= first + 2
+    assert stop_at not in out.token_ids[: first + 2]
+    # EOS from the model config ends a request unless ignore_eos
+    llm.eos_token_ids = (stop_at,)
+    out = llm.generate(TokensPrompt(tuple(prompt)), SamplingParams(temperature=0.0, max_tokens=12))[0].outputs[0]
+    assert out.token_ids == free[: first + 1] and out.finish_reason == "stop"
+    out = llm.generate(TokensPrompt(tuple(prompt)), SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))[0].outputs[0]
+    assert out.token_ids == free
+
+
+def test_penalties_change_greedy_tokens_as_the_plain_rule_says():
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["llama"]
+    llm = LLM.from_random(config, seed=seed, dtype="float32", page_size=page_size, num_pages=32)
+    weights = engine_weights(llm)
+    prompt = prompts_of(config, [15], seed=104)[0]
+    params = SamplingParams(temperature=0.0, max_tokens=10, repetition_penalty=1.6, frequency_penalty=0.4, presence_penalty=0.3)
+    got = list(llm.generate(TokensPrompt(tuple(prompt)), params)[0].outputs[0].token_ids)
+    tokens = list(prompt)
+    outputs = []
+    for _ in range(10):
+        logits = plain_model.forward_logits(config, weights, tokens)[-1]
+        logits = plain_model.apply_penalties(logits, prompt, outputs, repetition=1.6, frequency=0.4, presence=0.3)
+        token = int(logits.argmax())
+        outputs.append(token)
+        tokens.append(token)
+    assert got == outputs
+
+
+def test_kernels_refuse_cpu_tensors():
+    import kairyu_b200.kernels as kernels
+
+    with pytest.raises(kernels.KernelError):
+        kernels.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))

@@ -1,0 +1,499 @@
+"""Each CUDA kernel alone against its plain torch statement (tests/torch_kernels.py),
+at sizes other than the engine's: widths and vocabularies that are no power of
+two, head sizes in steps of 16, odd head groups, several page sizes.  Where
+random data would hide a fault the inputs are built so that it shows (one key
+among hundreds carries the whole softmax; keys at page, tile and split edges)."""
+
+import math
+
+import pytest
+import torch
+
+import torch_kernels as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def kernels():
+    import kairyu_b200.kernels as k
+
+    return k
+
+
+def rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(a, b, atol, rtol=0.0):
+    a = a.float().cpu()
+    b = b.float().cpu()
+    diff = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert bool((diff <= bound).all()), f"max abs diff {diff.max().item():.3e} (atol {atol}, rtol {rtol})"
+
+
+# ------------------------------------------------------------------ elementwise
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,H,T", [(331, 120, 17), (1000, 4096, 3)])
+def test_embedding(dtype, V, H, T):
+    table = rand(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32)
+    out = torch.empty(T, H, dtype=torch.float32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().embedding(table.to(DEV), ids.to(DEV), out, flag)
+    assert torch.equal(out.cpu(), table[ids.long()].float())
+    assert int(flag.item()) == 0
+
+
+def test_embedding_flags_a_bad_token():
+    table = rand(50, 24).to(DEV)
+    ids = torch.tensor([3, 50, -1], dtype=torch.int32, device=DEV)
+    out = torch.full((3, 24), 7.0, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().embedding(table, ids, out, flag)
+    assert int(flag.item()) == kernels().FLAG_BAD_TOKEN
+    assert torch.equal(out[1:].cpu(), torch.zeros(2, 24))
+
+
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("wdtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,T,eps", [(120, 9, 3e-6), (4096, 5, 1e-5), (96, 33, 1e-6)])
+def test_rmsnorm_with_residual_sum(act, wdtype, H, T, eps):
+    x = rand(T, H, seed=1)
+    delta = rand(T, H, dtype=act, seed=2)
+    w = (1 + 0.1 * rand(H, seed=3)).to(wdtype)
+    # reference on the CPU
+    x_ref = x.clone()
+    out_ref = torch.empty(T, H, dtype=act)
+    ref.rmsnorm(x_ref, w, eps, out_ref, delta=delta)
+    x_dev = x.to(DEV)
+    out = torch.empty(T, H, dtype=act, device=DEV)
+    kernels().rmsnorm(x_dev, w.to(DEV), eps, out, delta=delta.to(DEV))
+    close(x_dev, x_ref, 1e-6)  # the fp32 residual sum
+    close(out, out_ref, 2e-6 if act == torch.float32 else 0.0, rtol=0.0 if act == torch.float32 else 1e-2)
+    # without delta
+    out2 = torch.empty(T, H, dtype=act, device=DEV)
+    kernels().rmsnorm(x_dev, w.to(DEV), eps, out2)
+    ref.rmsnorm(x_ref, w, eps, out_ref)
+    close(out2, out_ref, 2e-6 if act == torch.float32 else 0.0, rtol=0.0 if act == torch.float32 else 1e-2)
+
+
+def test_rmsnorm_rows_leave_the_residual_alone():
+    T, H = 12, 200
+    x = rand(T, H, seed=4)
+    delta = rand(T, H, seed=5)
+    w = 1 + 0.1 * rand(H, seed=6)
+    rows = torch.tensor([11, 0, 5], dtype=torch.int32)
+    out_ref = torch.empty(3, H)
+    ref.rmsnorm(x.clone(), w, 1e-5, out_ref, delta=delta, rows=rows)
+    x_dev = x.to(DEV)
+    out = torch.empty(3, H, device=DEV)
+    kernels().rmsnorm(x_dev, w.to(DEV), 1e-5, out, delta=delta.to(DEV), rows=rows.to(DEV))
+    assert torch.equal(x_dev.cpu(), x)
+    close(out, out_ref, 2e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,I", [(7, 200), (3, 14336), (70, 160)])
+def test_swiglu(dtype, T, I):
+    gate_up = rand(T, 2 * I, dtype=dtype, seed=7, scale=2.0)
+    out_ref = torch.empty(T, I, dtype=dtype)
+    ref.swiglu(gate_up, out_ref)
+    out = torch.empty(T, I, dtype=dtype, device=DEV)
+    kernels().swiglu(gate_up.to(DEV), out)
+    close(out, out_ref, 1e-6 if dtype == torch.float32 else 0.0, rtol=1e-6 if dtype == torch.float32 else 1e-2)
+
+
+# ------------------------------------------------------------------ fp32 matrix product
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 331, 120), (65, 129, 17), (8, 4096, 4096), (130, 64, 200)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_gemm_f32_is_true_fp32(M, N, K, bias):
+    x = rand(M, K, seed=8)
+    w = rand(N, K, seed=9, scale=0.05)
+    b = rand(N, seed=10) if bias else None
+    expected = (x.double() @ w.double().t() + (b.double() if bias else 0)).float()
+    out = torch.empty(M, N, device=DEV)
+    kernels().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out)
+    # fp32 accumulation error for K terms of magnitude ~0.05: far below TF32's 1e-3
+    close(out, expected, 2e-6 * math.sqrt(K), rtol=1e-6)
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    x = rand(70, 200, seed=11)
+    w = rand(300, 200, seed=12, scale=0.05)
+    full = torch.empty(70, 300, device=DEV)
+    kernels().linear(x.to(DEV), w.to(DEV), None, full)
+    for start, stop in ((0, 1), (5, 6), (64, 70), (3, 68)):
+        part = torch.empty(stop - start, 300, device=DEV)
+        kernels().linear(x[start:stop].contiguous().to(DEV), w.to(DEV), None, part)
+        assert torch.equal(part, full[start:stop])
+
+
+@pytest.mark.parametrize("M,N,K", [(5, 96, 64), (64, 28672, 4096), (2048, 6144, 4096)])
+def test_linear_bf16(M, N, K):
+    x = rand(M, K, dtype=torch.bfloat16, seed=13)
+    w = rand(N, K, dtype=torch.bfloat16, seed=14, scale=0.02)
+    expected = x.float().to(DEV) @ w.float().to(DEV).t()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    kernels().linear(x.to(DEV), w.to(DEV), None, out)
+    close(out, expected, 2e-3 * math.sqrt(K / 64), rtol=1e-2)
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    kernels().linear(x.to(DEV), w.to(DEV), None, out32)
+    close(out32, expected, 1e-4 * math.sqrt(K / 64), rtol=1e-4)
+
+
+# ------------------------------------------------------------------ rope + cache write
+
+
+def _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed):
+    from kairyu_b200.parts.rope import rotary_tables
+
+    g = torch.Generator().manual_seed(seed)
+    max_pos = 300
+    cos, sin = rotary_tables(rot_dim, 10000.0, None, max_pos)
+    rows = 3
+    row_ids = torch.sort(torch.randint(0, rows, (T,), generator=g)).values.to(torch.int32)
+    positions = torch.randint(0, max_pos, (T,), generator=g).to(torch.int32)
+    # distinct (row, position) pairs so that no two tokens write one slot
+    seen = set()
+    for t in range(T):
+        while (int(row_ids[t]), int(positions[t])) in seen:
+            positions[t] = (int(positions[t]) + 1) % max_pos
+        seen.add((int(row_ids[t]), int(positions[t])))
+    max_pages = -(-max_pos // page_size)
+    num_pages = rows * max_pages + 1
+    table = (torch.randperm(num_pages - 1, generator=g)[: rows * max_pages] + 1).view(rows, max_pages).to(torch.int32)
+    write_from = torch.tensor([0, 40, 0], dtype=torch.int32)
+    qkv = rand(T, (Hq + 2 * Hkv) * D, dtype=dtype, seed=seed + 1)
+    qw = (1 + 0.1 * rand(D, seed=seed + 2)) if qk_norm else None
+    kw = (1 + 0.1 * rand(D, seed=seed + 3)) if qk_norm else None
+    return dict(cos=cos, sin=sin, row_ids=row_ids, positions=positions, table=table, write_from=write_from, qkv=qkv, qw=qw, kw=kw, num_pages=num_pages)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize(
+    "Hq,Hkv,D,page_size,qk_norm,rot_dim",
+    [(4, 2, 16, 16, False, 16), (6, 3, 32, 8, True, 32), (5, 1, 48, 16, True, 48), (32, 8, 128, 16, False, 128), (3, 3, 80, 4, True, 32)],
+)
+def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, page_size, qk_norm, rot_dim):
+    T = 37
+    case = _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed=20)
+    kc_ref = torch.zeros(case["num_pages"], page_size, Hkv, D, dtype=dtype)
+    vc_ref = torch.zeros_like(kc_ref)
+    qkv_ref = case["qkv"].clone()
+    common = dict(positions=case["positions"], row_ids=case["row_ids"], eps=1e-6)
+    ref.qk_norm_rope_kv_write(
+        qkv_ref, Hq, Hkv, D, q_norm_weight=case["qw"], k_norm_weight=case["kw"], cos=case["cos"], sin=case["sin"],
+        block_table=case["table"], write_from=case["write_from"], k_cache=kc_ref, v_cache=vc_ref, **common,
+    )
+    to = lambda t: None if t is None else t.to(DEV)
+    qkv = case["qkv"].to(DEV)
+    kc = torch.zeros_like(kc_ref, device=DEV)
+    vc = torch.zeros_like(kc_ref, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().qk_norm_rope_kv_write(
+        qkv, Hq, Hkv, D, positions=to(case["positions"]), row_ids=to(case["row_ids"]), q_norm_weight=to(case["qw"]),
+        k_norm_weight=to(case["kw"]), eps=1e-6, cos=to(case["cos"]), sin=to(case["sin"]), block_table=to(case["table"]),
+        write_from=to(case["write_from"]), k_cache=kc, v_cache=vc, flag=flag,
+    )
+    assert int(flag.item()) == 0
+    atol, rtol = (3e-6, 1e-6) if dtype == torch.float32 else (0.0, 1e-2)
+    q_size, kv_size = Hq * D, Hkv * D
+    close(qkv[:, : q_size + kv_size], qkv_ref[:, : q_size + kv_size], atol, rtol)
+    assert torch.equal(qkv[:, q_size + kv_size :].cpu(), qkv_ref[:, q_size + kv_size :])  # v untouched
+    close(kc, kc_ref, atol, rtol)
+    assert torch.equal(vc.cpu(), vc_ref)
+    # positions below write_from wrote nothing: the slots of row 1 below position 40 stay zero
+    written = (kc_ref.abs().sum(dim=(2, 3)) > 0)
+    assert torch.equal((kc.cpu().float().abs().sum(dim=(2, 3)) > 0), written)
+
+
+def test_rope_flags_a_position_outside_the_table():
+    from kairyu_b200.parts.rope import rotary_tables
+
+    cos, sin = rotary_tables(16, 10000.0, None, 8)
+    qkv = rand(2, 4 * 16).to(DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().qk_norm_rope_kv_write(
+        qkv, 2, 1, 16, positions=torch.tensor([3, 8], dtype=torch.int32, device=DEV),
+        row_ids=torch.zeros(2, dtype=torch.int32, device=DEV), cos=cos.to(DEV), sin=sin.to(DEV), flag=flag,
+    )
+    assert int(flag.item()) == kernels().FLAG_BAD_POS
+
+
+# ------------------------------------------------------------------ attention
+
+
+def _attention_case(dtype, Hq, Hkv, D, page_size, seq_lens, chunk_lens, seed, hot=None):
+    """A cache filled with random keys and values for `len(seq_lens)` requests and
+    the queries of their last `chunk_lens[i]` positions.  ``hot`` = (row, key
+    position): that key is made to dominate the softmax of every later query of
+    the row, and its value is set apart, so a kernel that skips or misplaces it
+    returns something visibly different."""
+    g = torch.Generator().manual_seed(seed)
+    rows = len(seq_lens)
+    max_pages = max(-(-s // page_size) for s in seq_lens) + 1
+    num_pages = rows * max_pages + 3
+    perm = torch.randperm(num_pages - 1, generator=g) + 1
+    table = torch.full((rows, max_pages), -1, dtype=torch.int32)
+    kc = torch.zeros(num_pages, page_size, Hkv, D)
+    vc = torch.zeros_like(kc)
+    used = 0
+    for r, s in enumerate(seq_lens):
+        n = -(-s // page_size)
+        table[r, :n] = perm[used : used + n].to(torch.int32)
+        used += n
+        for j in range(s):
+            page = int(table[r, j // page_size])
+            kc[page, j % page_size] = torch.randn(Hkv, D, generator=g) * 0.5
+            vc[page, j % page_size] = torch.randn(Hkv, D, generator=g)
+    tokens = sum(chunk_lens)
+    q = torch.randn(tokens, Hq * D, generator=g) * 0.5
+    positions, row_ids, qo = [], [], [0]
+    for r, (s, c) in enumerate(zip(seq_lens, chunk_lens)):
+        positions += list(range(s - c, s))
+        row_ids += [r] * c
+        qo.append(qo[-1] + c)
+    if hot is not None:
+        r, key = hot
+        page = int(table[r, key // page_size])
+        direction = torch.randn(D, generator=g)
+        direction = direction / direction.norm()
+        kc[page, key % page_size] = direction * 16.0
+        vc[page, key % page_size] = 25.0
+        for t in range(qo[r], qo[r + 1]):
+            q[t] = (direction * 16.0).repeat(Hq)
+    return dict(
+        q=q.to(dtype), kc=kc.to(dtype), vc=vc.to(dtype), table=table,
+        positions=torch.tensor(positions, dtype=torch.int32), row_ids=torch.tensor(row_ids, dtype=torch.int32),
+        qo=torch.tensor(qo, dtype=torch.int32), seq_lens=torch.tensor(seq_lens, dtype=torch.int32),
+    )
+
+
+def _reference_attention(case, Hq, scale, window):
+    out = torch.empty(case["q"].shape[0], case["q"].shape[1])
+    ref.paged_attention_generic(
+        case["q"].float(), out, case["kc"].float(), case["vc"].float(), positions=case["positions"],
+        row_ids=case["row_ids"], block_table=case["table"], num_q_heads=Hq, scale=scale, window=window,
+    )
+    return out
+
+
+GEOMETRIES = [(4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 16), (32, 8, 128, 16), (8, 2, 80, 32), (2, 2, 256, 16), (6, 1, 64, 4)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,D,page_size", GEOMETRIES)
+@pytest.mark.parametrize("window", [0, 37])
+def test_generic_attention(dtype, Hq, Hkv, D, page_size, window):
+    case = _attention_case(dtype, Hq, Hkv, D, page_size, [70, 1, 130], [70, 1, 9], seed=30)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    out = torch.empty(case["q"].shape, dtype=dtype, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().paged_attention_generic(
+        case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), positions=case["positions"].to(DEV),
+        row_ids=case["row_ids"].to(DEV), block_table=case["table"].to(DEV), num_q_heads=Hq, scale=scale, window=window, flag=flag,
+    )
+    assert int(flag.item()) == 0
+    close(out, expected, 2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def _run_mma(case, Hq, scale, window, workspace):
+    """Both tensor-core kernels over a case: tiles for rows with several tokens, split-KV for single-token rows."""
+    k = kernels()
+    qo = case["qo"].tolist()
+    tile_rows, tile_starts, decode_rows, decode_tokens = [], [], [], []
+    for r in range(len(qo) - 1):
+        count = qo[r + 1] - qo[r]
+        if count == 1:
+            decode_rows.append(r)
+            decode_tokens.append(qo[r])
+        else:
+            for start in range(0, count, 64):
+                tile_rows.append(r)
+                tile_starts.append(start)
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    q = case["q"].to(DEV)
+    out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+    kc, vc = case["kc"].to(DEV), case["vc"].to(DEV)
+    if tile_rows:
+        k.attention_prefill_mma(
+            q, out, kc, vc, qo_indptr=case["qo"].to(DEV), seq_lens=case["seq_lens"].to(DEV), block_table=case["table"].to(DEV),
+            tile_rows=dev(tile_rows), tile_starts=dev(tile_starts), num_tiles=len(tile_rows), num_q_heads=Hq, scale=scale, window=window,
+        )
+    if decode_rows:
+        k.attention_decode_mma(
+            q, out, kc, vc, seq_lens=case["seq_lens"].to(DEV), block_table=case["table"].to(DEV), decode_rows=dev(decode_rows),
+            decode_tokens=dev(decode_tokens), num_rows=len(decode_rows), max_seq_len=int(case["seq_lens"].max()),
+            num_q_heads=Hq, scale=scale, window=window, workspace=workspace,
+        )
+    return out
+
+
+@pytest.fixture
+def workspace():
+    from kairyu_b200.engine.workspace import Workspace
+
+    return Workspace(DEV)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page_size", GEOMETRIES)
+@pytest.mark.parametrize("window", [0, 37, 300])
+def test_mma_attention_random(Hq, Hkv, D, page_size, window, workspace):
+    # rows: a whole prompt of several tiles, a portion in the middle of a long request,
+    # decode rows at 1, just under/over a split (256) and further, a 2-token portion
+    seq_lens = [150, 400, 1, 255, 257, 700, 66]
+    chunk_lens = [150, 70, 1, 1, 1, 1, 2]
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, chunk_lens, seed=31)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    out = _run_mma(case, Hq, scale, window, workspace)
+    close(out, expected, 2e-2)
+
+
+@pytest.mark.parametrize("hot_key", [0, 15, 16, 17, 63, 64, 255, 256, 257, 511, 512, 640, 699])
+@pytest.mark.parametrize("chunk", [1, 2, 61])
+def test_mma_attention_finds_one_far_key(hot_key, chunk, workspace):
+    """One key among 700 carries the softmax; the output must be its value."""
+    Hq, Hkv, D, page_size = 8, 2, 64, 16
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, [700, 300], [chunk, 1], seed=32, hot=(0, hot_key))
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, 0)
+    visible = [t for t in range(chunk) if 700 - chunk + t >= hot_key]
+    assert visible and float(expected[visible].min()) > 24.0  # the reference itself is dominated by that key
+    out = _run_mma(case, Hq, scale, 0, workspace)
+    close(out, expected, 2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("window,hot_key,inside", [(64, 636, True), (64, 635, False), (300, 400, True), (300, 399, False)])
+def test_mma_attention_window_edge(window, hot_key, inside, workspace):
+    """The dominating key sits exactly on, or one before, the window's edge of the last query."""
+    Hq, Hkv, D, page_size = 4, 4, 32, 8
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, [700], [1], seed=33, hot=(0, hot_key))
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    assert (float(expected.min()) > 24.0) == inside
+    out = _run_mma(case, Hq, scale, window, workspace)
+    close(out, expected, 2e-2, rtol=1e-2)
+    generic = torch.empty(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+    kernels().paged_attention_generic(
+        case["q"].to(DEV), generic, case["kc"].to(DEV), case["vc"].to(DEV), positions=case["positions"].to(DEV),
+        row_ids=case["row_ids"].to(DEV), block_table=case["table"].to(DEV), num_q_heads=Hq, scale=scale, window=window,
+    )
+    close(generic, expected, 2e-2, rtol=1e-2)
+
+
+def test_attention_flags_a_page_outside_the_pool():
+    case = _attention_case(torch.float32, 2, 1, 16, 16, [40], [1], seed=34)
+    table = case["table"].clone()
+    table[0, 1] = 10_000
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty(case["q"].shape, device=DEV)
+    kernels().paged_attention_generic(
+        case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), positions=case["positions"].to(DEV),
+        row_ids=case["row_ids"].to(DEV), block_table=table.to(DEV), num_q_heads=2, scale=0.25, flag=flag,
+    )
+    assert int(flag.item()) == kernels().FLAG_BAD_PAGE
+
+
+# ------------------------------------------------------------------ sampling
+
+
+@pytest.mark.parametrize("n,V", [(1, 331), (5, 128256), (64, 1000)])
+def test_argmax(n, V):
+    logits = rand(n, V, seed=40)
+    logits[0, V - 1] = 50.0
+    if n > 1:
+        logits[1, 7] = logits[1, 300] = 60.0  # a tie: the first index wins
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    kernels().argmax(logits.to(DEV), out)
+    assert out.cpu().tolist() == logits.argmax(dim=-1).tolist()
+    if n > 1:
+        assert int(out[1]) == 7
+
+
+def test_edit_logits():
+    logits = rand(3, 50, seed=41)
+    rows = torch.tensor([0, 0, 2, 1], dtype=torch.int32)
+    tokens = torch.tensor([4, 9, 4, 49], dtype=torch.int32)
+    mul = torch.tensor([1.3, 1.0, 0.7, 1.0])
+    sub = torch.tensor([0.0, 0.9, 0.2, 0.0])
+    mask = torch.tensor([0, 0, 0, 1], dtype=torch.int32)
+    expected = logits.clone()
+    ref.edit_logits(expected, rows, tokens, mul, sub, mask)
+    dev = logits.to(DEV)
+    kernels().edit_logits(dev, rows.to(DEV), tokens.to(DEV), mul.to(DEV), sub.to(DEV), mask.to(DEV))
+    close(dev, expected, 1e-6)
+    assert math.isinf(float(dev[1, 49]))
+
+
+def _sample_both(logits, temperature, top_k, top_p, min_p, seeds):
+    n, V = logits.shape
+    t = lambda values, dtype: torch.tensor(values, dtype=dtype)
+    args = (t(temperature, torch.float32), t(top_k, torch.int32), t(top_p, torch.float32), t(min_p, torch.float32), t(seeds, torch.int64))
+    expected = torch.empty(n, dtype=torch.int32)
+    ref.sample(logits, None, *args, expected)
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    work = torch.empty(n * V, device=DEV)
+    kernels().sample(logits.to(DEV), work, *(a.to(DEV) for a in args), out)
+    return out.cpu().tolist(), expected.tolist()
+
+
+@pytest.mark.parametrize("V", [331, 5000])
+def test_sample_matches_the_reference_draws(V):
+    from kairyu_b200.sampling.rng import as_signed64, mix_seed
+
+    n = 24
+    logits = rand(n, V, seed=42, scale=2.0)
+    temperature = [0.8] * 6 + [1.0] * 6 + [0.0] * 2 + [1.7] * 10
+    top_k = [-1, 5, 50, -1, 1, 20] * 4
+    top_p = [1.0, 1.0, 0.9, 0.9, 0.5, 0.3] * 4
+    min_p = [0.0, 0.0, 0.0, 0.05, 0.0, 0.2] * 4
+    seeds = [as_signed64(mix_seed(1234 + r, r)) for r in range(n)]
+    got, expected = _sample_both(logits, temperature, top_k, top_p, min_p, seeds)
+    assert got == expected
+
+
+def test_sample_respects_the_filters_over_many_seeds():
+    from kairyu_b200.sampling.rng import as_signed64, mix_seed
+
+    V = 200
+    base = torch.zeros(V)
+    base[:4] = torch.log(torch.tensor([0.5, 0.25, 0.15, 0.1])) + 10.0
+    base[4:] = -20.0
+    n = 64
+    logits = base.repeat(n, 1)
+    seeds = [as_signed64(mix_seed(99, p)) for p in range(n)]
+    got, expected = _sample_both(logits, [1.0] * n, [-1] * n, [0.7] * n, [0.0] * n, seeds)
+    assert got == expected
+    assert set(got) <= {0, 1}  # 0.5 + 0.25 reaches 0.7; the third token is cut
+    assert len(set(got)) == 2
+    got, _ = _sample_both(logits, [1.0] * n, [3] * n, [1.0] * n, [0.0] * n, seeds)
+    assert set(got) == {0, 1, 2}
+
+
+def test_sample_frequencies_follow_the_distribution():
+    from kairyu_b200.sampling.rng import as_signed64, mix_seed
+
+    V = 50
+    probs = torch.tensor([0.4, 0.3, 0.2, 0.1] + [0.0] * (V - 4))
+    logits = torch.log(probs.clamp(min=1e-30))
+    n = 4000
+    seeds = [as_signed64(mix_seed(7, p)) for p in range(n)]
+    out = torch.empty(n, dtype=torch.int32, device=DEV)
+    t = lambda values, dtype: torch.tensor(values, dtype=dtype, device=DEV)
+    kernels().sample(
+        logits.repeat(n, 1).to(DEV), torch.empty(n * V, device=DEV), t([1.0] * n, torch.float32), t([-1] * n, torch.int32),
+        t([1.0] * n, torch.float32), t([0.0] * n, torch.float32), t(seeds, torch.int64), out,
+    )
+    counts = torch.bincount(out.cpu().long(), minlength=V).float() / n
+    assert (counts[:4] - probs[:4]).abs().max() < 0.03
+    assert counts[4:].sum() == 0

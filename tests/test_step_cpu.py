@@ -1,0 +1,132 @@
+"""The step function, cache and replay cuts on the CPU, with the kernels replaced
+by their plain torch statements (tests/torch_kernels.py).  This checks the host
+side: metadata packing, block tables, page reuse, wanted rows.  The kernels
+themselves are checked on the GPU."""
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import torch_kernels
+import traces
+from golden_inputs import golden_weights
+from tiny_configs import TINY
+
+from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+from kairyu_b200.engine.engine import build_model
+from kairyu_b200.engine.runner import ModelRunner, StepEntry, StepError
+
+
+def make_runner(name, *, num_pages, page_size=None, dtype="float32", max_requests=8):
+    config, seed, default_page = TINY[name]
+    page_size = page_size or default_page
+    model, _ = build_model(config, dtype=dtype, device="cpu")
+    weights = golden_weights(config, seed)
+    tensors = {spec.name: weights[spec.alias_of or spec.name if spec.name not in weights else spec.name] for spec in model.tensor_specs()}
+    model.load({k: v.to(model.dtype) for k, v in tensors.items()})
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cpu")
+    runner = ModelRunner(model, cache, storage, max_model_len=config["max_position_embeddings"], decode_mode="eager")
+    return runner, config, weights
+
+
+def plain_logits(config, weights, requests):
+    return {name: plain_model.forward_logits(config, weights, tokens).numpy() for name, tokens in requests.items()}
+
+
+def assert_matches(result, expected, tolerance):
+    worst = 0.0
+    for (name, position), row in result.items():
+        worst = max(worst, float(np.abs(row - expected[name][position]).max()))
+    assert worst < tolerance, f"max abs difference {worst}"
+    return worst
+
+
+@pytest.fixture(autouse=True)
+def cpu_kernels(monkeypatch):
+    torch_kernels.install(monkeypatch)
+
+
+@pytest.mark.parametrize("name", ["llama", "qwen3", "odd"])
+def test_whole_prompts_match_plain(name):
+    runner, config, weights = make_runner(name, num_pages=40)
+    requests = traces.make_requests(config["vocab_size"], [1, 7, 33, 50], seed=11)
+    result = traces.run_in_process(runner, traces.trace_whole(requests))
+    assert len(result) == sum(len(t) for t in requests.values())
+    assert_matches(result, plain_logits(config, weights, requests), 2e-5)
+    assert runner.cache.live_requests == 0
+
+
+@pytest.mark.parametrize("name", ["llama", "qwen3"])
+def test_every_cut_gives_the_same_logits(name):
+    runner, config, weights = make_runner(name, num_pages=40)
+    requests = traces.make_requests(config["vocab_size"], [70, 45, 101, 38, 64, 83], seed=5)
+    expected = plain_logits(config, weights, requests)
+    for steps in (traces.trace_decode_tail(requests), traces.trace_chunks(requests)):
+        assert_matches(traces.run_in_process(runner, steps), expected, 2e-5)
+    mixed = traces.trace_mixed(requests, seed=3)
+    assert max(len(step["entries"]) for step in mixed) > 1
+    assert_matches(traces.run_in_process(runner, mixed), expected, 2e-5)
+
+
+def test_mixed_trace_reuses_pages_of_a_small_pool():
+    config, _, page_size = TINY["qwen3"]
+    requests = traces.make_requests(config["vocab_size"], [70, 45, 101, 38, 64, 83, 90, 55], seed=9)
+    steps = traces.trace_mixed(requests, seed=1)
+    pool_tokens = traces.peak_tokens(steps)
+    total = sum(len(t) for t in requests.values())
+    assert pool_tokens < total  # pages have to be used again
+    runner, config, weights = make_runner("qwen3", num_pages=pool_tokens // page_size + 1)
+    result = traces.run_in_process(runner, steps)
+    assert_matches(result, plain_logits(config, weights, requests), 2e-5)
+
+
+def test_stale_pages_do_not_leak_into_a_new_request():
+    """Poison every page that is given back: a step that read stale keys would return NaN."""
+    runner, config, weights = make_runner("llama", num_pages=12)
+    requests = traces.make_requests(config["vocab_size"], [60, 50, 70, 40], seed=2)
+    expected = plain_logits(config, weights, requests)
+    for name, tokens in requests.items():
+        logits = runner.step([StepEntry(name, tokens, tuple(range(len(tokens))))])
+        assert np.abs(logits.numpy() - expected[name]).max() < 2e-5
+        pages = [p for p in runner.cache.block_table(name, 0) if p >= 0]
+        runner.cache.release(name)
+        runner.storage.poison_pages(0, pages)
+
+
+def test_wanted_rows_only():
+    runner, config, weights = make_runner("llama", num_pages=20)
+    tokens = traces.make_requests(config["vocab_size"], [30], seed=4)["r0"]
+    expected = plain_model.forward_logits(config, weights, tokens).numpy()
+    assert runner.step([StepEntry("a", tokens[:10], ())]) is None
+    logits = runner.step([StepEntry("a", tokens[10:30], (0, 19, 7))])
+    assert logits.shape == (3, config["vocab_size"])
+    for row, position in enumerate((10, 29, 17)):
+        assert np.abs(logits[row].numpy() - expected[position]).max() < 2e-5
+
+
+def test_step_rejects_bad_entries():
+    runner, config, _ = make_runner("llama", num_pages=20)
+    with pytest.raises(StepError):
+        runner.step([])
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [], ())])
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [config["vocab_size"]], ())])
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [1, 2], (2,))])
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [1], ()), StepEntry("a", [2], ())])
+    with pytest.raises(StepError):
+        runner.step([StepEntry("a", [1] * (config["max_position_embeddings"] + 1), ())])
+
+
+def test_step_runs_out_of_pages_loudly():
+    from kairyu_b200.cache import OutOfPages
+
+    runner, config, _ = make_runner("llama", num_pages=3)  # two usable pages of 16
+    runner.step([StepEntry("a", [1] * 32, ())])
+    with pytest.raises(OutOfPages):
+        runner.step([StepEntry("a", [1], ())])
