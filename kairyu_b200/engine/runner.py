@@ -58,6 +58,7 @@ class _Graph:
     logits: torch.Tensor
     generation: int
     layout: dict[str, tuple[int, int]]
+    keepalive: tuple = ()  # tensors the captured kernels read; freeing them would hand their memory to others
 
 
 class ModelRunner:
@@ -367,7 +368,7 @@ class ModelRunner:
             raise StepError("the graph workspace changed during capture")
         # a grown workspace invalidates graphs captured against the old buffers
         self._graphs = {k: g for k, g in self._graphs.items() if g.generation == generation}
-        held = _Graph(graph, meta, logits, generation, graph_layout)
+        held = _Graph(graph, meta, logits, generation, graph_layout, keepalive=(ctx, want_all))
         self._graphs[key] = held
         self.counters["graph_captures"] += 1
         return held

@@ -150,3 +150,24 @@ def test_long_decoding(case, dtype, tolerance):
     steps = traces.trace_decode_tail({"r0": tokens}, tail=length - 3)
     result = traces.run_in_process(runner, steps)
     assert worst(result, {"r0": expected}) < tolerance
+
+
+def test_graph_replays_of_several_rows_survive_other_work_between_steps(case):
+    """Replays read index tensors made at capture time; allocations and kernels
+    between steps (a sampler, say) must not land on them."""
+    from kairyu_b200.engine.runner import StepEntry
+    import kairyu_b200.kernels as kernels
+
+    requests = dict(list(case["requests"].items())[:4])
+    expected = case["expected"]["float32"]
+    runner = make_runner(case, "float32", num_pages=40, decode_mode="cuda_graph")
+    head = 20
+    runner.step([StepEntry(name, tokens[:head], ()) for name, tokens in requests.items()])
+    for index in range(head, head + 12):
+        logits = runner.step([StepEntry(name, [tokens[index]], (0,)) for name, tokens in requests.items()])
+        scratch = [torch.empty(4, dtype=torch.int32, device="cuda") for _ in range(8)]
+        for tensor in scratch:
+            kernels.argmax(logits, tensor)
+        for row, name in enumerate(requests):
+            assert np.abs(logits[row].cpu().numpy() - expected[name][index]).max() < FP32_TOL
+    assert runner.counters["graph_replays"] >= 12
