@@ -1,0 +1,397 @@
+#!/usr/bin/env python3
+"""Measures decoding and prefill of the Llama-3.1-8B shape (random bf16 weights)
+on one B200 and prints one JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  ``value`` is decoded tokens a
+second of the step function plus token selection, timed on the device with CUDA
+events; ``e2e`` is the same through ``LLM.generate`` (host token ids in, host
+token ids out).  The line also carries the prefill of a 2,048-token prompt, the
+roofline fraction of the decode step, decoding at batch 1 and 64, the clocks
+seen during the timed region, and how many of this package's kernels ran in it.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama-3.1-8B shape
+MODEL = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 4096,
+    "num_hidden_layers": 32,
+    "num_attention_heads": 32,
+    "num_key_value_heads": 8,
+    "head_dim": 128,
+    "intermediate_size": 14336,
+    "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {
+        "rope_type": "llama3",
+        "factor": 8.0,
+        "low_freq_factor": 1.0,
+        "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 8192,
+    },
+    "max_position_embeddings": 8192,
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+}
+FULL_LAYERS = 32
+SEED = 2
+CONTEXT_LEN = 8192
+PROMPT_LEN = 2048
+GEN_LEN = 256
+PAGE_SIZE = 16
+PREFILL_TOKENS = 2048
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as handle:
+                data = json.load(handle)
+            peaks = dict(FALLBACK_PEAKS)
+            for key in peaks:
+                if isinstance(data.get(key), (int, float)):
+                    peaks[key] = float(data[key])
+            return peaks, "measured"
+        except (OSError, ValueError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = (
+        "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, device_index: int = 0) -> None:
+        self.process = None
+        self.device_index = device_index
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL,
+                text=True,
+            )
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            output, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            output, _ = self.process.communicate()
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in output.splitlines():
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) < 8:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                maxima.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, value in zip(names, fields[4:8]):
+                if value.lower() == "active":
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def build_engine(layers: int, max_batch: int):
+    import torch
+
+    from kairyu_b200.config.engine_config import EngineConfig
+    from kairyu_b200.engine.engine import Engine
+
+    config = dict(MODEL)
+    config["num_hidden_layers"] = layers
+    per_request = -(-(PROMPT_LEN + GEN_LEN + 64) // PAGE_SIZE)
+    engine_config = EngineConfig(
+        dtype="bfloat16",
+        page_size=PAGE_SIZE,
+        num_pages=max_batch * per_request + 1,
+        max_num_batched_tokens=PREFILL_TOKENS,
+        max_num_seqs=max(max_batch, 1),
+        max_model_len=CONTEXT_LEN,
+        max_num_partial_prefills=1,
+        seed=SEED,
+    )
+    engine = Engine.from_random(config, SEED, engine_config)
+    torch.cuda.synchronize()
+    return engine, config
+
+
+def random_tokens(count: int, vocab: int, seed: int) -> list[int]:
+    import torch
+
+    generator = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (count,), generator=generator).tolist()
+
+
+def time_decode(engine, batch: int, steps: int, warmup: int, sample_clocks: bool):
+    """Device time of ``steps`` decode steps of ``batch`` requests that each hold a
+    PROMPT_LEN-token prompt: step function + greedy token selection."""
+    import torch
+
+    from kairyu_b200.engine.runner import StepEntry
+    from kairyu_b200.sampling.params import SamplingParams
+    from kairyu_b200.sampling.sampler import SamplingRow
+
+    runner, cache = engine.runner, engine.cache
+    vocab = MODEL["vocab_size"]
+    names = [f"bench{index}" for index in range(batch)]
+    for index, name in enumerate(names):
+        runner.step([StepEntry(name, random_tokens(PROMPT_LEN, vocab, 100 + index), ())])
+    feed = [random_tokens(batch, vocab, 1000 + step) for step in range(warmup + steps)]
+    rows = [SamplingRow(name, SamplingParams(temperature=0.0), 0) for name in names]
+
+    def one(step: int):
+        logits = runner.step([StepEntry(name, [feed[step][index]], (0,)) for index, name in enumerate(names)])
+        return engine.sampler.sample(logits, rows)
+
+    for step in range(warmup):
+        one(step)
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    if sample_clocks:
+        sampler.start()
+        time.sleep(0.3)
+    launches_before = runner.counters["kernel_launches"]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for step in range(warmup, warmup + steps):
+        one(step)
+    stop.record()
+    torch.cuda.synchronize()
+    milliseconds = start.elapsed_time(stop)
+    clocks = sampler.stop() if sample_clocks else None
+    launches = runner.counters["kernel_launches"] - launches_before + steps  # + one argmax per step
+    runner.check_errors()
+    context = PROMPT_LEN + warmup + steps / 2.0  # mean tokens a request holds during the timed steps
+    for name in names:
+        cache.release(name)
+    return milliseconds, launches, clocks, context
+
+
+def time_prefill(engine, iterations: int = 5, warmup: int = 3):
+    import torch
+
+    from kairyu_b200.engine.runner import StepEntry
+
+    runner, cache = engine.runner, engine.cache
+    tokens = random_tokens(PREFILL_TOKENS, MODEL["vocab_size"], 7)
+    times = []
+    for index in range(warmup + iterations):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry("prefill", tokens, (PREFILL_TOKENS - 1,))])
+        stop.record()
+        torch.cuda.synchronize()
+        cache.release("prefill")
+        if index >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def prefill_flops(config: dict, tokens: int) -> float:
+    hidden, inter = config["hidden_size"], config["intermediate_size"]
+    heads, kv_heads, dim = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    per_token = 2 * hidden * (heads + 2 * kv_heads) * dim + 2 * heads * dim * hidden + 2 * hidden * 2 * inter + 2 * inter * hidden
+    linear = per_token * tokens * config["num_hidden_layers"]
+    attention = 4 * heads * dim * (tokens * (tokens + 1) / 2) * config["num_hidden_layers"]  # causal half of QK^T and PV
+    head = 2 * hidden * config["vocab_size"]  # one row of logits
+    return float(linear + attention + head)
+
+
+def time_e2e(engine, batch: int, steps: int):
+    """Decode tokens/s through ``LLM.generate``: (time of 1+steps tokens) - (time of 1 token)."""
+    import torch
+
+    from kairyu_b200 import SamplingParams, TokensPrompt
+    from kairyu_b200.entrypoints.llm import LLM
+
+    llm = LLM.__new__(LLM)
+    llm.model = "random"
+    llm.seed = SEED
+    llm._model_dir = None
+    llm.engine = engine
+    llm._finish_init(None)
+    prompts = [TokensPrompt(tuple(random_tokens(PROMPT_LEN, MODEL["vocab_size"], 200 + index))) for index in range(batch)]
+
+    def run(max_tokens: int) -> float:
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        outputs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True))
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - begin
+        assert all(len(output.outputs[0].token_ids) == max_tokens for output in outputs)
+        return elapsed
+
+    run(2)  # warm: graphs for this batch size
+    short = min(run(1) for _ in range(2))
+    long = min(run(1 + steps) for _ in range(2))
+    seconds = max(long - short, 1e-9)
+    meta_ints = batch * 10 + 2 + batch * (CONTEXT_LEN // PAGE_SIZE)  # the packed int32 step description
+    return batch * steps / seconds, meta_ints * 4, batch * 4 + 4
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "kairyu")):
+        print(json.dumps({"impl": "reference", "unavailable": "ytworks/kairyu is not installed under baseline/_ref"}))
+        return 0
+    try:
+        from baseline.reference_bench import run_reference
+
+        line = run_reference(args, MODEL, dict(prompt_len=PROMPT_LEN, gen_len=GEN_LEN, page_size=PAGE_SIZE, context_len=CONTEXT_LEN, seed=SEED))
+    except Exception as error:  # the reference arm must never take the driver down
+        line = {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:200]}"}
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers only where memory or time needs it")
+    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device; kairyu_b200 has no CPU path", file=sys.stderr)
+        return 1
+    torch.cuda.set_device(0)
+    peaks, peak_source = load_peaks()
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    engine, config = build_engine(args.layers, max_batch)
+    model = engine.model
+    weight_bytes = model.bytes_streamed_per_step()
+    kv_bytes_per_token = 2 * config["num_hidden_layers"] * config["num_key_value_heads"] * config["head_dim"] * 2
+
+    milliseconds, launches, clocks, context = time_decode(engine, args.batch, args.steps, args.warmup, True)
+    ms_per_step = milliseconds / args.steps
+    value = args.batch * args.steps / (milliseconds / 1e3)
+    step_bytes = weight_bytes + args.batch * context * kv_bytes_per_token
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    prefill_ms = time_prefill(engine)
+    flops = prefill_flops(config, PREFILL_TOKENS)
+    prefill = {
+        "value": PREFILL_TOKENS / (prefill_ms / 1e3),
+        "tokens": PREFILL_TOKENS,
+        "ms": prefill_ms,
+        "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
+    }
+
+    points = {}
+    e2e = None
+    if not args.no_points:
+        for batch, key in ((1, "decode_b1"), (64, "decode_b64")):
+            steps = max(16, min(args.steps, 64))
+            ms, _, _, _ = time_decode(engine, batch, steps, args.warmup, False)
+            points[key] = batch * steps / (ms / 1e3)
+        rate, h2d, d2h = time_e2e(engine, args.batch, min(args.steps, 64))
+        e2e = {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    line = {
+        "metric": "decode tok/s @bs8 (Llama-3.1-8B shape, 2048-token prompts)",
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_per_step,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: seeded random token ids, seeded random weights (no checkpoint, no dataset)",
+        "impl": "ours",
+        "config": {
+            "model": "Llama-3.1-8B shape",
+            "layers": config["num_hidden_layers"],
+            "layers_full": FULL_LAYERS,
+            "hidden": config["hidden_size"],
+            "heads": config["num_attention_heads"],
+            "kv_heads": config["num_key_value_heads"],
+            "head_dim": config["head_dim"],
+            "intermediate": config["intermediate_size"],
+            "vocab": config["vocab_size"],
+            "global_batch": args.batch,
+            "seq_len": PROMPT_LEN,
+            "gen_len": GEN_LEN,
+            "context_len": CONTEXT_LEN,
+            "page_size": PAGE_SIZE,
+            "parallelism": "single_gpu",
+            "l2": "inputs>L2 (weights and cache exceed the 126 MB L2)",
+            "peaks": peak_source,
+        },
+        "prefill": prefill,
+        "roofline": {
+            "bound": "hbm",
+            "achieved": achieved,
+            "peak": peaks["hbm_gbs"],
+            "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"],
+        },
+        "points": points,
+        "clocks": clocks,
+        "gpu_launches": launches,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

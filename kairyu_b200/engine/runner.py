@@ -19,6 +19,7 @@ from typing import Any, Hashable, Optional, Sequence
 
 import torch
 
+from kairyu_b200 import kernels
 from kairyu_b200.cache.manager import CacheManager
 from kairyu_b200.cache.page_pool import OutOfPages
 from kairyu_b200.cache.storage import CacheStorage
@@ -58,6 +59,7 @@ class _Graph:
     logits: torch.Tensor
     generation: int
     layout: dict[str, tuple[int, int]]
+    launches: int = 0  # kernels of this package inside the graph
     keepalive: tuple = ()  # tensors the captured kernels read; freeing them would hand their memory to others
 
 
@@ -94,7 +96,9 @@ class ModelRunner:
         self._graphs: dict[tuple[int, int], _Graph] = {}
         self._graph_pool = None
         self._buckets = decode_buckets(max_graph_batch)
-        self.counters = {"steps": 0, "graph_replays": 0, "graph_captures": 0, "eager_steps": 0, "tokens": 0}
+        self.counters = {
+            "steps": 0, "graph_replays": 0, "graph_captures": 0, "eager_steps": 0, "tokens": 0, "kernel_launches": 0,
+        }
 
     # ------------------------------------------------------------------ host-side packing
     def _prepare_rows(self, entries: Sequence[StepEntry]) -> list[tuple[StepEntry, int, int]]:
@@ -299,7 +303,10 @@ class ModelRunner:
         meta.copy_(host, non_blocking=True)
         ctx, want = self._context(meta, layout, facts, self.workspace)
         self.counters["eager_steps"] += 1
-        return self.model.forward(ctx, self._views, want)
+        before = kernels.launch_count
+        logits = self.model.forward(ctx, self._views, want)
+        self.counters["kernel_launches"] += kernels.launch_count - before
+        return logits
 
     # ------------------------------------------------------------------ graphs
     def _graph_key(self, num_rows: int, max_seq_len: int) -> tuple[int, int]:
@@ -325,6 +332,7 @@ class ModelRunner:
         held.meta.copy_(host, non_blocking=True)
         held.graph.replay()
         self.counters["graph_replays"] += 1
+        self.counters["kernel_launches"] += held.launches
         wanted_rows = [row for row, (entry, _, _) in enumerate(rows) if entry.want]
         if not wanted_rows:
             return None
@@ -360,15 +368,17 @@ class ModelRunner:
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
                 self._graph_pool = torch.cuda.graph_pool_handle()
+            before = kernels.launch_count
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 logits = run()
+            launches = kernels.launch_count - before
         finally:
             workspace.freeze(False)
         if generation != workspace.generation:
             raise StepError("the graph workspace changed during capture")
         # a grown workspace invalidates graphs captured against the old buffers
         self._graphs = {k: g for k, g in self._graphs.items() if g.generation == generation}
-        held = _Graph(graph, meta, logits, generation, graph_layout, keepalive=(ctx, want_all))
+        held = _Graph(graph, meta, logits, generation, graph_layout, launches=launches, keepalive=(ctx, want_all))
         self._graphs[key] = held
         self.counters["graph_captures"] += 1
         return held

@@ -35,8 +35,13 @@ class KernelError(RuntimeError):
     pass
 
 
-def _check(code: int, what: str) -> None:
+launch_count = 0  # kernel launches made through this module (library products not counted)
+
+
+def _check(code: int, what: str, launches: int = 1) -> None:
+    global launch_count
     if code == 0:
+        launch_count += launches
         return
     if code < 0:
         raise KernelError(f"{what}: {_CODES.get(code, f'error {code}')}")
@@ -389,6 +394,7 @@ def attention_decode_mma(
             float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _stream(),
         ),
         what,
+        launches=2,
     )
 
 
