@@ -1,0 +1,179 @@
+"""A toy architecture defined here, outside the package: a mixer with per-request
+state of its own, registered, built and stepped without a change to the
+framework's files.  Its layers differ (attention, the toy mixer, an attention
+that reads another layer's keys and values) and its run order names one layer
+twice.  The result is compared with a plain whole-sequence computation under
+different cuts.  Runs on the CPU with the torch statements of the kernels and
+on the GPU with the kernels."""
+
+from typing import Mapping
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model
+import torch_kernels
+import traces
+
+from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+from kairyu_b200.engine.engine import build_model
+from kairyu_b200.engine.runner import ModelRunner
+from kairyu_b200.parts import MIXERS, LayerCall, LayerSpec, Mixer, ModelSpec, PartSpec, StateSpec, TensorSpec
+from kairyu_b200.registry import register_architecture, unregister_architecture
+from kairyu_b200.weights.random_init import random_tensors
+
+HIDDEN, STATE, VOCAB, HEADS, KV_HEADS, HEAD_DIM, INTER, EPS = 48, 20, 97, 3, 1, 16, 72, 1e-5
+DECAY = 0.8
+
+
+class DecayMixer(Mixer):
+    """state <- DECAY * state + (1 - DECAY) * (x W_in^T), y = state W_out^T, token by token.
+    The state lives in the request's slot between steps."""
+
+    def __init__(self, *, prefix, hidden_size, state_size, dtype, device, **_):
+        self.prefix, self.hidden_size, self.state_size, self.dtype = prefix, hidden_size, state_size, dtype
+        self.w_in = self.w_out = None
+
+    def tensor_specs(self):
+        return [
+            TensorSpec(f"{self.prefix}.in_proj.weight", (self.state_size, self.hidden_size)),
+            TensorSpec(f"{self.prefix}.out_proj.weight", (self.hidden_size, self.state_size)),
+        ]
+
+    def load(self, tensors):
+        self.w_in = tensors[f"{self.prefix}.in_proj.weight"]
+        self.w_out = tensors[f"{self.prefix}.out_proj.weight"]
+
+    def cache_specs(self):
+        return (StateSpec((self.state_size,), "float32"),)
+
+    def forward(self, x, ctx, cache):
+        assert cache.state is not None and cache.k is None
+        out = torch.empty(x.shape[0], self.hidden_size, dtype=x.dtype, device=x.device)
+        drive = x.float() @ self.w_in.float().t()
+        slots = ctx.state_slots.tolist()
+        for row in range(len(ctx.host_qo_indptr) - 1):
+            state = cache.state[slots[row]]
+            for t in range(ctx.host_qo_indptr[row], ctx.host_qo_indptr[row + 1]):
+                state.mul_(DECAY).add_(drive[t], alpha=1 - DECAY)
+                out[t] = (state @ self.w_out.float().t()).to(x.dtype)
+        return out
+
+
+def toy_spec(config) -> ModelSpec:
+    def norm(name):
+        return PartSpec("rmsnorm", name=name, size=HIDDEN, eps=EPS)
+
+    position = PartSpec("rope", rotary_dim=HEAD_DIM, theta=10000.0, scaling=None, max_positions=256)
+
+    def attention(prefix):
+        return PartSpec(
+            "gqa_attention", prefix=prefix, hidden_size=HIDDEN, num_heads=HEADS, num_kv_heads=KV_HEADS, head_dim=HEAD_DIM,
+            qk_norm=False, norm_eps=EPS, qkv_bias=False, o_bias=False, position=position,
+        )
+
+    def ffn(prefix):
+        return PartSpec("swiglu", prefix=prefix, hidden_size=HIDDEN, intermediate_size=INTER, activation="silu")
+
+    mixers = [attention("layers.0.attn"), PartSpec("toy_decay", prefix="layers.1.decay", hidden_size=HIDDEN, state_size=STATE), attention("layers.2.attn")]
+    layers = tuple(
+        LayerSpec(f"layers.{i}", "pre_norm", mixers[i], ffn(f"layers.{i}.mlp"), norm(f"layers.{i}.norm1.weight"), norm(f"layers.{i}.norm2.weight"))
+        for i in range(3)
+    )
+    schedule = (
+        LayerCall(0, cache_slot=0),
+        LayerCall(1, cache_slot=1),
+        LayerCall(2, cache_slot=0, writes_cache=False),  # reads layer 0's keys and values
+        LayerCall(1, cache_slot=2),  # the stateful layer again, with a second state of its own
+    )
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", name="embed.weight", vocab_size=VOCAB, hidden_size=HIDDEN),
+        layers=layers, schedule=schedule, final_norm=norm("final_norm.weight"),
+        head=PartSpec("linear_head", name="head.weight", vocab_size=VOCAB, hidden_size=HIDDEN, tied_to=None),
+        vocab_size=VOCAB, hidden_size=HIDDEN, max_position_embeddings=256,
+    )
+
+
+@pytest.fixture
+def toy():
+    MIXERS.register("toy_decay")(DecayMixer)
+    register_architecture("ToyDecayForCausalLM", lambda config: dict(config), toy_spec)
+    yield {"architectures": ["ToyDecayForCausalLM"]}
+    unregister_architecture("ToyDecayForCausalLM")
+    MIXERS.unregister("toy_decay")
+
+
+def plain_toy_logits(w: Mapping[str, torch.Tensor], tokens) -> torch.Tensor:
+    """Whole sequence, no cache."""
+    cfg = {"head_dim": HEAD_DIM, "theta": 10000.0, "rope_kind": None, "rope": {}}
+    lin = torch.nn.functional.linear
+    T = len(tokens)
+    positions = torch.arange(T)
+    x = w["embed.weight"][torch.tensor(tokens)]
+
+    def qkv(prefix, h):
+        q = lin(h, w[f"{prefix}.q_proj.weight"]).view(T, HEADS, HEAD_DIM)
+        k = lin(h, w[f"{prefix}.k_proj.weight"]).view(T, KV_HEADS, HEAD_DIM)
+        v = lin(h, w[f"{prefix}.v_proj.weight"]).view(T, KV_HEADS, HEAD_DIM)
+        cos, sin = plain_model.rope_cos_sin(cfg, positions)
+        q, k = plain_model.apply_rope(q, k, cos, sin)
+        return q, k, v
+
+    def decay(prefix, h):
+        drive = lin(h, w[f"{prefix}.in_proj.weight"])
+        state = torch.zeros(STATE)
+        rows = []
+        for t in range(T):
+            state = DECAY * state + (1 - DECAY) * drive[t]
+            rows.append(lin(state, w[f"{prefix}.out_proj.weight"]))
+        return torch.stack(rows)
+
+    def ffn(i, x):
+        return x + plain_model.swiglu_mlp(w, f"layers.{i}.mlp", plain_model.rms_norm(x, w[f"layers.{i}.norm2.weight"], EPS))
+
+    # call 1: layer 0, attention that writes slot 0
+    h = plain_model.rms_norm(x, w["layers.0.norm1.weight"], EPS)
+    q0, k0, v0 = qkv("layers.0.attn", h)
+    x = ffn(0, x + lin(plain_model.causal_attention(q0, k0, v0), w["layers.0.attn.o_proj.weight"]))
+    # call 2: layer 1, decay mixer
+    x = ffn(1, x + decay("layers.1.decay", plain_model.rms_norm(x, w["layers.1.norm1.weight"], EPS)))
+    # call 3: layer 2, its own queries over layer 0's keys and values
+    h = plain_model.rms_norm(x, w["layers.2.norm1.weight"], EPS)
+    q2, _, _ = qkv("layers.2.attn", h)
+    x = ffn(2, x + lin(plain_model.causal_attention(q2, k0, v0), w["layers.2.attn.o_proj.weight"]))
+    # call 4: layer 1 again (same weights, fresh state)
+    x = ffn(1, x + decay("layers.1.decay", plain_model.rms_norm(x, w["layers.1.norm1.weight"], EPS)))
+    return lin(plain_model.rms_norm(x, w["final_norm.weight"], EPS), w["head.weight"])
+
+
+def build(toy, device):
+    model, _ = build_model(toy, dtype="float32", device=device)
+    weights = random_tensors(model.tensor_specs(), seed=9, device="cpu")
+    model.load({name: tensor.to(device) for name, tensor in weights.items()})
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    assert [g.slots for g in layout.groups] == [(0,)] and [b.slot for b in layout.states] == [1, 2]
+    cache = CacheManager(layout, num_pages=24, page_size=8, max_requests=4)
+    storage = CacheStorage(layout, num_pages=24, page_size=8, max_requests=4, dtype=model.dtype, device=device)
+    runner = ModelRunner(model, cache, storage, max_model_len=256, decode_mode="eager")
+    return runner, weights
+
+
+def check(toy, device):
+    runner, weights = build(toy, device)
+    requests = traces.make_requests(VOCAB, [37, 20, 51, 9, 44, 30], seed=6)
+    expected = {name: plain_toy_logits(weights, tokens).numpy() for name, tokens in requests.items()}
+    for steps in (traces.trace_whole(requests), traces.trace_chunks(requests), traces.trace_mixed(requests, seed=2)):
+        result = traces.run_in_process(runner, steps)  # slots change hands: a stale state would show
+        worst = max(float(np.abs(row - expected[n][p]).max()) for (n, p), row in result.items())
+        assert worst < 3e-5, worst
+
+
+def test_toy_architecture_on_cpu(toy, monkeypatch):
+    torch_kernels.install(monkeypatch)
+    check(toy, "cpu")
+
+
+@pytest.mark.gpu
+def test_toy_architecture_on_gpu(toy):
+    check(toy, "cuda")
