@@ -274,7 +274,15 @@ def reference_arm(args) -> int:
     """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "kairyu")):
-        print(json.dumps({"impl": "reference", "unavailable": "ytworks/kairyu is not installed under baseline/_ref"}))
+        print(
+            json.dumps(
+                {
+                    "impl": "reference",
+                    "unavailable": "ytworks/kairyu is not installed under baseline/_ref: its offline pip install fails "
+                    "(build backend hatchling is neither installed nor in the wheelhouse)",
+                }
+            )
+        )
         return 0
     try:
         from baseline.reference_bench import run_reference
