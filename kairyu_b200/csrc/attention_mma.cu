@@ -1,576 +1,5 @@
-// bf16 paged GQA attention on tensor cores (mma.sync m16n8k16, fp32 softmax and
-// accumulation): a flash-attention kernel over 64-query tiles for rows that
-// carry several tokens, and a split-KV kernel plus a merge for rows that carry
-// one token.  Keys and values are read through the block table, 64 keys at a
-// time, with cp.async double buffering.
-//
-// Semantics (kairyu/engine/core/attention/torch_backend.py:57-71): the query at
-// absolute position p sees keys max(0, p+1-window) <= j <= p; query head h reads
-// KV head h / (Hq/Hkv); S = q.k * scale; softmax over keys; P.V.
-//
-// Head sizes: any multiple of 16 up to 256; the kernels are instantiated for a
-// padded size DP in {32, 64, 128, 256} and zero-fill the columns above D.
-// Partition boundaries of the split-KV kernel are absolute key positions
-// (multiples of DEC_SPLIT), so a row's result depends only on its own length.
-#include "common.cuh"
-
-#define TILE_M 64
-#define TILE_N 64
-#define MMA_THREADS 128
-#define DEC_SPLIT 256
-#define LOG2E 1.4426950408889634f
-
-// ------------------------------------------------------------------ PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
-// 16-byte async copy; when !valid the destination is zero-filled and the source not read.
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-    const int bytes = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(smem_u32(p)));
-}
-// d += a(16x16, row) * b(16x8, col), bf16 inputs, fp32 accumulate
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
-}
-
-// Rows of a shared tile are DP + 8 elements apart: the 16 extra bytes put eight
-// consecutive rows in distinct bank groups, so ldmatrix is conflict-free.
-template <int DP>
-struct Tile {
-    static constexpr int STRIDE = DP + 8;
-    static constexpr int CHUNKS = DP / 8;  // 16-byte chunks per row
-};
-
-// Copies `rows` keys starting at absolute key `key0` of one KV head into a tile
-// (row r of the tile = key key0 + r).  Keys >= key_end, keys on pages the table
-// marks absent, and columns >= D are zero-filled.
-template <int DP>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* __restrict__ cache,
-                                             const int* __restrict__ table, int max_pages, int num_pages,
-                                             int page_size, int Hkv, int kvh, int D, int key0, int key_lo,
-                                             int key_end, int rows) {
-    constexpr int CH = Tile<DP>::CHUNKS;
-    for (int c = threadIdx.x; c < rows * CH; c += MMA_THREADS) {
-        const int r = c / CH;
-        const int col = (c % CH) * 8;
-        const int key = key0 + r;
-        bool valid = key >= key_lo && key < key_end && col < D;
-        const __nv_bfloat16* src = cache;
-        if (valid) {
-            const int page_index = key / page_size;
-            const int page = page_index < max_pages ? table[page_index] : -1;
-            if (page < 0 || page >= num_pages) {
-                valid = false;
-            } else {
-                src = cache + (((size_t)page * page_size + (key % page_size)) * Hkv + kvh) * D + col;
-            }
-        }
-        cp_async16(tile + r * Tile<DP>::STRIDE + col, src, valid);
-    }
-}
-
-// ------------------------------------------------------------------ prefill: 64-query tiles
-template <int DP>
-__global__ void __launch_bounds__(MMA_THREADS)
-attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
-                         int out_stride, const __nv_bfloat16* __restrict__ k_cache,
-                         const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ qo_indptr,
-                         const int* __restrict__ seq_lens, const int* __restrict__ block_table,
-                         int max_pages, const int* __restrict__ tile_rows,
-                         const int* __restrict__ tile_starts, int Hq, int Hkv, int D, int page_size,
-                         int num_pages, float scale, int window) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int STRIDE = Tile<DP>::STRIDE;
-    constexpr int CH = Tile<DP>::CHUNKS;
-    constexpr int KSTEPS = DP / 16;
-    constexpr int DTILES = DP / 8;
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sK = sQ + TILE_M * STRIDE;               // 2 stages
-    __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;           // 2 stages
-
-    const int tile = blockIdx.x;
-    const int h = blockIdx.y;
-    const int kvh = h / (Hq / Hkv);
-    const int row = tile_rows[tile];
-    const int q0 = tile_starts[tile];
-    const int tok0 = qo_indptr[row];
-    const int chunk_len = qo_indptr[row + 1] - tok0;
-    const int seq_len = seq_lens[row];
-    const int chunk_pos = seq_len - chunk_len;  // absolute position of the chunk's first token
-    const int* table = block_table + (size_t)row * max_pages;
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2;      // row within 8
-    const int tq = lane & 3;      // column pair
-
-    const int rows_here = min(TILE_M, chunk_len - q0);
-    const int first_pos = chunk_pos + q0;
-    const int last_pos = first_pos + rows_here - 1;
-    const int key_end = last_pos + 1;  // causal bound of the tile (<= seq_len)
-    const int key_lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
-    const int first_kt = key_lo / TILE_N;
-    const int last_kt = (key_end - 1) / TILE_N;
-
-    // Q tile (rows beyond the chunk and columns beyond D are zero)
-    for (int c = threadIdx.x; c < TILE_M * CH; c += MMA_THREADS) {
-        const int r = c / CH;
-        const int col = (c % CH) * 8;
-        const bool valid = r < rows_here && col < D;
-        const __nv_bfloat16* src = valid ? q + (size_t)(tok0 + q0 + r) * q_stride + (size_t)h * D + col : q;
-        cp_async16(sQ + r * STRIDE + col, src, valid);
-    }
-    load_kv_tile<DP>(sK, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end, TILE_N);
-    load_kv_tile<DP>(sV, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end, TILE_N);
-    cp_async_commit();
-
-    uint32_t qf[KSTEPS][4];
-    float o[DTILES][4];
-#pragma unroll
-    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.0f, 0.0f};
-    const float sl2 = scale * LOG2E;
-    const int qpos0 = first_pos + warp * 16 + g;  // absolute position of this thread's first row
-    const int qpos1 = qpos0 + 8;
-
-    int stage = 0;
-    for (int kt = first_kt; kt <= last_kt; ++kt) {
-        if (kt + 1 <= last_kt) {
-            load_kv_tile<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end, TILE_N);
-            load_kv_tile<DP>(sV + (stage ^ 1) * TILE_N * STRIDE, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end, TILE_N);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        if (kt == first_kt) {
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                const int m = lane >> 3;
-                const int r = warp * 16 + (m & 1) * 8 + (lane & 7);
-                const int col = ks * 16 + (m >> 1) * 8;
-                ldmatrix_x4(qf[ks], sQ + r * STRIDE + col);
-            }
-        }
-        const __nv_bfloat16* tK = sK + stage * TILE_N * STRIDE;
-        const __nv_bfloat16* tV = sV + stage * TILE_N * STRIDE;
-
-        // S = Q K^T for this warp's 16 queries and the tile's 64 keys
-        float s[TILE_N / 8][4];
-#pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-#pragma unroll
-            for (int np = 0; np < TILE_N / 16; ++np) {
-                uint32_t b[4];
-                const int m = lane >> 3;
-                const int key = np * 16 + (m >> 1) * 8 + (lane & 7);
-                const int col = ks * 16 + (m & 1) * 8;
-                ldmatrix_x4(b, tK + key * STRIDE + col);
-                mma_16816(s[2 * np], qf[ks], b[0], b[1]);
-                mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
-            }
-        }
-        // scale, mask, online softmax (log2 domain)
-        const int key_base = kt * TILE_N + tq * 2;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key_base + nt * 8 + e;
-                const bool ok0 = key <= qpos0 && (window <= 0 || key > qpos0 - window);
-                const bool ok1 = key <= qpos1 && (window <= 0 || key > qpos1 - window);
-                s[nt][e] = ok0 ? s[nt][e] * sl2 : -INFINITY;
-                s[nt][2 + e] = ok1 ? s[nt][2 + e] * sl2 : -INFINITY;
-                mx0 = fmaxf(mx0, s[nt][e]);
-                mx1 = fmaxf(mx1, s[nt][2 + e]);
-            }
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m_run[0], mx0);
-        const float mn1 = fmaxf(m_run[1], mx1);
-        const float base0 = mn0 == -INFINITY ? 0.0f : mn0;  // a fully masked row stays at zero
-        const float base1 = mn1 == -INFINITY ? 0.0f : mn1;
-        const float alpha0 = exp2f(m_run[0] - base0);
-        const float alpha1 = exp2f(m_run[1] - base1);
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-        float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - base0);
-            s[nt][1] = exp2f(s[nt][1] - base0);
-            s[nt][2] = exp2f(s[nt][2] - base1);
-            s[nt][3] = exp2f(s[nt][3] - base1);
-            sum0 += s[nt][0] + s[nt][1];
-            sum1 += s[nt][2] + s[nt][3];
-        }
-        l_run[0] = l_run[0] * alpha0 + sum0;
-        l_run[1] = l_run[1] * alpha1 + sum1;
-#pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt) {
-            o[dt][0] *= alpha0;
-            o[dt][1] *= alpha0;
-            o[dt][2] *= alpha1;
-            o[dt][3] *= alpha1;
-        }
-        // O += P V
-#pragma unroll
-        for (int kk = 0; kk < TILE_N / 16; ++kk) {
-            uint32_t a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-            for (int dp = 0; dp < DTILES / 2; ++dp) {
-                uint32_t b[4];
-                const int m = lane >> 3;
-                const int key = kk * 16 + (m & 1) * 8 + (lane & 7);
-                const int col = dp * 16 + (m >> 1) * 8;
-                ldmatrix_x4_trans(b, tV + key * STRIDE + col);
-                mma_16816(o[2 * dp], a, b[0], b[1]);
-                mma_16816(o[2 * dp + 1], a, b[2], b[3]);
-            }
-        }
-        __syncthreads();
-        stage ^= 1;
-    }
-
-    // finish: row sums across the quad, normalise, store
-    float l0 = l_run[0], l1 = l_run[1];
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f;
-    const float inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
-    const int r0 = warp * 16 + g;
-    const int r1 = r0 + 8;
-#pragma unroll
-    for (int dt = 0; dt < DTILES; ++dt) {
-        const int col = dt * 8 + tq * 2;
-        if (col < D) {
-            if (r0 < rows_here) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][0] * inv0, o[dt][1] * inv0);
-                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r0) * out_stride + (size_t)h * D + col) = v;
-            }
-            if (r1 < rows_here) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][2] * inv1, o[dt][3] * inv1);
-                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r1) * out_stride + (size_t)h * D + col) = v;
-            }
-        }
-    }
-}
-
-// ------------------------------------------------------------------ decode: split-KV
-// grid (rows, Hkv, splits).  The G = Hq/Hkv query heads of one KV head are the
-// 16-row M tile (rows >= G are zero).  Split s covers absolute keys
-// [s*DEC_SPLIT, (s+1)*DEC_SPLIT); warp w takes keys w*16..w*16+15 of every
-// 64-key tile.  Partials (unnormalised O, running max, running sum) go to
-// scratch; the merge kernel combines splits in order.
-template <int DP>
-__global__ void __launch_bounds__(MMA_THREADS)
-attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
-                              const __nv_bfloat16* __restrict__ k_cache,
-                              const __nv_bfloat16* __restrict__ v_cache,
-                              const int* __restrict__ seq_lens, const int* __restrict__ block_table,
-                              int max_pages, const int* __restrict__ decode_rows,
-                              const int* __restrict__ decode_tokens, int Hq, int Hkv, int D,
-                              int page_size, int num_pages, float scale, int window, int num_splits,
-                              float* __restrict__ part_o, float* __restrict__ part_ml) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    constexpr int STRIDE = Tile<DP>::STRIDE;
-    constexpr int CH = Tile<DP>::CHUNKS;
-    constexpr int KSTEPS = DP / 16;
-    constexpr int DTILES = DP / 8;
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
-    __nv_bfloat16* sK = sQ + 16 * STRIDE;                             // 2 stages of 64 keys
-    __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;
-
-    const int slot = blockIdx.x;
-    const int kvh = blockIdx.y;
-    const int split = blockIdx.z;
-    const int row = decode_rows[slot];
-    const int token = decode_tokens[slot];
-    const int seq_len = seq_lens[row];
-    const int G = Hq / Hkv;
-    const int qpos = seq_len - 1;
-    const int key_lo_all = (window > 0 && qpos + 1 > window) ? qpos + 1 - window : 0;
-    const int key0 = max(split * DEC_SPLIT, (key_lo_all / TILE_N) * TILE_N);
-    const int key_end = min((split + 1) * DEC_SPLIT, seq_len);
-    if (key0 >= key_end || split * DEC_SPLIT + DEC_SPLIT <= key_lo_all) return;  // nothing of this split is visible
-    const int* table = block_table + (size_t)row * max_pages;
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
-    const int g = lane >> 2;
-    const int tq = lane & 3;
-
-    for (int c = threadIdx.x; c < 16 * CH; c += MMA_THREADS) {
-        const int r = c / CH;
-        const int col = (c % CH) * 8;
-        const bool valid = r < G && col < D;
-        const __nv_bfloat16* src = valid ? q + (size_t)token * q_stride + (size_t)(kvh * G + r) * D + col : q;
-        cp_async16(sQ + r * STRIDE + col, src, valid);
-    }
-    const int first_tile = key0 / TILE_N;
-    const int last_tile = (key_end - 1) / TILE_N;
-    load_kv_tile<DP>(sK, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end, TILE_N);
-    load_kv_tile<DP>(sV, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end, TILE_N);
-    cp_async_commit();
-
-    uint32_t qf[KSTEPS][4];
-    float o[DTILES][4];
-#pragma unroll
-    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.0f, 0.0f};
-    const float sl2 = scale * LOG2E;
-
-    int stage = 0;
-    for (int kt = first_tile; kt <= last_tile; ++kt) {
-        if (kt + 1 <= last_tile) {
-            load_kv_tile<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end, TILE_N);
-            load_kv_tile<DP>(sV + (stage ^ 1) * TILE_N * STRIDE, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end, TILE_N);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        if (kt == first_tile) {
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                const int m = lane >> 3;
-                const int r = (m & 1) * 8 + (lane & 7);
-                const int col = ks * 16 + (m >> 1) * 8;
-                ldmatrix_x4(qf[ks], sQ + r * STRIDE + col);
-            }
-        }
-        const __nv_bfloat16* tK = sK + stage * TILE_N * STRIDE + warp * 16 * STRIDE;
-        const __nv_bfloat16* tV = sV + stage * TILE_N * STRIDE + warp * 16 * STRIDE;
-        float s[2][4];
-        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.0f;
-        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            uint32_t b[4];
-            const int m = lane >> 3;
-            const int key = (m >> 1) * 8 + (lane & 7);
-            const int col = ks * 16 + (m & 1) * 8;
-            ldmatrix_x4(b, tK + key * STRIDE + col);
-            mma_16816(s[0], qf[ks], b[0], b[1]);
-            mma_16816(s[1], qf[ks], b[2], b[3]);
-        }
-        const int key_base = kt * TILE_N + warp * 16 + tq * 2;
-        // every row of the M tile has the same query position
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key_base + nt * 8 + e;
-                const bool ok = key < key_end && key >= key_lo_all;
-                s[nt][e] = ok ? s[nt][e] * sl2 : -INFINITY;
-                s[nt][2 + e] = ok ? s[nt][2 + e] * sl2 : -INFINITY;
-            }
-        }
-        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m_run[0], mx0);
-        const float mn1 = fmaxf(m_run[1], mx1);
-        const float base0 = mn0 == -INFINITY ? 0.0f : mn0;
-        const float base1 = mn1 == -INFINITY ? 0.0f : mn1;
-        const float alpha0 = exp2f(m_run[0] - base0);
-        const float alpha1 = exp2f(m_run[1] - base1);
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-        float sum0 = 0.0f, sum1 = 0.0f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - base0);
-            s[nt][1] = exp2f(s[nt][1] - base0);
-            s[nt][2] = exp2f(s[nt][2] - base1);
-            s[nt][3] = exp2f(s[nt][3] - base1);
-            sum0 += s[nt][0] + s[nt][1];
-            sum1 += s[nt][2] + s[nt][3];
-        }
-        l_run[0] = l_run[0] * alpha0 + sum0;
-        l_run[1] = l_run[1] * alpha1 + sum1;
-#pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt) {
-            o[dt][0] *= alpha0;
-            o[dt][1] *= alpha0;
-            o[dt][2] *= alpha1;
-            o[dt][3] *= alpha1;
-        }
-        uint32_t a[4];
-        a[0] = pack_bf16(s[0][0], s[0][1]);
-        a[1] = pack_bf16(s[0][2], s[0][3]);
-        a[2] = pack_bf16(s[1][0], s[1][1]);
-        a[3] = pack_bf16(s[1][2], s[1][3]);
-#pragma unroll
-        for (int dp = 0; dp < DTILES / 2; ++dp) {
-            uint32_t b[4];
-            const int m = lane >> 3;
-            const int key = (m & 1) * 8 + (lane & 7);
-            const int col = dp * 16 + (m >> 1) * 8;
-            ldmatrix_x4_trans(b, tV + key * STRIDE + col);
-            mma_16816(o[2 * dp], a, b[0], b[1]);
-            mma_16816(o[2 * dp + 1], a, b[2], b[3]);
-        }
-        __syncthreads();
-        stage ^= 1;
-    }
-
-    // combine the four warps (in warp order) through shared memory
-    float l0 = l_run[0], l1 = l_run[1];
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float* sO = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][DP]
-    float* sM = sO + 4 * 16 * DP;                     // [4][16]
-    float* sL = sM + 4 * 16;                          // [4][16]
-    // (the loop's last __syncthreads already separates this from the tile reads)
-#pragma unroll
-    for (int dt = 0; dt < DTILES; ++dt) {
-        const int col = dt * 8 + tq * 2;
-        float* base = sO + (size_t)warp * 16 * DP;
-        base[g * DP + col] = o[dt][0];
-        base[g * DP + col + 1] = o[dt][1];
-        base[(g + 8) * DP + col] = o[dt][2];
-        base[(g + 8) * DP + col + 1] = o[dt][3];
-    }
-    if (tq == 0) {
-        sM[warp * 16 + g] = m_run[0];
-        sM[warp * 16 + g + 8] = m_run[1];
-        sL[warp * 16 + g] = l0;
-        sL[warp * 16 + g + 8] = l1;
-    }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += MMA_THREADS) {
-        const int r = idx / D;
-        const int d = idx % D;
-        float big = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) big = fmaxf(big, sM[w * 16 + r]);
-        float acc = 0.0f, den = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = sM[w * 16 + r];
-            const float f = mw == -INFINITY ? 0.0f : exp2f(mw - big);
-            acc += sO[((size_t)w * 16 + r) * DP + d] * f;
-            den += sL[w * 16 + r] * f;
-        }
-        const size_t pidx = ((size_t)slot * Hq + (kvh * G + r)) * num_splits + split;
-        part_o[pidx * D + d] = acc;
-        if (d == 0) {
-            part_ml[pidx * 2] = big;
-            part_ml[pidx * 2 + 1] = den;
-        }
-    }
-}
-
-// grid (rows, Hq); combines the splits a row has, in split order.
-__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o,
-                                              const float* __restrict__ part_ml,
-                                              const int* __restrict__ seq_lens,
-                                              const int* __restrict__ decode_rows,
-                                              const int* __restrict__ decode_tokens,
-                                              __nv_bfloat16* __restrict__ out, int out_stride, int Hq,
-                                              int D, int window, int num_splits) {
-    const int slot = blockIdx.x;
-    const int h = blockIdx.y;
-    const int row = decode_rows[slot];
-    const int token = decode_tokens[slot];
-    const int seq_len = seq_lens[row];
-    const int qpos = seq_len - 1;
-    const int key_lo = (window > 0 && qpos + 1 > window) ? qpos + 1 - window : 0;
-    const int first = key_lo / DEC_SPLIT;
-    const int last = min((seq_len - 1) / DEC_SPLIT, num_splits - 1);
-    const size_t base = ((size_t)slot * Hq + h) * num_splits;
-    float big = -INFINITY;
-    for (int s = first; s <= last; ++s) big = fmaxf(big, part_ml[(base + s) * 2]);
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f, den = 0.0f;
-        for (int s = first; s <= last; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            const float f = ms == -INFINITY ? 0.0f : exp2f(ms - big);
-            acc += part_o[(base + s) * D + d] * f;
-            den += part_ml[(base + s) * 2 + 1] * f;
-        }
-        out[(size_t)token * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(den > 0.0f ? acc / den : 0.0f);
-    }
-}
-
-// ------------------------------------------------------------------ host entry points
-template <int DP>
-static size_t prefill_smem() { return (size_t)(TILE_M + 4 * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16); }
-
-template <int DP>
-static size_t decode_smem() {
-    const size_t tiles = (size_t)(16 + 4 * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16);
-    const size_t merge = (size_t)(4 * 16 * DP + 2 * 4 * 16) * sizeof(float);
-    return tiles > merge ? tiles : merge;
-}
-
-static int padded_dim(int D) {
-    if (D % 16 != 0 || D < 16 || D > 256) return 0;
-    if (D <= 32) return 32;
-    if (D <= 64) return 64;
-    if (D <= 128) return 128;
-    return 256;
-}
-
-template <int DP>
-static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int out_stride,
-                          const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
-                          const int* qo_indptr, const int* seq_lens, const int* block_table,
-                          int max_pages, const int* tile_rows, const int* tile_starts, int num_tiles,
-                          int Hq, int Hkv, int D, int page_size, int num_pages, float scale,
-                          int window, cudaStream_t stream) {
-    const size_t smem = prefill_smem<DP>();
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    dim3 grid(num_tiles, Hq);
-    attention_prefill_kernel<DP><<<grid, MMA_THREADS, smem, stream>>>(
-        q, q_stride, out, out_stride, k_cache, v_cache, qo_indptr, seq_lens, block_table, max_pages,
-        tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window);
-    return kb_launch_result();
-}
+// Exported entry points of the tensor-core attention kernels (attention_mma.cuh).
+#include "attention_mma.cuh"
 
 KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, int out_stride,
                                        const void* k_cache, const void* v_cache,
@@ -595,22 +24,6 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
         default: return KB_ERR_UNSUPPORTED_SIZE;
     }
 #undef ARGS
-}
-
-template <int DP>
-static int launch_decode(const __nv_bfloat16* q, int q_stride, const __nv_bfloat16* k_cache,
-                         const __nv_bfloat16* v_cache, const int* seq_lens, const int* block_table,
-                         int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows,
-                         int Hq, int Hkv, int D, int page_size, int num_pages, float scale, int window,
-                         int num_splits, float* part_o, float* part_ml, cudaStream_t stream) {
-    const size_t smem = decode_smem<DP>();
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_split_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return (int)e;
-    dim3 grid(num_rows, Hkv, num_splits);
-    attention_decode_split_kernel<DP><<<grid, MMA_THREADS, smem, stream>>>(
-        q, q_stride, k_cache, v_cache, seq_lens, block_table, max_pages, decode_rows, decode_tokens,
-        Hq, Hkv, D, page_size, num_pages, scale, window, num_splits, part_o, part_ml);
-    return kb_launch_result();
 }
 
 // part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch).
