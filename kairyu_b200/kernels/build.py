@@ -32,6 +32,7 @@ LIBRARIES: dict[str, list[str]] = {
     "rope_kv": [],
     "attention_generic": [],
     "attention_mma": [],
+    "attention_decode_static": [],
     "gemm_f32": [],
     "sampling": [],
 }
@@ -78,7 +79,7 @@ def build_dir() -> Path:
 def _signature(name: str, flags: list[str]) -> str:
     digest = hashlib.sha256()
     digest.update(" ".join(ARCH_FLAGS + COMMON_FLAGS + flags).encode())
-    for path in sorted(CSRC.glob("*.cuh")) + [CSRC / f"{name}.cu"]:
+    for path in sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + [CSRC / f"{name}.cu"]:
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
     return digest.hexdigest()
