@@ -65,10 +65,103 @@ __global__ void rmsnorm_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
     }
 }
 
+
+// Vector variant for H % 4 == 0 and H <= 16 * blockDim: each thread keeps up to four
+// 4-element chunks of the row in registers, so the row is read once, all loads are in
+// flight together, and one block-wide sum separates the two halves.
+#define NORM_MAX_CHUNKS 4
+
+template <typename T>
+struct Vec4;
+template <>
+struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 r = *reinterpret_cast<const float4*>(p);
+        v[0] = r.x; v[1] = r.y; v[2] = r.z; v[3] = r.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <>
+struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 r = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]);
+        __nv_bfloat162 b = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 r;
+        r.x = *reinterpret_cast<uint32_t*>(&a);
+        r.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = r;
+    }
+};
+
+template <typename TX, typename TA, typename TW>
+__global__ void rmsnorm_vec_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
+                                   const TW* __restrict__ w, TA* __restrict__ out,
+                                   const int* __restrict__ rows, int H, float eps, int write_back) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const int s = rows ? rows[r] : r;
+    TX* xr = x + (size_t)s * H;
+    const TA* dr = delta ? delta + (size_t)s * H : nullptr;
+    const int chunks = H >> 2;
+    float v[NORM_MAX_CHUNKS][4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+        const int chunk = threadIdx.x + c * blockDim.x;
+        if (chunk < chunks) {
+            Vec4<TX>::load(xr + 4 * chunk, v[c]);
+            if (dr) {
+                float d[4];
+                Vec4<TA>::load(dr + 4 * chunk, d);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[c][e] += d[e];
+                if (write_back) Vec4<TX>::store(xr + 4 * chunk, v[c]);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += v[c][e] * v[c][e];
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)H + eps);
+    TA* orow = out + (size_t)r * H;
+#pragma unroll
+    for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+        const int chunk = threadIdx.x + c * blockDim.x;
+        if (chunk < chunks) {
+            float wv[4], o[4];
+            Vec4<TW>::load(w + 4 * chunk, wv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = v[c][e] * inv * wv[e];
+            Vec4<TA>::store(orow + 4 * chunk, o);
+        }
+    }
+}
+
 template <typename TX, typename TA>
 static int rmsnorm_dispatch_w(void* x, const void* delta, const void* w, int w_bf16, void* out,
                               const int* rows, int R, int H, float eps, int write_back,
                               cudaStream_t stream) {
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
+                         (delta == nullptr || (uintptr_t)delta % 16 == 0);
+    if (H % 4 == 0 && H <= 16 * 1024 && aligned) {
+        int threads_v = ((H / 4 + 31) / 32) * 32;  // one chunk per thread while the block can hold the row
+        if (threads_v > 1024) threads_v = 1024;
+        if (w_bf16)
+            rmsnorm_vec_kernel<TX, TA, __nv_bfloat16><<<R, threads_v, 0, stream>>>(
+                (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back);
+        else
+            rmsnorm_vec_kernel<TX, TA, float><<<R, threads_v, 0, stream>>>(
+                (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back);
+        return kb_launch_result();
+    }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (w_bf16)
         rmsnorm_kernel<TX, TA, __nv_bfloat16><<<R, threads, 0, stream>>>(
@@ -113,11 +206,42 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     }
 }
 
+
+// 8 elements a thread (16-byte loads for bf16, two for fp32) when I % 8 == 0.
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    const int t = blockIdx.y;
+    const T* g = gate_up + (size_t)t * 2 * I;
+    const T* u = g + I;
+    T* o = out + (size_t)t * I;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8; i < I; i += gridDim.x * blockDim.x * 8) {
+        float gv[8], uv[8], ov[8];
+        Vec4<T>::load(g + i, *reinterpret_cast<float(*)[4]>(&gv[0]));
+        Vec4<T>::load(g + i + 4, *reinterpret_cast<float(*)[4]>(&gv[4]));
+        Vec4<T>::load(u + i, *reinterpret_cast<float(*)[4]>(&uv[0]));
+        Vec4<T>::load(u + i + 4, *reinterpret_cast<float(*)[4]>(&uv[4]));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ov[e] = gv[e] / (1.0f + expf(-gv[e])) * uv[e];
+        Vec4<T>::store(o + i, *reinterpret_cast<float(*)[4]>(&ov[0]));
+        Vec4<T>::store(o + i + 4, *reinterpret_cast<float(*)[4]>(&ov[4]));
+    }
+}
+
 KB_EXPORT int kb_swiglu(const void* gate_up, void* out, int is_bf16, int T, int I, cudaStream_t stream) {
     if (T == 0) return 0;
     if (!gate_up || !out) return KB_ERR_NULL;
     if (T > 65535) return KB_ERR_UNSUPPORTED_SIZE;
     const int threads = 256;
+    if (I % 8 == 0 && (uintptr_t)gate_up % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        int bxv = (I / 8 + threads - 1) / threads;
+        if (bxv > 1024) bxv = 1024;
+        dim3 gridv(bxv, T);
+        if (is_bf16)
+            swiglu_vec_kernel<__nv_bfloat16><<<gridv, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
+        else
+            swiglu_vec_kernel<float><<<gridv, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+        return kb_launch_result();
+    }
     int bx = (I + threads - 1) / threads;
     if (bx > 1024) bx = 1024;
     dim3 grid(bx, T);

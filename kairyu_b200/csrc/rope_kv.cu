@@ -14,6 +14,8 @@
 #define ROPE_WARPS 4
 #define ROPE_MAX_D 512
 
+// grid (tokens, ceil((Hq + 2*Hkv) / ROPE_WARPS)); one warp per head: q heads, then k
+// heads (norm + rotation, k also into the cache), then v heads (copied into the cache).
 template <typename T, typename TW>
 __global__ void __launch_bounds__(ROPE_WARPS * 32)
 qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hkv, int D,
@@ -28,77 +30,70 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * ROPE_WARPS + warp;
+    if (head >= Hq + 2 * Hkv) return;
     const int pos = positions[t];
     const int row = row_ids[t];
     T* token = qkv + (size_t)t * qkv_stride;
 
     const bool rotate = cos_table != nullptr && rot_half > 0;
     if (rotate && (pos < 0 || pos >= max_pos)) {
-        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+        if (lane == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
         return;
     }
-    const float* cos_row = rotate ? cos_table + (size_t)pos * rot_half : nullptr;
-    const float* sin_row = rotate ? sin_table + (size_t)pos * rot_half : nullptr;
+    const bool is_v = head >= Hq + Hkv;
+    const bool is_k = !is_v && head >= Hq;
 
     // Where this token's k and v go (or nowhere).
     long long slot = -1;
-    if (k_cache != nullptr && pos >= write_from[row]) {
+    if ((is_k || is_v) && k_cache != nullptr && pos >= write_from[row]) {
         const int page_index = pos / page_size;
-        if (page_index >= max_pages) {
-            if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
+        const int page = page_index < max_pages ? block_table[(size_t)row * max_pages + page_index] : -1;
+        if (page < 0 || page >= num_pages) {
+            if (lane == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
         } else {
-            const int page = block_table[(size_t)row * max_pages + page_index];
-            if (page < 0 || page >= num_pages) {
-                if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
-            } else {
-                slot = (long long)page * page_size + (pos % page_size);
-            }
+            slot = (long long)page * page_size + (pos % page_size);
         }
     }
-
+    T* x = token + (size_t)head * D;
+    if (is_v) {
+        if (slot >= 0) {
+            T* vdst = v_cache + ((size_t)slot * Hkv + (head - Hq - Hkv)) * D;
+            for (int i = lane; i < D; i += 32) vdst[i] = x[i];
+        }
+        return;
+    }
     float* buf = head_buf[warp];
-    // q heads [0, Hq), then k heads [Hq, Hq+Hkv): norm + rotation.
-    for (int head = warp; head < Hq + Hkv; head += ROPE_WARPS) {
-        const bool is_k = head >= Hq;
-        T* x = token + (size_t)head * D;
-        const TW* w = is_k ? k_norm_w : q_norm_w;
-        float ss = 0.0f;
-        for (int i = lane; i < D; i += 32) {
-            const float v = to_float(x[i]);
-            buf[i] = v;
-            ss += v * v;
-        }
-        if (w != nullptr) {
-            ss = warp_sum(ss);
-            const float inv = rsqrtf(ss / (float)D + eps);
-            for (int i = lane; i < D; i += 32) buf[i] = buf[i] * inv * to_float(w[i]);
-        }
-        __syncwarp();
-        T* kdst = nullptr;
-        if (is_k && slot >= 0) kdst = k_cache + ((size_t)slot * Hkv + (head - Hq)) * D;
-        for (int i = lane; i < D; i += 32) {
-            float out;
-            if (rotate && i < 2 * rot_half) {
-                const int j = i < rot_half ? i : i - rot_half;
-                const float c = cos_row[j];
-                const float s = sin_row[j];
-                // rotate_half(u) = cat(-u[half:], u[:half])
-                out = i < rot_half ? buf[i] * c - buf[i + rot_half] * s
-                                   : buf[i] * c + buf[i - rot_half] * s;
-            } else {
-                out = buf[i];
-            }
-            const T rounded = from_float<T>(out);
-            x[i] = rounded;
-            if (kdst) kdst[i] = rounded;
-        }
-        __syncwarp();
+    const TW* w = is_k ? k_norm_w : q_norm_w;
+    float ss = 0.0f;
+    for (int i = lane; i < D; i += 32) {
+        const float v = to_float(x[i]);
+        buf[i] = v;
+        ss += v * v;
     }
-    // v heads: copy into the cache.
-    if (slot >= 0 && v_cache != nullptr) {
-        const T* v = token + (size_t)(Hq + Hkv) * D;
-        T* vdst = v_cache + (size_t)slot * Hkv * D;
-        for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) vdst[i] = v[i];
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        for (int i = lane; i < D; i += 32) buf[i] = buf[i] * inv * to_float(w[i]);
+    }
+    __syncwarp();
+    const float* cos_row = rotate ? cos_table + (size_t)pos * rot_half : nullptr;
+    const float* sin_row = rotate ? sin_table + (size_t)pos * rot_half : nullptr;
+    T* kdst = (is_k && slot >= 0) ? k_cache + ((size_t)slot * Hkv + (head - Hq)) * D : nullptr;
+    for (int i = lane; i < D; i += 32) {
+        float out;
+        if (rotate && i < 2 * rot_half) {
+            const int j = i < rot_half ? i : i - rot_half;
+            const float c = cos_row[j];
+            const float sn = sin_row[j];
+            // rotate_half(u) = cat(-u[half:], u[:half])
+            out = i < rot_half ? buf[i] * c - buf[i + rot_half] * sn : buf[i] * c + buf[i - rot_half] * sn;
+        } else {
+            out = buf[i];
+        }
+        const T rounded = from_float<T>(out);
+        x[i] = rounded;
+        if (kdst) kdst[i] = rounded;
     }
 }
 
@@ -120,8 +115,10 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
     if ((q_norm_w == nullptr) != (k_norm_w == nullptr)) return KB_ERR_BAD_ARG;
     if (k_cache && (!block_table || !write_from || !v_cache || page_size < 1)) return KB_ERR_NULL;
     const int threads = ROPE_WARPS * 32;
+    if (Hq + 2 * Hkv > 65535 * ROPE_WARPS) return KB_ERR_UNSUPPORTED_SIZE;
+    dim3 grid(T, (Hq + 2 * Hkv + ROPE_WARPS - 1) / ROPE_WARPS);
 #define LAUNCH(T_, TW_)                                                                         \
-    qk_norm_rope_kv_write_kernel<T_, TW_><<<T, threads, 0, stream>>>(                           \
+    qk_norm_rope_kv_write_kernel<T_, TW_><<<grid, threads, 0, stream>>>(                           \
         (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps,      \
         cos_table, sin_table, rot_half, max_pos, positions, row_ids, block_table, max_pages,    \
         write_from, (T_*)k_cache, (T_*)v_cache, page_size, num_pages, flag)

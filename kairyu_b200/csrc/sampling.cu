@@ -47,14 +47,39 @@ __device__ __forceinline__ BestF block_argmax(BestF b, float* sv, int* si) {
 // ------------------------------------------------------------------ argmax
 // out[r] = first index of the maximum of logits[r, :] (NaN never wins).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out, int vectorised) {
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
     BestF b{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float v = row[i];
-        if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+    if (vectorised) {  // rows 16-byte aligned: four loads of four in flight per thread
+        const int quads = V >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int q0 = threadIdx.x; q0 < quads; q0 += 4 * blockDim.x) {
+            float4 part[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int q = q0 + u * blockDim.x;
+                part[u] = q < quads ? row4[q] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = (q0 + u * blockDim.x) * 4;
+                if (better(part[u].x, i, b.v, b.i)) { b.v = part[u].x; b.i = i; }
+                if (better(part[u].y, i + 1, b.v, b.i)) { b.v = part[u].y; b.i = i + 1; }
+                if (better(part[u].z, i + 2, b.v, b.i)) { b.v = part[u].z; b.i = i + 2; }
+                if (better(part[u].w, i + 3, b.v, b.i)) { b.v = part[u].w; b.i = i + 3; }
+            }
+        }
+        for (int i = (quads << 2) + threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
+        }
     }
     b = block_argmax(b, sv, si);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i == 0x7fffffff ? 0 : b.i;
@@ -64,7 +89,8 @@ KB_EXPORT int kb_argmax(const float* logits, int ld, int n, int V, int* out, cud
     if (n == 0) return 0;
     if (!logits || !out) return KB_ERR_NULL;
     if (V < 1) return KB_ERR_BAD_ARG;
-    argmax_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out);
+    const int vectorised = ((uintptr_t)logits % 16 == 0) && (ld % 4 == 0);
+    argmax_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out, vectorised);
     return kb_launch_result();
 }
 
