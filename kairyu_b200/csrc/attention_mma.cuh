@@ -66,32 +66,47 @@ struct Tile {
     static constexpr int CHUNKS = DP / 8;  // 16-byte chunks per row
 };
 
-// Copies `rows` keys starting at absolute key `key0` of one KV head into a tile
-// (row r of the tile = key key0 + r).  Keys >= key_end, keys on pages the table
-// marks absent, and columns >= D are zero-filled.
+// Copies the 64 keys and values starting at absolute key `key0` of one KV head into
+// a K tile and a V tile (row r of a tile = key key0 + r).  Keys outside
+// [key_lo, key_end), keys on pages the table marks absent, and columns >= D are
+// zero-filled.  A thread owns one 16-byte column of the rows r0, r0 + RPP, ...: the
+// page lookup is done once per row and shared by the K and the V copy.
 template <int DP>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const __nv_bfloat16* __restrict__ cache,
-                                             const int* __restrict__ table, int max_pages, int num_pages,
-                                             int page_size, int Hkv, int kvh, int D, int key0, int key_lo,
-                                             int key_end, int rows) {
+__device__ __forceinline__ void load_kv_tiles(__nv_bfloat16* tile_k, __nv_bfloat16* tile_v,
+                                              const __nv_bfloat16* __restrict__ k_cache,
+                                              const __nv_bfloat16* __restrict__ v_cache,
+                                              const int* __restrict__ table, int max_pages, int num_pages,
+                                              int page_size, int page_shift, int Hkv, int kvh, int D,
+                                              int key0, int key_lo, int key_end) {
     constexpr int CH = Tile<DP>::CHUNKS;
-    for (int c = threadIdx.x; c < rows * CH; c += MMA_THREADS) {
-        const int r = c / CH;
-        const int col = (c % CH) * 8;
+    constexpr int RPP = MMA_THREADS / CH;  // rows per pass
+    constexpr int PASSES = TILE_N / RPP;
+    const int col = (threadIdx.x % CH) * 8;
+    const int r0 = threadIdx.x / CH;
+    const bool col_ok = col < D;
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+        const int r = r0 + pass * RPP;
         const int key = key0 + r;
-        bool valid = key >= key_lo && key < key_end && col < D;
-        const __nv_bfloat16* src = cache;
+        bool valid = col_ok && key >= key_lo && key < key_end;
+        size_t offset = 0;
         if (valid) {
-            const int page_index = key / page_size;
+            const int page_index = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
             const int page = page_index < max_pages ? table[page_index] : -1;
             if (page < 0 || page >= num_pages) {
                 valid = false;
             } else {
-                src = cache + (((size_t)page * page_size + (key % page_size)) * Hkv + kvh) * D + col;
+                const int within = key - page_index * page_size;
+                offset = (((size_t)page * page_size + within) * Hkv + kvh) * D + col;
             }
         }
-        cp_async16(tile + r * Tile<DP>::STRIDE + col, src, valid);
+        cp_async16(tile_k + r * Tile<DP>::STRIDE + col, k_cache + offset, valid);
+        cp_async16(tile_v + r * Tile<DP>::STRIDE + col, v_cache + offset, valid);
     }
+}
+
+__device__ __forceinline__ int shift_of(int page_size) {
+    return (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 }
 
 // ------------------------------------------------------------------ prefill: 64-query tiles
@@ -144,8 +159,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         const __nv_bfloat16* src = valid ? q + (size_t)(tok0 + q0 + r) * q_stride + (size_t)h * D + col : q;
         cp_async16(sQ + r * STRIDE + col, src, valid);
     }
-    load_kv_tile<DP>(sK, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end, TILE_N);
-    load_kv_tile<DP>(sV, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end, TILE_N);
+    const int page_shift = shift_of(page_size);
+    load_kv_tiles<DP>(sK, sV, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end);
     cp_async_commit();
 
     uint32_t qf[KSTEPS][4];
@@ -161,8 +176,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     int stage = 0;
     for (int kt = first_kt; kt <= last_kt; ++kt) {
         if (kt + 1 <= last_kt) {
-            load_kv_tile<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end, TILE_N);
-            load_kv_tile<DP>(sV + (stage ^ 1) * TILE_N * STRIDE, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end, TILE_N);
+            load_kv_tiles<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, sV + (stage ^ 1) * TILE_N * STRIDE, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -346,8 +360,8 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     }
     const int first_tile = key0 / TILE_N;
     const int last_tile = (key_end - 1) / TILE_N;
-    load_kv_tile<DP>(sK, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end, TILE_N);
-    load_kv_tile<DP>(sV, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end, TILE_N);
+    const int page_shift = shift_of(page_size);
+    load_kv_tiles<DP>(sK, sV, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end);
     cp_async_commit();
 
     uint32_t qf[KSTEPS][4];
@@ -361,8 +375,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     int stage = 0;
     for (int kt = first_tile; kt <= last_tile; ++kt) {
         if (kt + 1 <= last_tile) {
-            load_kv_tile<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, k_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end, TILE_N);
-            load_kv_tile<DP>(sV + (stage ^ 1) * TILE_N * STRIDE, v_cache, table, max_pages, num_pages, page_size, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end, TILE_N);
+            load_kv_tiles<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, sV + (stage ^ 1) * TILE_N * STRIDE, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
