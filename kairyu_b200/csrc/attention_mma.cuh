@@ -20,6 +20,7 @@
 #define TILE_N 64
 #define MMA_THREADS 128
 #define DEC_SPLIT 256
+#define DEC_STAGES 3  // cp.async pipeline depth of the split-KV kernel: two tiles in flight while one is used
 #define LOG2E 1.4426950408889634f
 
 // ------------------------------------------------------------------ PTX helpers
@@ -330,8 +331,8 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     constexpr int KSTEPS = DP / 16;
     constexpr int DTILES = DP / 8;
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
-    __nv_bfloat16* sK = sQ + 16 * STRIDE;                             // 2 stages of 64 keys
-    __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;
+    __nv_bfloat16* sK = sQ + 16 * STRIDE;                             // DEC_STAGES stages of 64 keys
+    __nv_bfloat16* sV = sK + DEC_STAGES * TILE_N * STRIDE;
 
     const int slot = blockIdx.x;
     const int kvh = blockIdx.y;
@@ -361,8 +362,14 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const int first_tile = key0 / TILE_N;
     const int last_tile = (key_end - 1) / TILE_N;
     const int page_shift = shift_of(page_size);
-    load_kv_tiles<DP>(sK, sV, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, first_tile * TILE_N, key_lo_all, key_end);
-    cp_async_commit();
+    // prologue: the first DEC_STAGES-1 tiles (one commit group each, empty past the end)
+#pragma unroll
+    for (int ahead = 0; ahead < DEC_STAGES - 1; ++ahead) {
+        if (first_tile + ahead <= last_tile)
+            load_kv_tiles<DP>(sK + ahead * TILE_N * STRIDE, sV + ahead * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
+                              num_pages, page_size, page_shift, Hkv, kvh, D, (first_tile + ahead) * TILE_N, key_lo_all, key_end);
+        cp_async_commit();
+    }
 
     uint32_t qf[KSTEPS][4];
     float o[DTILES][4];
@@ -374,14 +381,16 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
 
     int stage = 0;
     for (int kt = first_tile; kt <= last_tile; ++kt) {
-        if (kt + 1 <= last_tile) {
-            load_kv_tiles<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, sV + (stage ^ 1) * TILE_N * STRIDE, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo_all, key_end);
+        cp_async_wait<DEC_STAGES - 2>();  // tile kt has landed
+        __syncthreads();                  // ... for every thread, and tile kt-1's stage is free
+        {
+            const int next = kt + DEC_STAGES - 1;
+            const int next_stage = (stage + DEC_STAGES - 1) % DEC_STAGES;
+            if (next <= last_tile)
+                load_kv_tiles<DP>(sK + next_stage * TILE_N * STRIDE, sV + next_stage * TILE_N * STRIDE, k_cache, v_cache, table,
+                                  max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, next * TILE_N, key_lo_all, key_end);
             cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
         }
-        __syncthreads();
         if (kt == first_tile) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) {
@@ -466,9 +475,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_16816(o[2 * dp], a, b[0], b[1]);
             mma_16816(o[2 * dp + 1], a, b[2], b[3]);
         }
-        __syncthreads();
-        stage ^= 1;
+        stage = (stage + 1) % DEC_STAGES;
     }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with the tiles before they become the merge buffer
 
     // combine the four warps (in warp order) through shared memory
     float l0 = l_run[0], l1 = l_run[1];
@@ -479,7 +489,6 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float* sO = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][DP]
     float* sM = sO + 4 * 16 * DP;                     // [4][16]
     float* sL = sM + 4 * 16;                          // [4][16]
-    // (the loop's last __syncthreads already separates this from the tile reads)
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) {
         const int col = dt * 8 + tq * 2;
@@ -557,7 +566,7 @@ static size_t prefill_smem() { return (size_t)(TILE_M + 4 * TILE_N) * Tile<DP>::
 
 template <int DP>
 static size_t decode_smem() {
-    const size_t tiles = (size_t)(16 + 4 * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16);
+    const size_t tiles = (size_t)(16 + 2 * DEC_STAGES * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)(4 * 16 * DP + 2 * 4 * 16) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }

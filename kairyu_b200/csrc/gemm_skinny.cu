@@ -1,0 +1,198 @@
+// Weight-streaming matrix product for a few tokens (decode):
+//     out[M, N] = x[M, K] . W[N, K]^T (+ bias),   M <= 16, bf16 in, fp32 accumulate,
+// optionally with the SiLU gate fused in:  out[M, N/2] = silu(x.Wg^T) * (x.Wu^T)
+// where Wg = W[:N/2] and Wu = W[N/2:] (kairyu/models/layers.py:244).
+//
+// At these M the product is bound by reading W once from HBM.  The weights are the
+// 16-row operand of mma.sync m16n8k16 and the tokens its 8 columns, so W is
+// consumed at tensor-core rate straight from registers: every thread loads 32
+// contiguous bytes of a weight row and 32 of a token row; because a dot product
+// does not care in which order k is summed, those 16 values are handed to four
+// MMAs as their (k, k+8) pairs without any shuffle.  A block owns 16 weight rows; its
+// warps split K and their partial sums are added in warp order through shared
+// memory, so the result does not depend on timing.
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_THREADS (SK_WARPS * 32)
+#define SK_UNROLL 2
+#define SK_STEP 64  // k per step: four lanes of a weight row load 32 bytes each, one full 128-byte line
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct Reg8 {
+    uint32_t r[8];
+};
+
+// streaming 32-byte load of weights (sm_100 has 256-bit loads): read once, keep out of L1
+__device__ __forceinline__ Reg8 load_stream32(const void* p) {
+    Reg8 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
+                 : "l"(p));
+    return v;
+}
+// 32-byte load of activations: small, shared by every block, kept in L1
+__device__ __forceinline__ Reg8 load_cached32(const void* p) {
+    Reg8 v;
+    asm volatile("ld.global.nc.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]), "=r"(v.r[7])
+                 : "l"(p));
+    return v;
+}
+
+// NT: token tiles of 8 (1 or 2).  GATED: warps 0..3 walk the gate rows and warps
+// 4..7 the rows N/2 further down (the "up" half); the epilogue writes silu(gate) * up.
+template <int NT, bool GATED, typename TO>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
+                   int ldw, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out, int ldo,
+                   int M, int N, int K) {
+    constexpr int HALVES = GATED ? 2 : 1;
+    constexpr int KWARPS = SK_WARPS / HALVES;  // warps that split K for one half
+    __shared__ float partial[SK_WARPS][NT][16][8 + 1];
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int tq = lane & 3;
+    const int half = warp / KWARPS;
+    const int kwarp = warp % KWARPS;
+    const int rows_out = GATED ? N / 2 : N;      // output columns
+    const int n0 = blockIdx.x * 16;              // first weight row (and output column) of the block
+
+    // K is cut into SK_STEP-wide steps; warp kwarp takes steps kwarp, kwarp + KWARPS, ...
+    const int steps = (K + SK_STEP - 1) / SK_STEP;
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+
+    const int row_lo = n0 + g;
+    const int row_hi = n0 + g + 8;
+    const bool lo_ok = row_lo < rows_out;
+    const bool hi_ok = row_hi < rows_out;
+    const __nv_bfloat16* w_lo = w + (size_t)(half * rows_out + (lo_ok ? row_lo : 0)) * ldw;
+    const __nv_bfloat16* w_hi = w + (size_t)(half * rows_out + (hi_ok ? row_hi : 0)) * ldw;
+    const __nv_bfloat16* x_row[NT];
+    bool x_ok[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        x_ok[t] = t * 8 + g < M;
+        x_row[t] = x + (size_t)(x_ok[t] ? t * 8 + g : 0) * ldx;
+    }
+    Reg8 zero;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) zero.r[i] = 0u;
+
+    // Two register sets: the loads of the next SK_UNROLL steps are issued before the
+    // MMAs of the current ones, so a warp always has a batch in flight.
+    Reg8 a_lo[2][SK_UNROLL], a_hi[2][SK_UNROLL], b[2][SK_UNROLL][NT];
+    auto load_batch = [&](int set, int step0) {
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int k = (step0 + u * KWARPS) * SK_STEP + tq * 16;
+            const bool k_ok = k < K;  // K % 16 == 0, so a 32-byte load is all in or all out
+            a_lo[set][u] = (k_ok && lo_ok) ? load_stream32(w_lo + k) : zero;
+            a_hi[set][u] = (k_ok && hi_ok) ? load_stream32(w_hi + k) : zero;
+#pragma unroll
+            for (int t = 0; t < NT; ++t) b[set][u][t] = (k_ok && x_ok[t]) ? load_cached32(x_row[t] + k) : zero;
+        }
+    };
+    // The 16 values a thread holds of a row feed four MMAs: MMA j takes values 4j..4j+3
+    // as its (k, k+1) and (k+8, k+9) pairs.  Which k a value is called does not matter to
+    // a dot product as long as the weight and the token agree, and they do: both come
+    // from the same 32 bytes of their rows.
+    auto mma_batch = [&](int set) {
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    mma_bf16(acc[t], a_lo[set][u].r[2 * j], a_hi[set][u].r[2 * j], a_lo[set][u].r[2 * j + 1],
+                             a_hi[set][u].r[2 * j + 1], b[set][u][t].r[2 * j], b[set][u][t].r[2 * j + 1]);
+    };
+    constexpr int STRIDE = KWARPS * SK_UNROLL;
+    int step0 = kwarp;
+    load_batch(0, step0);
+    while (true) {
+        load_batch(1, step0 + STRIDE);  // past the end: all zero, no memory touched
+        mma_batch(0);
+        step0 += STRIDE;
+        if (step0 >= steps) break;
+        load_batch(0, step0 + STRIDE);
+        mma_batch(1);
+        step0 += STRIDE;
+        if (step0 >= steps) break;
+    }
+
+    // acc[t]: c0,c1 = (row g, tokens t*8 + 2tq, +1); c2,c3 = (row g+8, same tokens)
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+        partial[warp][t][g][2 * tq] = acc[t][0];
+        partial[warp][t][g][2 * tq + 1] = acc[t][1];
+        partial[warp][t][g + 8][2 * tq] = acc[t][2];
+        partial[warp][t][g + 8][2 * tq + 1] = acc[t][3];
+    }
+    __syncthreads();
+    // one thread per (token, row): rows fastest so that stores of a token are contiguous
+    for (int idx = threadIdx.x; idx < NT * 8 * 16; idx += SK_THREADS) {
+        const int r = idx & 15;
+        const int token = idx >> 4;
+        const int t = token >> 3;
+        const int col = token & 7;
+        const int n = n0 + r;
+        if (token >= M || n >= rows_out) continue;
+        float value[HALVES];
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h) {
+            float sum = 0.0f;
+#pragma unroll
+            for (int wp = 0; wp < KWARPS; ++wp) sum += partial[h * KWARPS + wp][t][r][col];
+            if (bias) sum += __bfloat162float(bias[h * rows_out + n]);
+            value[h] = sum;
+        }
+        float result = value[0];
+        if (GATED) result = value[0] / (1.0f + expf(-value[0])) * value[HALVES - 1];
+        out[(size_t)token * ldo + n] = from_float<TO>(result);
+    }
+}
+
+template <int NT, bool GATED>
+static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw,
+                         const __nv_bfloat16* bias, void* out, int out_fp32, int ldo, int M, int N, int K,
+                         cudaStream_t stream) {
+    const int rows_out = GATED ? N / 2 : N;
+    const int blocks = (rows_out + 15) / 16;
+    if (out_fp32)
+        gemm_skinny_kernel<NT, GATED, float><<<blocks, SK_THREADS, 0, stream>>>(x, ldx, w, ldw, bias, (float*)out, ldo, M, N, K);
+    else
+        gemm_skinny_kernel<NT, GATED, __nv_bfloat16><<<blocks, SK_THREADS, 0, stream>>>(x, ldx, w, ldw, bias, (__nv_bfloat16*)out, ldo, M, N, K);
+    return kb_launch_result();
+}
+
+// x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), bias: [N] bf16 or null,
+// out: [M, N] (or [M, N/2] when gated) bf16 or fp32.  Needs M <= 16, K % 16 == 0 and
+// 32-byte aligned rows; anything else is refused (the caller has the library product).
+KB_EXPORT int kb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out,
+                             int out_fp32, int ldo, int M, int N, int K, int gated, cudaStream_t stream) {
+    if (M == 0 || N == 0) return 0;
+    if (!x || !w || !out) return KB_ERR_NULL;
+    if (M < 1 || M > 16 || K < 16 || K % 16 != 0 || ldx % 16 != 0 || ldw % 16 != 0) return KB_ERR_UNSUPPORTED_SIZE;
+    if (((uintptr_t)x | (uintptr_t)w) % 32 != 0) return KB_ERR_UNSUPPORTED_SIZE;
+    if (gated && N % 2 != 0) return KB_ERR_BAD_ARG;
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+    const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+    const __nv_bfloat16* bb = (const __nv_bfloat16*)bias;
+    if (M <= 8) {
+        if (gated) return launch_skinny<1, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+        return launch_skinny<1, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+    }
+    if (gated) return launch_skinny<2, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+    return launch_skinny<2, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+}

@@ -15,6 +15,10 @@ import torch
 
 from kairyu_b200.kernels.build import KernelBuildError, load_library
 
+# The library products (cuBLAS through torch) may otherwise add split-K partial sums in
+# bfloat16; this engine's products accumulate and reduce in fp32.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 c_int = ctypes.c_int
 c_float = ctypes.c_float
 c_void_p = ctypes.c_void_p
@@ -428,6 +432,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
         raise KernelError(f"linear: dtypes {x.dtype} / {weight.dtype} are not supported")
     if M == 0:
         return
+    if _skinny_ok(x, weight, bias, out):
+        _gemm_skinny(x, weight, bias, out, gated=False)
+        return
     if out.dtype == torch.bfloat16:
         if bias is not None:
             torch.addmm(bias, x, weight.t(), out=out)
@@ -439,6 +446,54 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
             out.add_(bias)
     else:
         raise KernelError(f"linear: output dtype {out.dtype} is not supported")
+
+
+SKINNY_MAX_ROWS = 16  # token rows the weight-streaming product takes (csrc/gemm_skinny.cu)
+
+
+def _skinny_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (
+        M <= SKINNY_MAX_ROWS
+        and K % 16 == 0
+        and x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1
+        and x.stride(0) % 16 == 0 and weight.stride(0) % 16 == 0
+        and x.data_ptr() % 32 == 0 and weight.data_ptr() % 32 == 0
+        and out.dtype in (torch.bfloat16, torch.float32)
+        and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous()))
+    )
+
+
+def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, gated: bool) -> None:
+    M, K = x.shape
+    N = weight.shape[0]
+    fn = _fn("gemm_skinny", "kb_gemm_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(
+        fn(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), out.data_ptr(),
+           1 if out.dtype == torch.float32 else 0, out.stride(0), M, N, K, 1 if gated else 0, _stream()),
+        "gemm_skinny",
+    )
+
+
+def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: object) -> None:
+    """out = silu(x @ Wg.T) * (x @ Wu.T) with ``weight_gate_up`` = [Wg; Wu] stacked by rows.
+
+    For a few bf16 token rows this is one weight-streaming kernel with the gate in
+    its epilogue; otherwise a product into ``scratch.buffer(...)`` and the gate kernel.
+    """
+    _need_cuda("linear_swiglu", x, weight_gate_up, out)
+    M = x.shape[0]
+    two_i = weight_gate_up.shape[0]
+    if two_i % 2 or out.shape != (M, two_i // 2):
+        raise KernelError("linear_swiglu: shape mismatch")
+    if M == 0:
+        return
+    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and _skinny_ok(x, weight_gate_up, None, out):
+        _gemm_skinny(x, weight_gate_up, None, out, gated=True)
+        return
+    gate_up = scratch.buffer("ffn.gate_up", M, two_i, x.dtype)
+    linear(x, weight_gate_up, None, gate_up)
+    swiglu(gate_up, out)
 
 
 # ----------------------------------------------------------------------------- sampling
@@ -513,6 +568,7 @@ __all__ = [
     "embedding",
     "gather_rows",
     "linear",
+    "linear_swiglu",
     "paged_attention_generic",
     "qk_norm_rope_kv_write",
     "rmsnorm",

@@ -34,6 +34,7 @@ LIBRARIES: dict[str, list[str]] = {
     "attention_mma": [],
     "attention_decode_static": [],
     "gemm_f32": [],
+    "gemm_skinny": [],
     "sampling": [],
 }
 

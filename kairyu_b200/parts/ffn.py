@@ -55,10 +55,8 @@ class SwiGLU(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         tokens = x.shape[0]
         ws = ctx.workspace
-        gate_up = ws.buffer("ffn.gate_up", tokens, 2 * self.intermediate_size, self.dtype)
-        kernels.linear(x, self.w_gate_up, None, gate_up)
         hidden = ws.buffer("ffn.hidden", tokens, self.intermediate_size, self.dtype)
-        kernels.swiglu(gate_up, hidden)
+        kernels.linear_swiglu(x, self.w_gate_up, hidden, ws)
         out = ws.buffer("ffn.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(hidden, self.w_down, None, out)
         return out

@@ -149,6 +149,59 @@ def test_linear_bf16(M, N, K):
     close(out32, expected, 1e-4 * math.sqrt(K / 64), rtol=1e-4)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(331, 144), (96, 64), (6144, 4096), (40, 16), (4096, 14336), (331, 120)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_weight_streaming_product_for_few_rows(M, N, K, bias):
+    """csrc/gemm_skinny.cu through ``linear`` (M <= 16): rows beyond M, weight rows beyond N and
+    k beyond K (K not a multiple of 32) must not leak in."""
+    x = rand(M, K, dtype=torch.bfloat16, seed=50)
+    w = rand(N, K, dtype=torch.bfloat16, seed=51, scale=0.05)
+    b = rand(N, dtype=torch.bfloat16, seed=52) if bias else None
+    expected = x.float() @ w.float().t() + (b.float() if bias else 0)
+    launches = kernels().launch_count
+    for dtype, atol, rtol in ((torch.float32, 2e-4 * math.sqrt(K / 64), 1e-4), (torch.bfloat16, 4e-3 * math.sqrt(K / 64), 1e-2)):
+        out = torch.full((M, N), 7.0, dtype=dtype, device=DEV)
+        kernels().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out)
+        close(out, expected, atol, rtol)
+    if K % 16 == 0:  # this package's kernel ran, not the library product (which takes the other sizes)
+        assert kernels().launch_count == launches + 2
+
+
+@pytest.mark.parametrize("M", [1, 8, 13])
+@pytest.mark.parametrize("I,K", [(200, 144), (14336, 4096), (24, 64), (200, 120)])
+def test_weight_streaming_product_with_the_gate_fused(M, I, K):
+    x = rand(M, K, dtype=torch.bfloat16, seed=53)
+    w = rand(2 * I, K, dtype=torch.bfloat16, seed=54, scale=0.05)
+    y = x.float() @ w.float().t()
+    g, u = y[:, :I], y[:, I:]
+    expected = g / (1 + torch.exp(-g)) * u
+    out = torch.full((M, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    from kairyu_b200.engine.workspace import Workspace
+
+    kernels().linear_swiglu(x.to(DEV), w.to(DEV), out, Workspace(DEV))
+    close(out, expected, 4e-3 * math.sqrt(K / 64), 1e-2)
+
+
+def test_gated_product_for_many_rows_uses_the_two_kernel_path():
+    from kairyu_b200.engine.workspace import Workspace
+
+    M, I, K = 70, 160, 96
+    x = rand(M, K, dtype=torch.bfloat16, seed=55)
+    w = rand(2 * I, K, dtype=torch.bfloat16, seed=56, scale=0.05)
+    expected = torch.empty(M, I, dtype=torch.bfloat16)
+    ref.linear_swiglu(x, w, expected, None)
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    kernels().linear_swiglu(x.to(DEV), w.to(DEV), out, Workspace(DEV))
+    close(out, expected, 2e-3, 1e-2)
+    x32, w32 = x.float(), w.float()
+    out32 = torch.empty(M, I, device=DEV)
+    kernels().linear_swiglu(x32.to(DEV), w32.to(DEV), out32, Workspace(DEV))
+    ref32 = torch.empty(M, I)
+    ref.linear_swiglu(x32, w32, ref32, None)
+    close(out32, ref32, 1e-5, 1e-5)
+
+
 # ------------------------------------------------------------------ rope + cache write
 
 

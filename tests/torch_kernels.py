@@ -149,6 +149,15 @@ def linear(x, weight, bias, out):
     out.copy_(y.to(out.dtype))
 
 
+def linear_swiglu(x, weight_gate_up, out, scratch):
+    inter = weight_gate_up.shape[0] // 2
+    y = x.float() @ weight_gate_up.float().t()
+    g, u = y[:, :inter], y[:, inter:]
+    if x.dtype != torch.float32:  # the two-kernel path rounds the product before the gate
+        g, u = g.to(x.dtype).float(), u.to(x.dtype).float()
+    out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+
 def argmax(logits, out):
     out.copy_(logits.argmax(dim=-1).to(torch.int32))
 
@@ -181,7 +190,7 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
 
 _NAMES = [
     "embedding", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
-    "attention_mma_supported", "attention_prefill_mma", "attention_decode_mma", "linear", "argmax",
+    "attention_mma_supported", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
     "edit_logits", "sample",
 ]
 
