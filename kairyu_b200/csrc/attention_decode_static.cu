@@ -59,7 +59,7 @@ KB_EXPORT int kb_attention_decode_mma_static(const void* q, int q_stride, void* 
     int rc;
 #define ARGS (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
              seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, Hkv, D,        \
-             page_size, num_pages, scale, window, (int)num_splits, part_o, part_ml, stream
+             page_size, num_pages, scale, window, (int)num_splits, part_o, part_ml, (int*)nullptr, stream
     switch (dp) {
         case 32: rc = launch_decode<32>(ARGS); break;
         case 64: rc = launch_decode<64>(ARGS); break;

@@ -13,9 +13,9 @@
 // inputs and the output here.
 //
 // How.  The scratch is a file-scope `static __device__` array inside the library,
-// KB_STATIC_SCRATCH_FLOATS floats (8 MiB) per GPU that loads the library, held
+// KB_STATIC_SCRATCH_FLOATS floats (16 MiB) per GPU that loads the library, held
 // until the process exits.  The call needs
-//     num_rows * Hq * num_splits * (D + 2)   floats,   num_splits = ceil(max_seq_len / 256),
+//     num_rows * Hq * num_splits * (D + 2)   floats,   num_splits = ceil(max_seq_len / 128),
 // and returns KB_ERR_SCRATCH_TOO_SMALL (-4) without launching anything when that
 // exceeds the array (8 rows of 32 heads of 128 at 8,192 tokens of context fit;
 // 64 such rows fit up to 1,024 tokens).
@@ -35,7 +35,7 @@
 
 #include <cuda_runtime.h>
 
-#define KB_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
+#define KB_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
 #define KB_ERR_SCRATCH_TOO_SMALL (-4)
 #define KB_ERR_SETUP_FAILED (-5)
 

@@ -32,7 +32,7 @@ KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, in
                                       const int* block_table, int max_pages, const int* decode_rows,
                                       const int* decode_tokens, int num_rows, int Hq, int Hkv, int D,
                                       int page_size, int num_pages, float scale, int window,
-                                      int num_splits, float* part_o, float* part_ml,
+                                      int num_splits, float* part_o, float* part_ml, int* flag,
                                       cudaStream_t stream) {
     if (num_rows == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !seq_lens || !block_table || !decode_rows || !decode_tokens || !part_o || !part_ml) return KB_ERR_NULL;
@@ -42,7 +42,7 @@ KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, in
     int rc;
 #define ARGS (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
              seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, Hkv, D,        \
-             page_size, num_pages, scale, window, num_splits, part_o, part_ml, stream
+             page_size, num_pages, scale, window, num_splits, part_o, part_ml, flag, stream
     switch (dp) {
         case 32: rc = launch_decode<32>(ARGS); break;
         case 64: rc = launch_decode<64>(ARGS); break;

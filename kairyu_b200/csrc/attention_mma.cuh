@@ -19,9 +19,17 @@
 #define TILE_M 64
 #define TILE_N 64
 #define MMA_THREADS 128
-#define DEC_SPLIT 256
-#define DEC_STAGES 3  // cp.async pipeline depth of the split-KV kernel: two tiles in flight while one is used
+#define DEC_SPLIT 128  // keys per split of the split-KV kernel
+#define DEC_STAGES 2  // tile buffers of the split-KV kernel: a split's tiles are all requested up front
 #define LOG2E 1.4426950408889634f
+
+// Rows of a shared tile are DP + 8 elements apart: the 16 extra bytes put eight
+// consecutive rows in distinct bank groups, so ldmatrix is conflict-free.
+template <int DP>
+struct Tile {
+    static constexpr int STRIDE = DP + 8;
+    static constexpr int CHUNKS = DP / 8;  // 16-byte chunks per row
+};
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -36,6 +44,74 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+
+// ---- mbarrier + bulk copy (the TMA unit moves whole key rows; one instruction per row)
+#define KB_FLAG_TIMEOUT 16
+#define MBAR_SPIN_LIMIT (1u << 20)
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Waits for the phase with the given parity to complete; gives up after a bounded
+// number of polls and returns false (the caller raises a flag and leaves).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = MBAR_SPIN_LIMIT) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < limit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+// global -> shared, `bytes` a multiple of 16, both addresses 16-byte aligned; completion is
+// counted on the mbarrier.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// One bulk copy per key row: thread t < 64 brings key row t of the K tile, thread
+// 64 + t the same row of the V tile.  A row that is outside [key_lo, key_end) or on an
+// absent page is read from position 0 of the reserved page instead: its score is masked,
+// and what stands there is finite, so the byte count of a tile is always the same.
+template <int DP>
+__device__ __forceinline__ void load_kv_rows_bulk(__nv_bfloat16* tile_k, __nv_bfloat16* tile_v,
+                                                  const __nv_bfloat16* __restrict__ k_cache,
+                                                  const __nv_bfloat16* __restrict__ v_cache,
+                                                  const int* __restrict__ table, int max_pages, int num_pages,
+                                                  int page_size, int page_shift, int Hkv, int kvh, int D,
+                                                  int key0, int key_lo, int key_end, uint64_t* bar) {
+    if (threadIdx.x == 0) mbar_arrive_expect_tx(bar, (uint32_t)(2 * TILE_N * D * sizeof(__nv_bfloat16)));
+    const int r = threadIdx.x & (TILE_N - 1);
+    const bool is_v = threadIdx.x >= TILE_N;
+    const int key = key0 + r;
+    size_t offset = (size_t)kvh * D;  // page 0, position 0
+    if (key >= key_lo && key < key_end) {
+        const int page_index = page_shift >= 0 ? (key >> page_shift) : (key / page_size);
+        const int page = page_index < max_pages ? table[page_index] : -1;
+        if (page >= 0 && page < num_pages) {
+            const int within = key - page_index * page_size;
+            offset = (((size_t)page * page_size + within) * Hkv + kvh) * D;
+        }
+    }
+    bulk_copy_g2s((is_v ? tile_v : tile_k) + r * Tile<DP>::STRIDE, (is_v ? v_cache : k_cache) + offset,
+                  (uint32_t)(D * sizeof(__nv_bfloat16)), bar);
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -59,13 +135,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Rows of a shared tile are DP + 8 elements apart: the 16 extra bytes put eight
-// consecutive rows in distinct bank groups, so ldmatrix is conflict-free.
-template <int DP>
-struct Tile {
-    static constexpr int STRIDE = DP + 8;
-    static constexpr int CHUNKS = DP / 8;  // 16-byte chunks per row
-};
 
 // Copies the 64 keys and values starting at absolute key `key0` of one KV head into
 // a K tile and a V tile (row r of a tile = key key0 + r).  Keys outside
@@ -324,7 +393,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               int max_pages, const int* __restrict__ decode_rows,
                               const int* __restrict__ decode_tokens, int Hq, int Hkv, int D,
                               int page_size, int num_pages, float scale, int window, int num_splits,
-                              float* __restrict__ part_o, float* __restrict__ part_ml) {
+                              float* __restrict__ part_o, float* __restrict__ part_ml, int* flag) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int STRIDE = Tile<DP>::STRIDE;
     constexpr int CH = Tile<DP>::CHUNKS;
@@ -333,6 +402,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // 16 rows
     __nv_bfloat16* sK = sQ + 16 * STRIDE;                             // DEC_STAGES stages of 64 keys
     __nv_bfloat16* sV = sK + DEC_STAGES * TILE_N * STRIDE;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sV + DEC_STAGES * TILE_N * STRIDE);  // one per stage
 
     const int slot = blockIdx.x;
     const int kvh = blockIdx.y;
@@ -359,16 +429,31 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         const __nv_bfloat16* src = valid ? q + (size_t)token * q_stride + (size_t)(kvh * G + r) * D + col : q;
         cp_async16(sQ + r * STRIDE + col, src, valid);
     }
+    cp_async_commit();  // the queries
     const int first_tile = key0 / TILE_N;
     const int last_tile = (key_end - 1) / TILE_N;
     const int page_shift = shift_of(page_size);
-    // prologue: the first DEC_STAGES-1 tiles (one commit group each, empty past the end)
+    if (threadIdx.x == 0) {
 #pragma unroll
-    for (int ahead = 0; ahead < DEC_STAGES - 1; ++ahead) {
+        for (int st = 0; st < DEC_STAGES; ++st) mbar_init(full_bar + st, 1);
+        fence_barrier_init();
+    }
+    if (D < DP) {  // columns the copies never write must not hold NaN bit patterns
+        for (int idx = threadIdx.x; idx < 2 * DEC_STAGES * TILE_N * (DP - D); idx += MMA_THREADS) {
+            const int r = idx / (DP - D);
+            const int col = D + idx % (DP - D);
+            sK[r * STRIDE + col] = __float2bfloat16_rn(0.0f);  // sK and sV are one contiguous run of rows
+        }
+    }
+    fence_proxy_async();
+    __syncthreads();
+    // prologue: request the first DEC_STAGES tiles (a whole split when DEC_SPLIT == DEC_STAGES * TILE_N)
+#pragma unroll
+    for (int ahead = 0; ahead < DEC_STAGES; ++ahead) {
         if (first_tile + ahead <= last_tile)
-            load_kv_tiles<DP>(sK + ahead * TILE_N * STRIDE, sV + ahead * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
-                              num_pages, page_size, page_shift, Hkv, kvh, D, (first_tile + ahead) * TILE_N, key_lo_all, key_end);
-        cp_async_commit();
+            load_kv_rows_bulk<DP>(sK + ahead * TILE_N * STRIDE, sV + ahead * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
+                                  num_pages, page_size, page_shift, Hkv, kvh, D, (first_tile + ahead) * TILE_N, key_lo_all,
+                                  key_end, full_bar + ahead);
     }
 
     uint32_t qf[KSTEPS][4];
@@ -380,16 +465,14 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     const float sl2 = scale * LOG2E;
 
     int stage = 0;
+    bool timed_out = false;
     for (int kt = first_tile; kt <= last_tile; ++kt) {
-        cp_async_wait<DEC_STAGES - 2>();  // tile kt has landed
-        __syncthreads();                  // ... for every thread, and tile kt-1's stage is free
-        {
-            const int next = kt + DEC_STAGES - 1;
-            const int next_stage = (stage + DEC_STAGES - 1) % DEC_STAGES;
-            if (next <= last_tile)
-                load_kv_tiles<DP>(sK + next_stage * TILE_N * STRIDE, sV + next_stage * TILE_N * STRIDE, k_cache, v_cache, table,
-                                  max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, next * TILE_N, key_lo_all, key_end);
-            cp_async_commit();
+        const int use = (kt - first_tile) / DEC_STAGES;  // how often this stage has been filled before
+        const bool landed = mbar_wait(full_bar + stage, use & 1);
+        if (kt == first_tile) cp_async_wait<0>();  // the queries
+        if (__syncthreads_or(!landed)) {  // every thread has tile kt (and the queries)
+            timed_out = true;
+            break;
         }
         if (kt == first_tile) {
 #pragma unroll
@@ -475,9 +558,25 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             mma_16816(o[2 * dp], a, b[0], b[1]);
             mma_16816(o[2 * dp + 1], a, b[2], b[3]);
         }
+        if (kt + DEC_STAGES <= last_tile) {  // more tiles than buffers: refill this one once everyone is done with it
+            __syncthreads();
+            load_kv_rows_bulk<DP>(sK + stage * TILE_N * STRIDE, sV + stage * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
+                                  num_pages, page_size, page_shift, Hkv, kvh, D, (kt + DEC_STAGES) * TILE_N, key_lo_all, key_end,
+                                  full_bar + stage);
+        }
         stage = (stage + 1) % DEC_STAGES;
     }
-    cp_async_wait<0>();
+    if (timed_out) {
+        // A copy did not land in time.  Say so, give the copies still in flight one more
+        // bounded wait (they target this block's shared memory), and leave without a result.
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+        cp_async_wait<0>();
+        for (int st = 0; st < DEC_STAGES; ++st) {
+            mbar_wait(full_bar + st, 0, 1u << 10);
+            mbar_wait(full_bar + st, 1, 1u << 10);
+        }
+        return;
+    }
     __syncthreads();  // every warp is done with the tiles before they become the merge buffer
 
     // combine the four warps (in warp order) through shared memory
@@ -486,17 +585,16 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float* sO = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][DP]
-    float* sM = sO + 4 * 16 * DP;                     // [4][16]
+    constexpr int OSTRIDE = DP + 8;                   // fp32 row stride of the merge buffer
+    float* sO = reinterpret_cast<float*>(smem_raw);   // [4 warps][16 rows][OSTRIDE]
+    float* sM = sO + 4 * 16 * OSTRIDE;                // [4][16]
     float* sL = sM + 4 * 16;                          // [4][16]
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) {
         const int col = dt * 8 + tq * 2;
-        float* base = sO + (size_t)warp * 16 * DP;
-        base[g * DP + col] = o[dt][0];
-        base[g * DP + col + 1] = o[dt][1];
-        base[(g + 8) * DP + col] = o[dt][2];
-        base[(g + 8) * DP + col + 1] = o[dt][3];
+        float* base = sO + (size_t)warp * 16 * OSTRIDE;
+        *reinterpret_cast<float2*>(base + g * OSTRIDE + col) = make_float2(o[dt][0], o[dt][1]);
+        *reinterpret_cast<float2*>(base + (g + 8) * OSTRIDE + col) = make_float2(o[dt][2], o[dt][3]);
     }
     if (tq == 0) {
         sM[warp * 16 + g] = m_run[0];
@@ -516,7 +614,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int w = 0; w < 4; ++w) {
             const float mw = sM[w * 16 + r];
             const float f = mw == -INFINITY ? 0.0f : exp2f(mw - big);
-            acc += sO[((size_t)w * 16 + r) * DP + d] * f;
+            acc += sO[((size_t)w * 16 + r) * OSTRIDE + d] * f;
             den += sL[w * 16 + r] * f;
         }
         const size_t pidx = ((size_t)slot * Hq + (kvh * G + r)) * num_splits + split;
@@ -566,8 +664,8 @@ static size_t prefill_smem() { return (size_t)(TILE_M + 4 * TILE_N) * Tile<DP>::
 
 template <int DP>
 static size_t decode_smem() {
-    const size_t tiles = (size_t)(16 + 2 * DEC_STAGES * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16);
-    const size_t merge = (size_t)(4 * 16 * DP + 2 * 4 * 16) * sizeof(float);
+    const size_t tiles = (size_t)(16 + 2 * DEC_STAGES * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16) + DEC_STAGES * sizeof(uint64_t);
+    const size_t merge = (size_t)(4 * 16 * (DP + 8) + 2 * 4 * 16) * sizeof(float);
     return tiles > merge ? tiles : merge;
 }
 
@@ -601,14 +699,14 @@ static int launch_decode(const __nv_bfloat16* q, int q_stride, const __nv_bfloat
                          const __nv_bfloat16* v_cache, const int* seq_lens, const int* block_table,
                          int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows,
                          int Hq, int Hkv, int D, int page_size, int num_pages, float scale, int window,
-                         int num_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                         int num_splits, float* part_o, float* part_ml, int* flag, cudaStream_t stream) {
     const size_t smem = decode_smem<DP>();
     cudaError_t e = cudaFuncSetAttribute(attention_decode_split_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(num_rows, Hkv, num_splits);
     attention_decode_split_kernel<DP><<<grid, MMA_THREADS, smem, stream>>>(
         q, q_stride, k_cache, v_cache, seq_lens, block_table, max_pages, decode_rows, decode_tokens,
-        Hq, Hkv, D, page_size, num_pages, scale, window, num_splits, part_o, part_ml);
+        Hq, Hkv, D, page_size, num_pages, scale, window, num_splits, part_o, part_ml, flag);
     return kb_launch_result();
 }
 

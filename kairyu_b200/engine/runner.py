@@ -398,4 +398,6 @@ class ModelRunner:
                 reasons.append("a row index outside the batch")
             if flag & 8:
                 reasons.append("a position outside the rotary table")
+            if flag & 16:
+                reasons.append("a copy into shared memory did not complete within its wait limit")
             raise StepError("a kernel refused an index: " + "; ".join(reasons))

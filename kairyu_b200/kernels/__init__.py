@@ -27,6 +27,7 @@ FLAG_BAD_PAGE = 1
 FLAG_BAD_TOKEN = 2
 FLAG_BAD_ROW = 4
 FLAG_BAD_POS = 8
+FLAG_TIMEOUT = 16
 
 _CODES = {
     -1: "bad argument",
@@ -288,7 +289,7 @@ def paged_attention_generic(
     )
 
 
-DECODE_SPLIT = 256  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
+DECODE_SPLIT = 128  # keys per split of the split-KV kernel (csrc/attention_mma.cu: DEC_SPLIT)
 
 
 def attention_mma_supported(head_dim: int, num_q_heads: int, num_kv_heads: int) -> bool:
@@ -369,6 +370,7 @@ def attention_decode_mma(
     scale: float,
     window: int = 0,
     workspace: object,
+    flag: Optional[torch.Tensor] = None,
 ) -> None:
     """Split-KV attention of rows that carry one token (bf16), then the merge.
 
@@ -388,14 +390,14 @@ def attention_decode_mma(
     fn = _fn(
         "attention_mma",
         "kb_attention_decode_mma",
-        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     )
     _check(
         fn(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
             decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
-            float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _stream(),
+            float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(flag), _stream(),
         ),
         what,
         launches=2,

@@ -99,6 +99,7 @@ def run_paged_attention(
             scale=scale,
             window=window,
             workspace=ctx.workspace,
+            flag=ctx.error_flag,
         )
 
 

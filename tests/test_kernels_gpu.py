@@ -412,7 +412,7 @@ def test_mma_attention_random(Hq, Hkv, D, page_size, window, workspace):
     close(out, expected, 2e-2)
 
 
-@pytest.mark.parametrize("hot_key", [0, 15, 16, 17, 63, 64, 255, 256, 257, 511, 512, 640, 699])
+@pytest.mark.parametrize("hot_key", [0, 15, 16, 17, 63, 64, 127, 128, 129, 255, 256, 257, 511, 512, 640, 699])
 @pytest.mark.parametrize("chunk", [1, 2, 61])
 def test_mma_attention_finds_one_far_key(hot_key, chunk, workspace):
     """One key among 700 carries the softmax; the output must be its value."""

@@ -72,7 +72,7 @@ def _call_ordinary(case, out):
 
 def test_static_entry_matches_the_ordinary_one_twice_in_a_row():
     library, function = _static_entry()
-    assert library.kb_attention_decode_static_capacity() == 2 * 1024 * 1024
+    assert library.kb_attention_decode_static_capacity() == 4 * 1024 * 1024
     # two calls in a row with different shapes: the second finds the first one's partials in the shared scratch
     cases = [_case([700, 1, 255, 257, 300], 8, 2, 64, 16, seed=1), _case([90, 513, 40], 6, 3, 32, 8, seed=2)]
     for case in cases:
@@ -93,9 +93,9 @@ def test_static_entry_refuses_what_its_scratch_cannot_hold():
     _, function = _static_entry()
     case = _case([64] * 4, 8, 2, 64, 16, seed=3)
     out = torch.zeros(case["count"], case["Hq"] * case["D"], dtype=torch.bfloat16, device="cuda")
-    case["max_seq_len"] = 4_000_000  # 4 rows * 8 heads * 15,625 splits * 66 floats: far beyond 2 Mi floats
+    case["max_seq_len"] = 4_000_000  # 4 rows * 8 heads * 31,250 splits * 66 floats: far beyond 4 Mi floats
     assert _call_static(function, case, out) in (ERR_SCRATCH_TOO_SMALL, -1)
-    case["max_seq_len"] = 300_000  # 1,172 splits: a valid grid, but 2.5 Mi floats
+    case["max_seq_len"] = 300_000  # 2,344 splits: a valid grid, but 4.9 Mi floats
     assert _call_static(function, case, out) == ERR_SCRATCH_TOO_SMALL
     torch.cuda.synchronize()
     assert float(out.float().abs().max()) == 0.0  # nothing ran
