@@ -6,7 +6,7 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
                                        const int* qo_indptr, const int* seq_lens,
                                        const int* block_table, int max_pages, const int* tile_rows,
                                        const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
-                                       int page_size, int num_pages, float scale, int window,
+                                       int page_size, int num_pages, float scale, int window, int* flag,
                                        cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
@@ -15,12 +15,12 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
     const int dp = padded_dim(D);
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache, \
              (const __nv_bfloat16*)v_cache, qo_indptr, seq_lens, block_table, max_pages, tile_rows,       \
-             tile_starts, num_tiles, Hq, Hkv, D, page_size, num_pages, scale, window, stream
+             tile_starts, num_tiles, Hq, Hkv, D, page_size, num_pages, scale, window, flag, stream
     switch (dp) {
-        case 32: return launch_prefill<32>(ARGS);
-        case 64: return launch_prefill<64>(ARGS);
-        case 128: return launch_prefill<128>(ARGS);
-        case 256: return launch_prefill<256>(ARGS);
+        case 32: return launch_prefill<32, 2>(ARGS);
+        case 64: return launch_prefill<64, 2>(ARGS);
+        case 128: return launch_prefill<128, 2>(ARGS);
+        case 256: return launch_prefill<256, 1>(ARGS);
         default: return KB_ERR_UNSUPPORTED_SIZE;
     }
 #undef ARGS
@@ -59,3 +59,6 @@ KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, in
 }
 
 KB_EXPORT int kb_attention_decode_split_size() { return DEC_SPLIT; }
+
+// Queries per tile the prefill kernel expects in its tile list, for a head size.
+KB_EXPORT int kb_attention_prefill_tile_rows(int D) { return prefill_tile_rows(D); }

@@ -16,7 +16,6 @@
 #pragma once
 #include "common.cuh"
 
-#define TILE_M 64
 #define TILE_N 64
 #define MMA_THREADS 128
 #define DEC_SPLIT 128  // keys per split of the split-KV kernel
@@ -179,8 +178,13 @@ __device__ __forceinline__ int shift_of(int page_size) {
     return (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 }
 
-// ------------------------------------------------------------------ prefill: 64-query tiles
-template <int DP>
+// ------------------------------------------------------------------ prefill: query tiles
+// grid (tiles, Hq).  A tile is 64*MT consecutive queries of one row's portion (MT = 2 up to
+// a padded head size of 128, else 1); warp w owns MT 16-row slices of it and every K/V
+// fragment it reads from shared memory feeds MT MMAs.  Keys stream through two 64-key
+// buffers, one bulk copy per key row (see load_kv_rows_bulk), the next tile requested as
+// soon as its buffer is free.  Tiles wholly below the diagonal skip the mask.
+template <int DP, int MT>
 __global__ void __launch_bounds__(MMA_THREADS)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16* __restrict__ out,
                          int out_stride, const __nv_bfloat16* __restrict__ k_cache,
@@ -188,15 +192,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ seq_lens, const int* __restrict__ block_table,
                          int max_pages, const int* __restrict__ tile_rows,
                          const int* __restrict__ tile_starts, int Hq, int Hkv, int D, int page_size,
-                         int num_pages, float scale, int window) {
+                         int num_pages, float scale, int window, int* flag) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int STRIDE = Tile<DP>::STRIDE;
     constexpr int CH = Tile<DP>::CHUNKS;
     constexpr int KSTEPS = DP / 16;
     constexpr int DTILES = DP / 8;
+    constexpr int ROWS = 64 * MT;  // queries per tile
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sK = sQ + TILE_M * STRIDE;               // 2 stages
-    __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;           // 2 stages
+    __nv_bfloat16* sK = sQ + ROWS * STRIDE;                 // 2 buffers
+    __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;           // 2 buffers
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sV + 2 * TILE_N * STRIDE);
 
     const int tile = blockIdx.x;
     const int h = blockIdx.y;
@@ -206,173 +212,229 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int tok0 = qo_indptr[row];
     const int chunk_len = qo_indptr[row + 1] - tok0;
     const int seq_len = seq_lens[row];
-    const int chunk_pos = seq_len - chunk_len;  // absolute position of the chunk's first token
+    const int chunk_pos = seq_len - chunk_len;  // absolute position of the portion's first token
     const int* table = block_table + (size_t)row * max_pages;
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2;      // row within 8
     const int tq = lane & 3;      // column pair
 
-    const int rows_here = min(TILE_M, chunk_len - q0);
+    const int rows_here = min(ROWS, chunk_len - q0);
     const int first_pos = chunk_pos + q0;
     const int last_pos = first_pos + rows_here - 1;
     const int key_end = last_pos + 1;  // causal bound of the tile (<= seq_len)
     const int key_lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
     const int first_kt = key_lo / TILE_N;
     const int last_kt = (key_end - 1) / TILE_N;
+    const int page_shift = shift_of(page_size);
 
-    // Q tile (rows beyond the chunk and columns beyond D are zero)
-    for (int c = threadIdx.x; c < TILE_M * CH; c += MMA_THREADS) {
+    // Q tile (rows beyond the portion and columns beyond D are zero)
+    for (int c = threadIdx.x; c < ROWS * CH; c += MMA_THREADS) {
         const int r = c / CH;
         const int col = (c % CH) * 8;
         const bool valid = r < rows_here && col < D;
         const __nv_bfloat16* src = valid ? q + (size_t)(tok0 + q0 + r) * q_stride + (size_t)h * D + col : q;
         cp_async16(sQ + r * STRIDE + col, src, valid);
     }
-    const int page_shift = shift_of(page_size);
-    load_kv_tiles<DP>(sK, sV, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, first_kt * TILE_N, key_lo, key_end);
     cp_async_commit();
-
-    uint32_t qf[KSTEPS][4];
-    float o[DTILES][4];
+    if (threadIdx.x == 0) {
+        mbar_init(full_bar, 1);
+        mbar_init(full_bar + 1, 1);
+        fence_barrier_init();
+    }
+    if (D < DP) {  // columns the copies never write must not hold NaN bit patterns
+        for (int idx = threadIdx.x; idx < 4 * TILE_N * (DP - D); idx += MMA_THREADS) {
+            const int r = idx / (DP - D);
+            sK[r * STRIDE + D + idx % (DP - D)] = __float2bfloat16_rn(0.0f);  // sK and sV are one run of rows
+        }
+    }
+    fence_proxy_async();
+    __syncthreads();
 #pragma unroll
-    for (int i = 0; i < DTILES; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    float m_run[2] = {-INFINITY, -INFINITY};
-    float l_run[2] = {0.0f, 0.0f};
+    for (int ahead = 0; ahead < 2; ++ahead) {
+        if (first_kt + ahead <= last_kt)
+            load_kv_rows_bulk<DP>(sK + ahead * TILE_N * STRIDE, sV + ahead * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
+                                  num_pages, page_size, page_shift, Hkv, kvh, D, (first_kt + ahead) * TILE_N, key_lo, key_end,
+                                  full_bar + ahead);
+    }
+
+    float o[MT][DTILES][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < DTILES; ++i) { o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f; }
+    float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        m_run[mt][0] = m_run[mt][1] = -INFINITY;
+        l_run[mt][0] = l_run[mt][1] = 0.0f;
+    }
     const float sl2 = scale * LOG2E;
-    const int qpos0 = first_pos + warp * 16 + g;  // absolute position of this thread's first row
-    const int qpos1 = qpos0 + 8;
+    const int warp_row0 = warp * 16 * MT;              // first tile row of this warp
+    const int warp_pos0 = first_pos + warp_row0;       // its absolute position
 
     int stage = 0;
+    bool timed_out = false;
     for (int kt = first_kt; kt <= last_kt; ++kt) {
-        if (kt + 1 <= last_kt) {
-            load_kv_tiles<DP>(sK + (stage ^ 1) * TILE_N * STRIDE, sV + (stage ^ 1) * TILE_N * STRIDE, k_cache, v_cache, table, max_pages, num_pages, page_size, page_shift, Hkv, kvh, D, (kt + 1) * TILE_N, key_lo, key_end);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        if (kt == first_kt) {
-#pragma unroll
-            for (int ks = 0; ks < KSTEPS; ++ks) {
-                const int m = lane >> 3;
-                const int r = warp * 16 + (m & 1) * 8 + (lane & 7);
-                const int col = ks * 16 + (m >> 1) * 8;
-                ldmatrix_x4(qf[ks], sQ + r * STRIDE + col);
-            }
+        const int use = (kt - first_kt) >> 1;
+        const bool landed = mbar_wait(full_bar + stage, use & 1);
+        if (kt == first_kt) cp_async_wait<0>();  // the queries
+        if (__syncthreads_or(!landed)) {
+            timed_out = true;
+            break;
         }
         const __nv_bfloat16* tK = sK + stage * TILE_N * STRIDE;
         const __nv_bfloat16* tV = sV + stage * TILE_N * STRIDE;
 
-        // S = Q K^T for this warp's 16 queries and the tile's 64 keys
-        float s[TILE_N / 8][4];
+        // S = Q K^T: this warp's 16*MT queries against the tile's 64 keys
+        float s[MT][TILE_N / 8][4];
 #pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f; }
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < TILE_N / 8; ++nt) { s[mt][nt][0] = s[mt][nt][1] = s[mt][nt][2] = s[mt][nt][3] = 0.0f; }
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ++ks) {
+            uint32_t a[MT][4];
+            const int m = lane >> 3;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                const int r = warp_row0 + mt * 16 + (m & 1) * 8 + (lane & 7);
+                ldmatrix_x4(a[mt], sQ + r * STRIDE + ks * 16 + (m >> 1) * 8);
+            }
 #pragma unroll
             for (int np = 0; np < TILE_N / 16; ++np) {
                 uint32_t b[4];
-                const int m = lane >> 3;
                 const int key = np * 16 + (m >> 1) * 8 + (lane & 7);
-                const int col = ks * 16 + (m & 1) * 8;
-                ldmatrix_x4(b, tK + key * STRIDE + col);
-                mma_16816(s[2 * np], qf[ks], b[0], b[1]);
-                mma_16816(s[2 * np + 1], qf[ks], b[2], b[3]);
+                ldmatrix_x4(b, tK + key * STRIDE + ks * 16 + (m & 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_16816(s[mt][2 * np], a[mt], b[0], b[1]);
+                    mma_16816(s[mt][2 * np + 1], a[mt], b[2], b[3]);
+                }
             }
         }
-        // scale, mask, online softmax (log2 domain)
+        // scale, mask (only where the tile reaches the diagonal or the window's edge), online softmax
         const int key_base = kt * TILE_N + tq * 2;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool need_mask = (kt * TILE_N + TILE_N - 1 > warp_pos0) || (window > 0 && kt * TILE_N < warp_pos0 + 16 * MT - window + 1);
 #pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) {
+        for (int mt = 0; mt < MT; ++mt) {
+            const int qpos0 = warp_pos0 + mt * 16 + g;
+            const int qpos1 = qpos0 + 8;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key_base + nt * 8 + e;
-                const bool ok0 = key <= qpos0 && (window <= 0 || key > qpos0 - window);
-                const bool ok1 = key <= qpos1 && (window <= 0 || key > qpos1 - window);
-                s[nt][e] = ok0 ? s[nt][e] * sl2 : -INFINITY;
-                s[nt][2 + e] = ok1 ? s[nt][2 + e] * sl2 : -INFINITY;
-                mx0 = fmaxf(mx0, s[nt][e]);
-                mx1 = fmaxf(mx1, s[nt][2 + e]);
+            for (int nt = 0; nt < TILE_N / 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    bool ok0 = true, ok1 = true;
+                    if (need_mask) {
+                        const int key = key_base + nt * 8 + e;
+                        ok0 = key <= qpos0 && (window <= 0 || key > qpos0 - window);
+                        ok1 = key <= qpos1 && (window <= 0 || key > qpos1 - window);
+                    }
+                    s[mt][nt][e] = ok0 ? s[mt][nt][e] * sl2 : -INFINITY;
+                    s[mt][nt][2 + e] = ok1 ? s[mt][nt][2 + e] * sl2 : -INFINITY;
+                    mx0 = fmaxf(mx0, s[mt][nt][e]);
+                    mx1 = fmaxf(mx1, s[mt][nt][2 + e]);
+                }
             }
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m_run[0], mx0);
-        const float mn1 = fmaxf(m_run[1], mx1);
-        const float base0 = mn0 == -INFINITY ? 0.0f : mn0;  // a fully masked row stays at zero
-        const float base1 = mn1 == -INFINITY ? 0.0f : mn1;
-        const float alpha0 = exp2f(m_run[0] - base0);
-        const float alpha1 = exp2f(m_run[1] - base1);
-        m_run[0] = mn0;
-        m_run[1] = mn1;
-        float sum0 = 0.0f, sum1 = 0.0f;
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m_run[mt][0], mx0);
+            const float mn1 = fmaxf(m_run[mt][1], mx1);
+            const float base0 = mn0 == -INFINITY ? 0.0f : mn0;  // a fully masked row stays at zero
+            const float base1 = mn1 == -INFINITY ? 0.0f : mn1;
+            const float alpha0 = exp2f(m_run[mt][0] - base0);
+            const float alpha1 = exp2f(m_run[mt][1] - base1);
+            m_run[mt][0] = mn0;
+            m_run[mt][1] = mn1;
+            float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-        for (int nt = 0; nt < TILE_N / 8; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - base0);
-            s[nt][1] = exp2f(s[nt][1] - base0);
-            s[nt][2] = exp2f(s[nt][2] - base1);
-            s[nt][3] = exp2f(s[nt][3] - base1);
-            sum0 += s[nt][0] + s[nt][1];
-            sum1 += s[nt][2] + s[nt][3];
-        }
-        l_run[0] = l_run[0] * alpha0 + sum0;
-        l_run[1] = l_run[1] * alpha1 + sum1;
+            for (int nt = 0; nt < TILE_N / 8; ++nt) {
+                s[mt][nt][0] = exp2f(s[mt][nt][0] - base0);
+                s[mt][nt][1] = exp2f(s[mt][nt][1] - base0);
+                s[mt][nt][2] = exp2f(s[mt][nt][2] - base1);
+                s[mt][nt][3] = exp2f(s[mt][nt][3] - base1);
+                sum0 += s[mt][nt][0] + s[mt][nt][1];
+                sum1 += s[mt][nt][2] + s[mt][nt][3];
+            }
+            l_run[mt][0] = l_run[mt][0] * alpha0 + sum0;
+            l_run[mt][1] = l_run[mt][1] * alpha1 + sum1;
 #pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt) {
-            o[dt][0] *= alpha0;
-            o[dt][1] *= alpha0;
-            o[dt][2] *= alpha1;
-            o[dt][3] *= alpha1;
+            for (int dt = 0; dt < DTILES; ++dt) {
+                o[mt][dt][0] *= alpha0;
+                o[mt][dt][1] *= alpha0;
+                o[mt][dt][2] *= alpha1;
+                o[mt][dt][3] *= alpha1;
+            }
         }
         // O += P V
 #pragma unroll
         for (int kk = 0; kk < TILE_N / 16; ++kk) {
-            uint32_t a[4];
-            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-            a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-            a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+            uint32_t a[MT][4];
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                a[mt][0] = pack_bf16(s[mt][2 * kk][0], s[mt][2 * kk][1]);
+                a[mt][1] = pack_bf16(s[mt][2 * kk][2], s[mt][2 * kk][3]);
+                a[mt][2] = pack_bf16(s[mt][2 * kk + 1][0], s[mt][2 * kk + 1][1]);
+                a[mt][3] = pack_bf16(s[mt][2 * kk + 1][2], s[mt][2 * kk + 1][3]);
+            }
 #pragma unroll
             for (int dp = 0; dp < DTILES / 2; ++dp) {
                 uint32_t b[4];
                 const int m = lane >> 3;
                 const int key = kk * 16 + (m & 1) * 8 + (lane & 7);
-                const int col = dp * 16 + (m >> 1) * 8;
-                ldmatrix_x4_trans(b, tV + key * STRIDE + col);
-                mma_16816(o[2 * dp], a, b[0], b[1]);
-                mma_16816(o[2 * dp + 1], a, b[2], b[3]);
+                ldmatrix_x4_trans(b, tV + key * STRIDE + dp * 16 + (m >> 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma_16816(o[mt][2 * dp], a[mt], b[0], b[1]);
+                    mma_16816(o[mt][2 * dp + 1], a[mt], b[2], b[3]);
+                }
             }
         }
-        __syncthreads();
+        if (kt + 2 <= last_kt) {  // this buffer's next tile, once every warp is done with it
+            __syncthreads();
+            load_kv_rows_bulk<DP>(sK + stage * TILE_N * STRIDE, sV + stage * TILE_N * STRIDE, k_cache, v_cache, table, max_pages,
+                                  num_pages, page_size, page_shift, Hkv, kvh, D, (kt + 2) * TILE_N, key_lo, key_end,
+                                  full_bar + stage);
+        }
         stage ^= 1;
+    }
+    if (timed_out) {
+        if (threadIdx.x == 0 && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+        cp_async_wait<0>();
+        for (int st = 0; st < 2; ++st) {
+            mbar_wait(full_bar + st, 0, 1u << 10);
+            mbar_wait(full_bar + st, 1, 1u << 10);
+        }
+        return;
     }
 
     // finish: row sums across the quad, normalise, store
-    float l0 = l_run[0], l1 = l_run[1];
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f;
-    const float inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
-    const int r0 = warp * 16 + g;
-    const int r1 = r0 + 8;
 #pragma unroll
-    for (int dt = 0; dt < DTILES; ++dt) {
-        const int col = dt * 8 + tq * 2;
-        if (col < D) {
-            if (r0 < rows_here) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][0] * inv0, o[dt][1] * inv0);
-                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r0) * out_stride + (size_t)h * D + col) = v;
-            }
-            if (r1 < rows_here) {
-                __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][2] * inv1, o[dt][3] * inv1);
-                *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r1) * out_stride + (size_t)h * D + col) = v;
+    for (int mt = 0; mt < MT; ++mt) {
+        float l0 = l_run[mt][0], l1 = l_run[mt][1];
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f;
+        const float inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+        const int r0 = warp_row0 + mt * 16 + g;
+        const int r1 = r0 + 8;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) {
+            const int col = dt * 8 + tq * 2;
+            if (col < D) {
+                if (r0 < rows_here) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(o[mt][dt][0] * inv0, o[mt][dt][1] * inv0);
+                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r0) * out_stride + (size_t)h * D + col) = v;
+                }
+                if (r1 < rows_here) {
+                    __nv_bfloat162 v = __floats2bfloat162_rn(o[mt][dt][2] * inv1, o[mt][dt][3] * inv1);
+                    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)(tok0 + q0 + r1) * out_stride + (size_t)h * D + col) = v;
+                }
             }
         }
     }
@@ -659,8 +721,10 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o,
 }
 
 // ------------------------------------------------------------------ host-side launchers
-template <int DP>
-static size_t prefill_smem() { return (size_t)(TILE_M + 4 * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16); }
+template <int DP, int MT>
+static size_t prefill_smem() {
+    return (size_t)(64 * MT + 4 * TILE_N) * Tile<DP>::STRIDE * sizeof(__nv_bfloat16) + 2 * sizeof(uint64_t);
+}
 
 template <int DP>
 static size_t decode_smem() {
@@ -677,20 +741,23 @@ static int padded_dim(int D) {
     return 256;
 }
 
-template <int DP>
+// Queries per tile of the prefill kernel for a head size: 128 up to a padded size of 128, else 64.
+static int prefill_tile_rows(int D) { return padded_dim(D) <= 128 ? 128 : 64; }
+
+template <int DP, int MT>
 static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int out_stride,
                           const __nv_bfloat16* k_cache, const __nv_bfloat16* v_cache,
                           const int* qo_indptr, const int* seq_lens, const int* block_table,
                           int max_pages, const int* tile_rows, const int* tile_starts, int num_tiles,
                           int Hq, int Hkv, int D, int page_size, int num_pages, float scale,
-                          int window, cudaStream_t stream) {
-    const size_t smem = prefill_smem<DP>();
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                          int window, int* flag, cudaStream_t stream) {
+    const size_t smem = prefill_smem<DP, MT>();
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(num_tiles, Hq);
-    attention_prefill_kernel<DP><<<grid, MMA_THREADS, smem, stream>>>(
+    attention_prefill_kernel<DP, MT><<<grid, MMA_THREADS, smem, stream>>>(
         q, q_stride, out, out_stride, k_cache, v_cache, qo_indptr, seq_lens, block_table, max_pages,
-        tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window);
+        tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
     return kb_launch_result();
 }
 

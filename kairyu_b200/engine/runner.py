@@ -26,7 +26,7 @@ from kairyu_b200.cache.storage import CacheStorage
 from kairyu_b200.engine.workspace import Workspace
 from kairyu_b200.parts.base import CacheView, StepContext
 
-ATTENTION_TILE_M = 64  # queries per tile of the prefill attention kernel
+ATTENTION_TILE_SIZES = (64, 128)  # query-tile granularities the attention kernels may ask for
 
 
 @dataclass
@@ -156,8 +156,8 @@ class ModelRunner:
         write_from: list[int] = []
         state_slots: list[int] = []
         want: list[int] = []
-        tile_rows: list[int] = []
-        tile_starts: list[int] = []
+        tile_rows: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
+        tile_starts: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
         decode_rows: list[int] = []
         decode_tokens: list[int] = []
         for row, (entry, start, seq_len) in enumerate(rows):
@@ -176,9 +176,10 @@ class ModelRunner:
                 decode_rows.append(row)
                 decode_tokens.append(base)
             else:
-                for tile_start in range(0, count, ATTENTION_TILE_M):
-                    tile_rows.append(row)
-                    tile_starts.append(tile_start)
+                for size in ATTENTION_TILE_SIZES:
+                    for tile_start in range(0, count, size):
+                        tile_rows[size].append(row)
+                        tile_starts[size].append(tile_start)
         for row in range(num_rows, padded_rows):  # padding rows of a replayed graph
             base = len(token_ids)
             token_ids.append(0)
@@ -210,8 +211,8 @@ class ModelRunner:
             "write_from": write_from,
             "state_slots": state_slots,
             "want": want,
-            "tile_rows": tile_rows,
-            "tile_starts": tile_starts,
+            **{f"tile_rows{size}": tile_rows[size] for size in ATTENTION_TILE_SIZES},
+            **{f"tile_starts{size}": tile_starts[size] for size in ATTENTION_TILE_SIZES},
             "decode_rows": decode_rows,
             "decode_tokens": decode_tokens,
             "tables": tables,
@@ -262,9 +263,10 @@ class ModelRunner:
             block_tables={group.index: tables[group.index] for group in self.cache.layout.groups},
             host_qo_indptr=facts["host_qo_indptr"],
             host_seq_lens=facts["host_seq_lens"],
-            num_prefill_tiles=layout["tile_rows"][1],
-            tile_rows=part("tile_rows"),
-            tile_starts=part("tile_starts"),
+            tiles={
+                size: (layout[f"tile_rows{size}"][1], part(f"tile_rows{size}"), part(f"tile_starts{size}"))
+                for size in ATTENTION_TILE_SIZES
+            },
             num_decode_rows=layout["decode_rows"][1],
             decode_rows=part("decode_rows"),
             decode_tokens=part("decode_tokens"),

@@ -303,6 +303,12 @@ def attention_mma_supported(head_dim: int, num_q_heads: int, num_kv_heads: int) 
     )
 
 
+def attention_prefill_tile_rows(head_dim: int) -> int:
+    """Queries per tile the prefill attention kernel expects in its tile list
+    (csrc/attention_mma.cuh: prefill_tile_rows)."""
+    return 128 if head_dim <= 128 else 64
+
+
 def _check_mma_common(what: str, q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError(f"{what}: bf16 only")
@@ -329,8 +335,10 @@ def attention_prefill_mma(
     num_q_heads: int,
     scale: float,
     window: int = 0,
+    flag: Optional[torch.Tensor] = None,
 ) -> None:
-    """Flash attention over 64-query tiles of rows with several tokens (bf16)."""
+    """Flash attention over query tiles (``attention_prefill_tile_rows`` queries each) of
+    rows with several tokens (bf16)."""
     what = "attention_prefill_mma"
     _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
     _need_i32(what, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
@@ -341,14 +349,14 @@ def attention_prefill_mma(
     fn = _fn(
         "attention_mma",
         "kb_attention_prefill_mma",
-        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
     )
     _check(
         fn(
             q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
             qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
             tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
-            page_size, num_pages, float(scale), int(window), _stream(),
+            page_size, num_pages, float(scale), int(window), _ptr(flag), _stream(),
         ),
         what,
     )
@@ -565,6 +573,7 @@ __all__ = [
     "argmax",
     "attention_decode_mma",
     "attention_mma_supported",
+    "attention_prefill_tile_rows",
     "attention_prefill_mma",
     "edit_logits",
     "embedding",

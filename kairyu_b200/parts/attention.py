@@ -42,7 +42,7 @@ def run_paged_attention(
     """Attention of every token of the step; picks the kernels for the dtype.
 
     float32: the fp32 kernel for all tokens (its arithmetic per token does not
-    depend on the batch).  bfloat16: tensor-core kernels, 64-query tiles for
+    depend on the batch).  bfloat16: tensor-core kernels, query tiles for
     rows with several tokens and split-KV for rows with one token; sizes those
     refuse go to the fp32-arithmetic kernel.
     """
@@ -67,7 +67,8 @@ def run_paged_attention(
             flag=ctx.error_flag,
         )
         return
-    if ctx.num_prefill_tiles:
+    num_tiles, tile_rows, tile_starts = ctx.tiles[kernels.attention_prefill_tile_rows(head_dim)]
+    if num_tiles:
         kernels.attention_prefill_mma(
             qkv,
             out,
@@ -76,12 +77,13 @@ def run_paged_attention(
             qo_indptr=ctx.qo_indptr,
             seq_lens=ctx.seq_lens,
             block_table=block_table,
-            tile_rows=ctx.tile_rows,
-            tile_starts=ctx.tile_starts,
-            num_tiles=ctx.num_prefill_tiles,
+            tile_rows=tile_rows,
+            tile_starts=tile_starts,
+            num_tiles=num_tiles,
             num_q_heads=num_q_heads,
             scale=scale,
             window=window,
+            flag=ctx.error_flag,
         )
     if ctx.num_decode_rows:
         kernels.attention_decode_mma(

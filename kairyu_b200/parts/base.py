@@ -146,9 +146,10 @@ class CacheView:
 class StepContext:
     """Device-side description of one step's batch, shared by every layer.
 
-    Rows are requests; tokens are flat over rows.  ``tile_*`` describe the
-    64-query tiles of rows that carry more than one token (prompt portions);
-    ``decode_*`` list rows that carry exactly one token.
+    Rows are requests; tokens are flat over rows.  ``tiles[n]`` describes the
+    n-query tiles (n = 64, 128) of rows that carry more than one token (prompt
+    portions) as (count, row of each tile, offset of each tile within the row's
+    tokens); ``decode_*`` list rows that carry exactly one token.
     """
 
     num_tokens: int
@@ -165,9 +166,7 @@ class StepContext:
     host_qo_indptr: tuple[int, ...]
     host_seq_lens: tuple[int, ...]
     # attention work lists
-    num_prefill_tiles: int = 0
-    tile_rows: torch.Tensor | None = None  # [tiles] i32
-    tile_starts: torch.Tensor | None = None  # [tiles] i32 (offset within the row's tokens)
+    tiles: dict[int, tuple[int, torch.Tensor, torch.Tensor]] = field(default_factory=dict)
     num_decode_rows: int = 0
     decode_rows: torch.Tensor | None = None  # [n] i32 row ids of 1-token rows
     decode_tokens: torch.Tensor | None = None  # [n] i32 flat token index of each

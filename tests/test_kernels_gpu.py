@@ -370,7 +370,7 @@ def _run_mma(case, Hq, scale, window, workspace):
             decode_rows.append(r)
             decode_tokens.append(qo[r])
         else:
-            for start in range(0, count, 64):
+            for start in range(0, count, k.attention_prefill_tile_rows(case["kc"].shape[-1])):
                 tile_rows.append(r)
                 tile_starts.append(start)
     dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)

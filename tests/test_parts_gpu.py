@@ -50,7 +50,7 @@ def context(dtype, tokens, kv_heads, head_dim):
     ctx = StepContext(
         num_tokens=T, num_rows=1, dtype=dtype, token_ids=ints(tokens), positions=ints(list(range(T))), row_ids=ints([0] * T),
         qo_indptr=ints([0, T]), seq_lens=ints([T]), write_from=ints([0]), state_slots=ints([0]), block_tables={0: table},
-        host_qo_indptr=(0, T), host_seq_lens=(T,), num_prefill_tiles=1, tile_rows=ints([0]), tile_starts=ints([0]),
+        host_qo_indptr=(0, T), host_seq_lens=(T,), tiles={64: (1, ints([0]), ints([0])), 128: (1, ints([0]), ints([0]))},
         num_decode_rows=0, decode_rows=ints([]), decode_tokens=ints([]), max_seq_len=T, workspace=Workspace(DEV),
         error_flag=torch.zeros(1, dtype=torch.int32, device=DEV),
     )

@@ -116,7 +116,11 @@ def attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
     return head_dim % 16 == 0 and 16 <= head_dim <= 256 and num_q_heads % num_kv_heads == 0 and num_q_heads // num_kv_heads <= 16
 
 
-def attention_prefill_mma(q, out, k_cache, v_cache, *, qo_indptr, seq_lens, block_table, tile_rows, tile_starts, num_tiles, num_q_heads, scale, window=0):
+def attention_prefill_tile_rows(head_dim):
+    return 128 if head_dim <= 128 else 64
+
+
+def attention_prefill_mma(q, out, k_cache, v_cache, *, qo_indptr, seq_lens, block_table, tile_rows, tile_starts, num_tiles, num_q_heads, scale, window=0, flag=None):
     dim = k_cache.shape[-1]
     for tile in range(num_tiles):
         row = int(tile_rows[tile])
@@ -124,7 +128,7 @@ def attention_prefill_mma(q, out, k_cache, v_cache, *, qo_indptr, seq_lens, bloc
         tok0 = int(qo_indptr[row])
         chunk = int(qo_indptr[row + 1]) - tok0
         chunk_pos = int(seq_lens[row]) - chunk
-        for i in range(q0, min(q0 + 64, chunk)):
+        for i in range(q0, min(q0 + attention_prefill_tile_rows(dim), chunk)):
             t = tok0 + i
             q_t = q[t, : num_q_heads * dim].float().view(num_q_heads, dim)
             res = _attend_token(q_t, k_cache, v_cache, block_table[row], chunk_pos + i, num_q_heads, scale, window)
@@ -190,7 +194,7 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
 
 _NAMES = [
     "embedding", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
-    "attention_mma_supported", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
+    "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
     "edit_logits", "sample",
 ]
 
