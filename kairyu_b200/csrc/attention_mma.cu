@@ -10,7 +10,7 @@ KB_EXPORT int kb_attention_prefill_mma(const void* q, int q_stride, void* out, i
                                        cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
-    if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KB_ERR_BAD_ARG;
+    if (Hkv < 1 || Hq % Hkv != 0 || num_tiles > 65535) return KB_ERR_BAD_ARG;
     if (q_stride % 8 != 0 || out_stride % 2 != 0) return KB_ERR_BAD_ARG;  // 16-byte rows for cp.async
     const int dp = padded_dim(D);
 #define ARGS (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache, \

@@ -179,7 +179,7 @@ __device__ __forceinline__ int shift_of(int page_size) {
 }
 
 // ------------------------------------------------------------------ prefill: query tiles
-// grid (tiles, Hq).  A tile is 64*MT consecutive queries of one row's portion (MT = 2 up to
+// grid (Hq, tiles).  A tile is 64*MT consecutive queries of one row's portion (MT = 2 up to
 // a padded head size of 128, else 1); warp w owns MT 16-row slices of it and every K/V
 // fragment it reads from shared memory feeds MT MMAs.  Keys stream through two 64-key
 // buffers, one bulk copy per key row (see load_kv_rows_bulk), the next tile requested as
@@ -204,8 +204,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     __nv_bfloat16* sV = sK + 2 * TILE_N * STRIDE;           // 2 buffers
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(sV + 2 * TILE_N * STRIDE);
 
-    const int tile = blockIdx.x;
-    const int h = blockIdx.y;
+    // Later tiles of a portion see more keys and run longer: hand them out first (heads
+    // vary fastest, so all heads of the longest tile start first) and let the short
+    // ones fill the tail of the grid.
+    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int h = blockIdx.x;
     const int kvh = h / (Hq / Hkv);
     const int row = tile_rows[tile];
     const int q0 = tile_starts[tile];
@@ -754,7 +757,7 @@ static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* o
     const size_t smem = prefill_smem<DP, MT>();
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid(num_tiles, Hq);
+    dim3 grid(Hq, num_tiles);
     attention_prefill_kernel<DP, MT><<<grid, MMA_THREADS, smem, stream>>>(
         q, q_stride, out, out_stride, k_cache, v_cache, qo_indptr, seq_lens, block_table, max_pages,
         tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
