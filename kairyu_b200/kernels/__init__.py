@@ -485,11 +485,70 @@ def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     )
 
 
+TC5_MAX_ROWS = 64  # token rows the tcgen05 weight-streaming product takes (csrc/gemm_tc5.cu)
+_tensor_maps: dict[tuple, ctypes.Array] = {}
+_tc5_scratch: list[torch.Tensor] = []  # old buffers stay alive: captured graphs may still point at them
+
+
+def _tensor_map(tensor: torch.Tensor, box_rows: int) -> int:
+    """Host address of a cached TMA descriptor of a row-major bf16 matrix (boxes of [box_rows, 64])."""
+    key = (tensor.data_ptr(), tensor.shape[0], tensor.shape[1], tensor.stride(0), box_rows)
+    held = _tensor_maps.get(key)
+    if held is None:
+        held = ctypes.create_string_buffer(128 + 64)
+        address = (ctypes.addressof(held) + 63) & ~63
+        fn = _fn("gemm_tc5", "kb_tc5_encode_map", [c_void_p, c_void_p, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, c_int])
+        code = fn(address, tensor.data_ptr(), tensor.shape[0], tensor.shape[1], tensor.stride(0), box_rows)
+        if code != 0:
+            raise KernelError(f"tensor map encoding failed with code {code}")
+        if len(_tensor_maps) > 4096:
+            _tensor_maps.clear()
+        _tensor_maps[key] = held
+    return (ctypes.addressof(held) + 63) & ~63
+
+
+def _tc5_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
+    M, K = x.shape
+    return (
+        M <= TC5_MAX_ROWS
+        and K % 8 == 0
+        and x.stride(1) == 1 and weight.stride(1) == 1 and out.stride(1) == 1
+        and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+        and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+        and out.dtype in (torch.bfloat16, torch.float32)
+        and (bias is None or (bias.dtype == torch.bfloat16 and bias.is_contiguous()))
+    )
+
+
+def _gemm_tc5(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, gated: bool,
+              flag: Optional[torch.Tensor] = None) -> None:
+    M, K = x.shape
+    N = weight.shape[0]
+    n_out = N // 2 if gated else N
+    splits_fn = _fn("gemm_tc5", "kb_gemm_tc5_splits", [c_int, c_int, c_int])
+    splits = splits_fn(n_out, K, 1 if gated else 0)
+    partial = None
+    if splits > 1:
+        need = splits * M * n_out
+        if not _tc5_scratch or _tc5_scratch[-1].numel() < need or _tc5_scratch[-1].device != x.device:
+            _tc5_scratch.append(torch.empty(max(need, 8 * 1024 * 1024), dtype=torch.float32, device=x.device))
+        partial = _tc5_scratch[-1]
+    box = 16 if M <= 16 else (32 if M <= 32 else 64)
+    fn = _fn("gemm_tc5", "kb_gemm_tc5", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(
+        fn(_tensor_map(weight, 128), _tensor_map(x, box), out.data_ptr(), 1 if out.dtype == torch.float32 else 0, out.stride(0),
+           _ptr(bias), _ptr(partial), M, N, K, 1 if gated else 0, _ptr(flag), _stream()),
+        "gemm_tc5",
+        launches=2 if splits > 1 else 1,
+    )
+
+
 def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: object) -> None:
     """out = silu(x @ Wg.T) * (x @ Wu.T) with ``weight_gate_up`` = [Wg; Wu] stacked by rows.
 
-    For a few bf16 token rows this is one weight-streaming kernel with the gate in
-    its epilogue; otherwise a product into ``scratch.buffer(...)`` and the gate kernel.
+    For up to 64 bf16 token rows this is one weight-streaming kernel with the gate in
+    its epilogue (tcgen05 + TMA, csrc/gemm_tc5.cu); otherwise a product into
+    ``scratch.buffer(...)`` and the gate kernel.
     """
     _need_cuda("linear_swiglu", x, weight_gate_up, out)
     M = x.shape[0]
@@ -498,9 +557,13 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tens
         raise KernelError("linear_swiglu: shape mismatch")
     if M == 0:
         return
-    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and _skinny_ok(x, weight_gate_up, None, out):
-        _gemm_skinny(x, weight_gate_up, None, out, gated=True)
-        return
+    if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
+        if _tc5_ok(x, weight_gate_up, None, out):  # tcgen05 + TMA: the fastest of the three for the wide gate/up band
+            _gemm_tc5(x, weight_gate_up, None, out, gated=True)
+            return
+        if _skinny_ok(x, weight_gate_up, None, out):
+            _gemm_skinny(x, weight_gate_up, None, out, gated=True)
+            return
     gate_up = scratch.buffer("ffn.gate_up", M, two_i, x.dtype)
     linear(x, weight_gate_up, None, gate_up)
     swiglu(gate_up, out)

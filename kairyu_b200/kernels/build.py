@@ -35,6 +35,7 @@ LIBRARIES: dict[str, list[str]] = {
     "attention_decode_static": [],
     "gemm_f32": [],
     "gemm_skinny": [],
+    "gemm_tc5": [],
     "sampling": [],
 }
 

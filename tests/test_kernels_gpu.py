@@ -202,6 +202,29 @@ def test_gated_product_for_many_rows_uses_the_two_kernel_path():
     close(out32, ref32, 1e-5, 1e-5)
 
 
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K,gated", [(128, 64, False), (331, 144, False), (6144, 4096, False), (4096, 14336, False), (400, 200, True), (28672, 4096, True), (130, 72, True)])
+@pytest.mark.parametrize("bias", [False, True])
+def test_tcgen05_weight_streaming_product(M, N, K, gated, bias):
+    """csrc/gemm_tc5.cu directly: TMA + tcgen05.mma with the accumulator in TMEM; weight rows beyond N,
+    tokens beyond M and k beyond K come in as zeros; K split over blocks where N is small."""
+    if gated and N == 28672 and bias:
+        pytest.skip("one large gated case is enough")
+    x = rand(M, K, dtype=torch.bfloat16, seed=60)
+    w = rand(N, K, dtype=torch.bfloat16, seed=61, scale=0.05)
+    b = rand(N, dtype=torch.bfloat16, seed=62) if bias else None
+    y = x.float() @ w.float().t() + (b.float() if bias else 0)
+    if gated:
+        g, u = y[:, : N // 2], y[:, N // 2 :]
+        y = g / (1 + torch.exp(-g)) * u
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for dtype, atol, rtol in ((torch.float32, 3e-4 * math.sqrt(K / 64), 1e-4), (torch.bfloat16, 4e-3 * math.sqrt(K / 64), 1e-2)):
+        out = torch.full(y.shape, 7.0, dtype=dtype, device=DEV)
+        kernels()._gemm_tc5(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out, gated=gated, flag=flag)
+        close(out, y, atol, rtol)
+    assert int(flag.item()) == 0
+
+
 # ------------------------------------------------------------------ rope + cache write
 
 
