@@ -26,6 +26,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restr
                                const int* __restrict__ block_table, int max_pages, int Hq, int Hkv,
                                int D, int page_size, int num_pages, float scale, int window,
                                int* flag) {
+    pdl_wait();
     __shared__ float sm_acc[ATT_WARPS][ATT_MAX_D];
     __shared__ float sm_m[ATT_WARPS];
     __shared__ float sm_l[ATT_WARPS];
@@ -124,12 +125,12 @@ KB_EXPORT int kb_paged_attention_generic(const void* q, int q_stride, void* out,
     if (Hkv < 1 || Hq % Hkv != 0 || Hq > 65535) return KB_ERR_BAD_ARG;
     dim3 grid(T, Hq);
     if (is_bf16)
-        paged_attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
+        kb_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(ATT_WARPS * 32), 0, stream, 
             (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
             (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, positions, row_ids,
             block_table, max_pages, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
     else
-        paged_attention_generic_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
+        kb_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), 0, stream, 
             (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache,
             (const float*)v_cache, positions, row_ids, block_table, max_pages, Hq, Hkv, D,
             page_size, num_pages, scale, window, flag);

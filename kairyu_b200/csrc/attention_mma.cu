@@ -53,7 +53,7 @@ KB_EXPORT int kb_attention_decode_mma(const void* q, int q_stride, void* out, in
 #undef ARGS
     if (rc != 0) return rc;
     dim3 grid(num_rows, Hq);
-    attention_decode_merge_kernel<<<grid, 128, 0, stream>>>(part_o, part_ml, seq_lens, decode_rows, decode_tokens,
+    kb_launch(attention_decode_merge_kernel, dim3(grid), dim3(128), 0, stream, part_o, part_ml, seq_lens, decode_rows, decode_tokens,
                                                             (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits);
     return kb_launch_result();
 }

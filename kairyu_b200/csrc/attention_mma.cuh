@@ -193,6 +193,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          int max_pages, const int* __restrict__ tile_rows,
                          const int* __restrict__ tile_starts, int Hq, int Hkv, int D, int page_size,
                          int num_pages, float scale, int window, int* flag) {
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int STRIDE = Tile<DP>::STRIDE;
     constexpr int CH = Tile<DP>::CHUNKS;
@@ -459,6 +460,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const int* __restrict__ decode_tokens, int Hq, int Hkv, int D,
                               int page_size, int num_pages, float scale, int window, int num_splits,
                               float* __restrict__ part_o, float* __restrict__ part_ml, int* flag) {
+    pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int STRIDE = Tile<DP>::STRIDE;
     constexpr int CH = Tile<DP>::CHUNKS;
@@ -699,6 +701,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o,
                                               const int* __restrict__ decode_tokens,
                                               __nv_bfloat16* __restrict__ out, int out_stride, int Hq,
                                               int D, int window, int num_splits) {
+    pdl_wait();
     const int slot = blockIdx.x;
     const int h = blockIdx.y;
     const int row = decode_rows[slot];
@@ -758,7 +761,7 @@ static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* o
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<DP, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(Hq, num_tiles);
-    attention_prefill_kernel<DP, MT><<<grid, MMA_THREADS, smem, stream>>>(
+    kb_launch(attention_prefill_kernel<DP, MT>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         q, q_stride, out, out_stride, k_cache, v_cache, qo_indptr, seq_lens, block_table, max_pages,
         tile_rows, tile_starts, Hq, Hkv, D, page_size, num_pages, scale, window, flag);
     return kb_launch_result();
@@ -774,7 +777,7 @@ static int launch_decode(const __nv_bfloat16* q, int q_stride, const __nv_bfloat
     cudaError_t e = cudaFuncSetAttribute(attention_decode_split_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(num_rows, Hkv, num_splits);
-    attention_decode_split_kernel<DP><<<grid, MMA_THREADS, smem, stream>>>(
+    kb_launch(attention_decode_split_kernel<DP>, dim3(grid), dim3(MMA_THREADS), smem, stream, 
         q, q_stride, k_cache, v_cache, seq_lens, block_table, max_pages, decode_rows, decode_tokens,
         Hq, Hkv, D, page_size, num_pages, scale, window, num_splits, part_o, part_ml, flag);
     return kb_launch_result();

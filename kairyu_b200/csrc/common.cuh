@@ -17,6 +17,31 @@
 
 static inline int kb_launch_result() { return (int)cudaGetLastError(); }
 
+// Programmatic dependent launch.  Every kernel of this package is launched with the
+// attribute below and calls pdl_wait() before it reads or writes anything that depends on
+// the kernel before it (pdl_wait blocks until that kernel has finished and its writes are
+// visible).  The attribute lets a kernel's blocks be scheduled while the previous kernel
+// drains, so launch latency, set-up and, for the weight-streaming products, the first weight
+// loads overlap its tail.  No kernel asks for its dependents to be launched earlier than that
+// (griddepcontrol.launch_dependents): measured on the decode step, dependents that sit
+// resident behind a running kernel cost more than the overlap gives.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline void kb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);  // the error, if any, is read by kb_launch_result()
+}
+
 // Bits of the device-side error word that indexing kernels set instead of
 // touching memory outside their tensors.
 #define KB_FLAG_BAD_PAGE 1

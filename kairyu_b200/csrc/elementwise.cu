@@ -8,6 +8,7 @@
 template <typename TT>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int H, int V, int* flag) {
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = out + (size_t)t * H;
@@ -26,9 +27,9 @@ KB_EXPORT int kb_embedding(const void* table, int table_is_bf16, const int* ids,
     if (!table || !ids || !out) return KB_ERR_NULL;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_is_bf16)
-        embedding_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H, V, flag);
+        kb_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, flag);
     else
-        embedding_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H, V, flag);
+        kb_launch(embedding_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, ids, out, H, V, flag);
     return kb_launch_result();
 }
 
@@ -41,6 +42,7 @@ template <typename TX, typename TA, typename TW>
 __global__ void rmsnorm_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
                                const TW* __restrict__ w, TA* __restrict__ out,
                                const int* __restrict__ rows, int H, float eps, int write_back) {
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
@@ -105,6 +107,7 @@ template <typename TX, typename TA, typename TW>
 __global__ void rmsnorm_vec_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
                                    const TW* __restrict__ w, TA* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps, int write_back) {
+    pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
@@ -155,19 +158,19 @@ static int rmsnorm_dispatch_w(void* x, const void* delta, const void* w, int w_b
         int threads_v = ((H / 4 + 31) / 32) * 32;  // one chunk per thread while the block can hold the row
         if (threads_v > 1024) threads_v = 1024;
         if (w_bf16)
-            rmsnorm_vec_kernel<TX, TA, __nv_bfloat16><<<R, threads_v, 0, stream>>>(
+            kb_launch(rmsnorm_vec_kernel<TX, TA, __nv_bfloat16>, dim3(R), dim3(threads_v), 0, stream, 
                 (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back);
         else
-            rmsnorm_vec_kernel<TX, TA, float><<<R, threads_v, 0, stream>>>(
+            kb_launch(rmsnorm_vec_kernel<TX, TA, float>, dim3(R), dim3(threads_v), 0, stream, 
                 (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back);
         return kb_launch_result();
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (w_bf16)
-        rmsnorm_kernel<TX, TA, __nv_bfloat16><<<R, threads, 0, stream>>>(
+        kb_launch(rmsnorm_kernel<TX, TA, __nv_bfloat16>, dim3(R), dim3(threads), 0, stream, 
             (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back);
     else
-        rmsnorm_kernel<TX, TA, float><<<R, threads, 0, stream>>>(
+        kb_launch(rmsnorm_kernel<TX, TA, float>, dim3(R), dim3(threads), 0, stream, 
             (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back);
     return kb_launch_result();
 }
@@ -195,6 +198,7 @@ KB_EXPORT int kb_rmsnorm(void* x, int x_bf16, const void* delta, const void* w, 
 // (kairyu/models/layers.py:244); out: [T, I].
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    pdl_wait();
     const int t = blockIdx.y;
     const T* g = gate_up + (size_t)t * 2 * I;
     const T* u = g + I;
@@ -210,6 +214,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
 // 8 elements a thread (16-byte loads for bf16, two for fp32) when I % 8 == 0.
 template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I) {
+    pdl_wait();
     const int t = blockIdx.y;
     const T* g = gate_up + (size_t)t * 2 * I;
     const T* u = g + I;
@@ -237,18 +242,18 @@ KB_EXPORT int kb_swiglu(const void* gate_up, void* out, int is_bf16, int T, int 
         if (bxv > 1024) bxv = 1024;
         dim3 gridv(bxv, T);
         if (is_bf16)
-            swiglu_vec_kernel<__nv_bfloat16><<<gridv, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
+            kb_launch(swiglu_vec_kernel<__nv_bfloat16>, dim3(gridv), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
         else
-            swiglu_vec_kernel<float><<<gridv, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+            kb_launch(swiglu_vec_kernel<float>, dim3(gridv), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I);
         return kb_launch_result();
     }
     int bx = (I + threads - 1) / threads;
     if (bx > 1024) bx = 1024;
     dim3 grid(bx, T);
     if (is_bf16)
-        swiglu_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
+        kb_launch(swiglu_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I);
     else
-        swiglu_kernel<float><<<grid, threads, 0, stream>>>((const float*)gate_up, (float*)out, I);
+        kb_launch(swiglu_kernel<float>, dim3(grid), dim3(threads), 0, stream, (const float*)gate_up, (float*)out, I);
     return kb_launch_result();
 }
 
@@ -256,6 +261,7 @@ KB_EXPORT int kb_swiglu(const void* gate_up, void* out, int is_bf16, int T, int 
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ src, const int* __restrict__ rows,
                                    T* __restrict__ out, int H) {
+    pdl_wait();
     const T* s = src + (size_t)rows[blockIdx.x] * H;
     T* o = out + (size_t)blockIdx.x * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = s[i];
@@ -266,8 +272,8 @@ KB_EXPORT int kb_gather_rows(const void* src, const int* rows, void* out, int is
     if (R == 0) return 0;
     if (!src || !rows || !out) return KB_ERR_NULL;
     if (is_bf16)
-        gather_rows_kernel<__nv_bfloat16><<<R, 256, 0, stream>>>((const __nv_bfloat16*)src, rows, (__nv_bfloat16*)out, H);
+        kb_launch(gather_rows_kernel<__nv_bfloat16>, dim3(R), dim3(256), 0, stream, (const __nv_bfloat16*)src, rows, (__nv_bfloat16*)out, H);
     else
-        gather_rows_kernel<float><<<R, 256, 0, stream>>>((const float*)src, rows, (float*)out, H);
+        kb_launch(gather_rows_kernel<float>, dim3(R), dim3(256), 0, stream, (const float*)src, rows, (float*)out, H);
     return kb_launch_result();
 }

@@ -12,6 +12,7 @@
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, int ldw,
                 const float* __restrict__ bias, float* __restrict__ y, int ldy, int M, int N, int K) {
+    pdl_wait();
     __shared__ float As[F32_BK][F32_BM + 1];
     __shared__ float Bs[F32_BK][F32_BN + 1];
     const int tid = threadIdx.x;
@@ -75,6 +76,6 @@ KB_EXPORT int kb_gemm_f32(const float* x, int ldx, const float* w, int ldw, cons
     if (K < 1) return KB_ERR_BAD_ARG;
     dim3 grid((N + F32_BN - 1) / F32_BN, (M + F32_BM - 1) / F32_BM);
     if (grid.y > 65535) return KB_ERR_UNSUPPORTED_SIZE;
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, ldx, w, ldw, bias, y, ldy, M, N, K);
+    kb_launch(gemm_f32_kernel, dim3(grid), dim3(256), 0, stream, x, ldx, w, ldw, bias, y, ldy, M, N, K);
     return kb_launch_result();
 }

@@ -92,16 +92,27 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     // Two register sets: the loads of the next SK_UNROLL steps are issued before the
     // MMAs of the current ones, so a warp always has a batch in flight.
     Reg8 a_lo[2][SK_UNROLL], a_hi[2][SK_UNROLL], b[2][SK_UNROLL][NT];
-    auto load_batch = [&](int set, int step0) {
+    auto load_weights = [&](int set, int step0) {
 #pragma unroll
         for (int u = 0; u < SK_UNROLL; ++u) {
             const int k = (step0 + u * KWARPS) * SK_STEP + tq * 16;
             const bool k_ok = k < K;  // K % 16 == 0, so a 32-byte load is all in or all out
             a_lo[set][u] = (k_ok && lo_ok) ? load_stream32(w_lo + k) : zero;
             a_hi[set][u] = (k_ok && hi_ok) ? load_stream32(w_hi + k) : zero;
+        }
+    };
+    auto load_tokens = [&](int set, int step0) {
+#pragma unroll
+        for (int u = 0; u < SK_UNROLL; ++u) {
+            const int k = (step0 + u * KWARPS) * SK_STEP + tq * 16;
+            const bool k_ok = k < K;
 #pragma unroll
             for (int t = 0; t < NT; ++t) b[set][u][t] = (k_ok && x_ok[t]) ? load_cached32(x_row[t] + k) : zero;
         }
+    };
+    auto load_batch = [&](int set, int step0) {
+        load_weights(set, step0);
+        load_tokens(set, step0);
     };
     // The 16 values a thread holds of a row feed four MMAs: MMA j takes values 4j..4j+3
     // as its (k, k+1) and (k+8, k+9) pairs.  Which k a value is called does not matter to
@@ -119,7 +130,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     };
     constexpr int STRIDE = KWARPS * SK_UNROLL;
     int step0 = kwarp;
-    load_batch(0, step0);
+    // The weights do not depend on the kernel before this one: their first loads go out
+    // before the wait, the tokens (that kernel's output) after it.
+    load_weights(0, step0);
+    pdl_wait();
+    load_tokens(0, step0);
     while (true) {
         load_batch(1, step0 + STRIDE);  // past the end: all zero, no memory touched
         mma_batch(0);
@@ -170,9 +185,9 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
     const int rows_out = GATED ? N / 2 : N;
     const int blocks = (rows_out + 15) / 16;
     if (out_fp32)
-        gemm_skinny_kernel<NT, GATED, float><<<blocks, SK_THREADS, 0, stream>>>(x, ldx, w, ldw, bias, (float*)out, ldo, M, N, K);
+        kb_launch(gemm_skinny_kernel<NT, GATED, float>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (float*)out, ldo, M, N, K);
     else
-        gemm_skinny_kernel<NT, GATED, __nv_bfloat16><<<blocks, SK_THREADS, 0, stream>>>(x, ldx, w, ldw, bias, (__nv_bfloat16*)out, ldo, M, N, K);
+        kb_launch(gemm_skinny_kernel<NT, GATED, __nv_bfloat16>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (__nv_bfloat16*)out, ldo, M, N, K);
     return kb_launch_result();
 }
 

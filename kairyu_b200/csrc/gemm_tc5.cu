@@ -174,7 +174,22 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ---------------- producer: TMA loads of the W band(s) and the token tile
         const uint64_t stream_policy = policy_evict_first();
         const uint64_t keep_policy = policy_evict_last();
-        for (int i = 0; i < num_kb; ++i) {
+        // The weights do not depend on the kernel before this one: the first round of W
+        // tiles is requested before the wait, the token tiles (that kernel's output) after.
+        const int first_round = min(num_kb, (int)Cfg::STAGES);
+        for (int i = 0; i < first_round; ++i) {
+            unsigned char* a = stage_base + (size_t)i * Cfg::STAGE_BYTES;
+            const int k = (kb_begin + i) * TC_BLOCK_K;
+            mbar_arrive_expect_tx(full_bar + i, Cfg::STAGE_BYTES);
+            tma_load_2d(a, &map_w, k, n0, full_bar + i, stream_policy);
+            if (GATED) tma_load_2d(a + Cfg::A_BYTES, &map_w, k, rows_out + n0, full_bar + i, stream_policy);
+        }
+        pdl_wait();
+        for (int i = 0; i < first_round; ++i) {
+            unsigned char* b = stage_base + (size_t)i * Cfg::STAGE_BYTES + Cfg::BANDS * Cfg::A_BYTES;
+            tma_load_2d(b, &map_x, (kb_begin + i) * TC_BLOCK_K, 0, full_bar + i, keep_policy);
+        }
+        for (int i = first_round; i < num_kb; ++i) {
             const int s = i % Cfg::STAGES;
             const uint32_t round = i / Cfg::STAGES;
             if (!mbar_wait(empty_bar + s, (round & 1) ^ 1, abort_word)) {
@@ -217,6 +232,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (ok) umma_commit(done_bar);    // the accumulator is complete
     } else if (warp >= 2) {
         // ---------------- epilogue: TMEM -> registers -> global
+        pdl_wait();  // the output (or the partial-sum scratch) may still be read by the kernel before
         const bool ready = num_kb > 0 && mbar_wait(done_bar, 0, abort_word);
         if (!ready && num_kb > 0) {
             if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
@@ -274,6 +290,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 template <typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out,
                                      int ldo, int M, int N, int splits) {
+    pdl_wait();
     const size_t total = (size_t)M * N;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / N);
@@ -332,7 +349,7 @@ static int launch_tc5(const CUtensorMap* map_w, const CUtensorMap* map_x, void* 
     const int per_split = (total_kb + k_splits - 1) / k_splits;
     const int splits = (total_kb + per_split - 1) / per_split;  // every split has work
     dim3 grid((rows_out + TC_BLOCK_ROWS - 1) / TC_BLOCK_ROWS, splits);
-    gemm_tc5_kernel<NTOK, GATED><<<grid, TC_THREADS, Cfg::SMEM, stream>>>(*map_w, *map_x, out, out_fp32, ldo, bias,
+    kb_launch(gemm_tc5_kernel<NTOK, GATED>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, *map_w, *map_x, out, out_fp32, ldo, bias,
                                                                          splits > 1 ? partial : nullptr, M, N, K, per_split, flag);
     int rc = kb_launch_result();
     if (rc != 0 || splits == 1) return rc;
@@ -340,9 +357,9 @@ static int launch_tc5(const CUtensorMap* map_w, const CUtensorMap* map_x, void* 
     int blocks = (int)((total + 255) / 256);
     if (blocks > 1184) blocks = 1184;
     if (out_fp32)
-        splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(partial, bias, (float*)out, ldo, M, rows_out, splits);
+        kb_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(256), 0, stream, partial, bias, (float*)out, ldo, M, rows_out, splits);
     else
-        splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(partial, bias, (__nv_bfloat16*)out, ldo, M, rows_out, splits);
+        kb_launch(splitk_reduce_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, partial, bias, (__nv_bfloat16*)out, ldo, M, rows_out, splits);
     return kb_launch_result();
 }
 

@@ -26,6 +26,7 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
                              const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ write_from, T* __restrict__ k_cache,
                              T* __restrict__ v_cache, int page_size, int num_pages, int* flag) {
+    pdl_wait();
     __shared__ float head_buf[ROPE_WARPS][ROPE_MAX_D];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5;
@@ -118,7 +119,7 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
     if (Hq + 2 * Hkv > 65535 * ROPE_WARPS) return KB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(T, (Hq + 2 * Hkv + ROPE_WARPS - 1) / ROPE_WARPS);
 #define LAUNCH(T_, TW_)                                                                         \
-    qk_norm_rope_kv_write_kernel<T_, TW_><<<grid, threads, 0, stream>>>(                           \
+    kb_launch(qk_norm_rope_kv_write_kernel<T_, TW_>, dim3(grid), dim3(threads), 0, stream,                            \
         (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps,      \
         cos_table, sin_table, rot_half, max_pos, positions, row_ids, block_table, max_pages,    \
         write_from, (T_*)k_cache, (T_*)v_cache, page_size, num_pages, flag)

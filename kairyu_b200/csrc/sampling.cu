@@ -48,6 +48,7 @@ __device__ __forceinline__ BestF block_argmax(BestF b, float* sv, int* si) {
 // out[r] = first index of the maximum of logits[r, :] (NaN never wins).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out, int vectorised) {
+    pdl_wait();
     __shared__ float sv[32];
     __shared__ int si[32];
     const float* row = logits + (size_t)blockIdx.x * ld;
@@ -90,7 +91,7 @@ KB_EXPORT int kb_argmax(const float* logits, int ld, int n, int V, int* out, cud
     if (!logits || !out) return KB_ERR_NULL;
     if (V < 1) return KB_ERR_BAD_ARG;
     const int vectorised = ((uintptr_t)logits % 16 == 0) && (ld % 4 == 0);
-    argmax_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, out, vectorised);
+    kb_launch(argmax_kernel, dim3(n), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, out, vectorised);
     return kb_launch_result();
 }
 
@@ -104,6 +105,7 @@ __global__ void edit_logits_kernel(float* __restrict__ logits, int ld, int V,
                                    const int* __restrict__ e_row, const int* __restrict__ e_tok,
                                    const float* __restrict__ e_mul, const float* __restrict__ e_sub,
                                    const int* __restrict__ e_mask, int E) {
+    pdl_wait();
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= E) return;
     const int tok = e_tok[e];
@@ -121,7 +123,7 @@ KB_EXPORT int kb_edit_logits(float* logits, int ld, int V, const int* e_row, con
                              cudaStream_t stream) {
     if (E == 0) return 0;
     if (!logits || !e_row || !e_tok || !e_mul || !e_sub || !e_mask) return KB_ERR_NULL;
-    edit_logits_kernel<<<(E + 255) / 256, 256, 0, stream>>>(logits, ld, V, e_row, e_tok, e_mul, e_sub, e_mask, E);
+    kb_launch(edit_logits_kernel, dim3((E + 255) / 256), dim3(256), 0, stream, logits, ld, V, e_row, e_tok, e_mul, e_sub, e_mask, E);
     return kb_launch_result();
 }
 
@@ -208,6 +210,7 @@ sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
               const unsigned long long* __restrict__ seeds, int* __restrict__ out) {
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ float sv[32];
     __shared__ int si[32];
@@ -320,6 +323,6 @@ KB_EXPORT int kb_sample(const float* logits, int ld, float* work, int n, int V,
     if (n == 0) return 0;
     if (!logits || !work || !temperature || !top_k || !top_p || !min_p || !seeds || !out) return KB_ERR_NULL;
     if (V < 1 || V >= (1 << 24)) return KB_ERR_UNSUPPORTED_SIZE;  // counts are kept in fp32
-    sample_kernel<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, work, V, temperature, top_k, top_p, min_p, seeds, out);
+    kb_launch(sample_kernel, dim3(n), dim3(SAMPLE_THREADS), 0, stream, logits, ld, work, V, temperature, top_k, top_p, min_p, seeds, out);
     return kb_launch_result();
 }
