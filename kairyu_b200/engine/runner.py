@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 from kairyu_b200 import kernels
@@ -61,6 +62,14 @@ class _Graph:
     layout: dict[str, tuple[int, int]]
     launches: int = 0  # kernels of this package inside the graph
     keepalive: tuple = ()  # tensors the captured kernels read; freeing them would hand their memory to others
+    # Host side of the static metadata: an authoritative mirror that is updated in place from
+    # step to step (a decode step changes a token, a position and now and then one page per
+    # row), which request sits in which row, and a ring of pinned staging buffers so that the
+    # copy of step N may still be in flight while step N+1 is prepared.
+    mirror: Any = None
+    row_state: list = field(default_factory=list)
+    staging: list = field(default_factory=list)
+    next_staging: int = 0
 
 
 class ModelRunner:
@@ -323,15 +332,20 @@ class ModelRunner:
         max_seq_len = max(seq_len for _, _, seq_len in rows)
         key = self._graph_key(num_rows, max_seq_len)
         bucket, context_bucket = key
-        host, layout, facts = self._pack(
-            rows, pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
-        )
-        # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
-        facts["max_seq_len"] = context_bucket
         held = self._graphs.get(key)
         if held is None or held.generation != self.graph_workspace.generation:
+            host, layout, facts = self._pack(
+                rows, pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
+            )
+            # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
+            facts["max_seq_len"] = context_bucket
             held = self._capture(key, host, layout, facts)
-        held.meta.copy_(host, non_blocking=True)
+            held.mirror = host.numpy().copy()
+            held.row_state = [None] * bucket
+            self._note_rows(held, rows)
+        else:
+            self._update_mirror(held, rows, bucket)
+        self._upload(held)
         held.graph.replay()
         self.counters["graph_replays"] += 1
         self.counters["kernel_launches"] += held.launches
@@ -342,6 +356,68 @@ class ModelRunner:
             return held.logits[:num_rows]
         index = torch.tensor(wanted_rows, dtype=torch.long, device=self.device)
         return held.logits.index_select(0, index)
+
+    def _needed_pages(self, seq_len: int) -> int:
+        return -(-seq_len // self.cache.page_size)
+
+    def _note_rows(self, held: _Graph, rows: Sequence[tuple[StepEntry, int, int]]) -> None:
+        groups = len(self.cache.layout.groups)
+        for row, (entry, _, seq_len) in enumerate(rows):
+            held.row_state[row] = (entry.request_id, [self._needed_pages(seq_len)] * groups)
+
+    def _update_mirror(self, held: _Graph, rows: Sequence[tuple[StepEntry, int, int]], bucket: int) -> None:
+        """Bring the host mirror of a graph's metadata to this step: per row the token, the
+        position, the length, and the pages that were added since the row was last written."""
+        mirror = held.mirror
+        layout = held.layout
+        token_at = layout["token_ids"][0]
+        position_at = layout["positions"][0]
+        length_at = layout["seq_lens"][0]
+        slot_at = layout["state_slots"][0]
+        table_at = layout["tables"][0]
+        width = self.max_pages_per_request
+        groups = self.cache.layout.groups
+        for row, (entry, start, seq_len) in enumerate(rows):
+            record = self.cache.get(entry.request_id)
+            mirror[token_at + row] = entry.tokens[0]
+            mirror[position_at + row] = start
+            mirror[length_at + row] = seq_len
+            mirror[slot_at + row] = record.state_slot
+            need = self._needed_pages(seq_len)
+            state = held.row_state[row]
+            same = state is not None and state[0] == entry.request_id
+            for group in groups:
+                base = table_at + (group.index * bucket + row) * width
+                table = record.tables[group.index]
+                have = state[1][group.index] if same else None
+                if have is None or have > need or group.spec.window is not None:
+                    mirror[base : base + width] = -1
+                    mirror[base : base + need] = table[:need]
+                elif need > have:
+                    mirror[base + have : base + need] = table[have:need]
+            held.row_state[row] = (entry.request_id, [need] * len(groups))
+        for row in range(len(rows), bucket):
+            if held.row_state[row] is not None:  # the row becomes padding: token 0 at position 0 of the reserved page
+                mirror[token_at + row] = 0
+                mirror[position_at + row] = 0
+                mirror[length_at + row] = 1
+                mirror[slot_at + row] = 0
+                for group in groups:
+                    base = table_at + (group.index * bucket + row) * width
+                    mirror[base : base + width] = 0
+                held.row_state[row] = None
+
+    def _upload(self, held: _Graph) -> None:
+        if not held.staging:
+            for _ in range(4):
+                pinned = torch.empty(held.mirror.shape[0], dtype=torch.int32, pin_memory=True)
+                held.staging.append((pinned, pinned.numpy(), torch.cuda.Event()))
+        pinned, view, event = held.staging[held.next_staging]
+        held.next_staging = (held.next_staging + 1) % len(held.staging)
+        event.synchronize()  # the copy that last used this buffer has run (a fresh event is complete)
+        view[:] = held.mirror
+        held.meta.copy_(pinned, non_blocking=True)
+        event.record()
 
     def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict) -> _Graph:
         bucket, _ = key
