@@ -143,7 +143,9 @@ def build_engine(layers: int, max_batch: int):
         dtype="bfloat16",
         page_size=PAGE_SIZE,
         num_pages=max_batch * per_request + 1,
-        max_num_batched_tokens=PREFILL_TOKENS,
+        # room to prefill the whole default batch in one step, so that the end-to-end run's
+        # decode steps are pure decode steps (prompt portions would otherwise ride along)
+        max_num_batched_tokens=max(PREFILL_TOKENS, 8 * PROMPT_LEN),
         max_num_seqs=max(max_batch, 1),
         max_model_len=CONTEXT_LEN,
         max_num_partial_prefills=1,

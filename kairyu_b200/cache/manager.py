@@ -165,12 +165,20 @@ class CacheManager:
         from ``query_start`` (default: the request's computed length).  All
         groups or nothing: returns False, changing nothing, if any pool is short."""
         record = self._requests[request_id]
+        last = -(-upto // self.page_size)
+        # The common case of a decode step: every table already reaches the last page.  (A
+        # table is only ever extended together with the allocation of its new entries, and a
+        # request's positions only grow, so a table that long covers what can be read.)
+        for table in record.tables:
+            if len(table) < last:
+                break
+        else:
+            return True
         if query_start is None:
             query_start = record.num_tokens
         needed = self.pages_needed(request_id, upto, query_start)
         if any(count > pool.num_free for count, pool in zip(needed, self.pools)):
             return False
-        last = self.pages_for(upto)
         for group, pool in zip(self.layout.groups, self.pools):
             table = record.tables[group.index]
             first = self._first_needed_page(group, query_start)
