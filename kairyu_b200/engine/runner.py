@@ -43,6 +43,18 @@ class StepError(RuntimeError):
     pass
 
 
+def context_bucket(max_seq_len: int) -> int:
+    """Context length a captured decode graph is sized for: the next multiple of an eighth of
+    the enclosing power of two (at least 256).  The attention grid of a graph has one block per
+    128 keys of this length, so a coarser bucket launches blocks that find nothing to do, and a
+    finer one captures more graphs."""
+    power = 256
+    while power < max_seq_len:
+        power *= 2
+    step = max(256, power // 8)
+    return max(256, -(-max_seq_len // step) * step)
+
+
 def decode_buckets(max_batch: int) -> list[int]:
     """Padded batch sizes graphs are captured for: 1, 2, 4, 8, 16, 24, 32, then
     every 8 (kairyu/engine/core/graph_buckets.py:9-28)."""
@@ -322,10 +334,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ graphs
     def _graph_key(self, num_rows: int, max_seq_len: int) -> tuple[int, int]:
         bucket = next(size for size in self._buckets if size >= num_rows)
-        context_bucket = 256
-        while context_bucket < max_seq_len:
-            context_bucket *= 2
-        return bucket, min(context_bucket, max(self.max_model_len, 256))
+        return bucket, min(context_bucket(max_seq_len), max(self.max_model_len, 256))
 
     def _graph_step(self, rows: Sequence[tuple[StepEntry, int, int]]) -> Optional[torch.Tensor]:
         num_rows = len(rows)

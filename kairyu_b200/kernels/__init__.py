@@ -379,11 +379,13 @@ def attention_decode_mma(
     window: int = 0,
     workspace: object,
     flag: Optional[torch.Tensor] = None,
+    num_splits: Optional[int] = None,
 ) -> None:
     """Split-KV attention of rows that carry one token (bf16), then the merge.
 
     ``max_seq_len`` bounds every row's length; it sizes the grid and the scratch
-    (``workspace.flat`` gives persistent fp32 buffers).
+    (``workspace.flat`` gives persistent fp32 buffers).  ``num_splits`` overrides the
+    number of splits of the TMA-fed kernel (tests use it to make a block stream many tiles).
     """
     what = "attention_decode_mma"
     _need_cuda(what, q, out, k_cache, v_cache, seq_lens, block_table, decode_rows, decode_tokens)
@@ -392,6 +394,30 @@ def attention_decode_mma(
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
+    if _decode_tma_ok(k_cache, v_cache):  # tiled TMA copies of whole runs of key rows, streamed through a ring
+        splits_fn = _fn("attention_decode_tma", "kb_attention_decode_tma_splits", [c_int, c_int, c_int, c_int])
+        if num_splits is None:
+            num_splits = splits_fn(int(num_rows), num_kv_heads, head_dim, max(1, int(max_seq_len)))
+        if num_splits < 1:
+            raise KernelError(f"{what}: choosing the number of splits failed with code {num_splits}")
+        part_o = workspace.flat("attn.part_o", num_rows * num_q_heads * num_splits * head_dim, torch.float32)
+        part_ml = workspace.flat("attn.part_ml", num_rows * num_q_heads * num_splits * 2, torch.float32)
+        fn = _fn(
+            "attention_decode_tma",
+            "kb_attention_decode_tma",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        )
+        _check(
+            fn(
+                _cache_map(k_cache), _cache_map(v_cache), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+                seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
+                decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
+                float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(flag), _stream(),
+            ),
+            what,
+            launches=2,
+        )
+        return
     num_splits = max(1, -(-int(max_seq_len) // DECODE_SPLIT))
     part_o = workspace.flat("attn.part_o", num_rows * num_q_heads * num_splits * head_dim, torch.float32)
     part_ml = workspace.flat("attn.part_ml", num_rows * num_q_heads * num_splits * 2, torch.float32)
@@ -410,6 +436,34 @@ def attention_decode_mma(
         what,
         launches=2,
     )
+
+
+def _decode_tma_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> bool:
+    num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
+    return (
+        head_dim in (64, 128, 192, 256)
+        and page_size >= 8 and page_size & (page_size - 1) == 0
+        and all(t.stride(3) == 1 and all(t.stride(i) % 8 == 0 for i in range(3)) and t.data_ptr() % 16 == 0 for t in (k_cache, v_cache))
+    )
+
+
+def _cache_map(cache: torch.Tensor) -> int:
+    """Host address of a cached TMA descriptor of one layer's key (or value) pages."""
+    key = ("cache", cache.data_ptr(), tuple(cache.shape), tuple(cache.stride()))
+    held = _tensor_maps.get(key)
+    if held is None:
+        held = ctypes.create_string_buffer(128 + 64)
+        address = (ctypes.addressof(held) + 63) & ~63
+        ll = ctypes.c_longlong
+        fn = _fn("attention_decode_tma", "kb_attention_encode_cache_map", [c_void_p, c_void_p, ll, c_int, c_int, c_int, ll, ll, ll])
+        num_pages, page_size, num_kv_heads, head_dim = cache.shape
+        code = fn(address, cache.data_ptr(), num_pages, page_size, num_kv_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2))
+        if code != 0:
+            raise KernelError(f"tensor map encoding of the cache failed with code {code}")
+        if len(_tensor_maps) > 4096:
+            _tensor_maps.clear()
+        _tensor_maps[key] = held
+    return (ctypes.addressof(held) + 63) & ~63
 
 
 # ----------------------------------------------------------------------------- matrix products

@@ -33,6 +33,7 @@ LIBRARIES: dict[str, list[str]] = {
     "attention_generic": [],
     "attention_mma": [],
     "attention_decode_static": [],
+    "attention_decode_tma": [],
     "gemm_f32": [],
     "gemm_skinny": [],
     "gemm_tc5": [],

@@ -100,7 +100,7 @@ def test_engine_config_validates_and_rejects_unknown_keys():
         EngineConfig.from_kwargs(num_page=3)
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen3", "odd"])
+@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide"])
 def test_random_folder_round_trip(name, tmp_path):
     config, seed, _ = TINY[name]
     folder = write_random_model(config, tmp_path / name, seed=seed, dtype="float32")

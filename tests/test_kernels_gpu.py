@@ -319,8 +319,12 @@ def _attention_case(dtype, Hq, Hkv, D, page_size, seq_lens, chunk_lens, seed, ho
     num_pages = rows * max_pages + 3
     perm = torch.randperm(num_pages - 1, generator=g) + 1
     table = torch.full((rows, max_pages), -1, dtype=torch.int32)
-    kc = torch.zeros(num_pages, page_size, Hkv, D)
-    vc = torch.zeros_like(kc)
+    # Everything no request holds is NaN, but for page 0, which the cache manager keeps
+    # aside (and finite) for rows that stand in for absent ones: a kernel that lets a
+    # stale row into its sums shows it.
+    kc = torch.full((num_pages, page_size, Hkv, D), float("nan"))
+    kc[0] = 0.0
+    vc = kc.clone()
     used = 0
     for r, s in enumerate(seq_lens):
         n = -(-s // page_size)
@@ -362,7 +366,10 @@ def _reference_attention(case, Hq, scale, window):
     return out
 
 
-GEOMETRIES = [(4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 16), (32, 8, 128, 16), (8, 2, 80, 32), (2, 2, 256, 16), (6, 1, 64, 4)]
+GEOMETRIES = [
+    (4, 2, 16, 16), (6, 3, 32, 8), (5, 1, 48, 16), (32, 8, 128, 16), (8, 2, 80, 32), (2, 2, 256, 16), (6, 1, 64, 4),
+    (6, 2, 192, 8), (4, 1, 64, 64), (4, 2, 128, 128), (3, 3, 64, 32),
+]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -435,6 +442,27 @@ def test_mma_attention_random(Hq, Hkv, D, page_size, window, workspace):
     close(out, expected, 2e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page_size", [(8, 2, 64, 16), (32, 8, 128, 16), (6, 2, 192, 8), (2, 1, 256, 64)])
+@pytest.mark.parametrize("num_splits", [1, 2, 3, 7])
+@pytest.mark.parametrize("window", [0, 333])
+def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_size, num_splits, window, workspace):
+    """Few splits and long rows: every block of the TMA-fed kernel refills its stages several times."""
+    seq_lens = [1000, 700, 257, 64, 1]
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, [1] * len(seq_lens), seed=35)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+    rows = torch.arange(len(seq_lens), dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().attention_decode_mma(
+        case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), seq_lens=case["seq_lens"].to(DEV),
+        block_table=case["table"].to(DEV), decode_rows=rows, decode_tokens=rows, num_rows=len(seq_lens), max_seq_len=max(seq_lens),
+        num_q_heads=Hq, scale=scale, window=window, workspace=workspace, flag=flag, num_splits=num_splits,
+    )
+    assert int(flag.item()) == 0
+    close(out, expected, 2e-2)
+
+
 @pytest.mark.parametrize("hot_key", [0, 15, 16, 17, 63, 64, 127, 128, 129, 255, 256, 257, 511, 512, 640, 699])
 @pytest.mark.parametrize("chunk", [1, 2, 61])
 def test_mma_attention_finds_one_far_key(hot_key, chunk, workspace):
@@ -450,9 +478,9 @@ def test_mma_attention_finds_one_far_key(hot_key, chunk, workspace):
 
 
 @pytest.mark.parametrize("window,hot_key,inside", [(64, 636, True), (64, 635, False), (300, 400, True), (300, 399, False)])
-def test_mma_attention_window_edge(window, hot_key, inside, workspace):
+@pytest.mark.parametrize("Hq,Hkv,D,page_size", [(4, 4, 32, 8), (4, 2, 64, 16), (8, 1, 128, 64)])
+def test_mma_attention_window_edge(window, hot_key, inside, Hq, Hkv, D, page_size, workspace):
     """The dominating key sits exactly on, or one before, the window's edge of the last query."""
-    Hq, Hkv, D, page_size = 4, 4, 32, 8
     case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, [700], [1], seed=33, hot=(0, hot_key))
     scale = 1.0 / math.sqrt(D)
     expected = _reference_attention(case, Hq, scale, window)

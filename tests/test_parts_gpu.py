@@ -71,7 +71,7 @@ def close(got, expected, atol, rtol):
     assert bool((diff <= atol + rtol * expected.abs()).all()), f"max abs diff {diff.max().item():.3e}"
 
 
-CASES = [(n, d) for n in ("llama", "qwen3", "odd") for d in (torch.float32, torch.bfloat16)]
+CASES = [(n, d) for n in ("llama", "qwen3", "odd", "wide") for d in (torch.float32, torch.bfloat16)]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)

@@ -33,7 +33,7 @@ def write_model(tmp_path_factory, name, dtype):
     return folder
 
 
-@pytest.fixture(scope="module", params=["llama", "qwen3", "odd"])
+@pytest.fixture(scope="module", params=["llama", "qwen3", "odd", "wide"])
 def case(request, tmp_path_factory):
     name = request.param
     config, seed, page_size = TINY[name]

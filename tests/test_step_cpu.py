@@ -49,7 +49,7 @@ def cpu_kernels(monkeypatch):
     torch_kernels.install(monkeypatch)
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen3", "odd"])
+@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide"])
 def test_whole_prompts_match_plain(name):
     runner, config, weights = make_runner(name, num_pages=40)
     requests = traces.make_requests(config["vocab_size"], [1, 7, 33, 50], seed=11)

@@ -62,4 +62,25 @@ TINY_ODD = {
     "hidden_act": "silu",
 }
 
-TINY = {"llama": (TINY_LLAMA, 0, 16), "qwen3": (TINY_QWEN3, 1, 8), "odd": (TINY_ODD, 5, 16)}  # config, seed, page size
+# A fourth with a head size of 64, the smallest that the TMA-fed decode attention takes
+# (the others run its row-copy sibling): three query heads on one KV head, q/k norm, yarn-free
+# plain rope, a width that is no multiple of the head size.
+TINY_WIDE = {
+    "architectures": ["Qwen3ForCausalLM"],
+    "hidden_size": 88,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 3,
+    "num_key_value_heads": 1,
+    "head_dim": 64,
+    "intermediate_size": 136,
+    "vocab_size": 203,
+    "rope_theta": 20000.0,
+    "max_position_embeddings": 384,
+    "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": False,
+    "hidden_act": "silu",
+}
+
+TINY = {  # config, seed, page size
+    "llama": (TINY_LLAMA, 0, 16), "qwen3": (TINY_QWEN3, 1, 8), "odd": (TINY_ODD, 5, 16), "wide": (TINY_WIDE, 7, 8),
+}

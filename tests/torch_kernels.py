@@ -14,7 +14,7 @@ import torch
 
 import plain_model
 
-DECODE_SPLIT = 256
+DECODE_SPLIT = 128
 
 
 def embedding(table, ids, out, flag=None):
@@ -135,7 +135,7 @@ def attention_prefill_mma(q, out, k_cache, v_cache, *, qo_indptr, seq_lens, bloc
             out[t].copy_(res.reshape(-1).to(out.dtype))
 
 
-def attention_decode_mma(q, out, k_cache, v_cache, *, seq_lens, block_table, decode_rows, decode_tokens, num_rows, max_seq_len, num_q_heads, scale, window=0, workspace=None, flag=None):
+def attention_decode_mma(q, out, k_cache, v_cache, *, seq_lens, block_table, decode_rows, decode_tokens, num_rows, max_seq_len, num_q_heads, scale, window=0, workspace=None, flag=None, num_splits=None):
     dim = k_cache.shape[-1]
     for slot in range(num_rows):
         row = int(decode_rows[slot])
