@@ -15,9 +15,11 @@
 // compute, and release it.  The number of splits is chosen so that the grid fills the SMs
 // once; a block pays its start-up latency and its epilogue once, however long the context.
 // Partial results (unnormalised O, running max, running sum) go to scratch and a merge
-// kernel combines a row's splits in order.  Sizes: head_dim a multiple of 64 up to 256,
-// page_size a power of two from 8 up; anything else goes to the row-copy kernel of
-// attention_mma.cuh.
+// kernel combines a row's splits in order.  (Letting the block that finishes last among a
+// row's splits do the combination saves the launch but was slower on the decode step: its
+// fence, its counter and its dependent loads all sit on the critical path of the kernel's
+// end.)  Sizes: head_dim a multiple of 64 up to 256, page_size a power of two from 8 up;
+// anything else goes to the row-copy kernel of attention_mma.cuh.
 #include "attention_mma.cuh"
 
 #include <cuda.h>
@@ -27,6 +29,8 @@ namespace {
 
 constexpr int HALF_ELEMS = TILE_N * 64;  // one 64-column band of a tile: 64 rows of 128 bytes
 constexpr int CONSUMER_WARPS = 4;
+constexpr int MAX_SPLITS = 256;
+constexpr int MIN_TILES_PER_SPLIT = 4;   // shorter splits cost more in the combination than they save
 constexpr int TMA_THREADS = (CONSUMER_WARPS + 1) * 32;  // the last warp is the producer
 
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
@@ -444,7 +448,7 @@ KB_EXPORT int kb_attention_decode_tma_supported(int D, int page_size) {
 
 // Splits this kernel should be launched with for `num_rows` rows of up to `max_seq_len`
 // keys: as many as let rows * kv_heads * splits blocks be resident at once, at least 1, at
-// most one per 64-key tile.  Returns a negative KB_ERR_* code on error.
+// most one per four 64-key tiles and at most 256.  Returns a negative KB_ERR_* code on error.
 KB_EXPORT int kb_attention_decode_tma_splits(int num_rows, int Hkv, int D, int max_seq_len) {
     if (num_rows < 1 || Hkv < 1 || max_seq_len < 1) return KB_ERR_BAD_ARG;
     const int resident = resident_blocks_for(D);
@@ -452,9 +456,10 @@ KB_EXPORT int kb_attention_decode_tma_splits(int num_rows, int Hkv, int D, int m
     const long long pairs = (long long)num_rows * Hkv;
     long long splits = resident / pairs;
     const int tiles = (max_seq_len + TILE_N - 1) / TILE_N;
-    if (splits > tiles) splits = tiles;
+    const int worthwhile = (tiles + MIN_TILES_PER_SPLIT - 1) / MIN_TILES_PER_SPLIT;
+    if (splits > worthwhile) splits = worthwhile;
+    if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits < 1) splits = 1;
-    if (splits > 65535) splits = 65535;
     return (int)splits;
 }
 
@@ -489,7 +494,8 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
                                       cudaStream_t stream) {
     if (num_rows == 0) return 0;
     if (!map_k || !map_v || !q || !out || !seq_lens || !block_table || !decode_rows || !decode_tokens || !part_o || !part_ml) return KB_ERR_NULL;
-    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || Hkv > 65535 || num_splits < 1 || num_splits > 65535) return KB_ERR_BAD_ARG;
+    if (out_stride % 2 != 0) return KB_ERR_BAD_ARG;
+    if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || Hkv > 65535 || num_splits < 1 || num_splits > MAX_SPLITS) return KB_ERR_BAD_ARG;
     if (q_stride % 8 != 0) return KB_ERR_BAD_ARG;
     if (!kb_attention_decode_tma_supported(D, page_size)) return KB_ERR_UNSUPPORTED_SIZE;
     const CUtensorMap* mk = (const CUtensorMap*)map_k;

@@ -107,6 +107,7 @@ template <typename TX, typename TA, typename TW>
 __global__ void rmsnorm_vec_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
                                    const TW* __restrict__ w, TA* __restrict__ out,
                                    const int* __restrict__ rows, int H, float eps, int write_back) {
+    pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
     const int r = blockIdx.x;

@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                    int ldw, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out, int ldo,
                    int M, int N, int K) {
+    pdl_trigger();
     constexpr int HALVES = GATED ? 2 : 1;
     constexpr int KWARPS = SK_WARPS / HALVES;  // warps that split K for one half
     __shared__ float partial[SK_WARPS][NT][16][8 + 1];

@@ -14,9 +14,22 @@
 #define ROPE_WARPS 4
 #define ROPE_MAX_D 512
 
+template <typename T> struct Pair;
+template <> struct Pair<float> { using type = float2; };
+template <> struct Pair<__nv_bfloat16> { using type = __nv_bfloat162; };
+__device__ __forceinline__ float2 pair_to_float(float2 v) { return v; }
+__device__ __forceinline__ float2 pair_to_float(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename T> __device__ __forceinline__ typename Pair<T>::type pair_from_float(float a, float b);
+template <> __device__ __forceinline__ float2 pair_from_float<float>(float a, float b) { return make_float2(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 pair_from_float<__nv_bfloat16>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+
 // grid (tokens, ceil((Hq + 2*Hkv) / ROPE_WARPS)); one warp per head: q heads, then k
 // heads (norm + rotation, k also into the cache), then v heads (copied into the cache).
-template <typename T, typename TW>
+// PAIRED (the whole head rotates, 2 * rot_half == D, D a multiple of 4, 16-byte aligned rows):
+// a lane holds two neighbouring elements of the first half and their partners of the second
+// half in registers, so the rotation needs no shared memory and every access is two elements
+// wide; the v heads are copied 16 bytes at a time.  The arithmetic is the same either way.
+template <typename T, typename TW, bool PAIRED>
 __global__ void __launch_bounds__(ROPE_WARPS * 32)
 qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hkv, int D,
                              const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w,
@@ -26,6 +39,7 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
                              const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ write_from, T* __restrict__ k_cache,
                              T* __restrict__ v_cache, int page_size, int num_pages, int* flag) {
+    pdl_trigger();
     pdl_wait();
     __shared__ float head_buf[ROPE_WARPS][ROPE_MAX_D];
     const int t = blockIdx.x;
@@ -60,7 +74,65 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
     if (is_v) {
         if (slot >= 0) {
             T* vdst = v_cache + ((size_t)slot * Hkv + (head - Hq - Hkv)) * D;
-            for (int i = lane; i < D; i += 32) vdst[i] = x[i];
+            if (PAIRED) {
+                constexpr int PER = 16 / sizeof(T);
+                for (int i = lane * PER; i < D; i += 32 * PER)
+                    *reinterpret_cast<uint4*>(vdst + i) = *reinterpret_cast<const uint4*>(x + i);
+            } else {
+                for (int i = lane; i < D; i += 32) vdst[i] = x[i];
+            }
+        }
+        return;
+    }
+    if (PAIRED) {
+        using P2 = typename Pair<T>::type;
+        constexpr int MAX_J = ROPE_MAX_D / 128;  // a lane's pairs per half
+        const int half = D >> 1;
+        const TW* w = is_k ? k_norm_w : q_norm_w;
+        float2 a[MAX_J], b[MAX_J];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MAX_J; ++j) {
+            const int i = 2 * lane + 64 * j;
+            if (i < half) {
+                a[j] = pair_to_float(*reinterpret_cast<const P2*>(x + i));
+                b[j] = pair_to_float(*reinterpret_cast<const P2*>(x + half + i));
+                ss += a[j].x * a[j].x + a[j].y * a[j].y + b[j].x * b[j].x + b[j].y * b[j].y;
+            }
+        }
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int j = 0; j < MAX_J; ++j) {
+                const int i = 2 * lane + 64 * j;
+                if (i < half) {
+                    a[j].x = a[j].x * inv * to_float(w[i]);
+                    a[j].y = a[j].y * inv * to_float(w[i + 1]);
+                    b[j].x = b[j].x * inv * to_float(w[half + i]);
+                    b[j].y = b[j].y * inv * to_float(w[half + i + 1]);
+                }
+            }
+        }
+        const float* cos_row = cos_table + (size_t)pos * rot_half;
+        const float* sin_row = sin_table + (size_t)pos * rot_half;
+        T* kdst = (is_k && slot >= 0) ? k_cache + ((size_t)slot * Hkv + (head - Hq)) * D : nullptr;
+#pragma unroll
+        for (int j = 0; j < MAX_J; ++j) {
+            const int i = 2 * lane + 64 * j;
+            if (i < half) {
+                const float2 c = *reinterpret_cast<const float2*>(cos_row + i);
+                const float2 sn = *reinterpret_cast<const float2*>(sin_row + i);
+                // rotate_half(u) = cat(-u[half:], u[:half])
+                const P2 lo = pair_from_float<T>(a[j].x * c.x - b[j].x * sn.x, a[j].y * c.y - b[j].y * sn.y);
+                const P2 hi = pair_from_float<T>(b[j].x * c.x + a[j].x * sn.x, b[j].y * c.y + a[j].y * sn.y);
+                *reinterpret_cast<P2*>(x + i) = lo;
+                *reinterpret_cast<P2*>(x + half + i) = hi;
+                if (kdst) {
+                    *reinterpret_cast<P2*>(kdst + i) = lo;
+                    *reinterpret_cast<P2*>(kdst + half + i) = hi;
+                }
+            }
         }
         return;
     }
@@ -118,18 +190,26 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
     const int threads = ROPE_WARPS * 32;
     if (Hq + 2 * Hkv > 65535 * ROPE_WARPS) return KB_ERR_UNSUPPORTED_SIZE;
     dim3 grid(T, (Hq + 2 * Hkv + ROPE_WARPS - 1) / ROPE_WARPS);
-#define LAUNCH(T_, TW_)                                                                         \
-    kb_launch(qk_norm_rope_kv_write_kernel<T_, TW_>, dim3(grid), dim3(threads), 0, stream,                            \
+    // The paired path wants the whole head rotated and every row of qkv and of the caches on a 16-byte boundary.
+    const size_t elem = is_bf16 ? 2 : 4;
+    const bool paired = cos_table != nullptr && sin_table != nullptr && rot_half > 0 && 2 * rot_half == D && D % 4 == 0 &&
+                        (D * elem) % 16 == 0 && ((size_t)qkv_stride * elem) % 16 == 0 && ((uintptr_t)qkv % 16) == 0 &&
+                        ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
+                        ((uintptr_t)cos_table % 8) == 0 && ((uintptr_t)sin_table % 8) == 0;
+#define LAUNCH(T_, TW_, P_)                                                                     \
+    kb_launch(qk_norm_rope_kv_write_kernel<T_, TW_, P_>, dim3(grid), dim3(threads), 0, stream,  \
         (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps,      \
         cos_table, sin_table, rot_half, max_pos, positions, row_ids, block_table, max_pages,    \
         write_from, (T_*)k_cache, (T_*)v_cache, page_size, num_pages, flag)
+#define PICK(T_, TW_) do { if (paired) LAUNCH(T_, TW_, true); else LAUNCH(T_, TW_, false); } while (0)
     if (is_bf16) {
-        if (norm_w_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
-        else LAUNCH(__nv_bfloat16, float);
+        if (norm_w_bf16) PICK(__nv_bfloat16, __nv_bfloat16);
+        else PICK(__nv_bfloat16, float);
     } else {
-        if (norm_w_bf16) LAUNCH(float, __nv_bfloat16);
-        else LAUNCH(float, float);
+        if (norm_w_bf16) PICK(float, __nv_bfloat16);
+        else PICK(float, float);
     }
+#undef PICK
 #undef LAUNCH
     return kb_launch_result();
 }
