@@ -1,0 +1,423 @@
+// Flash attention over the paged cache for rows that carry several tokens, on the
+// 5th-generation tensor cores (kairyu/models/attention.py:203-240 is the arithmetic):
+//
+//     S = Q K^T * scale (causal, optional window),  P = softmax rows online,  O = P V.
+//
+// A block owns 128 queries of one head (a tile of the tile list) and walks the keys it may see
+// in tiles of 64.  Roles (192 threads):
+//   warp 0     producer: TMA copies of the Q tile (2-D map over the packed qkv rows) and of
+//              every K and V tile (4-D map over the cache: a copy brings a page's run of rows
+//              for one KV head), two stages ahead of their use;
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T into 64 TMEM columns, O += P V into
+//              head_dim TMEM columns.  It issues the next tile's Q K^T before this tile's P V,
+//              so the tensor pipe works on the one while the softmax warps work on the other;
+//   warps 2-5  softmax: thread r owns query row r.  It reads its row of S from TMEM
+//              (tcgen05.ld), so the row maximum and sum need no shuffles; writes P as bf16
+//              into shared memory in the K-major swizzled layout the tensor core reads; and
+//              rescales O in TMEM only when the row maximum has grown by more than 2^8 since
+//              the reference it scales by (P stays below 256, sums stay exact enough in fp32).
+// V is the B operand of O += P V with its N index (the head dimension) contiguous: an
+// MN-major operand, read straight from the [key][dim] rows the cache holds.
+// Two blocks share an SM (2 x 256 TMEM columns, 2 x 113 KB of shared memory), so one block's
+// softmax overlaps the other's products.
+//
+// Every wait on an mbarrier is bounded: a role that gives up raises KB_FLAG_TIMEOUT, lets the
+// other roles leave through a shared abort word, and the block frees its TMEM and returns.
+// Sizes: head_dim 64 or 128, page_size a power of two from 8 up; others go to the mma.sync
+// kernel of attention_mma.cuh.
+#include "umma.cuh"
+
+#define FA_THREADS 192
+#define FA_BM 128
+#define FA_BN 64
+#define FA_STAGES 2
+#define FA_LOG2E 1.4426950408889634f
+#define FA_RESCALE_STEP 8.0f
+#define KB_FLAG_MISALIGNED 32
+
+template <int D>
+struct FaCfg {
+    static constexpr int BANDS = D / 64;                 // 64-column (128-byte) bands of a row
+    static constexpr int Q_BAND = FA_BM * 128;           // bytes of one band of the Q tile
+    static constexpr int KV_BAND = FA_BN * 128;          // bytes of one band of a K or V tile
+    static constexpr int Q_BYTES = BANDS * Q_BAND;
+    static constexpr int KV_BYTES = BANDS * KV_BAND;
+    static constexpr int P_BYTES = FA_BM * FA_BN * 2;
+    static constexpr int OFF_K = Q_BYTES;
+    static constexpr int OFF_V = OFF_K + FA_STAGES * KV_BYTES;
+    static constexpr int OFF_P = OFF_V + FA_STAGES * KV_BYTES;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;
+    static constexpr int NUM_BARS = 1 + 3 * FA_STAGES + 4;
+    static constexpr size_t SMEM = OFF_BAR + NUM_BARS * 8 + 16;
+    static constexpr int S_COL = 0;
+    static constexpr int O_COL = FA_BN;
+    static constexpr int TMEM_COLUMNS = (FA_BN + D) <= 128 ? 128 : 256;
+    static constexpr int BLOCKS_PER_SM = 2;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FA_THREADS, FaCfg<D>::BLOCKS_PER_SM)
+attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int out_stride,
+                             const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens,
+                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
+                             const int* __restrict__ tile_starts, int Hq, int Hkv, int page_size, int page_shift, int num_pages,
+                             float scale, int window, int* flag) {
+    using Cfg = FaCfg<D>;
+    constexpr int BANDS = Cfg::BANDS;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* sQ = smem;
+    unsigned char* sK = smem + Cfg::OFF_K;
+    unsigned char* sV = smem + Cfg::OFF_V;
+    unsigned char* sP = smem + Cfg::OFF_P;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+    uint64_t* q_full = bars;
+    uint64_t* k_full = bars + 1;
+    uint64_t* v_full = k_full + FA_STAGES;
+    uint64_t* kv_empty = v_full + FA_STAGES;
+    uint64_t* s_full = kv_empty + FA_STAGES;
+    uint64_t* s_free = s_full + 1;
+    uint64_t* p_full = s_free + 1;
+    uint64_t* pv_done = p_full + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
+    volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_q);
+        prefetch_tensormap(&map_k);
+        prefetch_tensormap(&map_v);
+        mbar_init(q_full, 1);
+        for (int s = 0; s < FA_STAGES; ++s) {
+            mbar_init(k_full + s, 1);
+            mbar_init(v_full + s, 1);
+            mbar_init(kv_empty + s, 1);
+        }
+        mbar_init(s_full, 1);
+        mbar_init(s_free, 4);
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        *abort_word = 0;
+        if ((smem_addr(smem) & 1023u) != 0) {  // the swizzled layouts below assume it
+            if (flag) atomicOr(flag, KB_FLAG_MISALIGNED);
+            *abort_word = 1;
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        fence_proxy_async_smem();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLUMNS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+
+    // Later tiles of a portion see more keys and run longer: hand them out first.
+    const int tile = gridDim.y - 1 - blockIdx.y;
+    const int h = blockIdx.x;
+    const int kvh = h / (Hq / Hkv);
+    const int row = tile_rows[tile];
+    const int q0 = tile_starts[tile];
+    const int tok0 = qo_indptr[row];
+    const int chunk_len = qo_indptr[row + 1] - tok0;
+    const int seq_len = seq_lens[row];
+    const int chunk_pos = seq_len - chunk_len;  // absolute position of the portion's first token
+    const int rows_here = min(FA_BM, chunk_len - q0);
+    const int first_pos = chunk_pos + q0;
+    const int last_pos = first_pos + rows_here - 1;
+    const int key_end = last_pos + 1;  // causal bound of the tile (<= seq_len)
+    const int key_lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+    const int first_kt = key_lo / FA_BN;
+    const int last_kt = (key_end - 1) / FA_BN;
+    const int num_kt = last_kt - first_kt + 1;
+
+    if (*abort_word) {
+        // fall through to the common exit
+    } else if (warp == 0) {
+        // ---------------- producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
+#pragma unroll
+            for (int band = 0; band < BANDS; ++band)
+                tma_load_2d_plain(sQ + band * Cfg::Q_BAND, &map_q, h * D + band * 64, tok0 + q0, q_full);
+        }
+        const int* table = block_table + (size_t)row * max_pages;
+        const int box_rows = page_size < FA_BN ? page_size : FA_BN;
+        const int runs = FA_BN / box_rows;
+        const int per_tile = 2 * BANDS * runs;
+        for (int j = 0; j < num_kt; ++j) {
+            const int st = j % FA_STAGES;
+            const int use = j / FA_STAGES;
+            if (use > 0 && !mbar_wait(kv_empty + st, (use - 1) & 1, abort_word)) {
+                if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+                *abort_word = 1;
+                break;
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(k_full + st, Cfg::KV_BYTES);
+                mbar_arrive_expect_tx(v_full + st, Cfg::KV_BYTES);
+            }
+            __syncwarp();
+            for (int op = lane; op < per_tile; op += 32) {
+                const int is_v = op / (BANDS * runs);
+                const int rest = op % (BANDS * runs);
+                const int band = rest / runs;
+                const int run = rest % runs;
+                const int key = (first_kt + j) * FA_BN + run * box_rows;
+                const int page_index = key >> page_shift;
+                int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
+                if (key < key_end && key + box_rows > key_lo && page_index < max_pages) {
+                    const int p = table[page_index];
+                    if (p >= 0 && p < num_pages) {
+                        page = p;
+                        within = key - (page_index << page_shift);
+                    }
+                }
+                unsigned char* dst = (is_v ? sV : sK) + st * Cfg::KV_BYTES + band * Cfg::KV_BAND + run * box_rows * 128;
+                tma_load_4d_plain(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, (is_v ? v_full : k_full) + st);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (one thread)
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc(FA_BN);
+            constexpr uint32_t idesc_pv = umma_idesc_b_mn(D);
+            const uint32_t q_addr = smem_addr(sQ);
+            const uint32_t p_addr = smem_addr(sP);
+            bool ok = true;
+            auto give_up = [&]() {
+                if (!*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+                *abort_word = 1;
+                ok = false;
+            };
+            auto issue_qk = [&](int j) {
+                const uint32_t k_addr = smem_addr(sK) + (j % FA_STAGES) * Cfg::KV_BYTES;
+#pragma unroll
+                for (int band = 0; band < BANDS; ++band)
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)  // 16 of the head dimension = 32 bytes along the swizzled row
+                        umma_bf16(tmem_base + Cfg::S_COL, umma_desc_sw128(q_addr + band * Cfg::Q_BAND + k * 32),
+                                  umma_desc_sw128(k_addr + band * Cfg::KV_BAND + k * 32), idesc_qk, (band > 0 || k > 0) ? 1u : 0u);
+                umma_commit(s_full);
+            };
+            if (!mbar_wait(q_full, 0, abort_word) || !mbar_wait(k_full, 0, abort_word)) give_up();
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; j < num_kt && ok; ++j) {
+                const int st = j % FA_STAGES;
+                if (j + 1 < num_kt) {
+                    // S is free once the softmax warps hold tile j in registers: start tile j + 1
+                    if (!mbar_wait(s_free, j & 1, abort_word) ||
+                        !mbar_wait(k_full + (j + 1) % FA_STAGES, ((j + 1) / FA_STAGES) & 1, abort_word)) {
+                        give_up();
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                if (!mbar_wait(p_full, j & 1, abort_word) || !mbar_wait(v_full + st, (j / FA_STAGES) & 1, abort_word)) {
+                    give_up();
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_addr = smem_addr(sV) + st * Cfg::KV_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < FA_BN / 16; ++ks)  // 16 keys: 32 bytes along a row of P, 16 rows of V
+                    umma_bf16(tmem_base + Cfg::O_COL, umma_desc_sw128(p_addr + ks * 32),
+                              umma_desc_mn_sw128(v_addr + ks * 16 * 128, Cfg::KV_BAND, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(kv_empty + st);  // the stage may be refilled once these products have read it
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        // ---------------- softmax and epilogue: thread r owns query row r
+        const int quarter = warp & 3;  // the TMEM lanes this warp may touch
+        const int r = quarter * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const bool valid = r < rows_here;
+        const int pos = valid ? first_pos + r : last_pos;
+        const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+        const int lo_last = (window > 0 && last_pos + 1 > window) ? last_pos + 1 - window : 0;
+        const int soft_tid = threadIdx.x - 64;  // 0..127
+        const float sl2 = scale * FA_LOG2E;
+        float m_ref = -INFINITY;  // the maximum the row's P and O are scaled by
+        float l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < num_kt; ++j) {
+            const int key0 = (first_kt + j) * FA_BN;
+            if (!mbar_wait(s_full, j & 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t raw[2][32];
+            tmem_load32_nowait(lane_base + Cfg::S_COL, raw[0]);
+            tmem_load32_nowait(lane_base + Cfg::S_COL + 32, raw[1]);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
+            float t[FA_BN];
+#pragma unroll
+            for (int c = 0; c < FA_BN; ++c) t[c] = __uint_as_float(raw[c >> 5][c & 31]) * sl2;
+            if (key0 + FA_BN - 1 > first_pos || key0 < lo_last) {  // the diagonal or the window's edge crosses this tile
+#pragma unroll
+                for (int c = 0; c < FA_BN; ++c) {
+                    const int key = key0 + c;
+                    t[c] = (key <= pos && key >= lo) ? t[c] : -INFINITY;
+                }
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < FA_BN; ++c) mx = fmaxf(mx, t[c]);
+            float alpha = 1.0f;
+            if (m_ref == -INFINITY) {
+                m_ref = mx;  // nothing accumulated for this row yet
+            } else if (mx > m_ref + FA_RESCALE_STEP) {
+                alpha = exp2f(m_ref - mx);
+                m_ref = mx;
+            }
+            // P V of the tile before must be complete before O is rescaled or P overwritten
+            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
+            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_load32_nowait(lane_base + Cfg::O_COL + c * 32, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_store32(lane_base + Cfg::O_COL + c * 32, o);
+                }
+                tmem_wait_st();
+                l *= alpha;
+            }
+            const float base = m_ref == -INFINITY ? 0.0f : m_ref;
+            float sum = 0.0f;
+            uint32_t packed[FA_BN / 2];
+#pragma unroll
+            for (int c = 0; c < FA_BN; c += 2) {
+                const float p0 = exp2f(t[c] - base);
+                const float p1 = exp2f(t[c + 1] - base);
+                sum += p0 + p1;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+            }
+            l += sum;
+            unsigned char* p_row = sP + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)  // 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) =
+                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            if (key0 + FA_BN > key_end) {
+                // Keys beyond the last query have probability 0, but 0 * NaN is NaN and what lies
+                // beyond a request's length may be anything: clear those rows of V.
+                const int st = j % FA_STAGES;
+                if (!mbar_wait(v_full + st, (j / FA_STAGES) & 1, abort_word)) { ok = false; break; }
+                unsigned char* v_tile = sV + st * Cfg::KV_BYTES;
+                for (int idx = soft_tid; idx < FA_BN * BANDS * 8; idx += 128) {
+                    const int vr = idx / (BANDS * 8);
+                    const int c = idx % (BANDS * 8);
+                    if (key0 + vr >= key_end)
+                        *reinterpret_cast<uint4*>(v_tile + (c >> 3) * Cfg::KV_BAND + vr * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (ok && !mbar_wait(pv_done, (num_kt - 1) & 1, abort_word)) ok = false;
+        if (!ok) {
+            if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+            *abort_word = 1;
+        } else {
+            tc_fence_after();
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_load32_nowait(lane_base + Cfg::O_COL + c * 32, o);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(o[8 * i + 2 * e]) * inv,
+                                                                        __uint_as_float(o[8 * i + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<uint32_t*>(&pair);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_word && threadIdx.x == 0) {
+        // copies that are still in flight target this block's shared memory: one more bounded wait
+        volatile int never = 0;
+        for (int s = 0; s < 1 + 2 * FA_STAGES; ++s) {
+            for (uint32_t spin = 0; spin < 1024; ++spin) {
+                uint32_t done;
+                asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                             : "=r"(done)
+                             : "r"(smem_addr(bars + s)), "r"(0u)
+                             : "memory");
+                if (done || never) break;
+            }
+        }
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLUMNS);
+    }
+}
+
+template <int D>
+static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, __nv_bfloat16* out, int out_stride,
+                     const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages, const int* tile_rows,
+                     const int* tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int num_pages, float scale, int window,
+                     int* flag, cudaStream_t stream) {
+    const size_t smem = FaCfg<D>::SMEM;
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
+    dim3 grid(Hq, num_tiles);
+    kb_launch(attention_prefill_tc5_kernel<D>, dim3(grid), dim3(FA_THREADS), smem, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
+              seq_lens, block_table, max_pages, tile_rows, tile_starts, Hq, Hkv, page_size, shift, num_pages, scale, window, flag);
+    return kb_launch_result();
+}
+
+// 1 when (head_dim, page_size) fit this kernel.
+KB_EXPORT int kb_attention_prefill_tc5_supported(int D, int page_size) {
+    if (D != 64 && D != 128) return 0;
+    if (page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
+    return 1;
+}
+
+// map_q: 2-D map over the packed qkv rows [tokens, q_stride] with boxes of [128 rows, 64 columns];
+// map_k, map_v: 4-D maps over the caches [pages, page_size, kv_heads, head_dim] with boxes of
+// 64 columns x 1 head x min(page_size, 64) positions x 1 page; all with the 128-byte swizzle
+// (host pointers).  The tile list holds 128 queries per tile.
+KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, const void* map_v, void* out, int out_stride,
+                                       const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages,
+                                       const int* tile_rows, const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
+                                       int page_size, int num_pages, float scale, int window, int* flag, cudaStream_t stream) {
+    if (num_tiles == 0) return 0;
+    if (!map_q || !map_k || !map_v || !out || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
+    if (Hkv < 1 || Hq % Hkv != 0 || num_tiles > 65535) return KB_ERR_BAD_ARG;
+    if (out_stride % 8 != 0 || ((uintptr_t)out % 16) != 0) return KB_ERR_BAD_ARG;  // 16-byte stores of whole rows
+    if (!kb_attention_prefill_tc5_supported(D, page_size)) return KB_ERR_UNSUPPORTED_SIZE;
+#define ARGS (const CUtensorMap*)map_q, (const CUtensorMap*)map_k, (const CUtensorMap*)map_v, (__nv_bfloat16*)out, out_stride, qo_indptr, \
+             seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, num_pages, scale, window, flag, stream
+    if (D == 64) return launch_fa<64>(ARGS);
+    return launch_fa<128>(ARGS);
+#undef ARGS
+}

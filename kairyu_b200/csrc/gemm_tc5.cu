@@ -13,109 +13,11 @@
 //
 // Every wait on an mbarrier is bounded: a block that gives up raises KB_FLAG_TIMEOUT, lets
 // its other roles leave through a shared abort word, frees its TMEM and returns.
-#include <cuda.h>
-#include <cudaTypedefs.h>
+#include "umma.cuh"
 
-#include "common.cuh"
-
-#define KB_FLAG_TIMEOUT 16
 #define TC_THREADS 192
-#define TC_BLOCK_ROWS 128  // weight rows per block (UMMA M)
 #define TC_BLOCK_K 64      // k per pipeline stage: 128 bytes of bf16, one swizzle row
-#define TC_SPIN_LIMIT (1u << 22)
 #define TC_SMEM_BUDGET (200 * 1024)
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait; also leaves when another role of the block has raised `abort`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if ((spin & 63) == 63 && *abort) return false;
-    }
-    return false;
-}
-__device__ __forceinline__ uint64_t policy_evict_first() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(p));
-    return p;
-}
-__device__ __forceinline__ uint64_t policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;\n" : "=l"(p));
-    return p;
-}
-// 2-D tiled TMA load: box at (c0 = k element, c1 = row) into shared memory, bytes counted on `bar`.
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;\n" ::"r"(
-            smem_addr(dst)),
-        "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "l"(policy)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t columns) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(slot_in_smem)), "r"(columns) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(address), "r"(columns) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-// D[tmem] (+)= A[smem] * B[smem]^T, bf16 inputs, fp32 accumulate, issued by one thread.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// The mbarrier gets one arrival when every MMA issued so far by this thread has finished.
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-// 16 consecutive fp32 columns of this warp's 32 TMEM lanes (thread t gets lane t of the warp's quarter).
-__device__ __forceinline__ void tmem_load16(uint32_t address, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(address)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory operand descriptor: K-major tile whose rows are 128 bytes (64 bf16), written by
-// TMA with the 128-byte swizzle; groups of 8 rows are 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_byte_address) {
-    uint64_t desc = 0;
-    desc |= (uint64_t)((smem_byte_address & 0x3FFFF) >> 4);  // start address
-    desc |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle)
-    desc |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: next 8-row group
-    desc |= (uint64_t)1 << 46;                               // descriptor version of sm_100
-    desc |= (uint64_t)2 << 61;                               // 128-byte swizzle
-    return desc;
-}
-// Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BLOCK_ROWS >> 4) << 24);
-}
 
 template <int NTOK, bool GATED>
 struct TcConfig {

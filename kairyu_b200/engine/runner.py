@@ -487,4 +487,6 @@ class ModelRunner:
                 reasons.append("a position outside the rotary table")
             if flag & 16:
                 reasons.append("a copy into shared memory did not complete within its wait limit")
+            if flag & 32:
+                reasons.append("a block's shared memory did not start on the 1024-byte boundary its swizzled tiles need")
             raise StepError("a kernel refused an index: " + "; ".join(reasons))

@@ -28,6 +28,7 @@ FLAG_BAD_TOKEN = 2
 FLAG_BAD_ROW = 4
 FLAG_BAD_POS = 8
 FLAG_TIMEOUT = 16
+FLAG_MISALIGNED = 32
 
 _CODES = {
     -1: "bad argument",
@@ -346,6 +347,22 @@ def attention_prefill_mma(
     num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
     if not attention_mma_supported(head_dim, num_q_heads, num_kv_heads):
         raise KernelError(f"{what}: head_dim {head_dim} with {num_q_heads}/{num_kv_heads} heads is not supported")
+    if _prefill_tc5_ok(q, out, k_cache, v_cache):  # tcgen05 + TMA: S and O in tensor memory
+        fn = _fn(
+            "attention_prefill_tc5",
+            "kb_attention_prefill_tc5",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+        )
+        _check(
+            fn(
+                _tensor_map(q, 128), _cache_map(k_cache), _cache_map(v_cache), out.data_ptr(), out.stride(0),
+                qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+                tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
+                page_size, num_pages, float(scale), int(window), _ptr(flag), _stream(),
+            ),
+            what,
+        )
+        return
     fn = _fn(
         "attention_mma",
         "kb_attention_prefill_mma",
@@ -435,6 +452,16 @@ def attention_decode_mma(
         ),
         what,
         launches=2,
+    )
+
+
+def _prefill_tc5_ok(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> bool:
+    head_dim = k_cache.shape[3]
+    return (
+        head_dim in (64, 128)
+        and _decode_tma_ok(k_cache, v_cache)
+        and q.stride(1) == 1 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+        and out.stride(1) == 1 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
     )
 
 

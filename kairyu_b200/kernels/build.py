@@ -34,6 +34,7 @@ LIBRARIES: dict[str, list[str]] = {
     "attention_mma": [],
     "attention_decode_static": [],
     "attention_decode_tma": [],
+    "attention_prefill_tc5": [],
     "gemm_f32": [],
     "gemm_skinny": [],
     "gemm_tc5": [],
