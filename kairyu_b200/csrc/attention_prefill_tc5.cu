@@ -8,17 +8,18 @@
 //   warp 0     producer: TMA copies of the Q tile (2-D map over the packed qkv rows) and of
 //              every K and V tile (4-D map over the cache: a copy brings a page's run of rows
 //              for one KV head), two stages ahead of their use;
-//   warp 1     one thread issues tcgen05.mma: S = Q K^T into 64 TMEM columns, O += P V into
-//              head_dim TMEM columns.  It issues the next tile's Q K^T before this tile's P V,
-//              so the tensor pipe works on the one while the softmax warps work on the other;
+//   warp 1     one thread issues tcgen05.mma: S = Q K^T into one of two buffers of 64 TMEM
+//              columns, O += P V into head_dim TMEM columns.  Q K^T runs two tiles ahead of
+//              P V, so the softmax warps never wait for their S;
 //   warps 2-5  softmax: thread r owns query row r.  It reads its row of S from TMEM
 //              (tcgen05.ld), so the row maximum and sum need no shuffles; writes P as bf16
-//              into shared memory in the K-major swizzled layout the tensor core reads; and
-//              rescales O in TMEM only when the row maximum has grown by more than 2^8 since
-//              the reference it scales by (P stays below 256, sums stay exact enough in fp32).
+//              pairs back into tensor memory over its row of S (tcgen05.st), from where the
+//              tensor core reads it as the A operand of P V; and rescales O in TMEM only when
+//              the row maximum has grown by more than 2^8 since the reference it scales by
+//              (P stays below 256, sums stay exact enough in fp32).
 // V is the B operand of O += P V with its N index (the head dimension) contiguous: an
 // MN-major operand, read straight from the [key][dim] rows the cache holds.
-// Two blocks share an SM (2 x 256 TMEM columns, 2 x 113 KB of shared memory), so one block's
+// Two blocks share an SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory), so one block's
 // softmax overlaps the other's products.
 //
 // Every wait on an mbarrier is bounded: a role that gives up raises KB_FLAG_TIMEOUT, lets the
@@ -42,16 +43,14 @@ struct FaCfg {
     static constexpr int KV_BAND = FA_BN * 128;          // bytes of one band of a K or V tile
     static constexpr int Q_BYTES = BANDS * Q_BAND;
     static constexpr int KV_BYTES = BANDS * KV_BAND;
-    static constexpr int P_BYTES = FA_BM * FA_BN * 2;
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + FA_STAGES * KV_BYTES;
-    static constexpr int OFF_P = OFF_V + FA_STAGES * KV_BYTES;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;
-    static constexpr int NUM_BARS = 1 + 3 * FA_STAGES + 4;
+    static constexpr int OFF_BAR = OFF_V + FA_STAGES * KV_BYTES;
+    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 2;
     static constexpr size_t SMEM = OFF_BAR + NUM_BARS * 8 + 16;
-    static constexpr int S_COL = 0;
-    static constexpr int O_COL = FA_BN;
-    static constexpr int TMEM_COLUMNS = (FA_BN + D) <= 128 ? 128 : 256;
+    static constexpr int S_COL = 0;          // two S buffers of FA_BN columns each; P (bf16 pairs) overwrites the first half of its S
+    static constexpr int O_COL = 2 * FA_BN;
+    static constexpr int TMEM_COLUMNS = 256;
     static constexpr int BLOCKS_PER_SM = 2;
 };
 
@@ -69,15 +68,14 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     unsigned char* sQ = smem;
     unsigned char* sK = smem + Cfg::OFF_K;
     unsigned char* sV = smem + Cfg::OFF_V;
-    unsigned char* sP = smem + Cfg::OFF_P;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
     uint64_t* q_full = bars;
     uint64_t* k_full = bars + 1;
     uint64_t* v_full = k_full + FA_STAGES;
-    uint64_t* kv_empty = v_full + FA_STAGES;
-    uint64_t* s_full = kv_empty + FA_STAGES;
-    uint64_t* s_free = s_full + 1;
-    uint64_t* p_full = s_free + 1;
+    uint64_t* k_empty = v_full + FA_STAGES;
+    uint64_t* v_empty = k_empty + FA_STAGES;
+    uint64_t* s_full = v_empty + FA_STAGES;  // one per S buffer
+    uint64_t* p_full = s_full + 2;
     uint64_t* pv_done = p_full + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -92,10 +90,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         for (int s = 0; s < FA_STAGES; ++s) {
             mbar_init(k_full + s, 1);
             mbar_init(v_full + s, 1);
-            mbar_init(kv_empty + s, 1);
+            mbar_init(k_empty + s, 1);
+            mbar_init(v_empty + s, 1);
         }
         mbar_init(s_full, 1);
-        mbar_init(s_free, 4);
+        mbar_init(s_full + 1, 1);
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
         *abort_word = 0;
@@ -145,37 +144,39 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int* table = block_table + (size_t)row * max_pages;
         const int box_rows = page_size < FA_BN ? page_size : FA_BN;
         const int runs = FA_BN / box_rows;
-        const int per_tile = 2 * BANDS * runs;
-        for (int j = 0; j < num_kt; ++j) {
+        const int per_kind = BANDS * runs;  // copies of a K (or V) tile
+        bool ok = true;
+        for (int j = 0; j < num_kt && ok; ++j) {
             const int st = j % FA_STAGES;
             const int use = j / FA_STAGES;
-            if (use > 0 && !mbar_wait(kv_empty + st, (use - 1) & 1, abort_word)) {
-                if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
-                *abort_word = 1;
-                break;
-            }
-            if (lane == 0) {
-                mbar_arrive_expect_tx(k_full + st, Cfg::KV_BYTES);
-                mbar_arrive_expect_tx(v_full + st, Cfg::KV_BYTES);
-            }
-            __syncwarp();
-            for (int op = lane; op < per_tile; op += 32) {
-                const int is_v = op / (BANDS * runs);
-                const int rest = op % (BANDS * runs);
-                const int band = rest / runs;
-                const int run = rest % runs;
-                const int key = (first_kt + j) * FA_BN + run * box_rows;
-                const int page_index = key >> page_shift;
-                int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
-                if (key < key_end && key + box_rows > key_lo && page_index < max_pages) {
-                    const int p = table[page_index];
-                    if (p >= 0 && p < num_pages) {
-                        page = p;
-                        within = key - (page_index << page_shift);
-                    }
+#pragma unroll
+            for (int is_v = 0; is_v < 2; ++is_v) {
+                // K's slot is free once Q K^T of the tile that used it is done, V's once its P V is done
+                if (use > 0 && !mbar_wait((is_v ? v_empty : k_empty) + st, (use - 1) & 1, abort_word)) {
+                    if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+                    *abort_word = 1;
+                    ok = false;
+                    break;
                 }
-                unsigned char* dst = (is_v ? sV : sK) + st * Cfg::KV_BYTES + band * Cfg::KV_BAND + run * box_rows * 128;
-                tma_load_4d_plain(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, (is_v ? v_full : k_full) + st);
+                uint64_t* bar = (is_v ? v_full : k_full) + st;
+                if (lane == 0) mbar_arrive_expect_tx(bar, Cfg::KV_BYTES);
+                __syncwarp();
+                for (int op = lane; op < per_kind; op += 32) {
+                    const int band = op / runs;
+                    const int run = op % runs;
+                    const int key = (first_kt + j) * FA_BN + run * box_rows;
+                    const int page_index = key >> page_shift;
+                    int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
+                    if (key < key_end && key + box_rows > key_lo && page_index < max_pages) {
+                        const int p = table[page_index];
+                        if (p >= 0 && p < num_pages) {
+                            page = p;
+                            within = key - (page_index << page_shift);
+                        }
+                    }
+                    unsigned char* dst = (is_v ? sV : sK) + st * Cfg::KV_BYTES + band * Cfg::KV_BAND + run * box_rows * 128;
+                    tma_load_4d_plain(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, bar);
+                }
             }
         }
     } else if (warp == 1) {
@@ -183,53 +184,65 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc(FA_BN);
             constexpr uint32_t idesc_pv = umma_idesc_b_mn(D);
-            const uint32_t q_addr = smem_addr(sQ);
-            const uint32_t p_addr = smem_addr(sP);
+            // Descriptors differ only in their start address (bits 0-13, in 16-byte units): build
+            // one of each kind and add offsets.
+            const uint64_t q_desc = umma_desc_sw128(smem_addr(sQ));
+            const uint64_t k_desc = umma_desc_sw128(smem_addr(sK));
+            const uint64_t v_desc = umma_desc_mn_sw128(smem_addr(sV), Cfg::KV_BAND, 1024);
             bool ok = true;
             auto give_up = [&]() {
                 if (!*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
                 *abort_word = 1;
                 ok = false;
             };
+            // S[j % 2] = Q K_j^T; releases K's slot and tells the softmax warps
             auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_addr(sK) + (j % FA_STAGES) * Cfg::KV_BYTES;
+                const int st = j % FA_STAGES;
+                const uint64_t k_tile = k_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
 #pragma unroll
                 for (int band = 0; band < BANDS; ++band)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)  // 16 of the head dimension = 32 bytes along the swizzled row
-                        umma_bf16(tmem_base + Cfg::S_COL, umma_desc_sw128(q_addr + band * Cfg::Q_BAND + k * 32),
-                                  umma_desc_sw128(k_addr + band * Cfg::KV_BAND + k * 32), idesc_qk, (band > 0 || k > 0) ? 1u : 0u);
-                umma_commit(s_full);
+                        umma_bf16(tmem_base + Cfg::S_COL + (j & 1) * FA_BN, q_desc + (uint64_t)((band * Cfg::Q_BAND + k * 32) >> 4),
+                                  k_tile + (uint64_t)((band * Cfg::KV_BAND + k * 32) >> 4), idesc_qk, (band > 0 || k > 0) ? 1u : 0u);
+                umma_commit(k_empty + st);
+                umma_commit(s_full + (j & 1));
             };
             if (!mbar_wait(q_full, 0, abort_word) || !mbar_wait(k_full, 0, abort_word)) give_up();
             if (ok) {
                 tc_fence_after();
                 issue_qk(0);
             }
+            if (ok && num_kt > 1) {
+                if (!mbar_wait(k_full + 1, 0, abort_word)) give_up();
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(1);
+                }
+            }
             for (int j = 0; j < num_kt && ok; ++j) {
                 const int st = j % FA_STAGES;
-                if (j + 1 < num_kt) {
-                    // S is free once the softmax warps hold tile j in registers: start tile j + 1
-                    if (!mbar_wait(s_free, j & 1, abort_word) ||
-                        !mbar_wait(k_full + (j + 1) % FA_STAGES, ((j + 1) / FA_STAGES) & 1, abort_word)) {
-                        give_up();
-                        break;
-                    }
-                    tc_fence_after();
-                    issue_qk(j + 1);
-                }
                 if (!mbar_wait(p_full, j & 1, abort_word) || !mbar_wait(v_full + st, (j / FA_STAGES) & 1, abort_word)) {
                     give_up();
                     break;
                 }
                 tc_fence_after();
-                const uint32_t v_addr = smem_addr(sV) + st * Cfg::KV_BYTES;
+                const uint64_t v_tile = v_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < FA_BN / 16; ++ks)  // 16 keys: 32 bytes along a row of P, 16 rows of V
-                    umma_bf16(tmem_base + Cfg::O_COL, umma_desc_sw128(p_addr + ks * 32),
-                              umma_desc_mn_sw128(v_addr + ks * 16 * 128, Cfg::KV_BAND, 1024), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                umma_commit(kv_empty + st);  // the stage may be refilled once these products have read it
+                for (int ks = 0; ks < FA_BN / 16; ++ks)  // 16 keys: 8 columns of P in tensor memory, 16 rows of V
+                    umma_bf16_a_tmem(tmem_base + Cfg::O_COL, tmem_base + Cfg::S_COL + (j & 1) * FA_BN + ks * 8,
+                                     v_tile + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(v_empty + st);  // the slot may be refilled once these products have read it
                 umma_commit(pv_done);
+                if (j + 2 < num_kt) {
+                    // the softmax warps hold S_j in registers (they have written P_j): its buffer takes tile j + 2
+                    if (!mbar_wait(k_full + st, ((j + 2) / FA_STAGES) & 1, abort_word)) {
+                        give_up();
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_qk(j + 2);
+                }
             }
         }
     } else {
@@ -248,15 +261,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         bool ok = true;
         for (int j = 0; j < num_kt; ++j) {
             const int key0 = (first_kt + j) * FA_BN;
-            if (!mbar_wait(s_full, j & 1, abort_word)) { ok = false; break; }
+            if (!mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_word)) { ok = false; break; }
             tc_fence_after();
             uint32_t raw[2][32];
-            tmem_load32_nowait(lane_base + Cfg::S_COL, raw[0]);
-            tmem_load32_nowait(lane_base + Cfg::S_COL + 32, raw[1]);
+            tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN, raw[0]);
+            tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN + 32, raw[1]);
             tmem_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free);
             float t[FA_BN];
 #pragma unroll
             for (int c = 0; c < FA_BN; ++c) t[c] = __uint_as_float(raw[c >> 5][c & 31]) * sl2;
@@ -277,9 +287,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 alpha = exp2f(m_ref - mx);
                 m_ref = mx;
             }
-            // P V of the tile before must be complete before O is rescaled or P overwritten
-            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
             if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                // P V of the tile before must be complete before O is rescaled (alpha != 1 implies j > 0)
+                if (!mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
@@ -305,11 +315,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
             l += sum;
-            unsigned char* p_row = sP + r * 128;
-#pragma unroll
-            for (int c = 0; c < 8; ++c)  // 16-byte chunk c of row r sits at chunk c ^ (r & 7)
-                *reinterpret_cast<uint4*>(p_row + ((c ^ (r & 7)) << 4)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            // P_j takes the place of the first half of S_j: this thread's own row, which it holds in registers
+            tmem_store32(lane_base + Cfg::S_COL + (j & 1) * FA_BN, packed);
+            tmem_wait_st();
             if (key0 + FA_BN > key_end) {
                 // Keys beyond the last query have probability 0, but 0 * NaN is NaN and what lies
                 // beyond a request's length may be anything: clear those rows of V.
@@ -322,8 +330,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     if (key0 + vr >= key_end)
                         *reinterpret_cast<uint4*>(v_tile + (c >> 3) * Cfg::KV_BAND + vr * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
+                fence_proxy_async_smem();
             }
-            fence_proxy_async_smem();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);

@@ -167,3 +167,11 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_byte_addres
 }
 // Instruction descriptor like umma_idesc, with the B operand MN-major.
 __host__ __device__ constexpr uint32_t umma_idesc_b_mn(int n) { return umma_idesc(n) | (1u << 16); }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (row m of A in
+// lane m, two consecutive bf16 of K per 32-bit column).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
