@@ -36,6 +36,31 @@
 #define FA_RESCALE_STEP 8.0f
 #define KB_FLAG_MISALIGNED 32
 
+// 2^x, flushing denormals: one MUFU instruction (exp2f adds range handling around it).
+__device__ __forceinline__ float ex2_ftz(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two fp32 operations in one instruction (sm_100 packs two floats in a 64-bit register).
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)), "l"(*reinterpret_cast<uint64_t*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(*reinterpret_cast<uint64_t*>(&a)), "l"(*reinterpret_cast<uint64_t*>(&b)));
+    return *reinterpret_cast<float2*>(&d);
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 template <int D>
 struct FaCfg {
     static constexpr int BANDS = D / 64;                 // 64-column (128-byte) bands of a row
@@ -267,9 +292,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN, raw[0]);
             tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN + 32, raw[1]);
             tmem_wait_ld();
+            // Work on the raw scores: the row maximum is taken before the scale (scale > 0), and
+            // scale and reference enter the exponent's argument as one fused multiply-add.
             float t[FA_BN];
 #pragma unroll
-            for (int c = 0; c < FA_BN; ++c) t[c] = __uint_as_float(raw[c >> 5][c & 31]) * sl2;
+            for (int c = 0; c < FA_BN; ++c) t[c] = __uint_as_float(raw[c >> 5][c & 31]);
             if (key0 + FA_BN - 1 > first_pos || key0 < lo_last) {  // the diagonal or the window's edge crosses this tile
 #pragma unroll
                 for (int c = 0; c < FA_BN; ++c) {
@@ -277,9 +304,15 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     t[c] = (key <= pos && key >= lo) ? t[c] : -INFINITY;
                 }
             }
-            float mx = -INFINITY;
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < FA_BN; ++c) mx = fmaxf(mx, t[c]);
+            for (int c = 0; c < FA_BN; c += 8) {
+                mx4[0] = max3(mx4[0], t[c], t[c + 1]);
+                mx4[1] = max3(mx4[1], t[c + 2], t[c + 3]);
+                mx4[2] = max3(mx4[2], t[c + 4], t[c + 5]);
+                mx4[3] = max3(mx4[3], t[c + 6], t[c + 7]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // -inf stays -inf
             float alpha = 1.0f;
             if (m_ref == -INFINITY) {
                 m_ref = mx;  // nothing accumulated for this row yet
@@ -303,17 +336,20 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 tmem_wait_st();
                 l *= alpha;
             }
-            const float base = m_ref == -INFINITY ? 0.0f : m_ref;
-            float sum = 0.0f;
+            const float neg_base = m_ref == -INFINITY ? 0.0f : -m_ref;
+            const float2 scale2 = make_float2(sl2, sl2);
+            const float2 base2 = make_float2(neg_base, neg_base);
+            float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
             uint32_t packed[FA_BN / 2];
 #pragma unroll
             for (int c = 0; c < FA_BN; c += 2) {
-                const float p0 = exp2f(t[c] - base);
-                const float p1 = exp2f(t[c + 1] - base);
-                sum += p0 + p1;
-                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                const float2 arg = ffma2(make_float2(t[c], t[c + 1]), scale2, base2);  // (-inf) * scale + base = -inf
+                const float2 p = make_float2(ex2_ftz(arg.x), ex2_ftz(arg.y));
+                sum2[(c >> 1) & 1] = fadd2(sum2[(c >> 1) & 1], p);
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
                 packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
             }
+            const float sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
             l += sum;
             // P_j takes the place of the first half of S_j: this thread's own row, which it holds in registers
             tmem_store32(lane_base + Cfg::S_COL + (j & 1) * FA_BN, packed);
