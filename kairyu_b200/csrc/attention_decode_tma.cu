@@ -29,6 +29,7 @@ namespace {
 
 constexpr int HALF_ELEMS = TILE_N * 64;  // one 64-column band of a tile: 64 rows of 128 bytes
 constexpr int CONSUMER_WARPS = 4;
+constexpr int KB_FLAG_TIMEOUT_DECODE = 64;  // this kernel's own bit, beside the common KB_FLAG_TIMEOUT
 constexpr int MAX_SPLITS = 256;
 constexpr int MIN_TILES_PER_SPLIT = 4;   // shorter splits cost more in the combination than they save
 constexpr int TMA_THREADS = (CONSUMER_WARPS + 1) * 32;  // the last warp is the producer
@@ -293,7 +294,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // A wait ran out.  Say so, give the copies still in flight one more bounded wait
         // (they target this block's shared memory), and leave without a result.
         if (threadIdx.x == 0) {
-            if (flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+            if (flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_DECODE);
             for (int st = 0; st < STAGES; ++st) {
                 mbar_wait(full_bar + st, 0, 1u << 10);
                 mbar_wait(full_bar + st, 1, 1u << 10);

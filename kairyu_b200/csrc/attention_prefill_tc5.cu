@@ -35,6 +35,7 @@
 #define FA_LOG2E 1.4426950408889634f
 #define FA_RESCALE_STEP 8.0f
 #define KB_FLAG_MISALIGNED 32
+#define KB_FLAG_TIMEOUT_PREFILL 128  // this kernel's own bit, beside the common KB_FLAG_TIMEOUT
 
 // 2^x, flushing denormals: one MUFU instruction (exp2f adds range handling around it).
 __device__ __forceinline__ float ex2_ftz(float x) {
@@ -178,7 +179,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int is_v = 0; is_v < 2; ++is_v) {
                 // K's slot is free once Q K^T of the tile that used it is done, V's once its P V is done
                 if (use > 0 && !mbar_wait((is_v ? v_empty : k_empty) + st, (use - 1) & 1, abort_word)) {
-                    if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+                    if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
                     *abort_word = 1;
                     ok = false;
                     break;
@@ -216,7 +217,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const uint64_t v_desc = umma_desc_mn_sw128(smem_addr(sV), Cfg::KV_BAND, 1024);
             bool ok = true;
             auto give_up = [&]() {
-                if (!*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+                if (!*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
                 *abort_word = 1;
                 ok = false;
             };
@@ -320,9 +321,10 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 alpha = exp2f(m_ref - mx);
                 m_ref = mx;
             }
+            // Every phase of pv_done is observed (a parity wait cannot tell a phase from the one two
+            // before it); P V of the tile before must also be complete before O is rescaled.
+            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
             if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-                // P V of the tile before must be complete before O is rescaled (alpha != 1 implies j > 0)
-                if (!mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
@@ -374,7 +376,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         }
         if (ok && !mbar_wait(pv_done, (num_kt - 1) & 1, abort_word)) ok = false;
         if (!ok) {
-            if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT);
+            if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
             *abort_word = 1;
         } else {
             tc_fence_after();

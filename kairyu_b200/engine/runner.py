@@ -487,6 +487,10 @@ class ModelRunner:
                 reasons.append("a position outside the rotary table")
             if flag & 16:
                 reasons.append("a copy into shared memory did not complete within its wait limit")
+            if flag & 64:
+                reasons.append("(the wait was in the TMA-fed decode attention)")
+            if flag & 128:
+                reasons.append("(the wait was in the tcgen05 prefill attention)")
             if flag & 32:
                 reasons.append("a block's shared memory did not start on the 1024-byte boundary its swizzled tiles need")
             raise StepError("a kernel refused an index: " + "; ".join(reasons))
