@@ -149,6 +149,7 @@ def build_engine(layers: int, max_batch: int):
         max_num_seqs=max(max_batch, 1),
         max_model_len=CONTEXT_LEN,
         max_num_partial_prefills=1,
+        pipeline_depth=2,  # schedule-ahead: step N+1 is launched while step N runs (end-to-end run)
         seed=SEED,
     )
     engine = Engine.from_random(config, SEED, engine_config)
@@ -382,6 +383,7 @@ def main() -> int:
             "context_len": CONTEXT_LEN,
             "page_size": PAGE_SIZE,
             "parallelism": "single_gpu",
+            "pipeline_depth": 2,
             "l2": "inputs>L2 (weights and cache exceed the 126 MB L2)",
             "peaks": peak_source,
         },

@@ -45,6 +45,9 @@ class EngineConfig:
     gpu_memory_utilization: float = 0.9
     decode_mode: str | None = None  # None -> "cuda_graph" on CUDA, "eager" elsewhere
     cuda_graph_max_batch: int | None = None
+    # Steps that may be launched before the oldest one's tokens are read (the reference's option
+    # of this name, default 1 there too): 2 plans and launches step N+1 while step N runs.
+    pipeline_depth: int = 1
     seed: int = 0
 
     def __post_init__(self) -> None:
@@ -63,6 +66,8 @@ class EngineConfig:
             raise ValueError("prefill_chunk_size must be >= 1")
         if self.decode_mode not in (None, "eager", "cuda_graph"):
             raise ValueError("decode_mode must be None, 'eager' or 'cuda_graph'")
+        if self.pipeline_depth not in (1, 2):
+            raise ValueError("pipeline_depth must be 1 or 2")
         if not 0.0 < self.gpu_memory_utilization <= 1.0:
             raise ValueError("gpu_memory_utilization must be in (0, 1]")
 

@@ -33,6 +33,32 @@ KB_EXPORT int kb_embedding(const void* table, int table_is_bf16, const int* ids,
     return kb_launch_result();
 }
 
+// ------------------------------------------------------------------ tokens that are still on the device
+// ids[t] = sampled[source[t]] where source[t] >= 0: the token a step is fed may be the one the
+// step before it has just chosen, which the host has not seen yet
+// (kairyu/engine/core/model_runner.py:1998-2041, 2080-2162: device-resident future tokens).
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ source,
+                                    const int* __restrict__ sampled, int T, int sampled_len, int* flag) {
+    pdl_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const int s = source[t];
+    if (s < 0) return;
+    if (s >= sampled_len) {
+        if (flag) atomicOr(flag, KB_FLAG_BAD_ROW);
+        return;
+    }
+    ids[t] = sampled[s];
+}
+
+KB_EXPORT int kb_patch_tokens(int* ids, const int* source, const int* sampled, int T, int sampled_len, int* flag,
+                              cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (!ids || !source || !sampled) return KB_ERR_NULL;
+    kb_launch(patch_tokens_kernel, dim3((T + 127) / 128), dim3(128), 0, stream, ids, source, sampled, T, sampled_len, flag);
+    return kb_launch_result();
+}
+
 // ------------------------------------------------------------------ RMSNorm
 // One block per output row r; source row s = rows ? rows[r] : r.
 //   v = x[s] (+ delta[s]);  if write_back: x[s] = v  (the fp32 residual sum)

@@ -7,6 +7,7 @@ kairyu/engine/kairyu_backend.py:467-1179, without tokenizer and server parts).
 from __future__ import annotations
 
 import json
+from collections import deque
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping, Optional, Sequence
@@ -33,6 +34,18 @@ class FinishedRequest:
     output_token_ids: tuple[int, ...]
     finish_reason: str
     stop_reason: Optional[int | str] = None
+
+
+class _PendingStep:
+    """A launched step whose sampled ids have not been read yet."""
+
+    __slots__ = ("request_ids", "index", "host", "event")
+
+    def __init__(self, request_ids: list[str]) -> None:
+        self.request_ids = request_ids
+        self.index = {request_id: place for place, request_id in enumerate(request_ids)}  # row of each id in the sampled tensor
+        self.host: Optional[torch.Tensor] = None
+        self.event: Any = None
 
 
 def build_model(config: Mapping[str, Any], *, dtype: str, device: str) -> tuple[DecoderModel, Any]:
@@ -105,6 +118,10 @@ class Engine:
         self._finished: dict[str, FinishedRequest] = {}
         self._stop_checks: dict[str, Callable[[Sequence[int]], Optional[str]]] = {}
         self._steps_since_check = 0
+        self._pending: deque[_PendingStep] = deque()  # launched, not yet committed
+        self._sampled: Optional[torch.Tensor] = None   # device ids of the step launched last
+        self._host_ring: list[tuple[Optional[torch.Tensor], Any]] = [(None, None)] * 4
+        self._next_host = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -185,16 +202,30 @@ class Engine:
         self._stop_checks.pop(request_id, None)
         self.scheduler.forget(request_id)
 
-    def step(self) -> tuple[str, ...]:
-        """One engine step; returns the ids of requests that finished in it."""
+    # A step is launched (planned, enqueued on the GPU, its sampled ids copied towards the host)
+    # and later committed (ids read, requests updated and finished).  With pipeline_depth 2 the
+    # next step is launched before the oldest is committed: its decode rows take their token
+    # from the device tensor of sampled ids (kairyu/engine/engine_loop.py:1025-1136, 1282-1299).
+    def _depth_now(self) -> int:
+        if self.config.pipeline_depth < 2 or self._stop_checks:
+            return 1  # stop strings are judged on committed text, between steps
+        for request_id in self.scheduler.running_ids():
+            params = self.scheduler.state(request_id).request.params
+            if params.repetition_penalty != 1.0 or params.frequency_penalty != 0.0 or params.presence_penalty != 0.0:
+                return 1  # penalties read the committed outputs
+        return 2
+
+    def _launch(self, done: list[str]) -> bool:
+        """Plan one step and enqueue it; False when there was nothing to run."""
         plan = self.scheduler.schedule()
-        done: list[str] = list(plan.rejected)
+        done.extend(plan.rejected)
         for request_id in plan.rejected:
             self._collect(request_id)
         if not plan.scheduled:
-            if self.scheduler.has_unfinished() and not plan.rejected and not plan.preempted:
+            if self.scheduler.has_unfinished() and not plan.rejected and not plan.preempted and not self._pending:
                 raise RuntimeError("the scheduler made no progress")
-            return tuple(done)
+            return False
+        previous = self._pending[-1] if self._pending else None
         entries: list[StepEntry] = []
         rows: list[SamplingRow] = []
         for chunk in plan.scheduled:
@@ -204,52 +235,99 @@ class Engine:
                 raise RuntimeError(
                     f"request {chunk.request_id!r}: the cache holds {held} tokens, the plan starts at {chunk.start}"
                 )
-            tokens = state.tokens(chunk.start, chunk.num_tokens)
-            entries.append(StepEntry(chunk.request_id, tokens, want=(chunk.num_tokens - 1,) if chunk.samples else ()))
+            known = state.total_tokens
+            future = None
+            if chunk.start + chunk.num_tokens > known:
+                # the token it feeds was sampled by the step before and has not been read yet
+                if chunk.num_tokens != 1 or previous is None or chunk.request_id not in previous.index:
+                    raise RuntimeError(f"request {chunk.request_id!r}: a token in flight has no step to come from")
+                future = previous.index[chunk.request_id]
+                tokens: Sequence[int] = (0,)
+            else:
+                tokens = state.tokens(chunk.start, chunk.num_tokens)
+            entries.append(StepEntry(chunk.request_id, tokens, want=(chunk.num_tokens - 1,) if chunk.samples else (), future=future))
             if chunk.samples:
                 request = state.request
                 rows.append(
                     SamplingRow(
                         request_id=chunk.request_id,
                         params=request.params,
-                        position=len(state.outputs),
+                        position=len(state.outputs) + state.in_flight - 1,
                         prompt_token_ids=request.prompt_token_ids,
                         output_token_ids=state.outputs,
                         eos_token_ids=request.eos_token_ids,
                     )
                 )
-        logits = self.runner.step(entries)
-        if rows:
-            token_ids = self.sampler.sample(logits, rows).tolist()  # the step's one device->host read
-            # The kernels' error word is sticky: reading it every few steps (and whenever a
-            # request ends) reports the same faults with fewer round trips.
-            self._steps_since_check += 1
-            sampled = {row.request_id: int(token) for row, token in zip(rows, token_ids)}
-            finished = list(self.scheduler.update(sampled))
-            if finished or self._steps_since_check >= 16:
-                self._steps_since_check = 0
-                self.runner.check_errors()
-            for request_id in finished:
-                state = self.scheduler.state(request_id)
-                last = state.outputs[-1] if state.outputs else None
-                stop_reason = None
-                if state.finish_reason == "stop" and last in state.request.stop_token_ids:
-                    stop_reason = last
-                self._collect(request_id, stop_reason)
-            done.extend(finished)
-            for request_id in sampled:
-                check = self._stop_checks.get(request_id)
-                if check is None or request_id in self._finished:
-                    continue
-                hit = check(self.scheduler.state(request_id).outputs)
-                if hit is not None:
-                    self.scheduler.finish_early(request_id, "stop")
-                    self._collect(request_id, hit)
-                    done.append(request_id)
+        logits = self.runner.step(entries, self._sampled if previous is not None else None)
+        if not rows:
+            return True
+        if self._sampled is None or self._sampled.numel() < len(rows):
+            self._sampled = torch.zeros(max(len(rows), self.config.max_num_seqs), dtype=torch.int32, device=self.device)
+        out = self.sampler.sample(logits, rows, out=self._sampled[: len(rows)])
+        pending = _PendingStep([row.request_id for row in rows])
+        if str(self.device).startswith("cuda"):
+            slot = self._next_host
+            self._next_host = (slot + 1) % len(self._host_ring)
+            host, event = self._host_ring[slot]
+            if host is None or host.numel() < len(rows):
+                host = torch.empty(max(len(rows), self.config.max_num_seqs), dtype=torch.int32, pin_memory=True)
+                event = torch.cuda.Event()
+                self._host_ring[slot] = (host, event)
+            host[: len(rows)].copy_(out, non_blocking=True)  # the step's one device->host read, awaited at commit
+            event.record()
+            pending.host, pending.event = host, event
+        else:
+            pending.host = out.clone()
+        self._pending.append(pending)
+        return True
+
+    def _commit(self, pending: "_PendingStep", done: list[str]) -> None:
+        if pending.event is not None:
+            pending.event.synchronize()
+        token_ids = pending.host[: len(pending.request_ids)].tolist()
+        # The kernels' error word is sticky: reading it every few steps (and whenever a
+        # request ends) reports the same faults with fewer round trips.
+        self._steps_since_check += 1
+        sampled = {request_id: int(token) for request_id, token in zip(pending.request_ids, token_ids)}
+        alive = [request_id for request_id in sampled if request_id not in self._finished]
+        finished = list(self.scheduler.update(sampled))
+        if finished or self._steps_since_check >= 16:
+            self._steps_since_check = 0
+            self.runner.check_errors()
+        for request_id in finished:
+            state = self.scheduler.state(request_id)
+            last = state.outputs[-1] if state.outputs else None
+            stop_reason = None
+            if state.finish_reason == "stop" and last in state.request.stop_token_ids:
+                stop_reason = last
+            self._collect(request_id, stop_reason)
+        done.extend(finished)
+        for request_id in alive:
+            check = self._stop_checks.get(request_id)
+            if check is None or request_id in self._finished:
+                continue
+            hit = check(self.scheduler.state(request_id).outputs)
+            if hit is not None:
+                self.scheduler.finish_early(request_id, "stop")
+                self._collect(request_id, hit)
+                done.append(request_id)
+
+    def step(self) -> tuple[str, ...]:
+        """One engine step: launch until ``pipeline_depth`` steps are in flight, then commit the
+        oldest.  Returns the ids of requests that finished in it."""
+        done: list[str] = []
+        while len(self._pending) < self._depth_now():
+            before = len(self._pending)
+            if not self._launch(done):
+                break
+            if len(self._pending) == before:
+                break  # a step without sampling rows (prompt portions only): nothing to wait for
+        if self._pending:
+            self._commit(self._pending.popleft(), done)
         return tuple(done)
 
     def run_to_completion(self) -> dict[str, FinishedRequest]:
-        while self.scheduler.has_unfinished():
+        while self.scheduler.has_unfinished() or self._pending:
             self.step()
         finished, self._finished = self._finished, {}
         return finished

@@ -37,6 +37,9 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()  # places among ``tokens`` whose logits are wanted
+    # The single token of this entry is not known to the host yet: it is element ``future`` of the
+    # device tensor of sampled ids given to ``step`` (``tokens`` then holds one placeholder).
+    future: Optional[int] = None
 
 
 class StepError(RuntimeError):
@@ -119,6 +122,7 @@ class ModelRunner:
         self._buckets = decode_buckets(max_graph_batch)
         self.counters = {
             "steps": 0, "graph_replays": 0, "graph_captures": 0, "eager_steps": 0, "tokens": 0, "kernel_launches": 0,
+            "future_tokens": 0,  # tokens taken from the device because the host had not seen them yet
         }
 
     # ------------------------------------------------------------------ host-side packing
@@ -140,6 +144,8 @@ class ModelRunner:
                 raise StepError(f"request {entry.request_id!r} has a token id outside [0, {vocab})")
             if any(not 0 <= place < count for place in entry.want):
                 raise StepError(f"request {entry.request_id!r} wants a place outside its tokens")
+            if entry.future is not None and count != 1:
+                raise StepError(f"request {entry.request_id!r}: only a single token can come from the device")
             if entry.request_id not in self.cache:
                 self.cache.admit(entry.request_id)
             start = self.cache.get(entry.request_id).num_tokens
@@ -177,6 +183,7 @@ class ModelRunner:
         write_from: list[int] = []
         state_slots: list[int] = []
         want: list[int] = []
+        future_src: list[int] = []
         tile_rows: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
         tile_starts: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
         decode_rows: list[int] = []
@@ -185,6 +192,7 @@ class ModelRunner:
             count = len(entry.tokens)
             base = len(token_ids)
             token_ids.extend(entry.tokens)
+            future_src.extend([-1] * count if entry.future is None else [entry.future])
             positions.extend(range(start, seq_len))
             row_ids.extend([row] * count)
             qo_indptr.append(base + count)
@@ -204,6 +212,7 @@ class ModelRunner:
         for row in range(num_rows, padded_rows):  # padding rows of a replayed graph
             base = len(token_ids)
             token_ids.append(0)
+            future_src.append(-1)
             positions.append(0)
             row_ids.append(row)
             qo_indptr.append(base + 1)
@@ -225,6 +234,7 @@ class ModelRunner:
                 tables.extend([0] * table_width)  # the reserved page
         arrays = {
             "token_ids": token_ids,
+            "future_src": future_src,
             "positions": positions,
             "row_ids": row_ids,
             "qo_indptr": qo_indptr,
@@ -299,10 +309,18 @@ class ModelRunner:
         return ctx, want
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run one batch; returns ``[wanted, vocab]`` fp32 logits on the device,
-        in the order of the entries and of their ``want`` lists, or None."""
+        in the order of the entries and of their ``want`` lists, or None.
+        ``sampled``: device int32 ids that entries with ``future`` set take their token from."""
         rows = self._prepare_rows(entries)
+        has_future = any(entry.future is not None for entry in entries)
+        if has_future and sampled is None:
+            raise StepError("an entry takes its token from the device, but no tensor of sampled ids was given")
+        if not has_future:
+            sampled = None
+        else:
+            self.counters["future_tokens"] += sum(1 for entry in entries if entry.future is not None)
         self.storage.zero_state_slots(self.cache.take_fresh_state_slots())
         self.counters["steps"] += 1
         self.counters["tokens"] += sum(len(entry.tokens) for entry, _, _ in rows)
@@ -313,17 +331,25 @@ class ModelRunner:
             and self._is_cuda
             and len(rows) <= self.max_graph_batch
         ):
-            logits = self._graph_step(rows)
+            logits = self._graph_step(rows, sampled)
         else:
-            logits = self._eager_step(rows)
+            logits = self._eager_step(rows, sampled)
         for entry, _, seq_len in rows:
             self.cache.advance(entry.request_id, seq_len)
         return logits
 
-    def _eager_step(self, rows: Sequence[tuple[StepEntry, int, int]]) -> Optional[torch.Tensor]:
+    def _patch_tokens(self, meta: torch.Tensor, layout: dict[str, tuple[int, int]], sampled: Optional[torch.Tensor]) -> None:
+        if sampled is None:
+            return
+        offset, length = layout["token_ids"]
+        source_at, _ = layout["future_src"]
+        kernels.patch_tokens(meta[offset : offset + length], meta[source_at : source_at + length], sampled, self.error_flag)
+
+    def _eager_step(self, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         host, layout, facts = self._pack(rows)
         meta = self.workspace.flat("meta", host.numel(), torch.int32)
         meta.copy_(host, non_blocking=True)
+        self._patch_tokens(meta, layout, sampled)
         ctx, want = self._context(meta, layout, facts, self.workspace)
         self.counters["eager_steps"] += 1
         before = kernels.launch_count
@@ -336,7 +362,7 @@ class ModelRunner:
         bucket = next(size for size in self._buckets if size >= num_rows)
         return bucket, min(context_bucket(max_seq_len), max(self.max_model_len, 256))
 
-    def _graph_step(self, rows: Sequence[tuple[StepEntry, int, int]]) -> Optional[torch.Tensor]:
+    def _graph_step(self, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         num_rows = len(rows)
         max_seq_len = max(seq_len for _, _, seq_len in rows)
         key = self._graph_key(num_rows, max_seq_len)
@@ -348,13 +374,14 @@ class ModelRunner:
             )
             # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
             facts["max_seq_len"] = context_bucket
-            held = self._capture(key, host, layout, facts)
+            held = self._capture(key, host, layout, facts, sampled)
             held.mirror = host.numpy().copy()
             held.row_state = [None] * bucket
             self._note_rows(held, rows)
         else:
             self._update_mirror(held, rows, bucket)
         self._upload(held)
+        self._patch_tokens(held.meta, held.layout, sampled)
         held.graph.replay()
         self.counters["graph_replays"] += 1
         self.counters["kernel_launches"] += held.launches
@@ -380,6 +407,7 @@ class ModelRunner:
         mirror = held.mirror
         layout = held.layout
         token_at = layout["token_ids"][0]
+        future_at = layout["future_src"][0]
         position_at = layout["positions"][0]
         length_at = layout["seq_lens"][0]
         slot_at = layout["state_slots"][0]
@@ -389,6 +417,7 @@ class ModelRunner:
         for row, (entry, start, seq_len) in enumerate(rows):
             record = self.cache.get(entry.request_id)
             mirror[token_at + row] = entry.tokens[0]
+            mirror[future_at + row] = -1 if entry.future is None else entry.future
             mirror[position_at + row] = start
             mirror[length_at + row] = seq_len
             mirror[slot_at + row] = record.state_slot
@@ -408,6 +437,7 @@ class ModelRunner:
         for row in range(len(rows), bucket):
             if held.row_state[row] is not None:  # the row becomes padding: token 0 at position 0 of the reserved page
                 mirror[token_at + row] = 0
+                mirror[future_at + row] = -1
                 mirror[position_at + row] = 0
                 mirror[length_at + row] = 1
                 mirror[slot_at + row] = 0
@@ -428,11 +458,13 @@ class ModelRunner:
         held.meta.copy_(pinned, non_blocking=True)
         event.record()
 
-    def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict) -> _Graph:
+    def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict,
+                 sampled: Optional[torch.Tensor] = None) -> _Graph:
         bucket, _ = key
         workspace = self.graph_workspace
         meta = torch.zeros(host.numel(), dtype=torch.int32, device=self.device)
         meta.copy_(host)
+        self._patch_tokens(meta, layout, sampled)  # the warm-up runs below write keys and values of these tokens
         graph_layout = dict(layout)
         # inside the graph every row's single token gives logits
         want_all = torch.arange(bucket, dtype=torch.int32, device=self.device)

@@ -11,6 +11,13 @@ decodes.  The step that feeds the last token samples the next one.  This view
 makes recompute-preemption uniform: a victim's ``computed`` goes back to 0 and
 its prompt *and* outputs are fed again.
 
+Schedule-ahead (kairyu/engine/core/scheduler.py:1234-1242, engine_loop.py:1025-1136):
+a chunk that samples puts one token ``in_flight``; until ``update`` commits it the
+token counts as part of the request's work, so the next plan may already feed it
+(the step takes its value from the device).  A request with a token in flight is
+never preempted, and tokens that arrive for a request that has finished meanwhile
+are dropped.
+
 Order within a step (scheduler.py:1641-1657): decodes first (one token each),
 then running prefills, then admissions from the head of the queue.
 
@@ -64,13 +71,14 @@ class Status(Enum):
 
 
 class RequestState:
-    __slots__ = ("request", "status", "computed", "outputs", "finish_reason", "preemptions", "arrival")
+    __slots__ = ("request", "status", "computed", "outputs", "in_flight", "finish_reason", "preemptions", "arrival")
 
     def __init__(self, request: EngineRequest, arrival: int) -> None:
         self.request = request
         self.status = Status.WAITING
         self.computed = 0
         self.outputs: list[int] = []
+        self.in_flight = 0  # sampled by a launched step, not yet committed by update()
         self.finish_reason: Optional[str] = None
         self.preemptions = 0
         self.arrival = arrival
@@ -81,7 +89,8 @@ class RequestState:
 
     @property
     def remaining(self) -> int:
-        return self.total_tokens - self.computed
+        """Tokens left to feed, the ones in flight included (their values come later)."""
+        return self.total_tokens + self.in_flight - self.computed
 
     def tokens(self, start: int, count: int) -> list[int]:
         prompt = self.request.prompt_token_ids
@@ -178,6 +187,9 @@ class Scheduler:
     def state(self, request_id: str) -> RequestState:
         return self._states[request_id]
 
+    def running_ids(self) -> tuple[str, ...]:
+        return tuple(self._running)
+
     @property
     def num_waiting(self) -> int:
         return len(self._waiting)
@@ -216,7 +228,7 @@ class Scheduler:
     def _pick_victim(self, needy: str, taken: set[str]) -> Optional[str]:
         fallback = None
         for candidate in reversed(self._running):
-            if candidate == needy or candidate in taken:
+            if candidate == needy or candidate in taken or self._states[candidate].in_flight:
                 continue
             if not self._states[candidate].outputs:
                 return candidate
@@ -239,8 +251,9 @@ class Scheduler:
     def schedule(self) -> SchedulerOutput:
         self.counters["steps"] += 1
         plan, preempted, rejected = self._plan()
-        if not plan and self.has_unfinished():
-            # Nothing can move.  Free something, or give up on the stuck head.
+        if not plan and self.has_unfinished() and not any(self._states[r].in_flight for r in self._running):
+            # Nothing can move (and nothing is merely waiting for a token in flight).  Free
+            # something, or give up on the stuck head.
             if self._running:
                 victim = self._running[-1]
                 self._preempt(victim)
@@ -268,6 +281,8 @@ class Scheduler:
             state = self._states.get(request_id)
             if state is None or state.status is not Status.RUNNING or state.remaining != 1:
                 continue
+            if len(state.outputs) + state.in_flight >= state.request.max_new_tokens:
+                continue  # its last token is in flight
             while not self._grow(state, 1):
                 victim = self._pick_victim(request_id, taken)
                 if victim is None:
@@ -277,10 +292,11 @@ class Scheduler:
             else:
                 plan.append(ScheduledChunk(request_id, state.computed, 1, False, True))
                 state.computed += 1
+                state.in_flight += 1
                 taken.add(request_id)
                 budget -= 1
                 continue
-            if len(self._running) == 1:
+            if len(self._running) == 1 and not state.in_flight:
                 # alone and the cache is exhausted: it cannot go on
                 self._finish(state, "length")
                 rejected.append(request_id)
@@ -301,6 +317,7 @@ class Scheduler:
             completes = count == state.remaining
             plan.append(ScheduledChunk(request_id, state.computed, count, True, completes))
             state.computed += count
+            state.in_flight += 1 if completes else 0
             taken.add(request_id)
             budget -= count
 
@@ -338,6 +355,7 @@ class Scheduler:
             completes = count == state.remaining
             plan.append(ScheduledChunk(head, state.computed, count, count > 1 or not completes, completes))
             state.computed += count
+            state.in_flight += 1 if completes else 0
             taken.add(head)
             budget -= count
         return plan, preempted, rejected
@@ -351,8 +369,11 @@ class Scheduler:
             if isinstance(token, bool) or not isinstance(token, int):
                 raise TypeError(f"request {request_id!r}: sampled tokens must be ints, got {token!r}")
             state = self._states.get(request_id)
-            if state is None or state.status is not Status.RUNNING or state.remaining != 0:
+            if state is None or state.status is Status.FINISHED:
+                continue  # it ended while this token was in flight (scheduler.py:1712-1720)
+            if state.in_flight < 1:
                 raise ValueError(f"request {request_id!r} is not awaiting a sampled token")
+            state.in_flight -= 1
             state.outputs.append(token)
             reason = self._terminal_reason(state, token)
             if reason is not None:

@@ -114,6 +114,16 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, flag: O
     _check(fn(table.data_ptr(), _is_bf16(table, "embedding"), ids.data_ptr(), out.data_ptr(), ids.numel(), H, V, _ptr(flag), _stream()), "embedding")
 
 
+def patch_tokens(ids: torch.Tensor, source: torch.Tensor, sampled: torch.Tensor, flag: Optional[torch.Tensor] = None) -> None:
+    """ids[t] = sampled[source[t]] wherever source[t] >= 0 (tokens the host has not seen yet)."""
+    _need_cuda("patch_tokens", ids, source, sampled, flag)
+    _need_i32("patch_tokens", ids, source, sampled)
+    if source.numel() != ids.numel() or not (ids.is_contiguous() and source.is_contiguous() and sampled.is_contiguous()):
+        raise KernelError("patch_tokens: ids and source must be contiguous and of one length")
+    fn = _fn("elementwise", "kb_patch_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(ids.data_ptr(), source.data_ptr(), sampled.data_ptr(), ids.numel(), sampled.numel(), _ptr(flag), _stream()), "patch_tokens")
+
+
 def rmsnorm(
     x: torch.Tensor,
     weight: torch.Tensor,
@@ -724,6 +734,7 @@ __all__ = [
     "gather_rows",
     "linear",
     "linear_swiglu",
+    "patch_tokens",
     "paged_attention_generic",
     "qk_norm_rope_kv_write",
     "rmsnorm",

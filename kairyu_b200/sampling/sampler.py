@@ -84,13 +84,17 @@ class Sampler:
             return None
         return e_row, e_tok, e_mul, e_sub, e_mask
 
-    def sample(self, logits: torch.Tensor, rows: Sequence[SamplingRow]) -> torch.Tensor:
+    def sample(self, logits: torch.Tensor, rows: Sequence[SamplingRow], out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``logits``: [n, vocab] fp32 on the device (edited in place when a row
-        has penalties or a min-tokens mask).  Returns int32 token ids [n] on the device."""
+        has penalties or a min-tokens mask).  Returns int32 token ids [n] on the device
+        (in ``out`` when given: a persistent buffer the next step can read them from)."""
         n = logits.shape[0]
         if n != len(rows):
             raise ValueError(f"{n} rows of logits for {len(rows)} sampling rows")
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(n, dtype=torch.int32, device=self.device)
+        elif out.shape != (n,) or out.dtype != torch.int32 or not out.is_contiguous():
+            raise ValueError("out must be a contiguous int32 tensor with one element per row")
         edits = self._edits(rows)
         if edits is not None:
             e_row, e_tok, e_mul, e_sub, e_mask = edits

@@ -85,3 +85,73 @@ def test_llm_rejects_unknown_options_and_parallel_sizes():
         LLM.from_random(config, seed=0, device="cpu", not_an_option=1)
     with pytest.raises(ValueError):
         LLM("/nonexistent", tensor_parallel_size=2)
+
+
+# ------------------------------------------------------------------ schedule-ahead (pipeline_depth=2)
+
+
+def test_pipeline_depth_two_gives_the_same_tokens_and_runs_ahead():
+    prompts = None
+    results = {}
+    for depth in (1, 2):
+        llm, config = make_llm("llama", num_pages=48, pipeline_depth=depth)
+        prompts = prompts or prompts_of(config, [5, 21, 40, 9], seed=110)
+        params = [SamplingParams(temperature=0.0, max_tokens=m) for m in (12, 3, 1, 7)]
+        outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+        results[depth] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason) for o in outputs]
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests == 0 and not llm.engine._pending
+        assert (llm.engine.runner.counters["future_tokens"] > 0) == (depth == 2)
+        if depth == 2:
+            weights = engine_weights(llm)
+            for prompt, output, p in zip(prompts, outputs, params):
+                assert list(output.outputs[0].token_ids) == plain_generate(config, weights, prompt, p.max_tokens)
+    assert results[1] == results[2]
+
+
+def test_pipeline_depth_two_drops_the_token_sampled_after_a_stop():
+    llm, config = make_llm("qwen3", num_pages=64, pipeline_depth=2)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [17, 30], seed=111)
+    free = [plain_generate(config, weights, p, 10) for p in prompts]
+    # stop request 0 at its 4th token and request 1 at its 7th: the step after each stop has
+    # already been launched with a row for it
+    stops = [free[0][3], free[1][6]]
+    params = [SamplingParams(temperature=0.0, max_tokens=10, stop_token_ids=[stops[i]]) for i in range(2)]
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    for i, output in enumerate(outputs):
+        expected = free[i][: free[i].index(stops[i]) + 1]
+        assert list(output.outputs[0].token_ids) == expected
+        assert output.outputs[0].finish_reason == "stop" and output.outputs[0].stop_reason == stops[i]
+    llm.engine.cache.check()
+    assert llm.engine.cache.live_requests == 0
+
+
+def test_pipeline_depth_two_under_page_pressure_and_with_sampling():
+    llm, config = make_llm("odd", num_pages=9, max_num_batched_tokens=7, max_num_seqs=4, pipeline_depth=2)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [30, 14, 46, 31, 15, 47], seed=102)
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], SamplingParams(temperature=0.0, max_tokens=20))
+    assert llm.engine.scheduler.counters["preemptions"] > 0
+    llm.engine.cache.check()
+    assert llm.engine.cache.live_requests == 0
+    for prompt, output in zip(prompts, outputs):
+        assert list(output.outputs[0].token_ids) == plain_generate(config, weights, prompt, 20)
+    llm2, config2 = make_llm("qwen3", num_pages=64, pipeline_depth=2)
+    weights2 = engine_weights(llm2)
+    prompts2 = prompts_of(config2, [3, 50, 27], seed=101)
+    params = [SamplingParams(temperature=0.8, top_p=0.9, seed=50 + i, max_tokens=6) for i in range(3)]
+    outputs2 = llm2.generate([TokensPrompt(tuple(p)) for p in prompts2], params)
+    for index, (prompt, output) in enumerate(zip(prompts2, outputs2)):
+        expected = plain_generate(config2, weights2, prompt, 6, dict(temperature=0.8, top_p=0.9), request_seed=50 + index)
+        assert list(output.outputs[0].token_ids) == expected
+
+
+def test_pipeline_depth_two_falls_back_to_one_for_penalties():
+    llm, config = make_llm("llama", num_pages=32, pipeline_depth=2)
+    prompt = prompts_of(config, [12], seed=112)[0]
+    one, _ = make_llm("llama", num_pages=32)
+    params = SamplingParams(temperature=0.0, max_tokens=8, repetition_penalty=1.3, presence_penalty=0.4)
+    a = llm.generate(TokensPrompt(tuple(prompt)), params)[0].outputs[0].token_ids
+    b = one.generate(TokensPrompt(tuple(prompt)), params)[0].outputs[0].token_ids
+    assert a == b

@@ -129,6 +129,38 @@ def test_generation_under_a_small_budget_and_few_pages(dtype):
         assert agree / total > 0.9
 
 
+@pytest.mark.parametrize("name,dtype", [("llama", "float32"), ("wide", "bfloat16"), ("qwen3", "bfloat16")])
+def test_schedule_ahead_gives_the_same_tokens(name, dtype):
+    """pipeline_depth=2 launches step N+1 before step N's tokens reach the host (its rows read
+    them from the device); the tokens, stops included, are those of pipeline_depth=1."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY[name]
+    prompts = prompts_of(config, [5, 21, 40, 9, 64], seed=120)
+    results = {}
+    stop = None
+    for depth in (1, 2):
+        llm = LLM.from_random(config, seed=seed, dtype=dtype, page_size=page_size, num_pages=64, pipeline_depth=depth)
+        if stop is None:  # a token request 0 produces on its own: make it a stop token for it
+            free = llm.generate(TokensPrompt(tuple(prompts[0])), SamplingParams(temperature=0.0, max_tokens=12))[0]
+            stop = free.outputs[0].token_ids[5]
+        params = [SamplingParams(temperature=0.0, max_tokens=24, stop_token_ids=[stop])] + [
+            SamplingParams(temperature=0.0, max_tokens=m) for m in (3, 1, 30, 17)
+        ]
+        outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+        results[depth] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason) for o in outputs]
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests == 0
+        assert (llm.engine.runner.counters["future_tokens"] > 0) == (depth == 2)
+        if depth == 2:
+            assert llm.engine.runner.counters["graph_replays"] > 0
+    assert results[1] == results[2]
+    assert results[2][0][1] == "stop" and results[2][0][0][-1] == stop and len(results[2][0][0]) <= 6
+    if dtype == "float32":
+        weights = engine_weights(LLM.from_random(config, seed=seed, dtype=dtype, page_size=page_size, num_pages=64))
+        assert list(results[2][3][0]) == plain_generate(config, weights, prompts[3], 30)
+
+
 def test_stop_token_and_eos():
     from kairyu_b200 import LLM, SamplingParams, TokensPrompt
 

@@ -207,3 +207,43 @@ def test_random_workloads_finish_and_leave_the_cache_empty(seed):
         assert reason == "length"
         outputs = len(scheduler.output_tokens(name))
         assert outputs == new or (outputs < new and not cache.can_hold(len(scheduler.state(name).request.prompt_token_ids) + new - 1))
+
+
+# ------------------------------------------------------------------ schedule-ahead
+
+
+def test_a_sampled_token_in_flight_can_be_fed_before_it_is_known():
+    scheduler, cache = make(num_pages=16, page_size=4)
+    scheduler.add_request(EngineRequest("a", tuple(range(1, 6)), max_new_tokens=3))
+    first = scheduler.schedule().scheduled
+    assert [(c.start, c.num_tokens, c.samples) for c in first] == [(0, 5, True)]
+    assert scheduler.state("a").in_flight == 1
+    ahead = scheduler.schedule().scheduled  # planned before update(): feeds the token in flight
+    assert [(c.start, c.num_tokens, c.samples) for c in ahead] == [(5, 1, True)]
+    assert ahead[0].start >= scheduler.state("a").total_tokens  # its value is not known to the host
+    assert scheduler.state("a").in_flight == 2
+    assert scheduler.schedule().scheduled[0].start == 6          # a third: max_new_tokens = 3 allows it
+    assert scheduler.schedule().scheduled == ()                  # but no fourth
+    assert scheduler.update({"a": 11}) == () and scheduler.state("a").in_flight == 2
+    assert scheduler.update({"a": 12}) == ()
+    assert scheduler.update({"a": 13}) == ("a",)
+    assert scheduler.output_tokens("a") == (11, 12, 13) and scheduler.finish_reason("a") == "length"
+    cache.check()
+
+
+def test_tokens_that_arrive_after_a_stop_are_dropped_and_in_flight_requests_are_not_victims():
+    scheduler, cache = make(num_pages=16, page_size=4)
+    scheduler.add_request(EngineRequest("a", (1, 2, 3), max_new_tokens=8, stop_token_ids=(42,)))
+    scheduler.schedule()
+    scheduler.schedule()  # ahead
+    assert scheduler.update({"a": 42}) == ("a",)      # the stop: finished with one token still in flight
+    assert scheduler.update({"a": 7}) == ()           # the late token is dropped
+    assert scheduler.output_tokens("a") == (42,)
+    assert "a" not in cache
+    # a request with a token in flight is never chosen as a victim
+    scheduler.add_request(EngineRequest("b", (1, 2, 3, 4), max_new_tokens=4))
+    scheduler.add_request(EngineRequest("c", (5, 6, 7, 8), max_new_tokens=4))
+    scheduler.schedule()
+    assert scheduler._pick_victim("b", set()) is None and scheduler.state("c").in_flight == 1
+    scheduler.update({"b": 1, "c": 2})
+    assert scheduler._pick_victim("b", set()) == "c"

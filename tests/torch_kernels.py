@@ -21,6 +21,12 @@ def embedding(table, ids, out, flag=None):
     out.copy_(table[ids.long()].float())
 
 
+def patch_tokens(ids, source, sampled, flag=None):
+    for t in range(ids.numel()):
+        if int(source[t]) >= 0:
+            ids[t] = sampled[int(source[t])]
+
+
 def rmsnorm(x, weight, eps, out, *, delta=None, rows=None):
     if rows is not None:
         v = x[rows.long()].float()
@@ -193,7 +199,7 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
 
 
 _NAMES = [
-    "embedding", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
+    "embedding", "patch_tokens", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
     "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
     "edit_logits", "sample",
 ]
