@@ -49,6 +49,7 @@ def _build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--max-num-seqs", type=int, default=256)
     generate.add_argument("--max-model-len", type=int, default=None)
     generate.add_argument("--decode-mode", choices=["eager", "cuda_graph"], default=None)
+    generate.add_argument("--pipeline-depth", type=int, choices=[1, 2], default=1, help="2: launch step N+1 while step N runs")
 
     validate = commands.add_parser("validate", help="Check a model folder against its architecture without a GPU.")
     validate.add_argument("model", type=Path, help="Path to the model folder")
@@ -90,7 +91,7 @@ def _generate(args: argparse.Namespace) -> int:
     llm = LLM(
         str(args.model), dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
         max_num_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
-        max_model_len=args.max_model_len, decode_mode=args.decode_mode,
+        max_model_len=args.max_model_len, decode_mode=args.decode_mode, pipeline_depth=args.pipeline_depth,
     )
     for output in llm.generate(prompts, params):
         print(
