@@ -57,6 +57,29 @@ GEN_LEN = 256
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
 
+# Further shapes (BASELINE.json configs[3] and [4]) for --shape; the default run and its JSON
+# contract are those of configs[2] above.
+SHAPES = {
+    "llama31-8b": None,
+    "qwen3-8b": dict(
+        model={
+            "architectures": ["Qwen3ForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 36, "num_attention_heads": 32,
+            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
+            "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
+        },
+        name="Qwen3-8B shape", seed=3, prompt_len=2048, gen_len=256, context_len=8192,
+    ),
+    "qwen3-32b": dict(
+        model={
+            "architectures": ["Qwen3ForCausalLM"], "hidden_size": 5120, "num_hidden_layers": 64, "num_attention_heads": 64,
+            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 25600, "vocab_size": 151936, "rope_theta": 1000000.0,
+            "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
+        },
+        name="Qwen3-32B shape", seed=4, prompt_len=1024, gen_len=128, context_len=8192,
+    ),
+}
+MODEL_NAME = "Llama-3.1-8B shape"
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -273,6 +296,47 @@ def time_e2e(engine, batch: int, steps: int):
     return batch * steps / seconds, meta_ints * 4, batch * 4 + 4
 
 
+def time_mixed(layers: int) -> dict:
+    """BASELINE.json configs[3]'s workload through ``LLM.generate``: 32 requests with prompt lengths
+    uniform in [128, 4096], prompts cut into portions of 512 tokens beside the decodes of the others,
+    128 generated tokens each.  Returns prompt+generated tokens a second and generated tokens a second."""
+    import torch
+
+    from kairyu_b200 import SamplingParams, TokensPrompt
+    from kairyu_b200.config.engine_config import EngineConfig
+    from kairyu_b200.engine.engine import Engine
+    from kairyu_b200.entrypoints.llm import LLM
+
+    config = dict(MODEL)
+    config["num_hidden_layers"] = layers
+    generator = torch.Generator().manual_seed(SEED)
+    lengths = torch.randint(128, 4097, (32,), generator=generator).tolist()
+    engine_config = EngineConfig(
+        dtype="bfloat16", page_size=PAGE_SIZE, num_pages=sum(-(-(n + 128 + 16) // PAGE_SIZE) for n in lengths) + 1,
+        max_num_batched_tokens=512 + 32, prefill_chunk_size=512, max_num_seqs=32, max_model_len=CONTEXT_LEN,
+        max_num_partial_prefills=1, pipeline_depth=2, seed=SEED,
+    )
+    engine = Engine.from_random(config, SEED, engine_config)
+    llm = LLM.__new__(LLM)
+    llm.model, llm.seed, llm._model_dir, llm.engine = "random", SEED, None, engine
+    llm._finish_init(None)
+    prompts = [TokensPrompt(tuple(random_tokens(n, MODEL["vocab_size"], 300 + i))) for i, n in enumerate(lengths)]
+    params = SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True)
+    llm.generate(prompts[:4], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))  # warm
+    torch.cuda.synchronize()
+    begin = time.perf_counter()
+    outputs = llm.generate(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - begin
+    generated = sum(len(output.outputs[0].token_ids) for output in outputs)
+    engine.runner.check_errors()
+    return {
+        "mixed_b32_total_tok_s": (sum(lengths) + generated) / seconds,
+        "mixed_b32_generated_tok_s": generated / seconds,
+        "mixed_b32_seconds": seconds,
+    }
+
+
 def reference_arm(args) -> int:
     """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
@@ -298,6 +362,7 @@ def reference_arm(args) -> int:
 
 
 def main() -> int:
+    global MODEL, MODEL_NAME, FULL_LAYERS, SEED, PROMPT_LEN, GEN_LEN, CONTEXT_LEN
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=128)
@@ -306,7 +371,16 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers only where memory or time needs it")
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31-8b", help="another shape than the default (its own lengths)")
+    parser.add_argument("--mixed", action="store_true", help="add the mixed workload of 32 requests (chunked prefill beside decode)")
     args = parser.parse_args()
+    if SHAPES[args.shape] is not None:
+        shape = SHAPES[args.shape]
+        MODEL, MODEL_NAME, SEED = shape["model"], shape["name"], shape["seed"]
+        PROMPT_LEN, GEN_LEN, CONTEXT_LEN = shape["prompt_len"], shape["gen_len"], shape["context_len"]
+        if args.layers == FULL_LAYERS:
+            args.layers = MODEL["num_hidden_layers"]
+        FULL_LAYERS = MODEL["num_hidden_layers"]
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
@@ -352,9 +426,13 @@ def main() -> int:
             points[key] = batch * steps / (ms / 1e3)
         rate, h2d, d2h = time_e2e(engine, args.batch, min(args.steps, 64))
         e2e = {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+    if args.mixed:
+        del engine
+        torch.cuda.empty_cache()
+        points.update(time_mixed(args.layers))
 
     line = {
-        "metric": "decode tok/s @bs8 (Llama-3.1-8B shape, 2048-token prompts)",
+        "metric": f"decode tok/s @bs{args.batch} ({MODEL_NAME}, {PROMPT_LEN}-token prompts)",
         "value": value,
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -368,7 +446,7 @@ def main() -> int:
         "data": "synthetic: seeded random token ids, seeded random weights (no checkpoint, no dataset)",
         "impl": "ours",
         "config": {
-            "model": "Llama-3.1-8B shape",
+            "model": MODEL_NAME,
             "layers": config["num_hidden_layers"],
             "layers_full": FULL_LAYERS,
             "hidden": config["hidden_size"],

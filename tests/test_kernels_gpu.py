@@ -304,6 +304,21 @@ def test_rope_flags_a_position_outside_the_table():
     assert int(flag.item()) == kernels().FLAG_BAD_POS
 
 
+def test_patch_tokens_takes_ids_from_the_device_and_flags_a_bad_source():
+    ids = torch.tensor([5, 0, 7, 0, 9], dtype=torch.int32, device=DEV)
+    source = torch.tensor([-1, 2, -1, 0, -1], dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([41, 42, 43], dtype=torch.int32, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels().patch_tokens(ids, source, sampled, flag)
+    assert ids.cpu().tolist() == [5, 43, 7, 41, 9] and int(flag.item()) == 0
+    expected = torch.tensor([5, 0, 7, 0, 9], dtype=torch.int32)
+    ref.patch_tokens(expected, source.cpu(), sampled.cpu())
+    assert expected.tolist() == ids.cpu().tolist()
+    source[1] = 3  # outside the sampled tensor: flagged, the id stays
+    kernels().patch_tokens(ids, source, sampled, flag)
+    assert int(flag.item()) == kernels().FLAG_BAD_ROW and ids.cpu().tolist() == [5, 43, 7, 41, 9]
+
+
 # ------------------------------------------------------------------ attention
 
 
