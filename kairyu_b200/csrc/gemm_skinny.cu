@@ -49,8 +49,11 @@ __device__ __forceinline__ Reg8 load_cached32(const void* p) {
 
 // NT: token tiles of 8 (1 or 2).  GATED: warps 0..3 walk the gate rows and warps
 // 4..7 the rows N/2 further down (the "up" half); the epilogue writes silu(gate) * up.
-template <int NT, bool GATED, typename TO>
-__global__ void __launch_bounds__(SK_THREADS)
+// MINB: blocks the compiler keeps room for on an SM (2 or 3).  A grid that does not fit at two
+// blocks per SM (q/k/v: 384 blocks, the head: thousands) runs faster at three, with 80
+// registers a thread and a few spilled bytes; one that fits (o, down: 256 blocks) does not.
+template <int NT, bool GATED, typename TO, int MINB>
+__global__ void __launch_bounds__(SK_THREADS, MINB)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                    int ldw, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out, int ldo,
                    int M, int N, int K) {
@@ -185,10 +188,20 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
                          cudaStream_t stream) {
     const int rows_out = GATED ? N / 2 : N;
     const int blocks = (rows_out + 15) / 16;
-    if (out_fp32)
-        kb_launch(gemm_skinny_kernel<NT, GATED, float>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (float*)out, ldo, M, N, K);
-    else
-        kb_launch(gemm_skinny_kernel<NT, GATED, __nv_bfloat16>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (__nv_bfloat16*)out, ldo, M, N, K);
+    static int two_per_sm = 0;  // blocks resident at two per SM
+    if (two_per_sm == 0) {
+        int device = 0, sms = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+        two_per_sm = 2 * sms;
+    }
+    const bool three = NT == 1 && !GATED && blocks > two_per_sm;
+#define GO(TO_, MINB_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K)
+    if (out_fp32) {
+        if (three) GO(float, 3); else GO(float, 2);
+    } else {
+        if (three) GO(__nv_bfloat16, 3); else GO(__nv_bfloat16, 2);
+    }
+#undef GO
     return kb_launch_result();
 }
 
