@@ -56,7 +56,10 @@ template <int NT, bool GATED, typename TO, int MINB>
 __global__ void __launch_bounds__(SK_THREADS, MINB)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                    int ldw, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out, int ldo,
-                   int M, int N, int K) {
+                   int M, int N, int K, int rows_per_block_arg) {
+    // Only the two-per-SM variant takes a runtime row count: at three per SM (80 registers) the
+    // extra predicates spill into the main loop.
+    const int rows_per_block = MINB == 2 ? rows_per_block_arg : 16;
     pdl_trigger();
     constexpr int HALVES = GATED ? 2 : 1;
     constexpr int KWARPS = SK_WARPS / HALVES;  // warps that split K for one half
@@ -68,7 +71,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     const int half = warp / KWARPS;
     const int kwarp = warp % KWARPS;
     const int rows_out = GATED ? N / 2 : N;      // output columns
-    const int n0 = blockIdx.x * 16;              // first weight row (and output column) of the block
+    // A block owns rows_per_block (<= 16) weight rows: fewer than 16 leaves rows of the MMA tile
+    // idle, which costs nothing here, and lets the host pick a grid that fills every SM evenly.
+    const int n0 = blockIdx.x * rows_per_block;  // first weight row (and output column) of the block
 
     // K is cut into SK_STEP-wide steps; warp kwarp takes steps kwarp, kwarp + KWARPS, ...
     const int steps = (K + SK_STEP - 1) / SK_STEP;
@@ -78,8 +83,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 
     const int row_lo = n0 + g;
     const int row_hi = n0 + g + 8;
-    const bool lo_ok = row_lo < rows_out;
-    const bool hi_ok = row_hi < rows_out;
+    const bool lo_ok = g < rows_per_block && row_lo < rows_out;
+    const bool hi_ok = g + 8 < rows_per_block && row_hi < rows_out;
     const __nv_bfloat16* w_lo = w + (size_t)(half * rows_out + (lo_ok ? row_lo : 0)) * ldw;
     const __nv_bfloat16* w_hi = w + (size_t)(half * rows_out + (hi_ok ? row_hi : 0)) * ldw;
     const __nv_bfloat16* x_row[NT];
@@ -166,7 +171,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         const int t = token >> 3;
         const int col = token & 7;
         const int n = n0 + r;
-        if (token >= M || n >= rows_out) continue;
+        if (token >= M || r >= rows_per_block || n >= rows_out) continue;
         float value[HALVES];
 #pragma unroll
         for (int h = 0; h < HALVES; ++h) {
@@ -187,15 +192,24 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
                          const __nv_bfloat16* bias, void* out, int out_fp32, int ldo, int M, int N, int K,
                          cudaStream_t stream) {
     const int rows_out = GATED ? N / 2 : N;
-    const int blocks = (rows_out + 15) / 16;
-    static int two_per_sm = 0;  // blocks resident at two per SM
-    if (two_per_sm == 0) {
-        int device = 0, sms = 0;
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
         if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
-        two_per_sm = 2 * sms;
     }
-    const bool three = NT == 1 && !GATED && blocks > two_per_sm;
-#define GO(TO_, MINB_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K)
+    // Grid: one wave that fills every SM evenly where the rows allow it (rows per block between
+    // 8 and 16, two blocks per SM); else 16-row blocks, three to an SM.
+    int rows_per_block = 16;
+    bool three = false;
+    if (!GATED && NT == 1) {
+        const int fit2 = (rows_out + 2 * sms - 1) / (2 * sms);
+        if (fit2 <= 16)
+            rows_per_block = fit2 < 8 ? 8 : fit2;
+        else
+            three = true;  // 16-row blocks, three to an SM
+    }
+    const int blocks = (rows_out + rows_per_block - 1) / rows_per_block;
+#define GO(TO_, MINB_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K, rows_per_block)
     if (out_fp32) {
         if (three) GO(float, 3); else GO(float, 2);
     } else {

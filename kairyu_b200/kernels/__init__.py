@@ -637,9 +637,12 @@ def _gemm_tc5(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
 def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: object) -> None:
     """out = silu(x @ Wg.T) * (x @ Wu.T) with ``weight_gate_up`` = [Wg; Wu] stacked by rows.
 
-    For up to 64 bf16 token rows this is one weight-streaming kernel with the gate in
-    its epilogue (tcgen05 + TMA, csrc/gemm_tc5.cu); otherwise a product into
-    ``scratch.buffer(...)`` and the gate kernel.
+    For up to 64 bf16 token rows this is one weight-streaming kernel with the gate in its
+    epilogue: the mma.sync skinny kernel up to 16 rows (csrc/gemm_skinny.cu; measured on the
+    decode step at 8 rows it is 2 % of the step faster than the tcgen05 kernel, whose fixed
+    costs - barrier and tensor-memory set-up, the accumulator read-back - weigh more on a 40 us
+    kernel), the tcgen05 + TMA kernel from 17 to 64 rows (csrc/gemm_tc5.cu); otherwise a product
+    into ``scratch.buffer(...)`` and the gate kernel.
     """
     _need_cuda("linear_swiglu", x, weight_gate_up, out)
     M = x.shape[0]
@@ -649,11 +652,11 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tens
     if M == 0:
         return
     if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-        if _tc5_ok(x, weight_gate_up, None, out):  # tcgen05 + TMA: the fastest of the three for the wide gate/up band
-            _gemm_tc5(x, weight_gate_up, None, out, gated=True)
-            return
         if _skinny_ok(x, weight_gate_up, None, out):
             _gemm_skinny(x, weight_gate_up, None, out, gated=True)
+            return
+        if _tc5_ok(x, weight_gate_up, None, out):
+            _gemm_tc5(x, weight_gate_up, None, out, gated=True)
             return
     gate_up = scratch.buffer("ffn.gate_up", M, two_i, x.dtype)
     linear(x, weight_gate_up, None, gate_up)
