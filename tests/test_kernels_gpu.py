@@ -478,6 +478,28 @@ def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_s
     close(out, expected, 2e-2)
 
 
+@pytest.mark.parametrize("num_splits", [None, 1, 5])
+def test_decode_attention_long_context(num_splits, workspace):
+    """Thousands of keys: tens of ring refills per block, a hot key far back, a window over most of it."""
+    Hq, Hkv, D, page_size = 8, 2, 128, 16
+    seq_lens = [5000, 4097, 3]
+    for window, hot in ((0, (0, 77)), (4500, (1, 1000))):
+        case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, [1] * 3, seed=36, hot=hot)
+        scale = 1.0 / math.sqrt(D)
+        expected = _reference_attention(case, Hq, scale, window)
+        assert float(expected[hot[0]].min()) > 24.0
+        out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+        rows = torch.arange(3, dtype=torch.int32, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        kernels().attention_decode_mma(
+            case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), seq_lens=case["seq_lens"].to(DEV),
+            block_table=case["table"].to(DEV), decode_rows=rows, decode_tokens=rows, num_rows=3, max_seq_len=max(seq_lens),
+            num_q_heads=Hq, scale=scale, window=window, workspace=workspace, flag=flag, num_splits=num_splits,
+        )
+        assert int(flag.item()) == 0
+        close(out, expected, 2e-2, rtol=1e-2)
+
+
 @pytest.mark.parametrize("hot_key", [0, 15, 16, 17, 63, 64, 127, 128, 129, 255, 256, 257, 511, 512, 640, 699])
 @pytest.mark.parametrize("chunk", [1, 2, 61])
 def test_mma_attention_finds_one_far_key(hot_key, chunk, workspace):
