@@ -473,11 +473,12 @@ class ModelRunner:
         def run() -> torch.Tensor:
             return self.model.forward(ctx, self._views, want_all)
 
-        # Warm up on a side stream: buffers reach their size, libraries initialise.
+        # Warm up on a side stream: buffers reach their size, libraries initialise (twice for the
+        # first graph of this runner, once for later ones, whose kernels have all run before).
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(2):
+            for _ in range(2 if self.counters["graph_captures"] == 0 else 1):
                 run()
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()

@@ -12,6 +12,7 @@ from kairyu_b200.parts.base import (
     EMBEDDINGS,
     HEADS,
     NORMS,
+    POSITION_ENCODINGS,
     CacheView,
     ModelSpec,
     PartSpec,
@@ -35,6 +36,9 @@ class DecoderModel:
         shared: dict[Any, Any] = {}
         context = dict(dtype=self.dtype, device=device, shared=shared)
         self.embedding = EMBEDDINGS.build(spec.embedding, **context)
+        self.embedding_position = (
+            POSITION_ENCODINGS.build(spec.embedding_position, **context) if spec.embedding_position is not None else None
+        )
         self.blocks = [
             BLOCKS.build(PartSpec(layer.block), layer=layer, **context) for layer in spec.layers
         ]
@@ -59,7 +63,8 @@ class DecoderModel:
 
     # -- weights
     def parts(self) -> list[Any]:
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        extra = [self.embedding_position] if self.embedding_position is not None else []
+        return [self.embedding, *extra, *self.blocks, self.final_norm, self.head]
 
     def tensor_specs(self) -> list[TensorSpec]:
         return [spec for part in self.parts() for spec in part.tensor_specs()]
@@ -92,6 +97,8 @@ class DecoderModel:
         """Run the step's tokens through every scheduled call; return fp32
         logits at ``want_rows`` (flat token indices), or None when none are wanted."""
         residual = self.embedding.forward(ctx)
+        if self.embedding_position is not None:
+            self.embedding_position.embed_hook(residual, ctx)
         delta: Optional[torch.Tensor] = None
         for call in self.schedule:
             view = cache_views[(call.cache_slot, call.writes_cache)]

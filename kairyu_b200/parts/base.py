@@ -15,7 +15,7 @@ here the switch is the spec.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Callable, Mapping, Sequence
+from typing import Any, Callable, Mapping, Optional, Sequence
 
 import torch
 
@@ -83,6 +83,9 @@ class ModelSpec:
     vocab_size: int
     hidden_size: int
     max_position_embeddings: int
+    # A position encoding that acts on the embedding (learned absolute positions and the like);
+    # rotary kinds belong to the mixers that use them.
+    embedding_position: Optional[PartSpec] = None
 
 
 # --------------------------------------------------------------------------- weights
@@ -214,7 +217,9 @@ class PositionEncoding(Part):
         return None
 
     def embed_hook(self, residual: torch.Tensor, ctx: StepContext) -> None:
-        """For encodings that act on the embedding rather than on q and k."""
+        """For encodings that act on the embedding rather than on q and k: called once a step
+        with the fp32 residual the embedding produced (``ModelSpec.embedding_position``); changes
+        it in place from ``ctx.positions``."""
 
 
 class Mixer(Part):

@@ -177,3 +177,151 @@ def test_toy_architecture_on_cpu(toy, monkeypatch):
 @pytest.mark.gpu
 def test_toy_architecture_on_gpu(toy):
     check(toy, "cuda")
+
+
+# ------------------------------------------------------------------ a second toy: routing and another position encoding
+# A feed-forward that routes every token to one of three experts, and learned absolute positions
+# added to the embedding, both defined here and registered from outside the package; attention
+# runs without rotary tables.  Compared with a plain whole-sequence computation under all cuts.
+
+from kairyu_b200.parts import FEED_FORWARDS, POSITION_ENCODINGS, FeedForward, PositionEncoding  # noqa: E402
+
+EXPERTS = 3
+R_HIDDEN, R_INTER, R_VOCAB, R_MAXPOS = 40, 24, 61, 160
+
+
+class LearnedPositions(PositionEncoding):
+    """residual[t] += table[position[t]]."""
+
+    def __init__(self, *, name, max_positions, hidden_size, dtype, device, **_):
+        self.name, self.max_positions, self.hidden_size = name, max_positions, hidden_size
+        self.table = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.max_positions, self.hidden_size))]
+
+    def load(self, tensors):
+        self.table = tensors[self.name]
+
+    def embed_hook(self, residual, ctx):
+        residual.add_(self.table[ctx.positions.long()].float())
+
+
+class TopOneExperts(FeedForward):
+    """Router logits in fp32, the best expert per token, y = W2_e relu(W1_e x) scaled by its softmax weight."""
+
+    def __init__(self, *, prefix, hidden_size, intermediate_size, num_experts, dtype, device, **_):
+        self.prefix, self.hidden_size, self.inter, self.num_experts = prefix, hidden_size, intermediate_size, num_experts
+        self.router = self.w1 = self.w2 = None
+
+    def tensor_specs(self):
+        return [
+            TensorSpec(f"{self.prefix}.router.weight", (self.num_experts, self.hidden_size)),
+            TensorSpec(f"{self.prefix}.w1", (self.num_experts * self.inter, self.hidden_size)),
+            TensorSpec(f"{self.prefix}.w2", (self.num_experts * self.hidden_size, self.inter)),
+        ]
+
+    def load(self, tensors):
+        self.router = tensors[f"{self.prefix}.router.weight"]
+        self.w1 = tensors[f"{self.prefix}.w1"].view(self.num_experts, self.inter, self.hidden_size)
+        self.w2 = tensors[f"{self.prefix}.w2"].view(self.num_experts, self.hidden_size, self.inter)
+
+    def forward(self, x, ctx):
+        return routed_ffn(x.float(), self.router.float(), self.w1.float(), self.w2.float()).to(x.dtype)
+
+
+def routed_ffn(x, router, w1, w2):
+    probs = torch.softmax(x @ router.t(), dim=-1)
+    best = probs.argmax(dim=-1)
+    out = torch.zeros(x.shape[0], w2.shape[1], dtype=torch.float32, device=x.device)
+    for expert in range(router.shape[0]):
+        rows = (best == expert).nonzero().flatten()
+        if rows.numel():
+            h = torch.relu(x[rows] @ w1[expert].t())
+            out[rows] = (h @ w2[expert].t()) * probs[rows, expert : expert + 1]
+    return out
+
+
+def routed_spec(config) -> ModelSpec:
+    def norm(name):
+        return PartSpec("rmsnorm", name=name, size=R_HIDDEN, eps=EPS)
+
+    def layer(i):
+        attention = PartSpec(
+            "gqa_attention", prefix=f"layers.{i}.attn", hidden_size=R_HIDDEN, num_heads=2, num_kv_heads=2, head_dim=16,
+            qk_norm=False, norm_eps=EPS, qkv_bias=False, o_bias=False, position=None,
+        )
+        ffn = PartSpec("toy_top_one", prefix=f"layers.{i}.moe", hidden_size=R_HIDDEN, intermediate_size=R_INTER, num_experts=EXPERTS)
+        return LayerSpec(f"layers.{i}", "pre_norm", attention, ffn, norm(f"layers.{i}.norm1.weight"), norm(f"layers.{i}.norm2.weight"))
+
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", name="embed.weight", vocab_size=R_VOCAB, hidden_size=R_HIDDEN),
+        layers=(layer(0), layer(1)), schedule=(LayerCall(0, cache_slot=0), LayerCall(1, cache_slot=1)),
+        final_norm=norm("final_norm.weight"),
+        head=PartSpec("linear_head", name="head.weight", vocab_size=R_VOCAB, hidden_size=R_HIDDEN, tied_to=None),
+        vocab_size=R_VOCAB, hidden_size=R_HIDDEN, max_position_embeddings=R_MAXPOS,
+        embedding_position=PartSpec("toy_learned_positions", name="positions.weight", max_positions=R_MAXPOS, hidden_size=R_HIDDEN),
+    )
+
+
+@pytest.fixture
+def routed():
+    FEED_FORWARDS.register("toy_top_one")(TopOneExperts)
+    POSITION_ENCODINGS.register("toy_learned_positions")(LearnedPositions)
+    register_architecture("ToyRoutedForCausalLM", lambda config: dict(config), routed_spec)
+    yield {"architectures": ["ToyRoutedForCausalLM"]}
+    unregister_architecture("ToyRoutedForCausalLM")
+    FEED_FORWARDS.unregister("toy_top_one")
+    POSITION_ENCODINGS.unregister("toy_learned_positions")
+
+
+def plain_routed_logits(w, tokens):
+    lin = torch.nn.functional.linear
+    T = len(tokens)
+    x = w["embed.weight"][torch.tensor(tokens)] + w["positions.weight"][:T]
+    for i in range(2):
+        h = plain_model.rms_norm(x, w[f"layers.{i}.norm1.weight"], EPS)
+        q = lin(h, w[f"layers.{i}.attn.q_proj.weight"]).view(T, 2, 16)
+        k = lin(h, w[f"layers.{i}.attn.k_proj.weight"]).view(T, 2, 16)
+        v = lin(h, w[f"layers.{i}.attn.v_proj.weight"]).view(T, 2, 16)
+        x = x + lin(plain_model.causal_attention(q, k, v), w[f"layers.{i}.attn.o_proj.weight"])
+        h = plain_model.rms_norm(x, w[f"layers.{i}.norm2.weight"], EPS)
+        x = x + routed_ffn(
+            h, w[f"layers.{i}.moe.router.weight"], w[f"layers.{i}.moe.w1"].view(EXPERTS, R_INTER, R_HIDDEN),
+            w[f"layers.{i}.moe.w2"].view(EXPERTS, R_HIDDEN, R_INTER),
+        )
+    return lin(plain_model.rms_norm(x, w["final_norm.weight"], EPS), w["head.weight"])
+
+
+def check_routed(config, device):
+    model, _ = build_model(config, dtype="float32", device=device)
+    weights = random_tensors(model.tensor_specs(), seed=12, device="cpu")
+    # Router rows far apart, so that a rounding difference between the two computations does not flip an expert
+    for i in range(2):
+        weights[f"layers.{i}.moe.router.weight"] = weights[f"layers.{i}.moe.router.weight"] * 40.0
+    model.load({name: tensor.to(device) for name, tensor in weights.items()})
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=24, page_size=8, max_requests=4)
+    storage = CacheStorage(layout, num_pages=24, page_size=8, max_requests=4, dtype=model.dtype, device=device)
+    runner = ModelRunner(model, cache, storage, max_model_len=R_MAXPOS, decode_mode="eager")
+    requests = traces.make_requests(R_VOCAB, [37, 20, 51, 9, 44, 30], seed=8)
+    expected = {name: plain_routed_logits(weights, tokens).numpy() for name, tokens in requests.items()}
+    experts_used = set()
+    for tokens in requests.values():
+        h = plain_model.rms_norm(weights["embed.weight"][torch.tensor(tokens)] + weights["positions.weight"][: len(tokens)], weights["layers.0.norm1.weight"], EPS)
+        experts_used |= set((h @ weights["layers.0.moe.router.weight"].t()).argmax(-1).tolist())
+    assert len(experts_used) > 1  # the routing does route
+    for steps in (traces.trace_whole(requests), traces.trace_chunks(requests), traces.trace_mixed(requests, seed=4)):
+        result = traces.run_in_process(runner, steps)
+        worst = max(float(np.abs(row - expected[n][p]).max()) for (n, p), row in result.items())
+        assert worst < 3e-5, worst
+
+
+def test_routed_toy_architecture_on_cpu(routed, monkeypatch):
+    torch_kernels.install(monkeypatch)
+    check_routed(routed, "cpu")
+
+
+@pytest.mark.gpu
+def test_routed_toy_architecture_on_gpu(routed):
+    check_routed(routed, "cuda")

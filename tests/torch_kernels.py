@@ -58,8 +58,8 @@ def qk_norm_rope_kv_write(
     T = qkv.shape[0]
     q_size = num_q_heads * head_dim
     kv_size = num_kv_heads * head_dim
-    q = qkv[:, :q_size].float().view(T, num_q_heads, head_dim)
-    k = qkv[:, q_size : q_size + kv_size].float().view(T, num_kv_heads, head_dim)
+    q = qkv[:, :q_size].float().clone().view(T, num_q_heads, head_dim)
+    k = qkv[:, q_size : q_size + kv_size].float().clone().view(T, num_kv_heads, head_dim)
     v = qkv[:, q_size + kv_size :].view(T, num_kv_heads, head_dim)
     if q_norm_weight is not None:
         q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm_weight.float()
