@@ -373,6 +373,8 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31-8b", help="another shape than the default (its own lengths)")
     parser.add_argument("--mixed", action="store_true", help="add the mixed workload of 32 requests (chunked prefill beside decode)")
+    parser.add_argument("--prompt-len", type=int, default=None, help="another prompt length than the shape's (with --gen-len, within the context length)")
+    parser.add_argument("--gen-len", type=int, default=None)
     args = parser.parse_args()
     if SHAPES[args.shape] is not None:
         shape = SHAPES[args.shape]
@@ -381,6 +383,13 @@ def main() -> int:
         if args.layers == FULL_LAYERS:
             args.layers = MODEL["num_hidden_layers"]
         FULL_LAYERS = MODEL["num_hidden_layers"]
+    if args.prompt_len is not None:
+        PROMPT_LEN = args.prompt_len
+    if args.gen_len is not None:
+        GEN_LEN = args.gen_len
+    if PROMPT_LEN + GEN_LEN > CONTEXT_LEN:
+        print(f"bench.py: prompt {PROMPT_LEN} + generation {GEN_LEN} exceeds the context length {CONTEXT_LEN}", file=sys.stderr)
+        return 1
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

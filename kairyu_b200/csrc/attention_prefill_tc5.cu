@@ -406,17 +406,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     tc_fence_before();
     __syncthreads();
     if (*abort_word && threadIdx.x == 0) {
-        // copies that are still in flight target this block's shared memory: one more bounded wait
-        volatile int never = 0;
+        // copies that are still in flight target this block's shared memory: one more short wait
+        // on the barriers they complete (q_full, k_full, v_full), whichever phase they are in
+        volatile int ignore = 0;
         for (int s = 0; s < 1 + 2 * FA_STAGES; ++s) {
-            for (uint32_t spin = 0; spin < 1024; ++spin) {
-                uint32_t done;
-                asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                             : "=r"(done)
-                             : "r"(smem_addr(bars + s)), "r"(0u)
-                             : "memory");
-                if (done || never) break;
-            }
+            mbar_wait(bars + s, 0, &ignore, 1024);
+            mbar_wait(bars + s, 1, &ignore, 1024);
         }
     }
     if (warp == 1) {

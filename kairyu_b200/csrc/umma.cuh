@@ -21,9 +21,9 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
 // Bounded wait; also leaves when another role of the block has raised `abort`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t limit = TC_SPIN_LIMIT) {
     const uint32_t addr = smem_addr(bar);
-    for (uint32_t spin = 0; spin < TC_SPIN_LIMIT; ++spin) {
+    for (uint32_t spin = 0; spin < limit; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
