@@ -11,12 +11,23 @@
 // MMAs as their (k, k+8) pairs without any shuffle.  A block owns 16 weight rows; its
 // warps split K and their partial sums are added in warp order through shared
 // memory, so the result does not depend on timing.
+//
+// RMSNorm around the product, without a kernel of its own (kairyu/models/layers.py:21-46 is the
+// norm, kairyu/models/llama.py:88-101 the residual arrangement).  With y = rmsnorm(r) * g feeding
+// a product, (y . W^T)[m] = rstd[m] * ((r[m] * g) . W^T): the product before can leave r * g
+// (rounded to bf16) and the sum of r^2, and this product scales its rows by rstd in the epilogue.
+//   * fold:  the epilogue adds the result to the fp32 residual r (in place), writes bf16(r * g)
+//     for the next product and, per block, the partial sums of r^2 over the block's columns;
+//   * scale: the epilogue multiplies row m by rsqrt(sum of the partial sums / H + eps) before
+//     bias and gate.  The partial sums are added in block order, so the result does not depend
+//     on timing.
 #include "common.cuh"
 
 #define SK_WARPS 8
 #define SK_THREADS (SK_WARPS * 32)
 #define SK_UNROLL 2
 #define SK_STEP 64  // k per step: four lanes of a weight row load 32 bytes each, one full 128-byte line
+#define SK_SUM_BLOCKS 384  // a scaling epilogue adds up to this many partial sums per row
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -28,6 +39,23 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 
 struct Reg8 {
     uint32_t r[8];
+};
+
+// What the epilogue does beside the product (all pointers null: nothing).
+struct SkinnyFusion {
+    // scale: rows come unnormalised; in_sumsq[b * 16 + m] are the producer's partial sums of row m
+    const float* in_sumsq;
+    int in_blocks;
+    float in_inv_hidden;
+    float in_eps;
+    // fold: residual[m, n] += result; values[m, n] = bf16(residual * norm_w[n]); out_sumsq[block * 16 + m]
+    float* residual;
+    int ldr;
+    const void* norm_w;
+    int norm_w_bf16;
+    __nv_bfloat16* values;
+    int ldv;
+    float* out_sumsq;
 };
 
 // streaming 32-byte load of weights (sm_100 has 256-bit loads): read once, keep out of L1
@@ -52,11 +80,12 @@ __device__ __forceinline__ Reg8 load_cached32(const void* p) {
 // MINB: blocks the compiler keeps room for on an SM (2 or 3).  A grid that does not fit at two
 // blocks per SM (q/k/v: 384 blocks, the head: thousands) runs faster at three, with 80
 // registers a thread and a few spilled bytes; one that fits (o, down: 256 blocks) does not.
-template <int NT, bool GATED, typename TO, int MINB>
+// FUSED: the epilogue does norm work (SkinnyFusion); the plain instantiation carries none of it.
+template <int NT, bool GATED, typename TO, int MINB, bool FUSED>
 __global__ void __launch_bounds__(SK_THREADS, MINB)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfloat16* __restrict__ w,
                    int ldw, const __nv_bfloat16* __restrict__ bias, TO* __restrict__ out, int ldo,
-                   int M, int N, int K, int rows_per_block_arg) {
+                   int M, int N, int K, int rows_per_block_arg, SkinnyFusion fusion) {
     // Only the two-per-SM variant takes a runtime row count: at three per SM (80 registers) the
     // extra predicates spill into the main loop.
     const int rows_per_block = MINB == 2 ? rows_per_block_arg : 16;
@@ -64,6 +93,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     constexpr int HALVES = GATED ? 2 : 1;
     constexpr int KWARPS = SK_WARPS / HALVES;  // warps that split K for one half
     __shared__ float partial[SK_WARPS][NT][16][8 + 1];
+    constexpr int SUM_TOKENS = NT * 8;                 // token rows the epilogue may scale
+    constexpr int SUM_CHUNKS = SK_THREADS / SUM_TOKENS;  // threads (chunks of blocks) that share a token's partial sums
+    constexpr int SUM_ROUNDS = SK_SUM_BLOCKS / SUM_CHUNKS;
+    __shared__ float sums[SUM_CHUNKS][SUM_TOKENS + 1];  // [chunk of blocks][token] partial sums of the rows' squares
+    __shared__ float row_scale[16];
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2;
@@ -144,6 +178,31 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     load_weights(0, step0);
     pdl_wait();
     load_tokens(0, step0);
+    // scale: thread (chunk, token) adds every 16th block's partial sum of its token's row; the
+    // loads overlap the first weights' way from memory
+    float my_sum = 0.0f;
+    if (FUSED && fusion.in_sumsq != nullptr) {
+        // up to SK_SUM_BLOCKS blocks; the loads go out together, not one per round trip
+        float part[SUM_ROUNDS];
+#pragma unroll
+        for (int i = 0; i < SUM_ROUNDS; ++i) {
+            const int b = threadIdx.x / SUM_TOKENS + SUM_CHUNKS * i;
+            part[i] = b < fusion.in_blocks ? fusion.in_sumsq[b * 16 + threadIdx.x % SUM_TOKENS] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < SUM_ROUNDS; ++i) my_sum += part[i];
+    }
+    // fold: this thread's element of the residual and of the norm weight, asked for now and used in the epilogue
+    float held_residual = 0.0f, held_weight = 0.0f;
+    if (FUSED && fusion.residual != nullptr && threadIdx.x < NT * 8 * 16) {
+        const int r = threadIdx.x & 15;
+        const int token = threadIdx.x >> 4;
+        const int n = n0 + r;
+        if (token < M && r < rows_per_block && n < rows_out) {
+            held_residual = fusion.residual[(size_t)token * fusion.ldr + n];
+            held_weight = fusion.norm_w_bf16 ? __bfloat162float(((const __nv_bfloat16*)fusion.norm_w)[n]) : ((const float*)fusion.norm_w)[n];
+        }
+    }
     while (true) {
         load_batch(1, step0 + STRIDE);  // past the end: all zero, no memory touched
         mma_batch(0);
@@ -163,35 +222,64 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         partial[warp][t][g + 8][2 * tq] = acc[t][2];
         partial[warp][t][g + 8][2 * tq + 1] = acc[t][3];
     }
+    if (FUSED) sums[threadIdx.x / SUM_TOKENS][threadIdx.x % SUM_TOKENS] = my_sum;
     __syncthreads();
-    // one thread per (token, row): rows fastest so that stores of a token are contiguous
+    if (FUSED && fusion.in_sumsq != nullptr) {
+        if (threadIdx.x < SUM_TOKENS) {
+            float total = 0.0f;
+#pragma unroll
+            for (int c = 0; c < SUM_CHUNKS; ++c) total += sums[c][threadIdx.x];
+            row_scale[threadIdx.x] = rsqrtf(total * fusion.in_inv_hidden + fusion.in_eps);
+        }
+        __syncthreads();
+    }
+    // one thread per (token, row): rows fastest so that stores of a token are contiguous.  Whole
+    // warps are inside the loop or outside it (its bound is a multiple of 32).
     for (int idx = threadIdx.x; idx < NT * 8 * 16; idx += SK_THREADS) {
         const int r = idx & 15;
         const int token = idx >> 4;
         const int t = token >> 3;
         const int col = token & 7;
         const int n = n0 + r;
-        if (token >= M || r >= rows_per_block || n >= rows_out) continue;
-        float value[HALVES];
+        const bool valid = token < M && r < rows_per_block && n < rows_out;
+        float result = 0.0f;
+        if (valid) {
+            float value[HALVES];
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-            float sum = 0.0f;
+            for (int h = 0; h < HALVES; ++h) {
+                float sum = 0.0f;
 #pragma unroll
-            for (int wp = 0; wp < KWARPS; ++wp) sum += partial[h * KWARPS + wp][t][r][col];
-            if (bias) sum += __bfloat162float(bias[h * rows_out + n]);
-            value[h] = sum;
+                for (int wp = 0; wp < KWARPS; ++wp) sum += partial[h * KWARPS + wp][t][r][col];
+                if (FUSED && fusion.in_sumsq != nullptr) sum *= row_scale[token];
+                if (bias) sum += __bfloat162float(bias[h * rows_out + n]);
+                value[h] = sum;
+            }
+            result = value[0];
+            if (GATED) result = value[0] / (1.0f + expf(-value[0])) * value[HALVES - 1];
         }
-        float result = value[0];
-        if (GATED) result = value[0] / (1.0f + expf(-value[0])) * value[HALVES - 1];
-        out[(size_t)token * ldo + n] = from_float<TO>(result);
+        if (!FUSED || fusion.residual == nullptr) {
+            if (valid) out[(size_t)token * ldo + n] = from_float<TO>(result);
+            continue;
+        }
+        float square = 0.0f;
+        if (valid) {
+            // (NT * 8 * 16 <= SK_THREADS: the loop runs once and idx == threadIdx.x, as when the values were fetched)
+            const float sum = held_residual + result;
+            fusion.residual[(size_t)token * fusion.ldr + n] = sum;
+            fusion.values[(size_t)token * fusion.ldv + n] = __float2bfloat16_rn(sum * held_weight);
+            square = sum * sum;
+        }
+        // the 16 rows of a token sit in 16 neighbouring lanes
+        square += __shfl_xor_sync(0xffffffffu, square, 8);
+        square += __shfl_xor_sync(0xffffffffu, square, 4);
+        square += __shfl_xor_sync(0xffffffffu, square, 2);
+        square += __shfl_xor_sync(0xffffffffu, square, 1);
+        if (r == 0) fusion.out_sumsq[(size_t)blockIdx.x * 16 + token] = square;
     }
 }
 
-template <int NT, bool GATED>
-static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw,
-                         const __nv_bfloat16* bias, void* out, int out_fp32, int ldo, int M, int N, int K,
-                         cudaStream_t stream) {
-    const int rows_out = GATED ? N / 2 : N;
+// rows per block and whether three blocks go on an SM, for (rows of output, token tiles, gated)
+static void skinny_grid(int rows_out, bool single_tile_plain, int& rows_per_block, bool& three) {
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
@@ -199,22 +287,31 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
     }
     // Grid: one wave that fills every SM evenly where the rows allow it (rows per block between
     // 8 and 16, two blocks per SM); else 16-row blocks, three to an SM.
-    int rows_per_block = 16;
-    bool three = false;
-    if (!GATED && NT == 1) {
+    rows_per_block = 16;
+    three = false;
+    if (single_tile_plain) {
         const int fit2 = (rows_out + 2 * sms - 1) / (2 * sms);
         if (fit2 <= 16)
             rows_per_block = fit2 < 8 ? 8 : fit2;
         else
-            three = true;  // 16-row blocks, three to an SM
+            three = true;
     }
+}
+
+template <int NT, bool GATED>
+static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, int ldw,
+                         const __nv_bfloat16* bias, void* out, int out_fp32, int ldo, int M, int N, int K,
+                         const SkinnyFusion& fusion, cudaStream_t stream) {
+    const int rows_out = GATED ? N / 2 : N;
+    int rows_per_block;
+    bool three;
+    skinny_grid(rows_out, !GATED && NT == 1, rows_per_block, three);
     const int blocks = (rows_out + rows_per_block - 1) / rows_per_block;
-#define GO(TO_, MINB_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K, rows_per_block)
-    if (out_fp32) {
-        if (three) GO(float, 3); else GO(float, 2);
-    } else {
-        if (three) GO(__nv_bfloat16, 3); else GO(__nv_bfloat16, 2);
-    }
+    const bool fused = fusion.in_sumsq != nullptr || fusion.residual != nullptr;
+#define GO(TO_, MINB_, F_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_, F_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K, rows_per_block, fusion)
+#define PICK(TO_) do { if (three) { if (fused) GO(TO_, 3, true); else GO(TO_, 3, false); } else { if (fused) GO(TO_, 2, true); else GO(TO_, 2, false); } } while (0)
+    if (out_fp32) PICK(float); else PICK(__nv_bfloat16);
+#undef PICK
 #undef GO
     return kb_launch_result();
 }
@@ -222,20 +319,62 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
 // x: [M, K] bf16 (row stride ldx), w: [N, K] bf16 (row stride ldw), bias: [N] bf16 or null,
 // out: [M, N] (or [M, N/2] when gated) bf16 or fp32.  Needs M <= 16, K % 16 == 0 and
 // 32-byte aligned rows; anything else is refused (the caller has the library product).
-KB_EXPORT int kb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out,
-                             int out_fp32, int ldo, int M, int N, int K, int gated, cudaStream_t stream) {
+static int skinny_entry(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out, int out_fp32, int ldo,
+                        int M, int N, int K, int gated, const SkinnyFusion& fusion, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
-    if (!x || !w || !out) return KB_ERR_NULL;
+    if (!x || !w || (!out && !fusion.residual)) return KB_ERR_NULL;
     if (M < 1 || M > 16 || K < 16 || K % 16 != 0 || ldx % 16 != 0 || ldw % 16 != 0) return KB_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)x | (uintptr_t)w) % 32 != 0) return KB_ERR_UNSUPPORTED_SIZE;
     if (gated && N % 2 != 0) return KB_ERR_BAD_ARG;
+    if (fusion.residual && (gated || !fusion.norm_w || !fusion.values || !fusion.out_sumsq)) return KB_ERR_BAD_ARG;
+    if (fusion.in_sumsq && (fusion.in_blocks < 1 || fusion.in_blocks > SK_SUM_BLOCKS)) return KB_ERR_BAD_ARG;
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
     const __nv_bfloat16* bb = (const __nv_bfloat16*)bias;
     if (M <= 8) {
-        if (gated) return launch_skinny<1, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
-        return launch_skinny<1, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+        if (gated) return launch_skinny<1, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, fusion, stream);
+        return launch_skinny<1, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, fusion, stream);
     }
-    if (gated) return launch_skinny<2, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
-    return launch_skinny<2, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, stream);
+    if (gated) return launch_skinny<2, true>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, fusion, stream);
+    return launch_skinny<2, false>(xb, ldx, wb, ldw, bb, out, out_fp32, ldo, M, N, K, fusion, stream);
+}
+
+KB_EXPORT int kb_gemm_skinny(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out,
+                             int out_fp32, int ldo, int M, int N, int K, int gated, cudaStream_t stream) {
+    SkinnyFusion none = {};
+    return skinny_entry(x, ldx, w, ldw, bias, out, out_fp32, ldo, M, N, K, gated, none, stream);
+}
+
+// Blocks the product of (M rows, N weight rows) is launched with: the number of partial sums
+// per row that a folding epilogue writes (out_sumsq holds blocks * 16 floats).
+KB_EXPORT int kb_gemm_skinny_blocks(int M, int N, int gated) {
+    const int rows_out = gated ? N / 2 : N;
+    int rows_per_block;
+    bool three;
+    skinny_grid(rows_out, !gated && M <= 8, rows_per_block, three);
+    return (rows_out + rows_per_block - 1) / rows_per_block;
+}
+
+// The product with RMSNorm work in its epilogue (see the top of the file).
+// in_sumsq (or null): the producer's partial sums [in_blocks, 16]; rows are scaled by
+//   rsqrt(sum / in_hidden + in_eps) before bias and gate.
+// residual (or null; not with gated): [M, N] fp32, row stride ldr; the result is added to it in
+//   place, values[M, N] = bf16(residual * norm_w) and out_sumsq[blocks, 16] are written; out is not.
+KB_EXPORT int kb_gemm_skinny_fused(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out, int out_fp32,
+                                   int ldo, int M, int N, int K, int gated, const float* in_sumsq, int in_blocks, int in_hidden,
+                                   float in_eps, float* residual, int ldr, const void* norm_w, int norm_w_bf16, void* values,
+                                   int ldv, float* out_sumsq, cudaStream_t stream) {
+    SkinnyFusion fusion = {};
+    fusion.in_sumsq = in_sumsq;
+    fusion.in_blocks = in_blocks;
+    fusion.in_inv_hidden = in_hidden > 0 ? 1.0f / (float)in_hidden : 0.0f;
+    fusion.in_eps = in_eps;
+    fusion.residual = residual;
+    fusion.ldr = ldr;
+    fusion.norm_w = norm_w;
+    fusion.norm_w_bf16 = norm_w_bf16;
+    fusion.values = (__nv_bfloat16*)values;
+    fusion.ldv = ldv;
+    fusion.out_sumsq = out_sumsq;
+    return skinny_entry(x, ldx, w, ldw, bias, out, out_fp32, ldo, M, N, K, gated, fusion, stream);
 }

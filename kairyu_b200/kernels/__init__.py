@@ -9,6 +9,7 @@ an error.  Model parts call these as ``kernels.<name>(...)``.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -513,14 +514,34 @@ def _cache_map(cache: torch.Tensor) -> int:
 # ----------------------------------------------------------------------------- matrix products
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor], *,
+           fold: Optional["ResidualNorm"] = None) -> None:
     """out = x @ weight.T (+ bias).
 
     float32: this package's own FMA kernel (true 32-bit, fixed summation order).
-    bfloat16: the library product (cuBLAS through torch), as the reference's
-    ``F.linear`` is (kairyu/models/packed_linear.py:217); accumulation is fp32,
-    ``out`` may be bfloat16 or float32.
+    bfloat16: the weight-streaming kernel up to 16 rows, else the library product (cuBLAS
+    through torch), as the reference's ``F.linear`` is (kairyu/models/packed_linear.py:217);
+    accumulation is fp32, ``out`` may be bfloat16 or float32.
+
+    ``x`` may be a :class:`PreNormed` (its rows are scaled in the epilogue) and ``fold`` a
+    :class:`ResidualNorm` (the result goes into the residual and towards the next norm instead
+    of ``out``); both need the weight-streaming kernel (``fused_norm_shapes_ok``).
     """
+    scale_by = x if isinstance(x, PreNormed) else None
+    if scale_by is not None or fold is not None:
+        values = scale_by.values if scale_by is not None else x
+        _need_cuda("linear", values, weight, bias, out)
+        if fold is None and (out is None or out.shape != (values.shape[0], weight.shape[0])):
+            raise KernelError("linear: out does not fit")
+        probe = out if out is not None else fold.values
+        if values.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != values.shape[1] or not _skinny_ok(values, weight, bias, probe):
+            raise KernelError("linear: a fused norm needs bf16 operands that the weight-streaming kernel takes (at most 16 rows, sizes in steps of 16)")
+        if fold is not None and (fold.residual.dtype != torch.float32 or fold.residual.shape != (values.shape[0], weight.shape[0])
+                                 or fold.values.shape != fold.residual.shape or fold.values.dtype != torch.bfloat16
+                                 or fold.sumsq.numel() < 16 * skinny_blocks(values.shape[0], weight.shape[0])):
+            raise KernelError("linear: the residual, values and partial sums of a folded norm do not fit the product")
+        _gemm_skinny(values, weight, bias, out, gated=False, scale_by=scale_by, fold=fold)
+        return
     _need_cuda("linear", x, weight, bias, out)
     M, K = x.shape
     N = weight.shape[0]
@@ -572,15 +593,86 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
     )
 
 
-def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, gated: bool) -> None:
+def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[torch.Tensor], *, gated: bool,
+                 scale_by: Optional["PreNormed"] = None, fold: Optional["ResidualNorm"] = None) -> None:
     M, K = x.shape
     N = weight.shape[0]
-    fn = _fn("gemm_skinny", "kb_gemm_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    if scale_by is None and fold is None:
+        fn = _fn("gemm_skinny", "kb_gemm_skinny", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        _check(
+            fn(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), out.data_ptr(),
+               1 if out.dtype == torch.float32 else 0, out.stride(0), M, N, K, 1 if gated else 0, _stream()),
+            "gemm_skinny",
+        )
+        return
+    fn = _fn(
+        "gemm_skinny", "kb_gemm_skinny_fused",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+         c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p],
+    )
     _check(
-        fn(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), out.data_ptr(),
-           1 if out.dtype == torch.float32 else 0, out.stride(0), M, N, K, 1 if gated else 0, _stream()),
+        fn(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), _ptr(out),
+           1 if out is not None and out.dtype == torch.float32 else 0, out.stride(0) if out is not None else 0, M, N, K, 1 if gated else 0,
+           _ptr(scale_by.sumsq) if scale_by is not None else None, scale_by.sumsq.shape[0] if scale_by is not None else 0,
+           scale_by.hidden if scale_by is not None else 0, float(scale_by.eps) if scale_by is not None else 0.0,
+           fold.residual.data_ptr() if fold is not None else None, fold.residual.stride(0) if fold is not None else 0,
+           fold.weight.data_ptr() if fold is not None else None, 1 if fold is not None and fold.weight.dtype == torch.bfloat16 else 0,
+           fold.values.data_ptr() if fold is not None else None, fold.values.stride(0) if fold is not None else 0,
+           fold.sumsq.data_ptr() if fold is not None else None, _stream()),
         "gemm_skinny",
     )
+
+
+# ---- RMSNorm inside the products around it (decode: a norm kernel of its own costs as much as
+# a third of the q/k/v product it feeds)
+
+
+@dataclass
+class PreNormed:
+    """Rows on their way into an RMSNorm whose work is split between two products: ``values`` =
+    bf16(x * norm weight), not yet scaled; ``sumsq[b, m]`` = partial sums of x[m]^2, one per block
+    of the product that wrote them.  The product that reads it scales row m by
+    rsqrt(sum_b sumsq[b, m] / hidden + eps)."""
+
+    values: torch.Tensor
+    sumsq: torch.Tensor
+    hidden: int
+    eps: float
+
+    @property
+    def shape(self) -> torch.Size:
+        return self.values.shape
+
+
+@dataclass
+class ResidualNorm:
+    """What a product does with its result instead of writing it: add it to the fp32 ``residual`` in
+    place, and leave ``values`` and ``sumsq`` of a :class:`PreNormed` for the norm (weight, eps) that follows."""
+
+    residual: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+    values: torch.Tensor
+    sumsq: torch.Tensor
+
+    def result(self) -> PreNormed:
+        return PreNormed(self.values, self.sumsq, self.residual.shape[1], self.eps)
+
+
+def fused_norm_available() -> bool:
+    """The products of this module can take the RMSNorm around them into their epilogues."""
+    return True
+
+
+def skinny_blocks(rows: int, out_features: int, gated: bool = False) -> int:
+    """Blocks the skinny product is launched with: partial sums per row a ``ResidualNorm`` needs room for."""
+    fn = _fn("gemm_skinny", "kb_gemm_skinny_blocks", [c_int, c_int, c_int])
+    return int(fn(int(rows), int(out_features), 1 if gated else 0))
+
+
+def fused_norm_shapes_ok(rows: int, *feature_sizes: int) -> bool:
+    """Whether products over these inner and outer sizes can all take the fused path."""
+    return 1 <= rows <= SKINNY_MAX_ROWS and all(size % 16 == 0 for size in feature_sizes)
 
 
 TC5_MAX_ROWS = 64  # token rows the tcgen05 weight-streaming product takes (csrc/gemm_tc5.cu)
@@ -641,7 +733,7 @@ def _gemm_tc5(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
     )
 
 
-def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: object) -> None:
+def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: object) -> None:
     """out = silu(x @ Wg.T) * (x @ Wu.T) with ``weight_gate_up`` = [Wg; Wu] stacked by rows.
 
     For up to 64 bf16 token rows this is one weight-streaming kernel with the gate in its
@@ -651,6 +743,13 @@ def linear_swiglu(x: torch.Tensor, weight_gate_up: torch.Tensor, out: torch.Tens
     kernel), the tcgen05 + TMA kernel from 17 to 64 rows (csrc/gemm_tc5.cu); otherwise a product
     into ``scratch.buffer(...)`` and the gate kernel.
     """
+    if isinstance(x, PreNormed):  # its rows are scaled in the epilogue, before the gate
+        _need_cuda("linear_swiglu", x.values, weight_gate_up, out)
+        if (x.values.dtype != torch.bfloat16 or weight_gate_up.dtype != torch.bfloat16 or out.dtype != torch.bfloat16
+                or out.shape != (x.values.shape[0], weight_gate_up.shape[0] // 2) or not _skinny_ok(x.values, weight_gate_up, None, out)):
+            raise KernelError("linear_swiglu: a fused norm needs bf16 operands that the weight-streaming kernel takes")
+        _gemm_skinny(x.values, weight_gate_up, None, out, gated=True, scale_by=x)
+        return
     _need_cuda("linear_swiglu", x, weight_gate_up, out)
     M = x.shape[0]
     two_i = weight_gate_up.shape[0]
@@ -734,6 +833,8 @@ def sample(
 __all__ = [
     "KernelBuildError",
     "KernelError",
+    "PreNormed",
+    "ResidualNorm",
     "argmax",
     "attention_decode_mma",
     "attention_mma_supported",
@@ -741,6 +842,8 @@ __all__ = [
     "attention_prefill_mma",
     "edit_logits",
     "embedding",
+    "fused_norm_available",
+    "fused_norm_shapes_ok",
     "gather_rows",
     "linear",
     "linear_swiglu",
@@ -749,5 +852,6 @@ __all__ = [
     "qk_norm_rope_kv_write",
     "rmsnorm",
     "sample",
+    "skinny_blocks",
     "swiglu",
 ]

@@ -100,9 +100,17 @@ class DecoderModel:
         if self.embedding_position is not None:
             self.embedding_position.embed_hook(residual, ctx)
         delta: Optional[torch.Tensor] = None
-        for call in self.schedule:
+        calls = self.schedule
+        for index, call in enumerate(calls):
             view = cache_views[(call.cache_slot, call.writes_cache)]
-            residual, delta = self.blocks[call.layer].forward(residual, delta, ctx, view)
+            block = self.blocks[call.layer]
+            if getattr(block, "takes_next_norm", False):
+                # a block may begin the first norm of the block that runs next, if that block offers one
+                following = self.blocks[calls[index + 1].layer] if index + 1 < len(calls) else None
+                offer = getattr(following, "prenorm_target", None)
+                residual, delta = block.forward(residual, delta, ctx, view, next_norm=offer(ctx) if offer else None)
+            else:
+                residual, delta = block.forward(residual, delta, ctx, view)
         if want_rows is None or want_rows.numel() == 0:
             return None
         hidden = self.final_norm.apply(residual, delta, ctx, rows=want_rows, tag="final_norm.out")

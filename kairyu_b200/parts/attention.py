@@ -214,7 +214,13 @@ class GQAAttention(Mixer):
         return (PagedKVSpec(self.num_kv_heads, self.head_dim, self.window),)
 
     # -- compute
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+    def fusable_norm(self, tokens: int) -> bool:
+        """Whether the q/k/v and the output product can take the norms around them into their epilogues."""
+        return kernels.fused_norm_shapes_ok(tokens, self.hidden_size, self.q_size)
+
+    def forward(self, x, ctx: StepContext, cache: CacheView, fold=None):
+        """``x``: rows, or a ``kernels.PreNormed``; ``fold`` (a ``kernels.ResidualNorm``): the output
+        product adds its result to the residual and returns the ``PreNormed`` for the next norm."""
         tokens = x.shape[0]
         ws = ctx.workspace
         qkv = ws.buffer("attn.qkv", tokens, self.qkv_width, self.dtype)
@@ -252,6 +258,9 @@ class GQAAttention(Mixer):
             scale=self.scale,
             window=self.window or 0,
         )
+        if fold is not None:
+            kernels.linear(mixed, self.w_o, self.b_o, None, fold=fold)
+            return fold.result()
         out = ws.buffer("attn.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(mixed, self.w_o, self.b_o, out)
         return out

@@ -6,6 +6,8 @@ from typing import Mapping, Optional
 
 import torch
 
+from kairyu_b200 import kernels
+from kairyu_b200.parts.norm import RMSNorm
 from kairyu_b200.parts.base import (
     BLOCKS,
     FEED_FORWARDS,
@@ -25,7 +27,15 @@ class PreNormBlock(Block):
 
     The residual is fp32.  Each sub-layer's output is handed on as a pending
     delta and added by the next norm's kernel.
+
+    For a few bf16 rows (decode) the norms have no kernel of their own: the product before a
+    norm adds its result to the residual and leaves the rows weighted and their sums of squares
+    (``kernels.ResidualNorm``), the product after it scales by the root mean square
+    (``kernels.PreNormed``).  That needs RMSNorms and a mixer and feed-forward that offer
+    ``fusable_norm``; any other part gets the plain flow.
     """
+
+    takes_next_norm = True  # forward accepts the norm of the block that runs next
 
     def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: str, shared: dict, **_: object) -> None:
         context = dict(dtype=dtype, device=device, shared=shared)
@@ -45,14 +55,35 @@ class PreNormBlock(Block):
     def bytes_streamed(self) -> int:
         return sum(part.bytes_streamed() for part in self._parts)
 
+    def _fused(self, ctx: StepContext) -> bool:
+        if ctx.dtype != torch.bfloat16 or not kernels.fused_norm_available():
+            return False
+        if not (isinstance(self.mixer_norm, RMSNorm) and isinstance(self.ffn_norm, RMSNorm)):
+            return False
+        mixer_ok = getattr(self.mixer, "fusable_norm", None)
+        ffn_ok = getattr(self.ffn, "fusable_norm", None)
+        return bool(mixer_ok and ffn_ok and mixer_ok(ctx.num_tokens) and ffn_ok(ctx.num_tokens))
+
+    def prenorm_target(self, ctx: StepContext) -> Optional[RMSNorm]:
+        """The norm the block before this one may fold into its last product, or None."""
+        return self.mixer_norm if self._fused(ctx) else None
+
     def forward(
         self,
         residual: torch.Tensor,
-        delta: Optional[torch.Tensor],
+        delta,
         ctx: StepContext,
         cache: CacheView,
-    ) -> tuple[torch.Tensor, Optional[torch.Tensor]]:
-        normed = self.mixer_norm.apply(residual, delta, ctx)
-        mixed = self.mixer.forward(normed, ctx, cache)
-        normed = self.ffn_norm.apply(residual, mixed, ctx)
-        return residual, self.ffn.forward(normed, ctx)
+        next_norm: Optional[RMSNorm] = None,
+    ):
+        if isinstance(delta, kernels.PreNormed):  # the block before has added its output and begun our norm
+            normed = delta
+        else:
+            normed = self.mixer_norm.apply(residual, delta, ctx)
+        if not self._fused(ctx):
+            mixed = self.mixer.forward(normed, ctx, cache)
+            normed = self.ffn_norm.apply(residual, mixed, ctx)
+            return residual, self.ffn.forward(normed, ctx)
+        mixed = self.mixer.forward(normed, ctx, cache, fold=self.ffn_norm.fold_target(residual, ctx, "ffn"))
+        fold = next_norm.fold_target(residual, ctx, "mixer") if next_norm is not None else None
+        return residual, self.ffn.forward(mixed, ctx, fold=fold)

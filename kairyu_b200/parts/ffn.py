@@ -52,11 +52,20 @@ class SwiGLU(FeedForward):
     def bytes_streamed(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.w_gate_up, self.w_down))
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def fusable_norm(self, tokens: int) -> bool:
+        """Whether both products can take the norms around them into their epilogues."""
+        return kernels.fused_norm_shapes_ok(tokens, self.hidden_size, self.intermediate_size)
+
+    def forward(self, x, ctx: StepContext, fold=None):
+        """``x``: rows, or a ``kernels.PreNormed``; ``fold`` (a ``kernels.ResidualNorm``): the down
+        product adds its result to the residual and returns the ``PreNormed`` for the next norm."""
         tokens = x.shape[0]
         ws = ctx.workspace
         hidden = ws.buffer("ffn.hidden", tokens, self.intermediate_size, self.dtype)
         kernels.linear_swiglu(x, self.w_gate_up, hidden, ws)
+        if fold is not None:
+            kernels.linear(hidden, self.w_down, None, None, fold=fold)
+            return fold.result()
         out = ws.buffer("ffn.out", tokens, self.hidden_size, self.dtype)
         kernels.linear(hidden, self.w_down, None, out)
         return out

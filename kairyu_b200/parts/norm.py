@@ -44,3 +44,12 @@ class RMSNorm(Norm):
         out = ctx.workspace.buffer(tag, count, self.size, self.dtype)
         kernels.rmsnorm(residual, self.weight, self.eps, out, delta=delta, rows=rows)
         return out
+
+    def fold_target(self, residual: torch.Tensor, ctx: StepContext, tag: str) -> "kernels.ResidualNorm":
+        """For a product that takes this norm's first half into its epilogue: it adds its result
+        to ``residual`` and leaves the rows weighted and their sums of squares; the product that
+        reads them scales by the root mean square (kernels.ResidualNorm / kernels.PreNormed)."""
+        rows = residual.shape[0]
+        values = ctx.workspace.buffer(f"norm.fold.{tag}.values", rows, self.size, torch.bfloat16)
+        sumsq = ctx.workspace.flat(f"norm.fold.{tag}.sumsq", 16 * kernels.skinny_blocks(rows, self.size), torch.float32).view(-1, 16)
+        return kernels.ResidualNorm(residual, self.weight, self.eps, values, sumsq)

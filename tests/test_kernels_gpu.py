@@ -304,6 +304,52 @@ def test_rope_flags_a_position_outside_the_table():
     assert int(flag.item()) == kernels().FLAG_BAD_POS
 
 
+@pytest.mark.parametrize("M,H,N,bias", [(1, 64, 48, False), (8, 4096, 6144, False), (5, 160, 208, True), (16, 1024, 512, True), (9, 96, 4096, False)])
+def test_rmsnorm_split_between_two_products(M, H, N, bias):
+    """fold: a product adds its result to the residual and leaves weighted rows and sums of squares;
+    scale: the next product finishes the norm in its epilogue (plain and gated).  Against the plain statement."""
+    k = kernels()
+    K0 = 320  # inner size of the folding product
+    g = torch.Generator().manual_seed(50 + M)
+    x0 = (torch.randn(M, K0, generator=g) * 0.5).bfloat16()
+    w0 = (torch.randn(H, K0, generator=g) * 0.05).bfloat16()
+    b0 = (torch.randn(H, generator=g) * 0.1).bfloat16() if bias else None
+    residual = torch.randn(M, H, generator=g) * 2.0
+    residual[0, 3] = 40.0  # an outlier channel, as residual streams have
+    norm_w = 1.0 + 0.1 * torch.randn(H, generator=g)
+    w1 = (torch.randn(N, H, generator=g) * 0.05).bfloat16()
+    b1 = (torch.randn(N, generator=g) * 0.1).bfloat16() if bias else None
+    eps = 1e-5
+    # plain: r' = r + x0 W0^T (+b0); y = rmsnorm(r') * g; out = y W1^T (+ b1)
+    r_new = residual + x0.float() @ w0.float().t() + (b0.float() if bias else 0.0)
+    y = r_new * torch.rsqrt(r_new.pow(2).mean(-1, keepdim=True) + eps) * norm_w
+    expected = y @ w1.float().t() + (b1.float() if bias else 0.0)
+    half = N // 2
+    expected_gated = torch.nn.functional.silu(expected[:, :half] - (b1.float()[:half] if bias else 0.0)) * (expected[:, half:] - (b1.float()[half:] if bias else 0.0))
+
+    dev_res = residual.to(DEV)
+    blocks = k.skinny_blocks(M, H)
+    fold = k.ResidualNorm(
+        dev_res, norm_w.to(DEV), eps, torch.empty(M, H, dtype=torch.bfloat16, device=DEV),
+        torch.full((blocks, 16), float("nan"), device=DEV),
+    )
+    k.linear(x0.to(DEV), w0.to(DEV), b0.to(DEV) if bias else None, None, fold=fold)
+    close(dev_res, r_new, 2e-3)
+    pre = fold.result()
+    sums = pre.sumsq[:, :M].sum(0).cpu()
+    close(sums, r_new.pow(2).sum(-1), 1e-2, rtol=1e-4)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    k.linear(pre, w1.to(DEV), b1.to(DEV) if bias else None, out)
+    close(out, expected, 3e-2, rtol=2e-2)
+    if N % 2 == 0:
+        gated = torch.empty(M, half, dtype=torch.bfloat16, device=DEV)
+        k.linear_swiglu(pre, w1.to(DEV), gated, None)
+        # an error e in gate or up shows as about e * |the other factor| in the product
+        gate, up = expected[:, :half] - (b1.float()[:half] if bias else 0.0), expected[:, half:] - (b1.float()[half:] if bias else 0.0)
+        bound = (3e-2 + 2e-2 * gate.abs()) * (1.0 + up.abs()) + (3e-2 + 2e-2 * up.abs()) * (1.0 + gate.abs())
+        assert bool(((gated.float().cpu() - expected_gated).abs() <= bound).all())
+
+
 def test_patch_tokens_takes_ids_from_the_device_and_flags_a_bad_source():
     ids = torch.tensor([5, 0, 7, 0, 9], dtype=torch.int32, device=DEV)
     source = torch.tensor([-1, 2, -1, 0, -1], dtype=torch.int32, device=DEV)

@@ -168,6 +168,10 @@ def linear_swiglu(x, weight_gate_up, out, scratch):
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 
+def fused_norm_available():
+    return False  # the CPU statements keep the norm a step of its own
+
+
 def argmax(logits, out):
     out.copy_(logits.argmax(dim=-1).to(torch.int32))
 
@@ -199,7 +203,7 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
 
 
 _NAMES = [
-    "embedding", "patch_tokens", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
+    "embedding", "patch_tokens", "fused_norm_available", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
     "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
     "edit_logits", "sample",
 ]
