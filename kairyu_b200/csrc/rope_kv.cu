@@ -170,6 +170,122 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
     }
 }
 
+// The paired path for many tokens and head sizes up to 128: a warp takes one head of TPW
+// consecutive tokens and asks for everything it needs of all of them (position, page, the head's
+// elements, cos and sin) before it uses any of it, so the round trips to memory overlap instead
+// of following one another token by token.  Same arithmetic as the kernel above.
+template <typename T, typename TW, int TPW>
+__global__ void __launch_bounds__(ROPE_WARPS * 32)
+qk_norm_rope_kv_write_many_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hkv, int D,
+                                  const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
+                                  const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_pos,
+                                  const int* __restrict__ positions, const int* __restrict__ row_ids,
+                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ write_from,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache, int page_size, int num_pages, int tokens,
+                                  int* flag) {
+    pdl_trigger();
+    pdl_wait();
+    using P2 = typename Pair<T>::type;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int head = blockIdx.y * ROPE_WARPS + warp;
+    if (head >= Hq + 2 * Hkv) return;
+    const int t0 = blockIdx.x * TPW;
+    const bool is_v = head >= Hq + Hkv;
+    const bool is_k = !is_v && head >= Hq;
+    const int half = D >> 1;
+    const int i = 2 * lane;  // this lane's pair of the first half (and its partners half further)
+    const bool lane_on = i < half;
+
+    int pos[TPW];
+    long long slot[TPW];
+    bool ok[TPW];
+#pragma unroll
+    for (int tt = 0; tt < TPW; ++tt) {
+        const int t = t0 + tt;
+        ok[tt] = t < tokens;
+        pos[tt] = ok[tt] ? positions[t] : 0;
+        slot[tt] = -1;
+        if (ok[tt] && (pos[tt] < 0 || pos[tt] >= max_pos)) {
+            if (lane == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+            ok[tt] = false;
+        }
+    }
+    if ((is_k || is_v) && k_cache != nullptr) {
+#pragma unroll
+        for (int tt = 0; tt < TPW; ++tt) {
+            if (!ok[tt]) continue;
+            const int row = row_ids[t0 + tt];
+            if (pos[tt] < write_from[row]) continue;
+            const int page_index = pos[tt] / page_size;
+            const int page = page_index < max_pages ? block_table[(size_t)row * max_pages + page_index] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (lane == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
+            } else {
+                slot[tt] = (long long)page * page_size + (pos[tt] % page_size);
+            }
+        }
+    }
+    if (is_v) {
+        constexpr int PER = 16 / sizeof(T);
+        uint4 held[TPW];
+        const bool mine = lane * PER < D;  // D <= 128: one 16-byte piece a lane
+#pragma unroll
+        for (int tt = 0; tt < TPW; ++tt)
+            if (mine && slot[tt] >= 0) held[tt] = *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + tt) * qkv_stride + (size_t)head * D + lane * PER);
+#pragma unroll
+        for (int tt = 0; tt < TPW; ++tt)
+            if (mine && slot[tt] >= 0)
+                *reinterpret_cast<uint4*>(v_cache + ((size_t)slot[tt] * Hkv + (head - Hq - Hkv)) * D + lane * PER) = held[tt];
+        return;
+    }
+    float2 a[TPW], b[TPW], c[TPW], sn[TPW];
+#pragma unroll
+    for (int tt = 0; tt < TPW; ++tt) {
+        a[tt] = b[tt] = c[tt] = sn[tt] = make_float2(0.0f, 0.0f);
+        if (ok[tt] && lane_on) {
+            const T* x = qkv + (size_t)(t0 + tt) * qkv_stride + (size_t)head * D;
+            a[tt] = pair_to_float(*reinterpret_cast<const P2*>(x + i));
+            b[tt] = pair_to_float(*reinterpret_cast<const P2*>(x + half + i));
+            c[tt] = *reinterpret_cast<const float2*>(cos_table + (size_t)pos[tt] * half + i);
+            sn[tt] = *reinterpret_cast<const float2*>(sin_table + (size_t)pos[tt] * half + i);
+        }
+    }
+    const TW* w = is_k ? k_norm_w : q_norm_w;
+    if (w != nullptr) {
+        float2 wa = make_float2(0.0f, 0.0f), wb = wa;
+        if (lane_on) {
+            wa = make_float2(to_float(w[i]), to_float(w[i + 1]));
+            wb = make_float2(to_float(w[half + i]), to_float(w[half + i + 1]));
+        }
+#pragma unroll
+        for (int tt = 0; tt < TPW; ++tt) {
+            float ss = a[tt].x * a[tt].x + a[tt].y * a[tt].y + b[tt].x * b[tt].x + b[tt].y * b[tt].y;
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / (float)D + eps);
+            a[tt].x = a[tt].x * inv * wa.x;
+            a[tt].y = a[tt].y * inv * wa.y;
+            b[tt].x = b[tt].x * inv * wb.x;
+            b[tt].y = b[tt].y * inv * wb.y;
+        }
+    }
+#pragma unroll
+    for (int tt = 0; tt < TPW; ++tt) {
+        if (!ok[tt] || !lane_on) continue;
+        T* x = qkv + (size_t)(t0 + tt) * qkv_stride + (size_t)head * D;
+        // rotate_half(u) = cat(-u[half:], u[:half])
+        const P2 lo = pair_from_float<T>(a[tt].x * c[tt].x - b[tt].x * sn[tt].x, a[tt].y * c[tt].y - b[tt].y * sn[tt].y);
+        const P2 hi = pair_from_float<T>(b[tt].x * c[tt].x + a[tt].x * sn[tt].x, b[tt].y * c[tt].y + a[tt].y * sn[tt].y);
+        *reinterpret_cast<P2*>(x + i) = lo;
+        *reinterpret_cast<P2*>(x + half + i) = hi;
+        if (is_k && slot[tt] >= 0) {
+            T* kdst = k_cache + ((size_t)slot[tt] * Hkv + (head - Hq)) * D;
+            *reinterpret_cast<P2*>(kdst + i) = lo;
+            *reinterpret_cast<P2*>(kdst + half + i) = hi;
+        }
+    }
+}
+
 // qkv: [T, qkv_stride] with q | k | v packed per token, head-major.
 // *_norm_w: [D] (both or neither), norm_w_bf16 says which type.
 // cos/sin: [max_pos, rot_half] fp32 or null.  caches: [num_pages, page_size, Hkv, D] or null.
@@ -196,6 +312,25 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
                         (D * elem) % 16 == 0 && ((size_t)qkv_stride * elem) % 16 == 0 && ((uintptr_t)qkv % 16) == 0 &&
                         ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
                         ((uintptr_t)cos_table % 8) == 0 && ((uintptr_t)sin_table % 8) == 0;
+    // many tokens, heads of up to 128: four tokens a warp, their memory round trips overlapped
+    if (paired && D <= 128 && T >= 256) {
+        constexpr int TPW = 4;
+        dim3 many((T + TPW - 1) / TPW, (Hq + 2 * Hkv + ROPE_WARPS - 1) / ROPE_WARPS);
+#define MANY(T_, TW_)                                                                                   \
+    kb_launch(qk_norm_rope_kv_write_many_kernel<T_, TW_, TPW>, dim3(many), dim3(threads), 0, stream,   \
+        (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps, cos_table,   \
+        sin_table, max_pos, positions, row_ids, block_table, max_pages, write_from, (T_*)k_cache,       \
+        (T_*)v_cache, page_size, num_pages, T, flag)
+        if (is_bf16) {
+            if (norm_w_bf16) MANY(__nv_bfloat16, __nv_bfloat16);
+            else MANY(__nv_bfloat16, float);
+        } else {
+            if (norm_w_bf16) MANY(float, __nv_bfloat16);
+            else MANY(float, float);
+        }
+#undef MANY
+        return kb_launch_result();
+    }
 #define LAUNCH(T_, TW_, P_)                                                                     \
     kb_launch(qk_norm_rope_kv_write_kernel<T_, TW_, P_>, dim3(grid), dim3(threads), 0, stream,  \
         (T_*)qkv, qkv_stride, Hq, Hkv, D, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps,      \

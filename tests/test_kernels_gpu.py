@@ -258,8 +258,8 @@ def _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed):
     "Hq,Hkv,D,page_size,qk_norm,rot_dim",
     [(4, 2, 16, 16, False, 16), (6, 3, 32, 8, True, 32), (5, 1, 48, 16, True, 48), (32, 8, 128, 16, False, 128), (3, 3, 80, 4, True, 32)],
 )
-def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, page_size, qk_norm, rot_dim):
-    T = 37
+@pytest.mark.parametrize("T", [37, 301])  # 301: the four-tokens-a-warp kernel (full rotation, heads up to 128), with a ragged end
+def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, page_size, qk_norm, rot_dim, T):
     case = _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed=20)
     kc_ref = torch.zeros(case["num_pages"], page_size, Hkv, D, dtype=dtype)
     vc_ref = torch.zeros_like(kc_ref)
