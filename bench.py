@@ -423,7 +423,8 @@ def main() -> int:
         "value": PREFILL_TOKENS / (prefill_ms / 1e3),
         "tokens": PREFILL_TOKENS,
         "ms": prefill_ms,
-        "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),
+        "frac": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops"] * 1e12),  # of the burst cuBLAS peak
+        "frac_of_sustained": flops / (prefill_ms / 1e3) / (peaks["bf16_tflops_sustained"] * 1e12),
     }
 
     points = {}
