@@ -187,7 +187,8 @@ class Engine:
         self._collect(request_id)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        """Requests are waiting or running, or a launched step has not been committed yet."""
+        return self.scheduler.has_unfinished() or bool(self._pending)
 
     # ------------------------------------------------------------------ the loop
     def _collect(self, request_id: str, stop_reason: Optional[int | str] = None) -> None:
@@ -327,7 +328,7 @@ class Engine:
         return tuple(done)
 
     def run_to_completion(self) -> dict[str, FinishedRequest]:
-        while self.scheduler.has_unfinished() or self._pending:
+        while self.has_unfinished():
             self.step()
         finished, self._finished = self._finished, {}
         return finished

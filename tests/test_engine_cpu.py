@@ -155,3 +155,34 @@ def test_pipeline_depth_two_falls_back_to_one_for_penalties():
     a = llm.generate(TokensPrompt(tuple(prompt)), params)[0].outputs[0].token_ids
     b = one.generate(TokensPrompt(tuple(prompt)), params)[0].outputs[0].token_ids
     assert a == b
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 7, 13, 21])
+def test_pipeline_depth_two_equals_depth_one_on_random_workloads(seed):
+    """Random prompt lengths, budgets, stop tokens and token limits on a pool so small that requests wait
+    and are preempted: schedule-ahead must not change a token or a finish reason."""
+    import random
+
+    rng = random.Random(seed)
+    count = rng.randint(3, 7)
+    lengths = [rng.randint(1, 60) for _ in range(count)]
+    limits = [rng.randint(1, 14) for _ in range(count)]
+    options = dict(num_pages=rng.randint(10, 16), max_num_batched_tokens=rng.choice([5, 16, 64]), max_num_seqs=rng.choice([2, 4, 8]))
+    results = {}
+    stops = None
+    for depth in (1, 2):
+        llm, config = make_llm("llama", pipeline_depth=depth, **options)
+        prompts = prompts_of(config, lengths, seed=200 + seed)
+        if stops is None:  # tokens the free run produces, so that some requests stop early
+            free = llm.generate([TokensPrompt(tuple(p)) for p in prompts], [SamplingParams(temperature=0.0, max_tokens=m) for m in limits])
+            stops = [o.outputs[0].token_ids[len(o.outputs[0].token_ids) // 2] if i % 2 == 0 else None for i, o in enumerate(free)]
+        params = [
+            SamplingParams(temperature=0.0 if i % 3 else 0.7, seed=5 + i, max_tokens=limits[i], stop_token_ids=[stops[i]] if stops[i] is not None else [])
+            for i in range(count)
+        ]
+        outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+        results[depth] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason, o.outputs[0].stop_reason) for o in outputs]
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests == 0 and not llm.engine._pending
+    assert results[1] == results[2]
+    assert any(reason == "stop" for _, reason, _ in results[2])
