@@ -161,6 +161,39 @@ def test_schedule_ahead_gives_the_same_tokens(name, dtype):
         assert list(results[2][3][0]) == plain_generate(config, weights, prompts[3], 30)
 
 
+@pytest.mark.parametrize("seed", [0, 5])
+def test_schedule_ahead_on_random_workloads_under_page_pressure(seed):
+    """bf16, CUDA graphs, a pool so small that requests wait and are preempted, random limits and stops:
+    pipeline_depth=2 gives the tokens and finish reasons of pipeline_depth=1."""
+    import random
+
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    rng = random.Random(seed)
+    config, model_seed, page_size = TINY["wide"]
+    count = rng.randint(4, 8)
+    lengths = [rng.randint(1, 90) for _ in range(count)]
+    limits = [rng.randint(1, 20) for _ in range(count)]
+    options = dict(num_pages=rng.randint(24, 40), max_num_batched_tokens=rng.choice([9, 32, 128]), max_num_seqs=rng.choice([3, 8]))
+    prompts = prompts_of(config, lengths, seed=300 + seed)
+    results, stops = {}, None
+    for depth in (1, 2):
+        llm = LLM.from_random(config, seed=model_seed, dtype="bfloat16", page_size=page_size, pipeline_depth=depth, **options)
+        if stops is None:
+            free = llm.generate([TokensPrompt(tuple(p)) for p in prompts], [SamplingParams(temperature=0.0, max_tokens=m) for m in limits])
+            stops = [o.outputs[0].token_ids[len(o.outputs[0].token_ids) // 2] if i % 2 == 0 else None for i, o in enumerate(free)]
+        params = [
+            SamplingParams(temperature=0.0 if i % 3 else 0.7, seed=5 + i, max_tokens=limits[i], stop_token_ids=[stops[i]] if stops[i] is not None else [])
+            for i in range(count)
+        ]
+        outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+        results[depth] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason, o.outputs[0].stop_reason) for o in outputs]
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests == 0 and not llm.engine.has_unfinished()
+        llm.engine.runner.check_errors()
+    assert results[1] == results[2]
+
+
 def test_stop_token_and_eos():
     from kairyu_b200 import LLM, SamplingParams, TokensPrompt
 
