@@ -2,10 +2,14 @@
 // and temperature / min-p / top-k / top-p sampling with a stateless Gumbel-max
 // draw (kairyu/engine/core/sampler.py:1198-1389, kairyu/kernels/sampling_gpu.py:51-128).
 //
-// One block per row.  Every reduction has a fixed order, so a draw is a pure
-// function of (logits row, parameters, seed): the same on every run and in
-// every batch composition.
+// Every reduction has a fixed order (over threads, warps, the blocks of a cluster, the chunks of
+// a row), so a draw is a pure function of (logits row, parameters, seed): the same on every run
+// and in every batch composition.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 #define SAMPLE_THREADS 1024
 #define SAMPLE_WARPS (SAMPLE_THREADS / 32)
@@ -142,8 +146,77 @@ __device__ __forceinline__ double gumbel_noise(int i, unsigned long long seed) {
     return -log(-log1p(-u));
 }
 
-// Sums 16 per-thread values over the block in a fixed order; result in s_out[16].
-__device__ __forceinline__ void block_sum16(float (&local)[16], float (*s_part)[16], float* s_out) {
+// ---- stage 1 runs as a thread-block cluster per row: SAMPLE_CLUSTER blocks share the row's passes
+// (each block owns a slice of the vocabulary) and combine their partial results through
+// distributed shared memory, in rank order, so every block holds the same totals.
+#define SAMPLE_CLUSTER 8
+#define STAGE1_THREADS 512
+#define STAGE1_WARPS (STAGE1_THREADS / 32)
+
+// Two slots, used in turn: a reduction writes one slot, meets the others at one cluster barrier and
+// reads theirs; the next reduction writes the other slot, so nobody overwrites what a slower block
+// is still reading (it cannot be more than one reduction behind: the barrier in between).
+struct ClusterScratch {
+    float vals[2][16];  // this block's partial result of the reduction in progress
+    int index[2];       // (argmax) the index that goes with vals[.][0]
+    int turn;           // which slot the next reduction uses (the same in every block)
+};
+
+// Every block calls this with its partial results in mine->vals[0..count); on return all[k] holds
+// op over the ranks, in rank order, the same in every block.  Two cluster barriers.
+template <int COUNT, typename Op>
+__device__ __forceinline__ void cluster_combine(cg::cluster_group& cluster, ClusterScratch* mine, int slot, float (&all)[COUNT], Op op) {
+    cluster.sync();  // every block's partials are in its shared memory
+#pragma unroll
+    for (int k = 0; k < COUNT; ++k) all[k] = cluster.map_shared_rank(mine, 0)->vals[slot][k];
+    for (unsigned rank = 1; rank < cluster.num_blocks(); ++rank) {
+        const ClusterScratch* theirs = cluster.map_shared_rank(mine, rank);
+#pragma unroll
+        for (int k = 0; k < COUNT; ++k) all[k] = op(all[k], theirs->vals[slot][k]);
+    }
+}
+// The slot this reduction uses; every thread of every block sees the same sequence of slots.
+__device__ __forceinline__ int next_slot(int& turn) {
+    const int slot = turn;
+    turn ^= 1;
+    return slot;
+}
+
+__device__ __forceinline__ float cluster_sum(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, float v, float* scratch) {
+    const int slot = next_slot(turn);
+    v = block_sum(v, scratch);
+    if (threadIdx.x == 0) mine->vals[slot][0] = v;
+    float all[1];
+    cluster_combine(cluster, mine, slot, all, [](float a, float b) { return a + b; });
+    return all[0];
+}
+__device__ __forceinline__ float cluster_max(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, float v, float* scratch) {
+    const int slot = next_slot(turn);
+    v = block_max(v, scratch);
+    if (threadIdx.x == 0) mine->vals[slot][0] = v;
+    float all[1];
+    cluster_combine(cluster, mine, slot, all, [](float a, float b) { return fmaxf(a, b); });
+    return all[0];
+}
+// First index of the maximum over the cluster's slices.
+__device__ __forceinline__ int cluster_argmax(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, BestF b, float* sv, int* si) {
+    const int slot = next_slot(turn);
+    b = block_argmax(b, sv, si);
+    if (threadIdx.x == 0) { mine->vals[slot][0] = b.v; mine->index[slot] = b.i; }
+    cluster.sync();
+    BestF best{-INFINITY, 0x7fffffff};
+    for (unsigned rank = 0; rank < cluster.num_blocks(); ++rank) {
+        const ClusterScratch* theirs = cluster.map_shared_rank(mine, rank);
+        if (better(theirs->vals[slot][0], theirs->index[slot], best.v, best.i)) { best.v = theirs->vals[slot][0]; best.i = theirs->index[slot]; }
+    }
+    cluster.sync();  // the last reduction of a row: nobody leaves while its shared memory is being read
+    return best.i;
+}
+
+// Sums 16 per-thread values over the block in a fixed order, then over the cluster; result in totals[16].
+__device__ __forceinline__ void cluster_sum16(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, float (&local)[16],
+                                              float (*s_part)[16], float (&totals)[16]) {
+    const int slot = next_slot(turn);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int d = 0; d < 16; ++d) local[d] = warp_sum(local[d]);
@@ -155,18 +228,18 @@ __device__ __forceinline__ void block_sum16(float (&local)[16], float (*s_part)[
     __syncthreads();
     if (threadIdx.x < 16) {
         float total = 0.0f;
-        for (int w = 0; w < SAMPLE_WARPS; ++w) total += s_part[w][threadIdx.x];
-        s_out[threadIdx.x] = total;
+        for (int w = 0; w < STAGE1_WARPS; ++w) total += s_part[w][threadIdx.x];
+        mine->vals[slot][threadIdx.x] = total;
     }
-    __syncthreads();
+    cluster_combine(cluster, mine, slot, totals, [](float a, float b) { return a + b; });
 }
 
 // Smallest 32-bit key u such that weight{ key_i > u, key_i >= lo_key } < target,
 // where key_i are the bits of the non-negative floats p_i and weight is a count
-// (use_sum = 0) or the sum of p_i (use_sum = 1).  Radix descent, 4 bits a round.
-// Requires target > 0.  Every thread returns u.
-__device__ unsigned int select_key(const float* __restrict__ p, int V, unsigned int lo_key,
-                                   float target, int use_sum, float (*s_part)[16], float* s_out) {
+// (use_sum = 0) or the sum of p_i (use_sum = 1).  Radix descent, 4 bits a round; every block
+// scans its slice [begin, end) and all of them return the same u.  Requires target > 0.
+__device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, const float* __restrict__ p, int begin,
+                                   int end, unsigned int lo_key, float target, int use_sum, float (*s_part)[16]) {
     unsigned int prefix = 0;
     float above = 0.0f;
     for (int shift = 28; shift >= 0; shift -= 4) {
@@ -174,7 +247,7 @@ __device__ unsigned int select_key(const float* __restrict__ p, int V, unsigned 
 #pragma unroll
         for (int d = 0; d < 16; ++d) local[d] = 0.0f;
         const unsigned int high_mask = shift == 28 ? 0u : (0xffffffffu << (shift + 4));
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
             const float pv = p[i];
             const unsigned int key = __float_as_uint(pv);
             if (key < lo_key) continue;
@@ -185,68 +258,92 @@ __device__ unsigned int select_key(const float* __restrict__ p, int V, unsigned 
             for (int d = 0; d < 16; ++d)
                 if (d == digit) local[d] += wgt;
         }
-        block_sum16(local, s_part, s_out);
+        float totals[16];
+        cluster_sum16(cluster, mine, turn, local, s_part, totals);
         // G(d) = above + sum_{e>d} S[e]; pick the smallest d with G(d) < target.
         int d = 15;
         float g = above;  // G(15)
         while (d > 0) {
-            const float g_next = g + s_out[d];  // G(d-1)
+            const float g_next = g + totals[d];  // G(d-1)
             if (!(g_next < target)) break;
             g = g_next;
             --d;
         }
         above = g;
         prefix |= (unsigned int)d << shift;
-        __syncthreads();  // s_out is rewritten next round
     }
     return prefix;
 }
 
+// Sampling runs as three launches.  Stage 1 (a cluster of SAMPLE_CLUSTER blocks per row, several
+// passes over the row): probabilities and the filters' threshold.  Stage 2 (SAMPLE_CHUNKS blocks
+// per row): the noisy argmax, whose 64-bit logarithms are the expensive part, over a chunk of the
+// vocabulary each.  Stage 3 (one warp per row): the best of the chunks, in chunk order.
+#define SAMPLE_CHUNKS 32
+#define SAMPLE_NOISE_THREADS 256
+struct SampleRowState {
+    unsigned int lo_key;  // keep p with bits >= lo_key (and p > 0)
+    float kept;           // their sum
+    int decided;          // 1: out[r] is final already (temperature 0, or everything filtered)
+    int pad;
+};
+
 // logits: [n, V] fp32 (read only); work: [n, V] fp32 scratch (probabilities).
 // Per row: temperature (0 = argmax), top_k (<=0 or >=V: off), top_p (>=1: off),
-// min_p (<=0: off), seed (already mixed with the output position).
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+// min_p (<=0: off).  One cluster (of up to SAMPLE_CLUSTER blocks) per row.
+__global__ void __launch_bounds__(STAGE1_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work, int V,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               const float* __restrict__ top_p, const float* __restrict__ min_p,
-              const unsigned long long* __restrict__ seeds, int* __restrict__ out) {
+              SampleRowState* __restrict__ state, int* __restrict__ out) {
     pdl_wait();
+    cg::cluster_group cluster = cg::this_cluster();
     __shared__ float scratch[32];
     __shared__ float sv[32];
     __shared__ int si[32];
-    __shared__ float s_part[SAMPLE_WARPS][16];
-    __shared__ float s_out[16];
-    __shared__ double dv[32];
-    __shared__ int di[32];
+    __shared__ float s_part[STAGE1_WARPS][16];
+    __shared__ ClusterScratch mine;
+    int turn = 0;
 
-    const int r = blockIdx.x;
+    const int blocks_per_row = (int)cluster.num_blocks();
+    const int r = blockIdx.x / blocks_per_row;
+    const int rank = (int)cluster.block_rank();
+    const int per = (V + blocks_per_row - 1) / blocks_per_row;
+    const int begin = rank * per;
+    const int end = min(begin + per, V);
     const float* row = logits + (size_t)r * ld;
     const float T = temperature[r];
 
-    if (T == 0.0f) {
+    auto plain_argmax = [&]() {
         BestF b{-INFINITY, 0x7fffffff};
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
             const float v = row[i];
             if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
         }
-        b = block_argmax(b, sv, si);
-        if (threadIdx.x == 0) out[r] = b.i == 0x7fffffff ? 0 : b.i;
+        const int index = cluster_argmax(cluster, &mine, turn, b, sv, si);
+        if (rank == 0 && threadIdx.x == 0) {
+            out[r] = index == 0x7fffffff ? 0 : index;
+            state[r].decided = 1;
+        }
+    };
+    if (T == 0.0f) {
+        plain_argmax();
         return;
     }
 
     float* p = work + (size_t)r * V;
     // softmax(logits / T)
     float mx = -INFINITY;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i] / T);
-    mx = block_max(mx, scratch);
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) mx = fmaxf(mx, row[i] / T);
+    mx = cluster_max(cluster, &mine, turn, mx, scratch);
     float sum = 0.0f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) sum += expf(row[i] / T - mx);
-    sum = block_sum(sum, scratch);
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) sum += expf(row[i] / T - mx);
+    sum = cluster_sum(cluster, &mine, turn, sum, scratch);
     // min-p: keep p >= min_p * max p (sampler.py:1244-1249)
     const float mp = min_p[r];
     const float p_max = 1.0f / sum;  // exp(0) / sum
     const float floor_p = mp > 0.0f ? mp * p_max : 0.0f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float pv = expf(row[i] / T - mx) / sum;
         if (pv < floor_p) pv = 0.0f;
         p[i] = pv;
@@ -256,66 +353,104 @@ sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work
     unsigned int lo_key = 0;
     // top-k: keep p >= k-th largest (ties kept) (sampler.py:1259-1291)
     const int k = top_k[r];
-    if (k > 0 && k < V) lo_key = select_key(p, V, lo_key, (float)k, 0, s_part, s_out);
+    if (k > 0 && k < V) lo_key = select_key(cluster, &mine, turn, p, begin, end, lo_key, (float)k, 0, s_part);
     // top-p: in descending order drop a token once the mass before it reaches
     // top_p * total (sampler.py:1349-1361); tokens tied with the last kept one stay.
     const float tp = top_p[r];
     if (tp < 1.0f) {
         float total = 0.0f;
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
             const float pv = p[i];
             if (__float_as_uint(pv) >= lo_key) total += pv;
         }
-        total = block_sum(total, scratch);
+        total = cluster_sum(cluster, &mine, turn, total, scratch);
         const float target = tp * fmaxf(total, 1e-12f);
-        const unsigned int u = select_key(p, V, lo_key, target, 1, s_part, s_out);
+        const unsigned int u = select_key(cluster, &mine, turn, p, begin, end, lo_key, target, 1, s_part);
         lo_key = u > lo_key ? u : lo_key;
     }
-    // renormalise over what is left, add the noise, take the argmax
+    // what is left; its sum renormalises the draw
     float kept = 0.0f;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
         const float pv = p[i];
         if (pv > 0.0f && __float_as_uint(pv) >= lo_key) kept += pv;
     }
-    kept = block_sum(kept, scratch);
+    kept = cluster_sum(cluster, &mine, turn, kept, scratch);
     if (!(kept > 0.0f)) {  // everything filtered: fall back to the argmax (sampler.py:1363-1378)
-        BestF b{-INFINITY, 0x7fffffff};
-        for (int i = threadIdx.x; i < V; i += blockDim.x) {
-            const float v = row[i];
-            if (better(v, i, b.v, b.i)) { b.v = v; b.i = i; }
-        }
-        b = block_argmax(b, sv, si);
-        if (threadIdx.x == 0) out[r] = b.i == 0x7fffffff ? 0 : b.i;
+        plain_argmax();
         return;
     }
-    const unsigned long long seed = seeds[r];
-    double best = -INFINITY;
-    int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float pv = p[i];
-        if (pv > 0.0f && __float_as_uint(pv) >= lo_key) {
-            const double v = (double)logf(pv / kept) + gumbel_noise(i, seed);
-            if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
-        }
-    }
-    {
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const double ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
-        }
-        if (lane == 0) { dv[warp] = best; di[warp] = best_i; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            for (int w = 1; w < SAMPLE_WARPS; ++w)
-                if (dv[w] > best || (dv[w] == best && di[w] < best_i)) { best = dv[w]; best_i = di[w]; }
-            out[r] = best_i == 0x7fffffff ? 0 : best_i;
-        }
+    cluster.sync();  // nobody leaves while its shared memory may still be read
+    if (rank == 0 && threadIdx.x == 0) {
+        state[r].lo_key = lo_key;
+        state[r].kept = kept;
+        state[r].decided = 0;
     }
 }
 
+// grid (rows, SAMPLE_CHUNKS): the best of log(p / kept) + noise over this block's chunk of the row
+// (ties: the lower index), written to best_v / best_i [rows, SAMPLE_CHUNKS].
+__global__ void __launch_bounds__(SAMPLE_NOISE_THREADS)
+sample_noise_kernel(const float* __restrict__ work, int V, const SampleRowState* __restrict__ state,
+                    const unsigned long long* __restrict__ seeds, double* __restrict__ best_v, int* __restrict__ best_i) {
+    pdl_wait();
+    __shared__ double dv[SAMPLE_NOISE_THREADS / 32];
+    __shared__ int di[SAMPLE_NOISE_THREADS / 32];
+    const int r = blockIdx.x;
+    const SampleRowState st = state[r];
+    if (st.decided) return;
+    const float* p = work + (size_t)r * V;
+    const int per = (V + SAMPLE_CHUNKS - 1) / SAMPLE_CHUNKS;
+    const int begin = blockIdx.y * per;
+    const int end = min(begin + per, V);
+    const unsigned long long seed = seeds[r];
+    double best = -INFINITY;
+    int best_index = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += SAMPLE_NOISE_THREADS) {
+        const float pv = p[i];
+        if (pv > 0.0f && __float_as_uint(pv) >= st.lo_key) {
+            const double v = (double)logf(pv / st.kept) + gumbel_noise(i, seed);
+            if (v > best || (v == best && i < best_index)) { best = v; best_index = i; }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const double ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_index, o);
+        if (ov > best || (ov == best && oi < best_index)) { best = ov; best_index = oi; }
+    }
+    if (lane == 0) { dv[warp] = best; di[warp] = best_index; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < SAMPLE_NOISE_THREADS / 32; ++w)
+            if (dv[w] > best || (dv[w] == best && di[w] < best_index)) { best = dv[w]; best_index = di[w]; }
+        best_v[(size_t)r * SAMPLE_CHUNKS + blockIdx.y] = best;
+        best_i[(size_t)r * SAMPLE_CHUNKS + blockIdx.y] = best_index;
+    }
+}
+
+// one warp per row: the best chunk (ties: the lower index)
+__global__ void sample_pick_kernel(const SampleRowState* __restrict__ state, const double* __restrict__ best_v,
+                                   const int* __restrict__ best_i, int* __restrict__ out) {
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (state[r].decided) return;
+    const int lane = threadIdx.x;
+    double best = lane < SAMPLE_CHUNKS ? best_v[(size_t)r * SAMPLE_CHUNKS + lane] : -INFINITY;
+    int best_index = lane < SAMPLE_CHUNKS ? best_i[(size_t)r * SAMPLE_CHUNKS + lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const double ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_index, o);
+        if (ov > best || (ov == best && oi < best_index)) { best = ov; best_index = oi; }
+    }
+    if (lane == 0) out[r] = best_index == 0x7fffffff ? 0 : best_index;
+}
+
+// Scratch floats kb_sample needs beyond the n * V probabilities.
+KB_EXPORT int kb_sample_extra_floats(int n) { return n * (4 + 3 * SAMPLE_CHUNKS) + 8; }
+
+// work: n * V + kb_sample_extra_floats(n) floats of scratch.
 KB_EXPORT int kb_sample(const float* logits, int ld, float* work, int n, int V,
                         const float* temperature, const int* top_k, const float* top_p,
                         const float* min_p, const unsigned long long* seeds, int* out,
@@ -323,6 +458,38 @@ KB_EXPORT int kb_sample(const float* logits, int ld, float* work, int n, int V,
     if (n == 0) return 0;
     if (!logits || !work || !temperature || !top_k || !top_p || !min_p || !seeds || !out) return KB_ERR_NULL;
     if (V < 1 || V >= (1 << 24)) return KB_ERR_UNSUPPORTED_SIZE;  // counts are kept in fp32
-    kb_launch(sample_kernel, dim3(n), dim3(SAMPLE_THREADS), 0, stream, logits, ld, work, V, temperature, top_k, top_p, min_p, seeds, out);
+    static_assert(SAMPLE_CHUNKS <= 32, "the last stage is one warp per row");
+    // scratch after the probabilities, on 8-byte boundaries: per-row state, then the chunks' best values and indices
+    size_t offset = ((size_t)n * V + 1) & ~(size_t)1;
+    SampleRowState* state = reinterpret_cast<SampleRowState*>(work + offset);
+    offset += (size_t)n * 4;
+    double* best_v = reinterpret_cast<double*>(work + offset);
+    offset += (size_t)n * SAMPLE_CHUNKS * 2;
+    int* best_i = reinterpret_cast<int*>(work + offset);
+    {
+        cudaLaunchConfig_t config = {};
+        // blocks per row: eight for up to 32 rows, fewer for more, so that the clusters fit the device at once
+        const int per_row = n <= 32 ? SAMPLE_CLUSTER : (n <= 64 ? 4 : 2);
+        config.gridDim = dim3(n * per_row);
+        config.blockDim = dim3(STAGE1_THREADS);
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = per_row;
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = 1;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes;
+        config.numAttrs = 2;
+        cudaLaunchKernelEx(&config, sample_kernel, logits, ld, work, V, temperature, top_k, top_p, min_p, state, out);
+    }
+    int rc = kb_launch_result();
+    if (rc != 0) return rc;
+    kb_launch(sample_noise_kernel, dim3(n, SAMPLE_CHUNKS), dim3(SAMPLE_NOISE_THREADS), 0, stream, (const float*)work, V,
+              (const SampleRowState*)state, seeds, best_v, best_i);
+    rc = kb_launch_result();
+    if (rc != 0) return rc;
+    kb_launch(sample_pick_kernel, dim3(n), dim3(32), 0, stream, (const SampleRowState*)state, (const double*)best_v, (const int*)best_i, out);
     return kb_launch_result();
 }

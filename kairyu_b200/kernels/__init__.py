@@ -803,6 +803,12 @@ def edit_logits(
     _check(fn(logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(), tokens.data_ptr(), mul.data_ptr(), sub.data_ptr(), mask.data_ptr(), E, _stream()), "edit_logits")
 
 
+def sample_work_floats(rows: int, vocab: int) -> int:
+    """Scratch floats ``sample`` needs: the rows' probabilities and the state of its three stages."""
+    fn = _fn("sampling", "kb_sample_extra_floats", [c_int])
+    return rows * vocab + 1 + int(fn(int(rows)))
+
+
 def sample(
     logits: torch.Tensor,
     work: torch.Tensor,
@@ -819,8 +825,8 @@ def sample(
     n, V = logits.shape
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be fp32 with unit inner stride")
-    if work.dtype != torch.float32 or not work.is_contiguous() or work.numel() < n * V:
-        raise KernelError("sample: work must be contiguous fp32 with at least rows*vocab elements")
+    if work.dtype != torch.float32 or not work.is_contiguous() or work.numel() < sample_work_floats(n, V) or work.data_ptr() % 8:
+        raise KernelError("sample: work must be contiguous fp32 with at least sample_work_floats(rows, vocab) elements")
     if seeds.dtype != torch.int64 or temperature.dtype != torch.float32 or top_p.dtype != torch.float32 or min_p.dtype != torch.float32:
         raise KernelError("sample: parameter dtypes are fp32 (temperature, top_p, min_p), int32 (top_k), int64 (seeds)")
     fn = _fn("sampling", "kb_sample", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
@@ -852,6 +858,7 @@ __all__ = [
     "qk_norm_rope_kv_write",
     "rmsnorm",
     "sample",
+    "sample_work_floats",
     "skinny_blocks",
     "swiglu",
 ]

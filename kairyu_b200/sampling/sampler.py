@@ -42,6 +42,10 @@ class Sampler:
         self.device = device
         self._work: Optional[torch.Tensor] = None
         self._is_cuda = str(device).startswith("cuda")
+        self._staging: Optional[list] = None  # pinned buffers for the rows' parameters
+        self._staging_rows = 0
+        self._device_words: Optional[torch.Tensor] = None
+        self._next_staging = 0
 
     def _host(self, values: list, dtype: torch.dtype) -> torch.Tensor:
         tensor = torch.tensor(values, dtype=dtype)
@@ -109,17 +113,50 @@ class Sampler:
         if all(row.params.temperature == 0.0 for row in rows):
             kernels.argmax(logits, out)
             return out
-        if self._work is None or self._work.numel() < n * self.vocab_size:
-            self._work = torch.empty(max(n, 8) * self.vocab_size, dtype=torch.float32, device=self.device)
-        seeds = [as_signed64(mix_seed(row.base_seed(), row.position)) for row in rows]
-        kernels.sample(
-            logits,
-            self._work,
-            self._host([float(row.params.temperature) for row in rows], torch.float32),
-            self._host([int(row.params.top_k) for row in rows], torch.int32),
-            self._host([float(row.params.top_p) for row in rows], torch.float32),
-            self._host([float(row.params.min_p) for row in rows], torch.float32),
-            self._host(seeds, torch.int64),
-            out,
-        )
+        needed = kernels.sample_work_floats(n, self.vocab_size)
+        if self._work is None or self._work.numel() < needed:
+            self._work = torch.empty(max(needed, kernels.sample_work_floats(8, self.vocab_size)), dtype=torch.float32, device=self.device)
+        temperature, top_k, top_p, min_p, seeds = self._row_parameters(rows)
+        kernels.sample(logits, self._work, temperature, top_k, top_p, min_p, seeds, out)
         return out
+
+    def _row_parameters(self, rows: Sequence[SamplingRow]) -> tuple[torch.Tensor, ...]:
+        """The rows' parameters on the device: packed into one pinned buffer (a ring of four, so that
+        the copy of one step may still be in flight while the next is packed) and sent in one copy."""
+        n = len(rows)
+        seeds = [as_signed64(mix_seed(row.base_seed(), row.position)) for row in rows]
+        if not self._is_cuda:
+            return (
+                torch.tensor([float(row.params.temperature) for row in rows], dtype=torch.float32),
+                torch.tensor([int(row.params.top_k) for row in rows], dtype=torch.int32),
+                torch.tensor([float(row.params.top_p) for row in rows], dtype=torch.float32),
+                torch.tensor([float(row.params.min_p) for row in rows], dtype=torch.float32),
+                torch.tensor(seeds, dtype=torch.int64),
+            )
+        if self._staging is None or self._staging_rows < n:
+            self._staging_rows = max(n, 64)
+            words = 6 * self._staging_rows  # seeds (two 32-bit words a row) first: 8-byte aligned
+            self._staging = [(torch.empty(words, dtype=torch.int32, pin_memory=True), torch.cuda.Event()) for _ in range(4)]
+            self._device_words = torch.empty(words, dtype=torch.int32, device=self.device)
+            self._next_staging = 0
+        host, event = self._staging[self._next_staging]
+        self._next_staging = (self._next_staging + 1) % len(self._staging)
+        event.synchronize()  # the copy that last used this buffer has run
+        cap = self._staging_rows
+        host[: 2 * n].view(torch.int64).copy_(torch.tensor(seeds, dtype=torch.int64))
+        as_float = host.view(torch.float32)
+        as_float[2 * cap : 2 * cap + n] = torch.tensor([float(row.params.temperature) for row in rows], dtype=torch.float32)
+        host[3 * cap : 3 * cap + n] = torch.tensor([int(row.params.top_k) for row in rows], dtype=torch.int32)
+        as_float[4 * cap : 4 * cap + n] = torch.tensor([float(row.params.top_p) for row in rows], dtype=torch.float32)
+        as_float[5 * cap : 5 * cap + n] = torch.tensor([float(row.params.min_p) for row in rows], dtype=torch.float32)
+        device = self._device_words
+        device.copy_(host, non_blocking=True)
+        event.record()
+        device_float = device.view(torch.float32)
+        return (
+            device_float[2 * cap : 2 * cap + n],
+            device[3 * cap : 3 * cap + n],
+            device_float[4 * cap : 4 * cap + n],
+            device_float[5 * cap : 5 * cap + n],
+            device[: 2 * n].view(torch.int64),
+        )

@@ -630,7 +630,7 @@ def _sample_both(logits, temperature, top_k, top_p, min_p, seeds):
     expected = torch.empty(n, dtype=torch.int32)
     ref.sample(logits, None, *args, expected)
     out = torch.empty(n, dtype=torch.int32, device=DEV)
-    work = torch.empty(n * V, device=DEV)
+    work = torch.empty(kernels().sample_work_floats(n, V), device=DEV)
     kernels().sample(logits.to(DEV), work, *(a.to(DEV) for a in args), out)
     return out.cpu().tolist(), expected.tolist()
 
@@ -679,7 +679,7 @@ def test_sample_frequencies_follow_the_distribution():
     out = torch.empty(n, dtype=torch.int32, device=DEV)
     t = lambda values, dtype: torch.tensor(values, dtype=dtype, device=DEV)
     kernels().sample(
-        logits.repeat(n, 1).to(DEV), torch.empty(n * V, device=DEV), t([1.0] * n, torch.float32), t([-1] * n, torch.int32),
+        logits.repeat(n, 1).to(DEV), torch.empty(kernels().sample_work_floats(n, V), device=DEV), t([1.0] * n, torch.float32), t([-1] * n, torch.int32),
         t([1.0] * n, torch.float32), t([0.0] * n, torch.float32), t(seeds, torch.int64), out,
     )
     counts = torch.bincount(out.cpu().long(), minlength=V).float() / n

@@ -189,6 +189,10 @@ def edit_logits(logits, rows, tokens, mul, sub, mask):
         logits[r, t] = value - float(sub[e])
 
 
+def sample_work_floats(rows, vocab):
+    return rows * vocab
+
+
 def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
     """Row-wise: the reference's filters and Gumbel-max draw.  ``seeds`` already
     carry the position (mix_seed on the host)."""
@@ -205,7 +209,7 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
 _NAMES = [
     "embedding", "patch_tokens", "fused_norm_available", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
     "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
-    "edit_logits", "sample",
+    "edit_logits", "sample", "sample_work_floats",
 ]
 
 
