@@ -36,7 +36,7 @@ template <int NTOK, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
                 int out_fp32, int ldo, const __nv_bfloat16* __restrict__ bias, float* __restrict__ partial, int M, int N, int K,
-                int k_blocks_per_split, int* flag) {
+                int k_blocks_per_split, int rows_per_block, int* flag) {
     using Cfg = TcConfig<NTOK, GATED>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -50,7 +50,11 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int rows_out = GATED ? N / 2 : N;
-    const int n0 = blockIdx.x * TC_BLOCK_ROWS;
+    // A block owns rows_per_block (<= 128) weight rows: the copies bring only those (the box of map_w
+    // is that high), the other rows of the 128-row MMA tile hold whatever the shared memory held and
+    // their TMEM lanes are never read.  Fewer than 128 lets the host spread the rows over every SM.
+    const int n0 = blockIdx.x * rows_per_block;
+    const uint32_t stage_tx = (uint32_t)(Cfg::BANDS * rows_per_block * TC_BLOCK_K * 2 + Cfg::B_BYTES);
     const int total_k_blocks = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
     const int kb_begin = blockIdx.y * k_blocks_per_split;
     const int kb_end = min(kb_begin + k_blocks_per_split, total_k_blocks);
@@ -82,7 +86,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int i = 0; i < first_round; ++i) {
             unsigned char* a = stage_base + (size_t)i * Cfg::STAGE_BYTES;
             const int k = (kb_begin + i) * TC_BLOCK_K;
-            mbar_arrive_expect_tx(full_bar + i, Cfg::STAGE_BYTES);
+            mbar_arrive_expect_tx(full_bar + i, stage_tx);
             tma_load_2d(a, &map_w, k, n0, full_bar + i, stream_policy);
             if (GATED) tma_load_2d(a + Cfg::A_BYTES, &map_w, k, rows_out + n0, full_bar + i, stream_policy);
         }
@@ -102,7 +106,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             unsigned char* a = stage_base + (size_t)s * Cfg::STAGE_BYTES;
             unsigned char* b = a + Cfg::BANDS * Cfg::A_BYTES;
             const int k = (kb_begin + i) * TC_BLOCK_K;
-            mbar_arrive_expect_tx(full_bar + s, Cfg::STAGE_BYTES);
+            mbar_arrive_expect_tx(full_bar + s, stage_tx);
             tma_load_2d(a, &map_w, k, n0, full_bar + s, stream_policy);
             if (GATED) tma_load_2d(a + Cfg::A_BYTES, &map_w, k, rows_out + n0, full_bar + s, stream_policy);
             tma_load_2d(b, &map_x, k, 0, full_bar + s, keep_policy);
@@ -151,7 +155,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 float v[16], u[16];
                 tmem_load16(lane_base + c * 16, v);
                 if (GATED) tmem_load16(lane_base + NTOK + c * 16, u);
-                if (n < rows_out) {
+                if (row < rows_per_block && n < rows_out) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int token = c * 16 + j;
@@ -240,7 +244,7 @@ KB_EXPORT int kb_tc5_encode_map(void* map_out, const void* base, long long rows,
 
 template <int NTOK, bool GATED>
 static int launch_tc5(const CUtensorMap* map_w, const CUtensorMap* map_x, void* out, int out_fp32, int ldo,
-                      const __nv_bfloat16* bias, float* partial, int M, int N, int K, int k_splits, int* flag,
+                      const __nv_bfloat16* bias, float* partial, int M, int N, int K, int k_splits, int rows_per_block, int* flag,
                       cudaStream_t stream) {
     using Cfg = TcConfig<NTOK, GATED>;
     static_assert(Cfg::STAGES >= 2, "pipeline needs two stages");
@@ -250,9 +254,9 @@ static int launch_tc5(const CUtensorMap* map_w, const CUtensorMap* map_x, void* 
     const int total_kb = (K + TC_BLOCK_K - 1) / TC_BLOCK_K;
     const int per_split = (total_kb + k_splits - 1) / k_splits;
     const int splits = (total_kb + per_split - 1) / per_split;  // every split has work
-    dim3 grid((rows_out + TC_BLOCK_ROWS - 1) / TC_BLOCK_ROWS, splits);
+    dim3 grid((rows_out + rows_per_block - 1) / rows_per_block, splits);
     kb_launch(gemm_tc5_kernel<NTOK, GATED>, dim3(grid), dim3(TC_THREADS), Cfg::SMEM, stream, *map_w, *map_x, out, out_fp32, ldo, bias,
-                                                                         splits > 1 ? partial : nullptr, M, N, K, per_split, flag);
+                                                                         splits > 1 ? partial : nullptr, M, N, K, per_split, rows_per_block, flag);
     int rc = kb_launch_result();
     if (rc != 0 || splits == 1) return rc;
     const size_t total = (size_t)M * rows_out;
@@ -279,22 +283,38 @@ KB_EXPORT int kb_gemm_tc5_splits(int n_out, int K, int gated) {
     return (total_kb + per_split - 1) / per_split;
 }
 
-// map_w, map_x: host pointers to tensor maps made by kb_tc5_encode_map (W with box_rows 128,
-// x with box_rows = the padded token count 16, 32 or 64).  Returns 0, a negative KB_ERR_* code
-// or a positive cudaError_t.
+// Weight rows a block should own for (rows of output, K): a multiple of 8 up to 128.  Without a
+// split of K the rows are spread over as many whole waves of one block per SM as it takes
+// (14,336 rows: 104 a block, 138 blocks; 25,600 rows: 88 a block, 291 blocks = two waves).
+KB_EXPORT int kb_gemm_tc5_rows(int n_out, int K, int gated) {
+    if (kb_gemm_tc5_splits(n_out, K, gated) > 1) return TC_BLOCK_ROWS;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+    for (int waves = 1; waves <= 64; ++waves) {
+        int rows = (n_out + sms * waves - 1) / (sms * waves);
+        rows = (rows + 7) / 8 * 8;
+        if (rows <= TC_BLOCK_ROWS) return rows < 8 ? 8 : rows;
+    }
+    return TC_BLOCK_ROWS;
+}
+
+// map_w, map_x: host pointers to tensor maps made by kb_tc5_encode_map (W with box_rows =
+// rows_per_block, as kb_gemm_tc5_rows gives it; x with box_rows = the padded token count 16, 32
+// or 64).  Returns 0, a negative KB_ERR_* code or a positive cudaError_t.
 KB_EXPORT int kb_gemm_tc5(const void* map_w, const void* map_x, void* out, int out_fp32, int ldo, const void* bias,
-                          float* partial, int M, int N, int K, int gated, int* flag, cudaStream_t stream) {
+                          float* partial, int M, int N, int K, int gated, int rows_per_block, int* flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     if (!map_w || !map_x || !out) return KB_ERR_NULL;
     if (M < 1 || M > 64 || K < 8 || K % 8 != 0) return KB_ERR_UNSUPPORTED_SIZE;
     if (gated && N % 2 != 0) return KB_ERR_BAD_ARG;
+    if (rows_per_block < 8 || rows_per_block > TC_BLOCK_ROWS || rows_per_block % 8 != 0) return KB_ERR_BAD_ARG;
     const int n_out = gated ? N / 2 : N;
     const int splits = kb_gemm_tc5_splits(n_out, K, gated);
     if (splits > 1 && partial == nullptr) return KB_ERR_NULL;
     const CUtensorMap* mw = (const CUtensorMap*)map_w;
     const CUtensorMap* mx = (const CUtensorMap*)map_x;
     const __nv_bfloat16* b = (const __nv_bfloat16*)bias;
-#define GO(NT, G) return launch_tc5<NT, G>(mw, mx, out, out_fp32, ldo, b, partial, M, N, K, splits, flag, stream)
+#define GO(NT, G) return launch_tc5<NT, G>(mw, mx, out, out_fp32, ldo, b, partial, M, N, K, splits, rows_per_block, flag, stream)
     if (M <= 16) { if (gated) GO(16, true); else GO(16, false); }
     if (M <= 32) { if (gated) GO(32, true); else GO(32, false); }
     if (gated) GO(64, true); else GO(64, false);

@@ -724,10 +724,12 @@ def _gemm_tc5(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor
             _tc5_scratch.append(torch.empty(max(need, 8 * 1024 * 1024), dtype=torch.float32, device=x.device))
         partial = _tc5_scratch[-1]
     box = 16 if M <= 16 else (32 if M <= 32 else 64)
-    fn = _fn("gemm_tc5", "kb_gemm_tc5", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    rows_fn = _fn("gemm_tc5", "kb_gemm_tc5_rows", [c_int, c_int, c_int])
+    rows_per_block = rows_fn(n_out, K, 1 if gated else 0)
+    fn = _fn("gemm_tc5", "kb_gemm_tc5", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(
-        fn(_tensor_map(weight, 128), _tensor_map(x, box), out.data_ptr(), 1 if out.dtype == torch.float32 else 0, out.stride(0),
-           _ptr(bias), _ptr(partial), M, N, K, 1 if gated else 0, _ptr(flag), _stream()),
+        fn(_tensor_map(weight, rows_per_block), _tensor_map(x, box), out.data_ptr(), 1 if out.dtype == torch.float32 else 0, out.stride(0),
+           _ptr(bias), _ptr(partial), M, N, K, 1 if gated else 0, rows_per_block, _ptr(flag), _stream()),
         "gemm_tc5",
         launches=2 if splits > 1 else 1,
     )
