@@ -98,6 +98,7 @@ class ModelRunner:
         decode_mode: str = "eager",
         max_graph_batch: int = 256,
         debug_poison: bool = False,
+        check_tables: bool = False,
     ) -> None:
         self.model = model
         self.cache = cache
@@ -108,6 +109,10 @@ class ModelRunner:
         self.decode_mode = decode_mode
         self.max_graph_batch = max_graph_batch
         self.debug_poison = debug_poison
+        # Per step, on the host: every page a row needs is there, and no page is named twice, in one
+        # row or in two (kairyu/engine/core/prefill.py:105-178).  The cache manager guarantees this
+        # by construction; the check costs a pass over the tables, so tests turn it on.
+        self.check_tables = check_tables
         self.workspace = Workspace(self.device)
         self.graph_workspace = Workspace(self.device)
         self._is_cuda = str(self.device).startswith("cuda")
@@ -159,7 +164,29 @@ class ModelRunner:
                     f"no pages left for request {entry.request_id!r} to reach {seq_len} tokens"
                 )
             rows.append((entry, start, seq_len))
+        if self.check_tables:
+            self._check_tables(rows)
         return rows
+
+    def _check_tables(self, rows: Sequence[tuple[StepEntry, int, int]]) -> None:
+        page_size = self.cache.page_size
+        for group in self.cache.layout.groups:
+            owner: dict[int, Hashable] = {}
+            for entry, _, seq_len in rows:
+                table = self.cache.block_table(entry.request_id, group.index)
+                needed = -(-seq_len // page_size)
+                if len(table) < needed:
+                    raise StepError(f"request {entry.request_id!r} has {len(table)} pages in group {group.index}, {needed} are needed")
+                first = 0
+                if group.spec.window is not None:  # pages the window has passed may be gone
+                    first = max(0, (seq_len - len(entry.tokens) + 1 - group.spec.window)) // page_size
+                for index in range(first, needed):
+                    page = table[index]
+                    if page <= 0 or page >= self.cache.num_pages:
+                        raise StepError(f"request {entry.request_id!r}: page {page} at place {index} of group {group.index} is not a page a request can hold")
+                    if page in owner:
+                        raise StepError(f"page {page} of group {group.index} is named by {owner[page]!r} and by {entry.request_id!r}")
+                    owner[page] = entry.request_id
 
     def _pack(
         self,

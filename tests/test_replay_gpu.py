@@ -55,7 +55,7 @@ def make_runner(case, dtype, *, num_pages, decode_mode="eager"):
     layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
     cache = CacheManager(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8)
     storage = CacheStorage(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8, dtype=model.dtype, device="cuda")
-    return ModelRunner(model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode, max_graph_batch=8)
+    return ModelRunner(model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode, max_graph_batch=8, check_tables=True)
 
 
 def worst(result, expected):

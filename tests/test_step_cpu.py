@@ -28,7 +28,7 @@ def make_runner(name, *, num_pages, page_size=None, dtype="float32", max_request
     layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
     cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
     storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cpu")
-    runner = ModelRunner(model, cache, storage, max_model_len=config["max_position_embeddings"], decode_mode="eager")
+    runner = ModelRunner(model, cache, storage, max_model_len=config["max_position_embeddings"], decode_mode="eager", check_tables=True)
     return runner, config, weights
 
 
@@ -130,3 +130,14 @@ def test_step_runs_out_of_pages_loudly():
     runner.step([StepEntry("a", [1] * 32, ())])
     with pytest.raises(OutOfPages):
         runner.step([StepEntry("a", [1], ())])
+
+
+def test_table_check_catches_a_page_named_twice(monkeypatch):
+    """With check_tables the step function refuses a step whose block tables share a page (the cache
+    manager never makes one; the check is the host-side guard the reference has, prefill.py:105-178)."""
+    torch_kernels.install(monkeypatch)
+    runner, _, _ = make_runner("llama", num_pages=12, page_size=8)
+    runner.step([StepEntry("a", list(range(10)), ()), StepEntry("b", list(range(5)), ())])
+    runner.cache.get("b").tables[0][0] = runner.cache.get("a").tables[0][1]  # corrupt: b now names a page of a
+    with pytest.raises(StepError, match="is named by"):
+        runner.step([StepEntry("a", [1], (0,)), StepEntry("b", [2], (0,))])
