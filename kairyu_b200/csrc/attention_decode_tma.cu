@@ -210,6 +210,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     if (key < key_lo || key >= seq_len)
                         *reinterpret_cast<uint4*>(tV + (c >> 3) * HALF_ELEMS + r * 64 + (c & 7) * 8) = make_uint4(0, 0, 0, 0);
                 }
+                fence_proxy_async();  // these writes stay ordered before the copy that refills the stage
                 __syncwarp();
             }
             float s[2][4];
