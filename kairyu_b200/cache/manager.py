@@ -12,6 +12,16 @@ or -1 once a windowed group has given the page back.
 The reference's dense pool is uniform (one table per request,
 kairyu/engine/core/radix_kv.py:144-149); groups generalise it the way its
 hybrid cache descriptors do (kairyu/engine/core/frontier_cache.py:19-75).
+
+Prefix sharing (``prefix_sharing=True``; off unless asked for).  Whole pages that a request has
+filled can be *published* to a tree keyed by their tokens (:mod:`kairyu_b200.cache.prefix`); a
+later request whose tokens start the same way is admitted with those pages at the head of its
+block tables and starts computing behind them.  A request's table is then ``shared pages ‖ its
+own pages``: shared pages are only read (a request writes at positions it computes, and those lie
+behind the shared pages), its own pages go back to the pool when it ends unless they were
+published, and published pages that no live request reads are taken back, oldest first, when a
+pool runs short.  It needs every paged group to keep all keys and no per-request state: a window
+gives pages back while the request runs, and state cannot be rebuilt from pages.
 """
 
 from __future__ import annotations
@@ -20,6 +30,7 @@ from dataclasses import dataclass, field
 from typing import Any, Hashable, Iterable, Mapping, Optional, Sequence
 
 from kairyu_b200.cache.page_pool import OutOfPages, PagePool
+from kairyu_b200.cache.prefix import PrefixIndex, PrefixNode
 from kairyu_b200.parts.base import PagedKVSpec, StateSpec
 
 
@@ -71,6 +82,8 @@ class RequestCache:
     tables: list[list[int]]  # per group: page index -> physical page or -1
     first_live: list[int]  # per group: lowest page index still held
     num_tokens: int = 0  # positions [0, num_tokens) have been computed
+    shared: list[PrefixNode] = field(default_factory=list)  # the leading pages it reads from the prefix tree
+    num_cached_tokens: int = 0  # how many tokens admission found in the tree
 
 
 class CacheManager:
@@ -82,9 +95,17 @@ class CacheManager:
         page_size: int,
         max_requests: int,
         reserved_pages: int = 1,
+        prefix_sharing: bool = False,
     ) -> None:
         if page_size < 1:
             raise ValueError("page_size must be >= 1")
+        if prefix_sharing:
+            windowed = [group.index for group in layout.groups if group.spec.window is not None]
+            if windowed or layout.states or not layout.groups:
+                raise ValueError(
+                    "prefix sharing needs paged groups that keep every key and no per-request state; "
+                    f"this model has windowed groups {windowed} and {len(layout.states)} state tensors"
+                )
         self.layout = layout
         self.page_size = page_size
         self.num_pages = num_pages
@@ -93,6 +114,7 @@ class CacheManager:
         self._free_state_slots = list(range(max_requests - 1, -1, -1))
         self._requests: dict[Hashable, RequestCache] = {}
         self.fresh_state_slots: list[int] = []  # slots handed out since the storage last zeroed them
+        self.prefix: Optional[PrefixIndex] = PrefixIndex(page_size) if prefix_sharing else None
 
     # ------------------------------------------------------------------ queries
     def __contains__(self, request_id: Hashable) -> bool:
@@ -107,6 +129,11 @@ class CacheManager:
 
     def free_pages(self, group: int = 0) -> int:
         return self.pools[group].num_free
+
+    def available_pages(self, group: int = 0) -> int:
+        """Free pages plus published pages that no live request reads (they can be taken back)."""
+        unread = self.prefix.num_unread if self.prefix is not None else 0
+        return self.pools[group].num_free + unread
 
     def pages_for(self, num_tokens: int) -> int:
         return -(-num_tokens // self.page_size)
@@ -144,7 +171,11 @@ class CacheManager:
         return True
 
     # ------------------------------------------------------------------ lifecycle
-    def admit(self, request_id: Hashable) -> RequestCache:
+    def admit(self, request_id: Hashable, tokens: Optional[Sequence[int]] = None) -> RequestCache:
+        """Make a request live.  With prefix sharing and its ``tokens`` given, the whole pages the
+        tree already holds for them head its block tables and count as computed; at least the
+        last token is left to compute, so that the request's first step has logits
+        (kairyu/engine/core/scheduler.py:1589-1593)."""
         if request_id in self._requests:
             raise ValueError(f"request {request_id!r} is already live")
         if not self._free_state_slots:
@@ -157,6 +188,13 @@ class CacheManager:
             tables=[[] for _ in self.layout.groups],
             first_live=[0 for _ in self.layout.groups],
         )
+        if self.prefix is not None and tokens is not None and len(tokens) > 1:
+            path = self.prefix.match(tokens, max_pages=(len(tokens) - 1) // self.page_size)
+            self.prefix.acquire(path)
+            record.shared = path
+            for group in self.layout.groups:
+                record.tables[group.index] = [node.pages[group.index] for node in path]
+            record.num_tokens = record.num_cached_tokens = len(path) * self.page_size
         self._requests[request_id] = record
         return record
 
@@ -177,8 +215,11 @@ class CacheManager:
         if query_start is None:
             query_start = record.num_tokens
         needed = self.pages_needed(request_id, upto, query_start)
-        if any(count > pool.num_free for count, pool in zip(needed, self.pools)):
-            return False
+        short = max(count - pool.num_free for count, pool in zip(needed, self.pools))
+        if short > 0:
+            if self.prefix is None or short > self.prefix.num_unread:
+                return False
+            self._take_back(short)
         for group, pool in zip(self.layout.groups, self.pools):
             table = record.tables[group.index]
             first = self._first_needed_page(group, query_start)
@@ -210,11 +251,44 @@ class CacheManager:
                 pool.free(stale)
             record.first_live[group.index] = max(record.first_live[group.index], min(keep_from, len(table)))
 
+    def _take_back(self, count: int) -> None:
+        """Return ``count`` published pages that nobody reads to every pool."""
+        for pages in self.prefix.evict(count):
+            for pool, page in zip(self.pools, pages):
+                pool.free([page])
+
+    def publish(self, request_id: Hashable, tokens: Sequence[int]) -> int:
+        """Make the whole pages this request has computed matchable; ``tokens`` are the tokens
+        at its positions.  The request goes on reading them as shared pages.  Where the tree
+        already holds a page of the same tokens (another request computed it meanwhile), this
+        request keeps its own copy and publishing stops there.  Returns the pages published
+        (kairyu/engine/core/radix_kv.py:765-777, 815-889)."""
+        if self.prefix is None:
+            return 0
+        record = self._requests[request_id]
+        size = self.page_size
+        whole = min(record.num_tokens, len(tokens)) // size
+        parent = record.shared[-1] if record.shared else None
+        published = 0
+        for index in range(len(record.shared), whole):
+            key = tuple(tokens[index * size : (index + 1) * size])
+            if self.prefix.child(parent, key) is not None:
+                break
+            pages = tuple(record.tables[group.index][index] for group in self.layout.groups)
+            parent = self.prefix.insert(parent, key, pages, readers=1)
+            record.shared.append(parent)
+            published += 1
+        return published
+
     def release(self, request_id: Hashable) -> None:
-        """The request ended (finished, aborted or preempted): everything goes back."""
+        """The request ended (finished, aborted or preempted): its own pages go back to the
+        pools; the shared pages it read lose a reader and stay in the tree."""
         record = self._requests.pop(request_id)
+        own_from = len(record.shared)
         for table, pool in zip(record.tables, self.pools):
-            pool.free([page for page in table if page >= 0])
+            pool.free([page for page in table[own_from:] if page >= 0])
+        if record.shared:
+            self.prefix.drop(record.shared)
         self._free_state_slots.append(record.state_slot)
 
     def block_table(self, request_id: Hashable, group: int) -> list[int]:
@@ -230,8 +304,17 @@ class CacheManager:
         for group, pool in zip(self.layout.groups, self.pools):
             pool.check()
             seen: dict[int, Hashable] = {}
+            if self.prefix is not None:
+                for node in self.prefix.nodes():
+                    page = node.pages[group.index]
+                    if page in seen or page < pool.reserved:
+                        raise AssertionError(f"group {group.index}: page {page} is in the prefix tree twice or reserved")
+                    seen[page] = "prefix tree"
             for record in self._requests.values():
-                for page in record.tables[group.index]:
+                shared = [node.pages[group.index] for node in record.shared]
+                if record.tables[group.index][: len(shared)] != shared:
+                    raise AssertionError(f"group {group.index}: {record.request_id!r} does not start with its shared pages")
+                for page in record.tables[group.index][len(shared) :]:
                     if page < 0:
                         continue
                     if page in seen:
@@ -245,6 +328,15 @@ class CacheManager:
                 raise AssertionError(
                     f"group {group.index}: pool holds {pool.num_held} pages, requests hold {len(seen)}"
                 )
+        if self.prefix is not None:
+            self.prefix.check()
+            readers: dict[int, int] = {}
+            for record in self._requests.values():
+                for node in record.shared:
+                    readers[id(node)] = readers.get(id(node), 0) + 1
+            for node in self.prefix.nodes():
+                if node.readers != readers.get(id(node), 0):
+                    raise AssertionError("a prefix page's reader count does not match the requests that read it")
         slots = [record.state_slot for record in self._requests.values()]
         if len(set(slots)) != len(slots):
             raise AssertionError("two requests share a state slot")

@@ -48,6 +48,9 @@ class EngineConfig:
     # Steps that may be launched before the oldest one's tokens are read (the reference's option
     # of this name, default 1 there too): 2 plans and launches step N+1 while step N runs.
     pipeline_depth: int = 1
+    # Whole pages of finished and running requests stay matchable by their tokens; a request whose
+    # tokens start the same way begins behind them (kairyu/engine/core/radix_kv.py:1-11).
+    enable_prefix_caching: bool = False
     seed: int = 0
 
     def __post_init__(self) -> None:

@@ -34,6 +34,7 @@ class FinishedRequest:
     output_token_ids: tuple[int, ...]
     finish_reason: str
     stop_reason: Optional[int | str] = None
+    num_cached_tokens: int = 0  # prompt tokens found in the prefix tree at admission
 
 
 class _PendingStep:
@@ -85,7 +86,11 @@ class Engine:
             num_pages = self._pages_that_fit(layout, element_size)
         self.num_pages = num_pages
         self.cache = CacheManager(
-            layout, num_pages=num_pages, page_size=config.page_size, max_requests=config.max_num_seqs
+            layout,
+            num_pages=num_pages,
+            page_size=config.page_size,
+            max_requests=config.max_num_seqs,
+            prefix_sharing=config.enable_prefix_caching,
         )
         self.storage = CacheStorage(
             layout,
@@ -199,6 +204,7 @@ class Engine:
             tuple(state.outputs),
             state.finish_reason or "abort",
             stop_reason,
+            state.num_cached_tokens,
         )
         self._stop_checks.pop(request_id, None)
         self.scheduler.forget(request_id)

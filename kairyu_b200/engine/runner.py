@@ -110,8 +110,9 @@ class ModelRunner:
         self.max_graph_batch = max_graph_batch
         self.debug_poison = debug_poison
         # Per step, on the host: every page a row needs is there, and no page is named twice, in one
-        # row or in two (kairyu/engine/core/prefill.py:105-178).  The cache manager guarantees this
-        # by construction; the check costs a pass over the tables, so tests turn it on.
+        # row or in two, except shared prefix pages, which no row may write
+        # (kairyu/engine/core/prefill.py:105-178).  The cache manager guarantees this by
+        # construction; the check costs a pass over the tables, so tests turn it on.
         self.check_tables = check_tables
         self.workspace = Workspace(self.device)
         self.graph_workspace = Workspace(self.device)
@@ -172,8 +173,11 @@ class ModelRunner:
         page_size = self.cache.page_size
         for group in self.cache.layout.groups:
             owner: dict[int, Hashable] = {}
-            for entry, _, seq_len in rows:
+            for entry, start, seq_len in rows:
                 table = self.cache.block_table(entry.request_id, group.index)
+                shared = len(self.cache.get(entry.request_id).shared)
+                if start < shared * page_size:
+                    raise StepError(f"request {entry.request_id!r} would write position {start}, which lies in a shared page")
                 needed = -(-seq_len // page_size)
                 if len(table) < needed:
                     raise StepError(f"request {entry.request_id!r} has {len(table)} pages in group {group.index}, {needed} are needed")
@@ -184,6 +188,10 @@ class ModelRunner:
                     page = table[index]
                     if page <= 0 or page >= self.cache.num_pages:
                         raise StepError(f"request {entry.request_id!r}: page {page} at place {index} of group {group.index} is not a page a request can hold")
+                    if index < shared:
+                        if owner.setdefault(page, "the prefix tree") != "the prefix tree":
+                            raise StepError(f"page {page} of group {group.index} is shared and also held by {owner[page]!r}")
+                        continue
                     if page in owner:
                         raise StepError(f"page {page} of group {group.index} is named by {owner[page]!r} and by {entry.request_id!r}")
                     owner[page] = entry.request_id

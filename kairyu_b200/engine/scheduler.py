@@ -1,8 +1,8 @@
 """The scheduler: admits requests, cuts prompts into portions under a token
 budget, decodes, finishes and frees.  Pure policy over the cache manager; it
 never touches a tensor (kairyu/engine/core/scheduler.py:404-1770 is the
-reference; priorities, scheduling classes, speculative reservations and prefix
-sharing are left out).
+reference; priorities, scheduling classes and speculative reservations are left
+out).
 
 A request's work is ``prompt + outputs``; ``computed`` counts how many of those
 tokens have been fed.  While more than one token is left to feed the request
@@ -17,6 +17,13 @@ token counts as part of the request's work, so the next plan may already feed it
 (the step takes its value from the device).  A request with a token in flight is
 never preempted, and tokens that arrive for a request that has finished meanwhile
 are dropped.
+
+Prefix sharing, when the cache manager has it on: admission hands the request's tokens to
+the cache, which may find their leading whole pages already computed; the request then
+starts behind them (``computed`` and ``num_cached_tokens``), always leaving its last token
+to compute (scheduler.py:1589-1593).  A request's whole pages are published when its first
+token commits and again when it finishes (scheduler.py:1724-1729; radix_kv.py:815-889);
+an aborted or preempted request publishes nothing more.
 
 Order within a step (scheduler.py:1641-1657): decodes first (one token each),
 then running prefills, then admissions from the head of the queue.
@@ -71,7 +78,10 @@ class Status(Enum):
 
 
 class RequestState:
-    __slots__ = ("request", "status", "computed", "outputs", "in_flight", "finish_reason", "preemptions", "arrival")
+    __slots__ = (
+        "request", "status", "computed", "outputs", "in_flight", "finish_reason", "preemptions", "arrival",
+        "num_cached_tokens",
+    )
 
     def __init__(self, request: EngineRequest, arrival: int) -> None:
         self.request = request
@@ -82,6 +92,7 @@ class RequestState:
         self.finish_reason: Optional[str] = None
         self.preemptions = 0
         self.arrival = arrival
+        self.num_cached_tokens = 0  # tokens its first admission found in the prefix tree
 
     @property
     def total_tokens(self) -> int:
@@ -91,6 +102,9 @@ class RequestState:
     def remaining(self) -> int:
         """Tokens left to feed, the ones in flight included (their values come later)."""
         return self.total_tokens + self.in_flight - self.computed
+
+    def all_tokens(self) -> list[int]:
+        return list(self.request.prompt_token_ids) + self.outputs
 
     def tokens(self, start: int, count: int) -> list[int]:
         prompt = self.request.prompt_token_ids
@@ -139,7 +153,7 @@ class Scheduler:
         self._waiting: deque[str] = deque()
         self._running: list[str] = []  # admission order; the last is the youngest
         self._arrivals = 0
-        self.counters = {"preemptions": 0, "rejections": 0, "steps": 0}
+        self.counters = {"preemptions": 0, "rejections": 0, "steps": 0, "prompt_tokens": 0, "cached_prompt_tokens": 0}
 
     # ------------------------------------------------------------------ intake
     def add_request(self, request: EngineRequest) -> None:
@@ -187,6 +201,13 @@ class Scheduler:
     def state(self, request_id: str) -> RequestState:
         return self._states[request_id]
 
+    @property
+    def prefix_hit_rate(self) -> float:
+        """Prompt tokens found in the prefix tree over prompt tokens admitted
+        (kairyu/engine/core/radix_kv.py:245-249)."""
+        total = self.counters["prompt_tokens"]
+        return self.counters["cached_prompt_tokens"] / total if total else 0.0
+
     def running_ids(self) -> tuple[str, ...]:
         return tuple(self._running)
 
@@ -211,6 +232,8 @@ class Scheduler:
         if in_running:
             self._running.remove(state.request.request_id)
         if state.request.request_id in self.cache:
+            if reason in ("stop", "length"):
+                self.cache.publish(state.request.request_id, state.all_tokens())
             self.cache.release(state.request.request_id)
 
     def _preempt(self, request_id: str) -> None:
@@ -338,17 +361,24 @@ class Scheduler:
                 self.counters["rejections"] += 1
                 rejected.append(head)
                 continue
-            needed = self.cache.pages_needed(None, state.total_tokens, 0)
-            if any(count > self.cache.free_pages(group) for group, count in enumerate(needed)):
-                break  # the head waits for pages
             try:
-                self.cache.admit(head)
+                record = self.cache.admit(head, state.all_tokens())
             except OutOfPages:
                 break
+            needed = self.cache.pages_needed(head, state.total_tokens, record.num_tokens)
+            if any(count > self.cache.available_pages(group) for group, count in enumerate(needed)):
+                self.cache.release(head)
+                break  # the head waits for pages
+            state.computed = record.num_tokens  # the pages the prefix tree already holds
             count = min(state.remaining, budget, self._chunk_cap(budget, 1))
             if not self._grow(state, count):
+                state.computed = 0
                 self.cache.release(head)
                 break
+            if state.preemptions == 0:
+                state.num_cached_tokens = record.num_cached_tokens
+                self.counters["prompt_tokens"] += state.total_tokens
+                self.counters["cached_prompt_tokens"] += record.num_cached_tokens
             self._waiting.popleft()
             state.status = Status.RUNNING
             self._running.append(head)
@@ -379,6 +409,8 @@ class Scheduler:
             if reason is not None:
                 self._finish(state, reason)
                 finished.append(request_id)
+            elif len(state.outputs) == 1 and request_id in self.cache:
+                self.cache.publish(request_id, state.all_tokens())  # its prompt's pages become matchable
         return tuple(finished)
 
     @staticmethod

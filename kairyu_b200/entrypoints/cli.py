@@ -50,6 +50,7 @@ def _build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--max-model-len", type=int, default=None)
     generate.add_argument("--decode-mode", choices=["eager", "cuda_graph"], default=None)
     generate.add_argument("--pipeline-depth", type=int, choices=[1, 2], default=1, help="2: launch step N+1 while step N runs")
+    generate.add_argument("--enable-prefix-caching", action="store_true", help="Share whole cache pages between requests whose tokens start the same way")
 
     validate = commands.add_parser("validate", help="Check a model folder against its architecture without a GPU.")
     validate.add_argument("model", type=Path, help="Path to the model folder")
@@ -92,6 +93,7 @@ def _generate(args: argparse.Namespace) -> int:
         str(args.model), dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
         max_num_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
         max_model_len=args.max_model_len, decode_mode=args.decode_mode, pipeline_depth=args.pipeline_depth,
+        enable_prefix_caching=args.enable_prefix_caching,
     )
     for output in llm.generate(prompts, params):
         print(

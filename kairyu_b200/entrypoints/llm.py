@@ -49,12 +49,14 @@ class LLM:
     ) -> None:
         if tensor_parallel_size != 1:
             raise ValueError("this engine runs on one GPU: tensor_parallel_size must be 1")
-        if enable_prefix_caching:
-            raise ValueError("prefix caching is not implemented in this engine")
         self.model = model
         self.seed = seed
         config = EngineConfig.from_kwargs(
-            dtype=dtype, seed=seed or 0, gpu_memory_utilization=gpu_memory_utilization, **engine_kwargs
+            dtype=dtype,
+            seed=seed or 0,
+            gpu_memory_utilization=gpu_memory_utilization,
+            enable_prefix_caching=bool(enable_prefix_caching),
+            **engine_kwargs,
         )
         self._model_dir: Optional[Path] = Path(model)
         self.engine = Engine.from_model_dir(model, config)
@@ -163,8 +165,10 @@ class LLM:
         results: list[RequestOutput] = []
         for request_id, children, token_ids, text, params in submitted:
             completions = []
+            cached = 0
             for sample, child_id in enumerate(children):
                 record = finished[child_id]
+                cached = max(cached, record.num_cached_tokens)
                 output_text = self._decode(record.output_token_ids, params.skip_special_tokens)
                 if isinstance(record.stop_reason, str) and record.stop_reason in output_text:
                     output_text = output_text[: output_text.index(record.stop_reason)]
@@ -183,6 +187,7 @@ class LLM:
                     prompt=text,
                     prompt_token_ids=token_ids,
                     outputs=tuple(completions),
+                    metrics={"num_cached_tokens": cached},
                 )
             )
         return results

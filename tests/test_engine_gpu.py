@@ -245,3 +245,48 @@ def test_kernels_refuse_cpu_tensors():
 
     with pytest.raises(kernels.KernelError):
         kernels.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-5, torch.zeros(2, 8))
+
+
+@pytest.mark.parametrize("name,dtype,depth", [("llama", "float32", 1), ("odd", "float32", 2), ("wide", "bfloat16", 2), ("qwen3", "bfloat16", 1)])
+def test_prefix_caching_gives_the_same_tokens(name, dtype, depth):
+    """Requests that start with the same tokens read the pages an earlier request computed
+    (kairyu tests/unit/test_engine_hf_parity.py:115-133): the tokens are those of the plain
+    implementation (fp32), or agree with it as far as generation without sharing does (bf16);
+    with so few pages that unread shared pages are taken back and the stem is computed again."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY[name]
+    stem = prompts_of(config, [5 * page_size + 3], seed=130)[0]
+    prompts = [stem + tail for tail in prompts_of(config, [1, 12, 2 * page_size, 7, 30, 3], seed=131)]
+    other = prompts_of(config, [9 * page_size], seed=132)  # pushes the stem's pages out in between
+    params = SamplingParams(temperature=0.0, max_tokens=16)
+    llm = LLM.from_random(
+        config, seed=seed, dtype=dtype, page_size=page_size, num_pages=22, max_num_seqs=3,
+        max_num_batched_tokens=40, enable_prefix_caching=True, pipeline_depth=depth,
+    )
+    llm.engine.runner.check_tables = True
+    weights = engine_weights(llm)
+    rounds = []
+    for workload in (prompts, other, prompts[::-1]):
+        outputs = llm.generate([TokensPrompt(tuple(p)) for p in workload], params)
+        rounds.append(outputs)
+        llm.engine.cache.check()
+        assert llm.engine.cache.live_requests == 0
+    assert llm.engine.scheduler.counters["cached_prompt_tokens"] >= 5 * page_size * 4
+    assert llm.engine.cache.prefix.counters["evicted_pages"] > 0
+    assert max(o.metrics["num_cached_tokens"] for o in rounds[0]) >= 5 * page_size
+    agree = total = 0
+    for workload, outputs in zip((prompts, other, prompts[::-1]), rounds):
+        for prompt, output in zip(workload, outputs):
+            expected = plain_generate(config, weights, prompt, 16)
+            got = list(output.outputs[0].token_ids)
+            assert len(got) == 16
+            if dtype == "float32":
+                assert got == expected
+            for a, b in zip(got, expected):
+                total += 1
+                if a != b:
+                    break
+                agree += 1
+    if dtype == "bfloat16":
+        assert agree / total > 0.9
