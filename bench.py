@@ -337,6 +337,54 @@ def time_mixed(layers: int) -> dict:
     }
 
 
+def time_shared_prefix(layers: int) -> dict:
+    """16 requests that share a 2,048-token stem (a system prompt) and differ in a 128-token tail,
+    64 generated tokens each, through ``LLM.generate`` with prefix caching off and on.  Prompts are
+    prefilled one at a time in portions of 512 tokens, so every request after the first is admitted
+    when the stem's pages have been published."""
+    import torch
+
+    from kairyu_b200 import SamplingParams, TokensPrompt
+    from kairyu_b200.config.engine_config import EngineConfig
+    from kairyu_b200.engine.engine import Engine
+    from kairyu_b200.entrypoints.llm import LLM
+
+    config = dict(MODEL)
+    config["num_hidden_layers"] = layers
+    stem = random_tokens(2048, MODEL["vocab_size"], 400)
+    prompts = [TokensPrompt(tuple(stem + random_tokens(128, MODEL["vocab_size"], 401 + i))) for i in range(16)]
+    warm = [TokensPrompt(tuple(random_tokens(600, MODEL["vocab_size"], 450 + i))) for i in range(4)]
+    params = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    result: dict = {}
+    for caching in (False, True):
+        engine_config = EngineConfig(
+            dtype="bfloat16", page_size=PAGE_SIZE, num_pages=20 * (-(-(2048 + 128 + 64 + 16) // PAGE_SIZE)) + 1,
+            max_num_batched_tokens=512 + 16, prefill_chunk_size=512, max_num_seqs=16, max_model_len=CONTEXT_LEN,
+            max_num_partial_prefills=1, pipeline_depth=2, enable_prefix_caching=caching, seed=SEED,
+        )
+        engine = Engine.from_random(config, SEED, engine_config)
+        llm = LLM.__new__(LLM)
+        llm.model, llm.seed, llm._model_dir, llm.engine = "random", SEED, None, engine
+        llm._finish_init(None)
+        llm.generate(warm, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        outputs = llm.generate(prompts, params)
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - begin
+        engine.runner.check_errors()
+        generated = sum(len(output.outputs[0].token_ids) for output in outputs)
+        key = "shared_prefix_cached" if caching else "shared_prefix_plain"
+        result[key + "_seconds"] = seconds
+        result[key + "_generated_tok_s"] = generated / seconds
+        if caching:
+            result["shared_prefix_cached_tokens"] = sum(output.metrics["num_cached_tokens"] for output in outputs)
+            result["shared_prefix_prompt_tokens"] = sum(len(prompt.prompt_token_ids) for prompt in prompts)
+        del llm, engine
+        torch.cuda.empty_cache()
+    return result
+
+
 def reference_arm(args) -> int:
     """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
@@ -373,6 +421,7 @@ def main() -> int:
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="llama31-8b", help="another shape than the default (its own lengths)")
     parser.add_argument("--mixed", action="store_true", help="add the mixed workload of 32 requests (chunked prefill beside decode)")
+    parser.add_argument("--shared-prefix", action="store_true", help="add the shared-stem workload of 16 requests, prefix caching off and on")
     parser.add_argument("--prompt-len", type=int, default=None, help="another prompt length than the shape's (with --gen-len, within the context length)")
     parser.add_argument("--gen-len", type=int, default=None)
     args = parser.parse_args()
@@ -440,6 +489,11 @@ def main() -> int:
         del engine
         torch.cuda.empty_cache()
         points.update(time_mixed(args.layers))
+        engine = None
+    if args.shared_prefix:
+        del engine
+        torch.cuda.empty_cache()
+        points.update(time_shared_prefix(args.layers))
 
     line = {
         "metric": f"decode tok/s @bs{args.batch} ({MODEL_NAME}, {PROMPT_LEN}-token prompts)",

@@ -62,6 +62,12 @@ def worst(result, expected):
     return max(float(np.abs(row - expected[name][position]).max()) for (name, position), row in result.items())
 
 
+def off_rows(result, expected, tolerance):
+    """For a failure's message: the rows beyond the tolerance, as (request, position, error)."""
+    errors = [(name, position, float(np.abs(row - expected[name][position]).max())) for (name, position), row in result.items()]
+    return [entry for entry in errors if not entry[2] < tolerance][:12]
+
+
 def cuts(case):
     requests = case["requests"]
     return {
@@ -84,7 +90,7 @@ def test_every_cut_matches_plain(case, dtype, tolerance, decode_mode):
     for cut, steps in all_cuts.items():
         results[cut] = traces.run_in_process(runner, steps)
         assert len(results[cut]) == total
-        assert worst(results[cut], case["expected"][dtype]) < tolerance, cut
+        assert worst(results[cut], case["expected"][dtype]) < tolerance, (cut, off_rows(results[cut], case["expected"][dtype], tolerance))
     if decode_mode == "cuda_graph":
         assert runner.counters["graph_replays"] > 0
     if dtype == "float32":
