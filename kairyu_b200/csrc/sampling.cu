@@ -99,6 +99,117 @@ KB_EXPORT int kb_argmax(const float* logits, int ld, int n, int V, int* out, cud
     return kb_launch_result();
 }
 
+// ------------------------------------------------------------------ log-probability report
+// For report r over row rows[r] of the logits: the log-softmax value of one token, and the k
+// largest log-softmax values with their indices, largest first, ties by the lower index
+// (kairyu/engine/core/sampler.py:1423-1437: taken from the raw logits, before any edit or
+// temperature).  One block per report.  values[r, 0] is the token's, values[r, 1 + i] and
+// indices[r, i] the i-th largest.  Pass i of the top-k finds the best entry that comes after
+// pass i-1's in the order (value down, index up), so nothing has to be remembered but the last.
+constexpr int REPORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(REPORT_THREADS)
+logprob_report_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ rows,
+                      const int* __restrict__ tokens, int tokens_by_row, int k, float* __restrict__ values,
+                      int* __restrict__ indices) {
+    pdl_wait();
+    __shared__ float red_m[REPORT_THREADS / 32];
+    __shared__ float red_s[REPORT_THREADS / 32];
+    __shared__ int red_i[REPORT_THREADS / 32];
+    __shared__ float bcast_v;
+    __shared__ int bcast_i;
+    const int r = blockIdx.x;
+    const int row = rows[r];
+    const float* x = logits + (size_t)row * ld;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+    // log of the sum of exponentials, with the running maximum taken out
+    float m = -INFINITY, sum = 0.0f;
+    for (int i = threadIdx.x; i < V; i += REPORT_THREADS) {
+        const float v = x[i];
+        if (v > m) {
+            sum = sum * expf(m - v) + 1.0f;  // m = -inf: sum is 0 and stays finite
+            m = v;
+        } else if (v > -INFINITY) {
+            sum += expf(v - m);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const float os = __shfl_xor_sync(0xffffffffu, sum, o);
+        const float nm = fmaxf(m, om);
+        if (nm > -INFINITY) sum = sum * expf(m - nm) + os * expf(om - nm);
+        m = nm;
+    }
+    if (lane == 0) { red_m[warp] = m; red_s[warp] = sum; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float bm = red_m[0], bs = red_s[0];
+        for (int w = 1; w < REPORT_THREADS / 32; ++w) {
+            const float nm = fmaxf(bm, red_m[w]);
+            if (nm > -INFINITY) bs = bs * expf(bm - nm) + red_s[w] * expf(red_m[w] - nm);
+            bm = nm;
+        }
+        const float lse = bm + logf(bs);
+        bcast_v = lse;
+        int token = tokens[tokens_by_row ? row : r];
+        token = min(max(token, 0), V - 1);
+        values[(size_t)r * (k + 1)] = x[token] - lse;
+    }
+    __syncthreads();
+    const float lse = bcast_v;
+
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int pass = 0; pass < k; ++pass) {
+        float best = -INFINITY;
+        int best_i = 0x7fffffff;
+        for (int i = threadIdx.x; i < V; i += REPORT_THREADS) {
+            const float v = x[i];
+            const bool after = v < prev_v || (v == prev_v && i > prev_i);
+            if (after && (v > best || (v == best && i < best_i))) { best = v; best_i = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
+        }
+        __syncthreads();  // the pass before has read bcast_v / bcast_i
+        if (lane == 0) { red_m[warp] = best; red_i[warp] = best_i; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int w = 1; w < REPORT_THREADS / 32; ++w)
+                if (red_i[w] != 0x7fffffff && (best_i == 0x7fffffff || red_m[w] > best || (red_m[w] == best && red_i[w] < best_i))) {
+                    best = red_m[w];
+                    best_i = red_i[w];
+                }
+            bcast_v = best;
+            bcast_i = best_i;
+            // fewer than k entries (k > V): the rest are marked absent
+            values[(size_t)r * (k + 1) + 1 + pass] = best_i == 0x7fffffff ? -INFINITY : best - lse;
+            indices[(size_t)r * k + pass] = best_i == 0x7fffffff ? -1 : best_i;
+        }
+        __syncthreads();
+        prev_v = bcast_v;
+        prev_i = bcast_i;
+        if (prev_i == 0x7fffffff) prev_v = -INFINITY;  // nothing is left: later passes find nothing either
+    }
+}
+
+// values: [reports, k + 1] floats, indices: [reports, k] ints (k may be 0: the token's value only).
+// tokens_by_row: the token of report r is tokens[rows[r]] (a step's sampled ids), else tokens[r].
+KB_EXPORT int kb_logprob_report(const float* logits, int ld, int n_rows, int V, const int* rows, const int* tokens,
+                                int tokens_by_row, int reports, int k, float* values, int* indices, cudaStream_t stream) {
+    if (reports == 0) return 0;
+    if (!logits || !rows || !tokens || !values || (k > 0 && !indices)) return KB_ERR_NULL;
+    if (V < 1 || k < 0 || n_rows < 1) return KB_ERR_BAD_ARG;
+    kb_launch(logprob_report_kernel, dim3(reports), dim3(REPORT_THREADS), 0, stream, logits, ld, V, rows, tokens, tokens_by_row, k,
+              values, indices);
+    return kb_launch_result();
+}
+
 // ------------------------------------------------------------------ logit edits
 // entry e: logits[row[e], tok[e]] <- -inf if mask[e], else
 //   l <- (l > 0 ? l / mul[e] : l * mul[e]) - sub[e]

@@ -7,6 +7,7 @@ kairyu/engine/kairyu_backend.py:467-1179, without tokenizer and server parts).
 from __future__ import annotations
 
 import json
+import dataclasses
 from collections import deque
 from dataclasses import dataclass
 from pathlib import Path
@@ -35,18 +36,22 @@ class FinishedRequest:
     finish_reason: str
     stop_reason: Optional[int | str] = None
     num_cached_tokens: int = 0  # prompt tokens found in the prefix tree at admission
+    logprobs: Optional[tuple[dict[int, float], ...]] = None  # per output token, when the request asked for them
+    cumulative_logprob: Optional[float] = None
 
 
 class _PendingStep:
     """A launched step whose sampled ids have not been read yet."""
 
-    __slots__ = ("request_ids", "index", "host", "event")
+    __slots__ = ("request_ids", "index", "host", "event", "report", "report_host")
 
     def __init__(self, request_ids: list[str]) -> None:
         self.request_ids = request_ids
         self.index = {request_id: place for place, request_id in enumerate(request_ids)}  # row of each id in the sampled tensor
         self.host: Optional[torch.Tensor] = None
         self.event: Any = None
+        self.report: Any = None  # the sampler's LogprobReport of the step, if a row asked for one
+        self.report_host: Any = None  # (values, indices) on the host
 
 
 def build_model(config: Mapping[str, Any], *, dtype: str, device: str) -> tuple[DecoderModel, Any]:
@@ -127,6 +132,7 @@ class Engine:
         self._sampled: Optional[torch.Tensor] = None   # device ids of the step launched last
         self._host_ring: list[tuple[Optional[torch.Tensor], Any]] = [(None, None)] * 4
         self._next_host = 0
+        self._logprobs: dict[str, list[dict[int, float]]] = {}  # per request that asked: one entry per output token
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -206,6 +212,13 @@ class Engine:
             stop_reason,
             state.num_cached_tokens,
         )
+        entries = self._logprobs.pop(request_id, None)
+        if state.request.params.logprobs is not None:
+            entries = entries or []
+            chosen = [entry[token] for entry, token in zip(entries, state.outputs)]
+            self._finished[request_id] = dataclasses.replace(
+                self._finished[request_id], logprobs=tuple(entries), cumulative_logprob=float(sum(chosen))
+            )
         self._stop_checks.pop(request_id, None)
         self.scheduler.forget(request_id)
 
@@ -272,6 +285,7 @@ class Engine:
             self._sampled = torch.zeros(max(len(rows), self.config.max_num_seqs), dtype=torch.int32, device=self.device)
         out = self.sampler.sample(logits, rows, out=self._sampled[: len(rows)])
         pending = _PendingStep([row.request_id for row in rows])
+        pending.report = self.sampler.take_report()
         if str(self.device).startswith("cuda"):
             slot = self._next_host
             self._next_host = (slot + 1) % len(self._host_ring)
@@ -281,10 +295,20 @@ class Engine:
                 event = torch.cuda.Event()
                 self._host_ring[slot] = (host, event)
             host[: len(rows)].copy_(out, non_blocking=True)  # the step's one device->host read, awaited at commit
+            if pending.report is not None:  # rare: its own pinned buffers, read after the same event
+                report = pending.report
+                pending.report_host = (
+                    torch.empty(report.values.shape, dtype=torch.float32, pin_memory=True),
+                    torch.empty(report.indices.shape, dtype=torch.int32, pin_memory=True),
+                )
+                pending.report_host[0].copy_(report.values, non_blocking=True)
+                pending.report_host[1].copy_(report.indices, non_blocking=True)
             event.record()
             pending.host, pending.event = host, event
         else:
             pending.host = out.clone()
+            if pending.report is not None:
+                pending.report_host = (pending.report.values.clone(), pending.report.indices.clone())
         self._pending.append(pending)
         return True
 
@@ -296,6 +320,12 @@ class Engine:
         # request ends) reports the same faults with fewer round trips.
         self._steps_since_check += 1
         sampled = {request_id: int(token) for request_id, token in zip(pending.request_ids, token_ids)}
+        if pending.report is not None:
+            values, indices = (tensor.tolist() for tensor in pending.report_host)
+            for row, entry, _ in pending.report.entries(values, indices, token_ids):
+                request_id = pending.request_ids[row]
+                if self.scheduler.is_unfinished(request_id):  # else the token is dropped, and its report with it
+                    self._logprobs.setdefault(request_id, []).append(entry)
         alive = [request_id for request_id in sampled if request_id not in self._finished]
         finished = list(self.scheduler.update(sampled))
         if finished or self._steps_since_check >= 16:

@@ -201,6 +201,10 @@ class Scheduler:
     def state(self, request_id: str) -> RequestState:
         return self._states[request_id]
 
+    def is_unfinished(self, request_id: str) -> bool:
+        state = self._states.get(request_id)
+        return state is not None and state.status is not Status.FINISHED
+
     @property
     def prefix_hit_rate(self) -> float:
         """Prompt tokens found in the prefix tree over prompt tokens admitted

@@ -43,6 +43,7 @@ def _build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--stop", action="append", default=[])
     generate.add_argument("--stop-token-ids", default="", help="Comma-separated token ids")
     generate.add_argument("--ignore-eos", action="store_true")
+    generate.add_argument("--logprobs", type=int, default=None, help="Report each generated token's log-probability and this many of the most likely")
     generate.add_argument("--page-size", type=int, default=16)
     generate.add_argument("--num-pages", type=int, default=None)
     generate.add_argument("--max-num-batched-tokens", type=int, default=2048)
@@ -87,7 +88,7 @@ def _generate(args: argparse.Namespace) -> int:
         n=args.n, presence_penalty=args.presence_penalty, frequency_penalty=args.frequency_penalty,
         repetition_penalty=args.repetition_penalty, temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
         min_p=args.min_p, seed=args.seed, stop=args.stop or None, stop_token_ids=_ids(args.stop_token_ids) or None,
-        max_tokens=args.max_tokens, min_tokens=args.min_tokens, ignore_eos=args.ignore_eos,
+        max_tokens=args.max_tokens, min_tokens=args.min_tokens, ignore_eos=args.ignore_eos, logprobs=args.logprobs,
     )
     llm = LLM(
         str(args.model), dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
@@ -105,6 +106,14 @@ def _generate(args: argparse.Namespace) -> int:
                         {
                             "index": c.index, "token_ids": list(c.token_ids), "text": c.text,
                             "finish_reason": c.finish_reason, "stop_reason": c.stop_reason,
+                            **(
+                                {}
+                                if c.logprobs is None
+                                else {
+                                    "cumulative_logprob": c.cumulative_logprob,
+                                    "logprobs": [{str(token): value for token, value in entry.items()} for entry in c.logprobs],
+                                }
+                            ),
                         }
                         for c in output.outputs
                     ],

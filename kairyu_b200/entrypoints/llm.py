@@ -135,8 +135,8 @@ class LLM:
         batch = uuid.uuid4().hex[:12]
         submitted: list[tuple[str, list[str], tuple[int, ...], str | None, SamplingParams]] = []
         for index, (prompt, params) in enumerate(zip(prompt_list, params_list)):
-            if params.logprobs is not None or params.prompt_logprobs is not None:
-                raise ValueError("logprobs reporting is not implemented in this engine")
+            if params.prompt_logprobs is not None:
+                raise ValueError("prompt_logprobs reporting is not implemented in this engine (logprobs of generated tokens is)")
             if params.best_of is not None and params.best_of != params.n:
                 raise ValueError("best_of different from n is not implemented in this engine")
             if params.stop and self._tokenizer is None:
@@ -177,6 +177,8 @@ class LLM:
                         index=sample,
                         text=output_text,
                         token_ids=record.output_token_ids,
+                        cumulative_logprob=record.cumulative_logprob,
+                        logprobs=record.logprobs,
                         finish_reason=record.finish_reason,
                         stop_reason=record.stop_reason,
                     )

@@ -805,6 +805,40 @@ def edit_logits(
     _check(fn(logits.data_ptr(), logits.stride(0), logits.shape[1], rows.data_ptr(), tokens.data_ptr(), mul.data_ptr(), sub.data_ptr(), mask.data_ptr(), E, _stream()), "edit_logits")
 
 
+def logprob_report(
+    logits: torch.Tensor,
+    rows: torch.Tensor,
+    tokens: torch.Tensor,
+    k: int,
+    values: torch.Tensor,
+    indices: torch.Tensor,
+    *,
+    tokens_by_row: bool,
+) -> None:
+    """For report r over row ``rows[r]`` of the raw logits: ``values[r, 0]`` = log-softmax of its
+    token (``tokens[rows[r]]`` when ``tokens_by_row``, else ``tokens[r]``), ``values[r, 1 + i]`` and
+    ``indices[r, i]`` the i-th largest log-softmax value and its token id (ties: the lower id)."""
+    _need_cuda("logprob_report", logits, rows, tokens, values, indices)
+    _need_i32("logprob_report", rows, tokens, indices)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("logprob_report: logits must be fp32 with unit inner stride")
+    reports = rows.numel()
+    n, V = logits.shape
+    k = int(k)
+    if k < 0 or values.dtype != torch.float32 or not values.is_contiguous() or values.shape != (reports, k + 1):
+        raise KernelError("logprob_report: values must be contiguous fp32 [reports, k + 1]")
+    if not indices.is_contiguous() or indices.shape != (reports, k):
+        raise KernelError("logprob_report: indices must be contiguous int32 [reports, k]")
+    if tokens.numel() < (n if tokens_by_row else reports):
+        raise KernelError("logprob_report: too few tokens")
+    fn = _fn("sampling", "kb_logprob_report", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(
+        fn(logits.data_ptr(), logits.stride(0), n, V, rows.data_ptr(), tokens.data_ptr(), 1 if tokens_by_row else 0, reports, k,
+           values.data_ptr(), indices.data_ptr() if k else None, _stream()),
+        "logprob_report",
+    )
+
+
 def sample_work_floats(rows: int, vocab: int) -> int:
     """Scratch floats ``sample`` needs: the rows' probabilities and the state of its three stages."""
     fn = _fn("sampling", "kb_sample_extra_floats", [c_int])
@@ -839,6 +873,7 @@ def sample(
 
 
 __all__ = [
+    "logprob_report",
     "KernelBuildError",
     "KernelError",
     "PreNormed",

@@ -4,6 +4,12 @@ Order of operations (kairyu/engine/core/sampler.py:1-27): min-tokens mask,
 penalties, then argmax when temperature is 0, else temperature, min-p, top-k,
 top-p and a seeded Gumbel-max draw.  One kernel launch edits logits (only when
 some row needs it) and one selects tokens for all rows.
+
+Rows whose parameters ask for ``logprobs`` get a report from the *raw* logits
+(before any edit or temperature, sampler.py:5-6): the log-softmax value of the
+chosen token and the k largest with their ids.  It stays on the device until
+the caller fetches it (``take_report``), so that it can ride the same
+device-to-host read as the sampled ids.
 """
 
 from __future__ import annotations
@@ -36,10 +42,34 @@ class SamplingRow:
         return stable_request_seed(self.request_id)
 
 
+@dataclass
+class LogprobReport:
+    """Device tensors of one step's report.  ``values[r, 0]``: the chosen token's log-probability of
+    report r; ``values[r, 1 + i]`` / ``indices[r, i]``: the i-th largest and its token id."""
+
+    rows: list[int]  # which rows of the step the reports are for
+    k: list[int]  # how many of the largest each row asked for
+    values: torch.Tensor
+    indices: torch.Tensor
+
+    def entries(self, values: Sequence[Sequence[float]], indices: Sequence[Sequence[int]], token_ids: Sequence[int]):
+        """Per report (row, {token id: log-probability}, the chosen token's log-probability), from host
+        copies of the tensors: the chosen token first, then the largest that are not it
+        (kairyu/engine/engine_loop.py:219-234)."""
+        for place, (row, k) in enumerate(zip(self.rows, self.k)):
+            chosen = float(values[place][0])
+            entry = {int(token_ids[row]): chosen}
+            for i in range(k):
+                if indices[place][i] >= 0:
+                    entry.setdefault(int(indices[place][i]), float(values[place][1 + i]))
+            yield row, entry, chosen
+
+
 class Sampler:
     def __init__(self, vocab_size: int, device: str) -> None:
         self.vocab_size = vocab_size
         self.device = device
+        self._report: Optional[LogprobReport] = None
         self._work: Optional[torch.Tensor] = None
         self._is_cuda = str(device).startswith("cuda")
         self._staging: Optional[list] = None  # pinned buffers for the rows' parameters
@@ -100,6 +130,10 @@ class Sampler:
         elif out.shape != (n,) or out.dtype != torch.int32 or not out.is_contiguous():
             raise ValueError("out must be a contiguous int32 tensor with one element per row")
         edits = self._edits(rows)
+        report_rows = [index for index, row in enumerate(rows) if row.params.logprobs is not None]
+        raw = logits
+        if report_rows and edits is not None:
+            raw = logits.clone()  # the report is of the logits as the model gave them
         if edits is not None:
             e_row, e_tok, e_mul, e_sub, e_mask = edits
             kernels.edit_logits(
@@ -112,13 +146,27 @@ class Sampler:
             )
         if all(row.params.temperature == 0.0 for row in rows):
             kernels.argmax(logits, out)
-            return out
-        needed = kernels.sample_work_floats(n, self.vocab_size)
-        if self._work is None or self._work.numel() < needed:
-            self._work = torch.empty(max(needed, kernels.sample_work_floats(8, self.vocab_size)), dtype=torch.float32, device=self.device)
-        temperature, top_k, top_p, min_p, seeds = self._row_parameters(rows)
-        kernels.sample(logits, self._work, temperature, top_k, top_p, min_p, seeds, out)
+        else:
+            needed = kernels.sample_work_floats(n, self.vocab_size)
+            if self._work is None or self._work.numel() < needed:
+                self._work = torch.empty(max(needed, kernels.sample_work_floats(8, self.vocab_size)), dtype=torch.float32, device=self.device)
+            temperature, top_k, top_p, min_p, seeds = self._row_parameters(rows)
+            kernels.sample(logits, self._work, temperature, top_k, top_p, min_p, seeds, out)
+        self._report = self._make_report(raw, rows, report_rows, out) if report_rows else None
         return out
+
+    def _make_report(self, raw: torch.Tensor, rows: Sequence[SamplingRow], report_rows: list[int], out: torch.Tensor) -> LogprobReport:
+        wanted = [min(max(int(rows[index].params.logprobs), 0), self.vocab_size) for index in report_rows]
+        k = max(wanted)
+        values = torch.empty((len(report_rows), k + 1), dtype=torch.float32, device=self.device)
+        indices = torch.empty((len(report_rows), k), dtype=torch.int32, device=self.device)
+        kernels.logprob_report(raw, self._host(report_rows, torch.int32), out, k, values, indices, tokens_by_row=True)
+        return LogprobReport(report_rows, wanted, values, indices)
+
+    def take_report(self) -> Optional[LogprobReport]:
+        """The report of the last ``sample`` call (None when no row asked for one)."""
+        report, self._report = self._report, None
+        return report
 
     def _row_parameters(self, rows: Sequence[SamplingRow]) -> tuple[torch.Tensor, ...]:
         """The rows' parameters on the device: packed into one pinned buffer (a ring of four, so that

@@ -244,3 +244,16 @@ def apply_penalties(logits: torch.Tensor, prompt, outputs, *, repetition: float,
     for token, count in counts.items():
         logits[token] -= frequency * count + presence
     return logits
+
+
+def logprob_entry(raw_logits: torch.Tensor, token: int, k: int) -> tuple[dict[int, float], float]:
+    """kairyu/engine/core/sampler.py:1423-1437 and kairyu/engine/engine_loop.py:219-234: the
+    log-softmax of the raw logits; the chosen token's value first, then the k largest that are
+    not it already.  Returns the per-token dict and the chosen token's log-probability."""
+    logp = torch.log_softmax(raw_logits.to(torch.float32), dim=-1)
+    entry = {int(token): float(logp[token])}
+    if k > 0:
+        values, indices = torch.topk(logp, min(k, logp.numel()))
+        for value, index in zip(values.tolist(), indices.tolist()):
+            entry.setdefault(int(index), float(value))
+    return entry, float(logp[token])

@@ -27,8 +27,10 @@ def test_generate_flags_are_the_sampling_fields():
     parser = cli._build_parser()
     args = parser.parse_args(
         ["generate", "m", "--prompt-token-ids", "1,2,3", "--temperature", "0.8", "--top-p", "0.9", "--top-k", "5",
-         "--min-p", "0.1", "--seed", "4", "--max-tokens", "7", "--repetition-penalty", "1.1", "--ignore-eos"]
+         "--min-p", "0.1", "--seed", "4", "--max-tokens", "7", "--repetition-penalty", "1.1", "--ignore-eos",
+         "--logprobs", "4", "--enable-prefix-caching", "--pipeline-depth", "2"]
     )
+    assert args.logprobs == 4 and args.enable_prefix_caching and args.pipeline_depth == 2
     assert (args.temperature, args.top_p, args.top_k, args.min_p, args.seed, args.max_tokens) == (0.8, 0.9, 5, 0.1, 4, 7)
     assert args.ignore_eos and args.repetition_penalty == 1.1
     with pytest.raises(SystemExit):

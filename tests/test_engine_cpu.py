@@ -71,7 +71,7 @@ def test_n_completions_and_param_lists():
     with pytest.raises(ValueError):
         llm.generate("text needs a tokenizer")
     with pytest.raises(ValueError):
-        llm.generate(TokensPrompt((1,)), SamplingParams(logprobs=1))
+        llm.generate(TokensPrompt((1,)), SamplingParams(prompt_logprobs=1))
     with pytest.raises(ValueError):
         llm.generate(TokensPrompt((1,) * 10), SamplingParams(max_tokens=100000))
     # vLLM-style dict prompts
@@ -186,3 +186,40 @@ def test_pipeline_depth_two_equals_depth_one_on_random_workloads(seed):
         assert llm.engine.cache.live_requests == 0 and not llm.engine._pending
     assert results[1] == results[2]
     assert any(reason == "stop" for _, reason, _ in results[2])
+
+
+def check_logprobs(config, weights, prompt, completion, k):
+    """Every generated token's entry against the plain log-softmax of the plain model's logits."""
+    tokens = list(prompt)
+    total = 0.0
+    assert len(completion.logprobs) == len(completion.token_ids)
+    for token, entry in zip(completion.token_ids, completion.logprobs):
+        logits = plain_model.forward_logits(config, weights, tokens)[-1]
+        expected, chosen = plain_model.logprob_entry(logits, token, k)
+        assert set(entry) == set(expected) and len(entry) in (max(k, 1), k + 1)
+        assert list(entry)[0] == token  # the chosen token comes first
+        for key, value in expected.items():
+            assert entry[key] == pytest.approx(value, abs=2e-4)
+        total += chosen
+        tokens.append(token)
+    assert completion.cumulative_logprob == pytest.approx(total, abs=2e-3)
+
+
+@pytest.mark.parametrize("depth", [1, 2])
+def test_logprobs_of_generated_tokens_match_plain(depth):
+    llm, config = make_llm("qwen3", num_pages=64, max_num_batched_tokens=24, pipeline_depth=depth)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [9, 30, 4, 17], seed=140)
+    params = [
+        SamplingParams(temperature=0.0, max_tokens=6, logprobs=3),
+        SamplingParams(temperature=0.9, top_k=12, seed=5, max_tokens=5, logprobs=0),
+        SamplingParams(temperature=0.0, max_tokens=4),  # asks for none
+        # penalties edit the logits; the report is of the raw ones
+        SamplingParams(temperature=0.0, max_tokens=7, logprobs=5, repetition_penalty=1.4, presence_penalty=0.3),
+    ]
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    assert outputs[2].outputs[0].logprobs is None and outputs[2].outputs[0].cumulative_logprob is None
+    for index in (0, 1, 3):
+        check_logprobs(config, weights, prompts[index], outputs[index].outputs[0], params[index].logprobs)
+    assert list(outputs[0].outputs[0].token_ids) == plain_generate(config, weights, prompts[0], 6)
+    assert not llm.engine._logprobs

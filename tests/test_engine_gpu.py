@@ -290,3 +290,43 @@ def test_prefix_caching_gives_the_same_tokens(name, dtype, depth):
                 agree += 1
     if dtype == "bfloat16":
         assert agree / total > 0.9
+
+
+@pytest.mark.parametrize("dtype,depth", [("float32", 1), ("float32", 2), ("bfloat16", 2)])
+def test_logprobs_of_generated_tokens(dtype, depth):
+    """``logprobs=k``: per generated token the chosen token's log-probability and the k largest, from
+    the raw logits (kairyu/engine/core/sampler.py:1423-1437); compared with the plain model's
+    log-softmax (fp32), or with its bf16 bound on logits (bf16), for greedy, sampled and penalised rows."""
+    from kairyu_b200 import LLM, SamplingParams, TokensPrompt
+
+    config, seed, page_size = TINY["wide"]
+    llm = LLM.from_random(config, seed=seed, dtype=dtype, page_size=page_size, num_pages=64, max_num_batched_tokens=24, pipeline_depth=depth)
+    weights = engine_weights(llm)
+    prompts = prompts_of(config, [9, 30, 4, 17], seed=140)
+    params = [
+        SamplingParams(temperature=0.0, max_tokens=6, logprobs=3),
+        SamplingParams(temperature=0.9, top_k=12, seed=5, max_tokens=5, logprobs=0),
+        SamplingParams(temperature=0.0, max_tokens=4),
+        SamplingParams(temperature=0.0, max_tokens=7, logprobs=5, repetition_penalty=1.4, presence_penalty=0.3),
+    ]
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    assert outputs[2].outputs[0].logprobs is None and outputs[2].outputs[0].cumulative_logprob is None
+    tolerance = 2e-4 if dtype == "float32" else 5e-2
+    for index in (0, 1, 3):
+        completion, k = outputs[index].outputs[0], params[index].logprobs
+        tokens = list(prompts[index])
+        total = 0.0
+        assert len(completion.logprobs) == len(completion.token_ids)
+        for token, entry in zip(completion.token_ids, completion.logprobs):
+            logits = plain_model.forward_logits(config, weights, tokens)[-1]
+            expected, chosen = plain_model.logprob_entry(logits, token, k)
+            assert list(entry)[0] == token and len(entry) in (max(k, 1), k + 1)
+            assert abs(entry[token] - chosen) < tolerance
+            if dtype == "float32":
+                assert set(entry) == set(expected)
+            logp = torch.log_softmax(logits.float(), dim=-1)
+            for key, value in entry.items():
+                assert abs(value - float(logp[key])) < tolerance
+            total += entry[token]
+            tokens.append(token)
+        assert completion.cumulative_logprob == pytest.approx(total, abs=1e-4)

@@ -623,6 +623,45 @@ def test_edit_logits():
     close(dev, expected, 1e-6)
 
 
+@pytest.mark.parametrize("n,V,k", [(3, 331, 5), (6, 128256, 20), (2, 1000, 0), (1, 7, 12)])
+def test_logprob_report(n, V, k):
+    """Log-softmax of the chosen token and the k largest, against torch.log_softmax / topk in fp32;
+    ties go to the lower index; more asked for than the vocabulary holds marks the rest absent."""
+    logits = rand(n, V, seed=44) * 4.0
+    if V > 300:
+        logits[0, 7] = logits[0, 300] = 30.0  # a tie at the top
+        logits[n - 1, V - 1] = 25.0
+    rows = list(range(n - 1, -1, -1))[: max(1, n - 1)]  # another order than the rows', and not all of them
+    tokens = torch.randint(0, V, (n,), generator=torch.Generator().manual_seed(45), dtype=torch.int32)
+    values = torch.full((len(rows), k + 1), float("nan"), device=DEV)
+    indices = torch.full((len(rows), k), -7, dtype=torch.int32, device=DEV)
+    kernels().logprob_report(
+        logits.to(DEV), torch.tensor(rows, dtype=torch.int32, device=DEV), tokens.to(DEV), k, values, indices, tokens_by_row=True
+    )
+    values, indices = values.cpu(), indices.cpu()
+    logp = torch.log_softmax(logits.double(), dim=-1)
+    have = min(k, V)
+    for place, row in enumerate(rows):
+        assert abs(float(values[place, 0]) - float(logp[row, tokens[row]])) < 2e-5
+        top_values, top_indices = torch.topk(logp[row], have)
+        assert torch.allclose(values[place, 1 : 1 + have].double(), top_values, atol=2e-5, rtol=0)
+        picked = indices[place, :have].tolist()
+        assert len(set(picked)) == have
+        assert torch.allclose(logp[row, picked], top_values, atol=1e-12, rtol=0)  # the same values, whatever the tie order
+        assert all(i == -1 for i in indices[place, have:].tolist())
+        assert all(math.isinf(v) and v < 0 for v in values[place, 1 + have :].tolist())
+    if V > 300 and 0 in rows:
+        assert indices[rows.index(0), :2].tolist() == [7, 300]
+    # tokens given per report instead of per row
+    per_report = torch.tensor([int(tokens[row]) for row in rows], dtype=torch.int32, device=DEV)
+    again = torch.empty((len(rows), 1), device=DEV)
+    kernels().logprob_report(
+        logits.to(DEV), torch.tensor(rows, dtype=torch.int32, device=DEV), per_report, 0, again,
+        torch.empty((len(rows), 0), dtype=torch.int32, device=DEV), tokens_by_row=False,
+    )
+    assert torch.equal(again.cpu()[:, 0], values[:, 0])
+
+
 def _sample_both(logits, temperature, top_k, top_p, min_p, seeds):
     n, V = logits.shape
     t = lambda values, dtype: torch.tensor(values, dtype=dtype)

@@ -206,10 +206,27 @@ def sample(logits, work, temperature, top_k, top_p, min_p, seeds, out):
         out[r] = int(torch.argmax(torch.log(probs).to(torch.float64) + noise))
 
 
+def logprob_report(logits, rows, tokens, k, values, indices, *, tokens_by_row):
+    for r in range(rows.numel()):
+        row = int(rows[r])
+        logp = torch.log_softmax(logits[row].to(torch.float32), dim=-1)
+        token = int(tokens[row] if tokens_by_row else tokens[r])
+        values[r, 0] = logp[token]
+        if k:
+            # largest first, ties by the lower index: sort on (-value, index)
+            order = sorted(range(logp.numel()), key=lambda i: (-float(logp[i]), i))[:k]
+            for place, index in enumerate(order):
+                values[r, 1 + place] = logp[index]
+                indices[r, place] = index
+            for place in range(len(order), k):
+                values[r, 1 + place] = float("-inf")
+                indices[r, place] = -1
+
+
 _NAMES = [
     "embedding", "patch_tokens", "fused_norm_available", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
     "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
-    "edit_logits", "sample", "sample_work_floats",
+    "edit_logits", "sample", "sample_work_floats", "logprob_report",
 ]
 
 
