@@ -495,7 +495,7 @@ def _decode_tma_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> bool:
 def _cache_map(cache: torch.Tensor) -> int:
     """Host address of a cached TMA descriptor of one layer's key (or value) pages."""
     key = ("cache", cache.data_ptr(), tuple(cache.shape), tuple(cache.stride()))
-    held = _tensor_maps.get(key)
+    held = _held_map(key)
     if held is None:
         held = ctypes.create_string_buffer(128 + 64)
         address = (ctypes.addressof(held) + 63) & ~63
@@ -505,9 +505,7 @@ def _cache_map(cache: torch.Tensor) -> int:
         code = fn(address, cache.data_ptr(), num_pages, page_size, num_kv_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2))
         if code != 0:
             raise KernelError(f"tensor map encoding of the cache failed with code {code}")
-        if len(_tensor_maps) > 4096:
-            _tensor_maps.clear()
-        _tensor_maps[key] = held
+        _keep_map(key, held)
     return (ctypes.addressof(held) + 63) & ~63
 
 
@@ -676,14 +674,39 @@ def fused_norm_shapes_ok(rows: int, *feature_sizes: int) -> bool:
 
 
 TC5_MAX_ROWS = 64  # token rows the tcgen05 weight-streaming product takes (csrc/gemm_tc5.cu)
+# Encoded TMA descriptors by what they describe.  A caller takes the host addresses of several of
+# them before it launches, so none may be freed while a call is being put together: when the table
+# is full it is set aside whole (and only dropped when the next one is full, thousands of
+# descriptors later) instead of being cleared.
+_TENSOR_MAP_LIMIT = 4096
 _tensor_maps: dict[tuple, ctypes.Array] = {}
+_tensor_maps_before: dict[tuple, ctypes.Array] = {}
+
+
+def _keep_map(key: tuple, held: ctypes.Array) -> None:
+    global _tensor_maps, _tensor_maps_before
+    if len(_tensor_maps) >= _TENSOR_MAP_LIMIT:
+        _tensor_maps_before = _tensor_maps
+        _tensor_maps = {}
+    _tensor_maps[key] = held
+
+
+def _held_map(key: tuple) -> Optional[ctypes.Array]:
+    held = _tensor_maps.get(key)
+    if held is None:
+        held = _tensor_maps_before.get(key)
+        if held is not None:
+            _keep_map(key, held)  # in use again: it moves to the current table
+    return held
+
+
 _tc5_scratch: list[torch.Tensor] = []  # old buffers stay alive: captured graphs may still point at them
 
 
 def _tensor_map(tensor: torch.Tensor, box_rows: int) -> int:
     """Host address of a cached TMA descriptor of a row-major bf16 matrix (boxes of [box_rows, 64])."""
     key = (tensor.data_ptr(), tensor.shape[0], tensor.shape[1], tensor.stride(0), box_rows)
-    held = _tensor_maps.get(key)
+    held = _held_map(key)
     if held is None:
         held = ctypes.create_string_buffer(128 + 64)
         address = (ctypes.addressof(held) + 63) & ~63
@@ -691,9 +714,7 @@ def _tensor_map(tensor: torch.Tensor, box_rows: int) -> int:
         code = fn(address, tensor.data_ptr(), tensor.shape[0], tensor.shape[1], tensor.stride(0), box_rows)
         if code != 0:
             raise KernelError(f"tensor map encoding failed with code {code}")
-        if len(_tensor_maps) > 4096:
-            _tensor_maps.clear()
-        _tensor_maps[key] = held
+        _keep_map(key, held)
     return (ctypes.addressof(held) + 63) & ~63
 
 

@@ -149,6 +149,26 @@ def test_linear_bf16(M, N, K):
     close(out32, expected, 1e-4 * math.sqrt(K / 64), rtol=1e-4)
 
 
+def test_products_stay_right_while_the_descriptor_table_turns_over(monkeypatch):
+    """The tcgen05 product takes two encoded TMA descriptors per call from a bounded table.  With the
+    table's limit at 4 every few calls turn it over; the descriptors of a call in progress must
+    stay alive through that (they were once freed by a clear between the two look-ups)."""
+    import kairyu_b200.kernels as module
+
+    monkeypatch.setattr(module, "_TENSOR_MAP_LIMIT", 4)
+    monkeypatch.setattr(module, "_tensor_maps", {})
+    monkeypatch.setattr(module, "_tensor_maps_before", {})
+    weights = [rand(N, K, dtype=torch.bfloat16, seed=60 + i, scale=0.05).to(DEV) for i, (N, K) in enumerate([(96, 64), (384, 96), (200, 160)])]
+    for round_ in range(6):
+        for w in weights:
+            for M in (17, 33, 64, 40):
+                x = rand(M, w.shape[1], dtype=torch.bfloat16, seed=70 + M + round_).to(DEV)
+                out = torch.empty(M, w.shape[0], dtype=torch.float32, device=DEV)
+                kernels().linear(x, w, None, out)
+                close(out, x.float() @ w.float().t(), 1e-4 * math.sqrt(w.shape[1] / 64), rtol=1e-4)
+    assert len(module._tensor_maps) <= 4
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(331, 144), (96, 64), (6144, 4096), (40, 16), (4096, 14336), (331, 120)])
 @pytest.mark.parametrize("bias", [False, True])

@@ -141,3 +141,35 @@ def test_table_check_catches_a_page_named_twice(monkeypatch):
     runner.cache.get("b").tables[0][0] = runner.cache.get("a").tables[0][1]  # corrupt: b now names a page of a
     with pytest.raises(StepError, match="is named by"):
         runner.step([StepEntry("a", [1], (0,)), StepEntry("b", [2], (0,))])
+
+
+def test_descriptor_table_never_frees_what_a_call_may_still_point_at(monkeypatch):
+    """A kernel call takes the host addresses of up to three encoded descriptors before it launches.
+    When the table of descriptors is full it is set aside, not cleared: the last `limit` descriptors
+    handed out stay referenced, whatever the order of insertions and repeated uses."""
+    import ctypes
+    import random
+    import weakref
+
+    import kairyu_b200.kernels as kernels
+
+    class Buffer:  # stands for a ctypes buffer; weakly referencable
+        pass
+
+    monkeypatch.setattr(kernels, "_TENSOR_MAP_LIMIT", 4)
+    monkeypatch.setattr(kernels, "_tensor_maps", {})
+    monkeypatch.setattr(kernels, "_tensor_maps_before", {})
+    rng = random.Random(0)
+    recent: list = []  # weak references to the last three descriptors handed out
+    for step in range(500):
+        key = ("k", rng.randrange(12))
+        held = kernels._held_map(key)
+        if held is None:
+            held = Buffer()
+            kernels._keep_map(key, held)
+        recent.append(weakref.ref(held))
+        del held
+        recent = recent[-3:]
+        assert all(ref() is not None for ref in recent), step
+    assert len(kernels._tensor_maps) <= 4 and len(kernels._tensor_maps_before) <= 4
+    del ctypes
