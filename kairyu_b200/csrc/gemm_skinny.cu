@@ -279,14 +279,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 }
 
 // rows per block and whether three blocks go on an SM, for (rows of output, token tiles, gated)
-static void skinny_grid(int rows_out, bool single_tile_plain, int& rows_per_block, bool& three) {
+static void skinny_grid(int rows_out, bool single_tile_plain, bool gated, int& rows_per_block, bool& three) {
     static int sms = 0;
     if (sms == 0) {
         int device = 0;
         if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
     }
     // Grid: one wave that fills every SM evenly where the rows allow it (rows per block between
-    // 8 and 16, two blocks per SM); else 16-row blocks, three to an SM.
+    // 8 and 16, two blocks per SM); else 16-row blocks, three to an SM, for the plain single-tile
+    // product; the others (gated, two token tiles) run two blocks per SM, the gated one with the
+    // rows per block that fill its last wave best.
     rows_per_block = 16;
     three = false;
     if (single_tile_plain) {
@@ -295,6 +297,21 @@ static void skinny_grid(int rows_out, bool single_tile_plain, int& rows_per_bloc
             rows_per_block = fit2 < 8 ? 8 : fit2;
         else
             three = true;
+    } else if (gated && rows_out > 2 * sms * 16) {
+        // Several waves of two blocks per SM: the last wave should be nearly full.  Cost of a
+        // choice = whole waves x rows per block (a wave's time goes with the rows its blocks
+        // stream); between 12 and 16 rows the fixed cost of a block does not change the order.
+        // (Llama-3.1-8B gate/up, 14,336 rows: 13 rows, 3.73 waves; measured 0.8 % of the decode
+        // step faster than 16 rows and 3.03 waves.)
+        long best = -1;
+        for (int rows = 16; rows >= 12; --rows) {
+            const long blocks = (rows_out + rows - 1) / rows;
+            const long waves = (blocks + 2 * sms - 1) / (2 * sms);
+            if (best < 0 || waves * rows < best) {
+                best = waves * rows;
+                rows_per_block = rows;
+            }
+        }
     }
 }
 
@@ -305,7 +322,7 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
     const int rows_out = GATED ? N / 2 : N;
     int rows_per_block;
     bool three;
-    skinny_grid(rows_out, !GATED && NT == 1, rows_per_block, three);
+    skinny_grid(rows_out, !GATED && NT == 1, GATED, rows_per_block, three);
     const int blocks = (rows_out + rows_per_block - 1) / rows_per_block;
     const bool fused = fusion.in_sumsq != nullptr || fusion.residual != nullptr;
 #define GO(TO_, MINB_, F_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_, F_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K, rows_per_block, fusion)
@@ -351,7 +368,7 @@ KB_EXPORT int kb_gemm_skinny_blocks(int M, int N, int gated) {
     const int rows_out = gated ? N / 2 : N;
     int rows_per_block;
     bool three;
-    skinny_grid(rows_out, !gated && M <= 8, rows_per_block, three);
+    skinny_grid(rows_out, !gated && M <= 8, gated != 0, rows_per_block, three);
     return (rows_out + rows_per_block - 1) / rows_per_block;
 }
 
