@@ -30,10 +30,11 @@ then running prefills, then admissions from the head of the queue.
 
 When pages run out:
 
-* at admission, the head waits (no skip-ahead) until the pages its whole
-  prompt needs are free; a prompt that could never fit, even in an empty
-  cache, is rejected: finished, reason ``"length"``, no output
-  (scheduler.py:1007-1019, 1479-1490);
+* at admission, the head waits until the pages its whole prompt needs are
+  free; while it waits and something runs, the one request right behind it may
+  be admitted in its place, once per head (scheduler.py:28, 1543-1577); a
+  prompt that could never fit, even in an empty cache, is rejected: finished,
+  reason ``"length"``, no output (scheduler.py:1007-1019, 1479-1490);
 * for a decode, the youngest running request that has no outputs yet is
   recompute-preempted (scheduler.py:1065-1110); if there is none, the youngest
   other running request is, outputs included (the reference raises here); the
@@ -71,6 +72,9 @@ class EngineRequest:
     params: SamplingParams = field(default_factory=lambda: SamplingParams(temperature=0.0))
 
 
+MAX_WAITING_BYPASSES = 1  # kairyu/engine/core/scheduler.py:28
+
+
 class Status(Enum):
     WAITING = "waiting"
     RUNNING = "running"
@@ -80,7 +84,7 @@ class Status(Enum):
 class RequestState:
     __slots__ = (
         "request", "status", "computed", "outputs", "in_flight", "finish_reason", "preemptions", "arrival",
-        "num_cached_tokens",
+        "num_cached_tokens", "bypasses",
     )
 
     def __init__(self, request: EngineRequest, arrival: int) -> None:
@@ -93,6 +97,7 @@ class RequestState:
         self.preemptions = 0
         self.arrival = arrival
         self.num_cached_tokens = 0  # tokens its first admission found in the prefix tree
+        self.bypasses = 0  # times the request behind it was admitted while it waited for pages
 
     @property
     def total_tokens(self) -> int:
@@ -274,6 +279,38 @@ class Scheduler:
             cap = min(cap, self.prefill_chunk_size)
         return cap
 
+    def _admit(self, request_id: str, budget: int, plan: list, taken: set) -> Optional[int]:
+        """Make a waiting request run if the pages its whole work needs are to be had: its first
+        portion goes into ``plan``.  Returns the tokens it took from the budget, or None, with
+        nothing changed, when it has to wait.  The caller takes it off the queue."""
+        state = self._states[request_id]
+        try:
+            record = self.cache.admit(request_id, state.all_tokens())
+        except OutOfPages:
+            return None
+        needed = self.cache.pages_needed(request_id, state.total_tokens, record.num_tokens)
+        if any(count > self.cache.available_pages(group) for group, count in enumerate(needed)):
+            self.cache.release(request_id)
+            return None
+        state.computed = record.num_tokens  # the pages the prefix tree already holds
+        count = min(state.remaining, budget, self._chunk_cap(budget, 1))
+        if not self._grow(state, count):
+            state.computed = 0
+            self.cache.release(request_id)
+            return None
+        if state.preemptions == 0:
+            state.num_cached_tokens = record.num_cached_tokens
+            self.counters["prompt_tokens"] += state.total_tokens
+            self.counters["cached_prompt_tokens"] += record.num_cached_tokens
+        state.status = Status.RUNNING
+        self._running.append(request_id)
+        completes = count == state.remaining
+        plan.append(ScheduledChunk(request_id, state.computed, count, count > 1 or not completes, completes))
+        state.computed += count
+        state.in_flight += 1 if completes else 0
+        taken.add(request_id)
+        return count
+
     # ------------------------------------------------------------------ one plan
     def schedule(self) -> SchedulerOutput:
         self.counters["steps"] += 1
@@ -365,33 +402,24 @@ class Scheduler:
                 self.counters["rejections"] += 1
                 rejected.append(head)
                 continue
-            try:
-                record = self.cache.admit(head, state.all_tokens())
-            except OutOfPages:
+            used = self._admit(head, budget, plan, taken)
+            if used is not None:
+                self._waiting.popleft()
+                budget -= used
+                continue
+            # The head waits for pages.  While something runs (and will free pages), the request
+            # right behind it may go first, once per head (scheduler.py:28, 1543-1577).
+            if not self._running or state.bypasses >= MAX_WAITING_BYPASSES or len(self._waiting) < 2:
                 break
-            needed = self.cache.pages_needed(head, state.total_tokens, record.num_tokens)
-            if any(count > self.cache.available_pages(group) for group, count in enumerate(needed)):
-                self.cache.release(head)
-                break  # the head waits for pages
-            state.computed = record.num_tokens  # the pages the prefix tree already holds
-            count = min(state.remaining, budget, self._chunk_cap(budget, 1))
-            if not self._grow(state, count):
-                state.computed = 0
-                self.cache.release(head)
+            successor = self._waiting[1]
+            if not self.cache.can_hold(self._states[successor].total_tokens):
                 break
-            if state.preemptions == 0:
-                state.num_cached_tokens = record.num_cached_tokens
-                self.counters["prompt_tokens"] += state.total_tokens
-                self.counters["cached_prompt_tokens"] += record.num_cached_tokens
-            self._waiting.popleft()
-            state.status = Status.RUNNING
-            self._running.append(head)
-            completes = count == state.remaining
-            plan.append(ScheduledChunk(head, state.computed, count, count > 1 or not completes, completes))
-            state.computed += count
-            state.in_flight += 1 if completes else 0
-            taken.add(head)
-            budget -= count
+            used = self._admit(successor, budget, plan, taken)
+            if used is None:
+                break
+            state.bypasses += 1
+            del self._waiting[1]
+            budget -= used
         return plan, preempted, rejected
 
     # ------------------------------------------------------------------ results

@@ -247,3 +247,36 @@ def test_tokens_that_arrive_after_a_stop_are_dropped_and_in_flight_requests_are_
     assert scheduler._pick_victim("b", set()) is None and scheduler.state("c").in_flight == 1
     scheduler.update({"b": 1, "c": 2})
     assert scheduler._pick_victim("b", set()) == "c"
+
+
+def test_the_request_behind_a_blocked_head_goes_first_once():
+    """kairyu/engine/core/scheduler.py:28, 1543-1577: while the head waits for pages and something
+    runs, its direct successor may be admitted, once; a second successor waits behind the head."""
+    scheduler, cache = make(num_pages=9, page_size=4, max_num_batched_tokens=64)  # 8 pages
+    scheduler.add_request(request("running", 10, max_new=8))   # 5 pages by its end
+    run_step(scheduler, cache)
+    scheduler.add_request(request("big", 24, max_new=2))       # 7 pages: must wait for "running"
+    scheduler.add_request(request("small", 5, max_new=2))      # 2 pages: fits beside "running"
+    scheduler.add_request(request("small2", 5, max_new=2))
+    plan, _ = run_step(scheduler, cache)
+    assert [c.request_id for c in plan.scheduled] == ["running", "small"]
+    assert scheduler.state("big").bypasses == 1 and scheduler.state("big").status is Status.WAITING
+    plan, _ = run_step(scheduler, cache)
+    # the head has been passed once: small2 stays behind it although it would fit
+    assert sorted(c.request_id for c in plan.scheduled) == ["running", "small"]
+    assert scheduler.num_waiting == 2
+    for _ in range(40):
+        if not scheduler.has_unfinished():
+            break
+        run_step(scheduler, cache)
+    assert not scheduler.has_unfinished()
+    for name, count in (("running", 8), ("big", 2), ("small", 2), ("small2", 2)):
+        assert len(scheduler.output_tokens(name)) == count
+
+
+def test_nothing_passes_a_blocked_head_when_nothing_runs():
+    scheduler, cache = make(num_pages=5, page_size=4, max_num_batched_tokens=64)  # 4 pages
+    scheduler.add_request(request("too-big", 30))   # 8 pages: can never fit
+    scheduler.add_request(request("fits", 6, max_new=2))
+    plan, _ = run_step(scheduler, cache)
+    assert plan.rejected == ("too-big",) and [c.request_id for c in plan.scheduled] == ["fits"]
