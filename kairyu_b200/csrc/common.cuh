@@ -54,6 +54,7 @@ static inline void kb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 #define KB_FLAG_BAD_PAGE 1
 #define KB_FLAG_BAD_TOKEN 2
 #define KB_FLAG_BAD_ROW 4
+#define KB_FLAG_BAD_POS 8
 
 template <typename T>
 __device__ __forceinline__ float to_float(T v);

@@ -56,6 +56,24 @@ struct SkinnyFusion {
     __nv_bfloat16* values;
     int ldv;
     float* out_sumsq;
+    // rope: the product is q | k | v of attention (heads of D columns: Hq, then Hkv, then Hkv).  The
+    // epilogue rotates q and k by the token's position (rotate-half over the whole head,
+    // kairyu/models/layers.py:129-148), writes q to out and k and v into their cache pages
+    // (kairyu/engine/core/kv_pool.py:171-348).  A block then owns columns j..j+7 and D/2+j..D/2+j+7
+    // of one head, so that both elements of a rotated pair meet in one warp.
+    const float* rope_cos;  // [max_pos, D/2] fp32; null: no rope work
+    const float* rope_sin;
+    int rope_max_pos;
+    int Hq, Hkv, D;
+    const int* positions;    // [M]
+    const int* row_ids;      // [M]
+    const int* block_table;  // [rows, max_pages]
+    int max_pages;
+    const int* write_from;   // [rows]
+    __nv_bfloat16* k_cache;  // [num_pages, page_size, Hkv, D]
+    __nv_bfloat16* v_cache;
+    int page_size, num_pages;
+    int* flag;
 };
 
 // streaming 32-byte load of weights (sm_100 has 256-bit loads): read once, keep out of L1
@@ -108,6 +126,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     // A block owns rows_per_block (<= 16) weight rows: fewer than 16 leaves rows of the MMA tile
     // idle, which costs nothing here, and lets the host pick a grid that fills every SM evenly.
     const int n0 = blockIdx.x * rows_per_block;  // first weight row (and output column) of the block
+    // Weight row (= output column) of the block's local row r.  With rope work the 16 rows are two
+    // runs of 8, half a head apart.
+    const bool roped = FUSED && fusion.rope_cos != nullptr;
+    const int rope_half = roped ? fusion.D >> 1 : 0;
+    int rope_base = 0;
+    if (roped) {
+        const int per_head = rope_half >> 3;  // blocks a head
+        rope_base = (blockIdx.x / per_head) * fusion.D + (blockIdx.x % per_head) * 8;
+    }
+    auto column_of = [&](int r) { return roped ? rope_base + (r & 7) + ((r & 8) ? rope_half : 0) : n0 + r; };
 
     // K is cut into SK_STEP-wide steps; warp kwarp takes steps kwarp, kwarp + KWARPS, ...
     const int steps = (K + SK_STEP - 1) / SK_STEP;
@@ -115,8 +143,8 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
 
-    const int row_lo = n0 + g;
-    const int row_hi = n0 + g + 8;
+    const int row_lo = column_of(g);
+    const int row_hi = column_of(g + 8);
     const bool lo_ok = g < rows_per_block && row_lo < rows_out;
     const bool hi_ok = g + 8 < rows_per_block && row_hi < rows_out;
     const __nv_bfloat16* w_lo = w + (size_t)(half * rows_out + (lo_ok ? row_lo : 0)) * ldw;
@@ -176,6 +204,48 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     // The weights do not depend on the kernel before this one: their first loads go out
     // before the wait, the tokens (that kernel's output) after it.
     load_weights(0, step0);
+    // rope: what this thread's (token, row) needs of the token's position, used in the epilogue: cos and
+    // sin for q and k, the slot in the cache for k and v.  Positions, row ids and block tables are
+    // written by the step's copy from the host and the tables never change, so these dependent loads
+    // need not wait for the kernel before this one: they run while the first weights are on their way.
+    // (kept in shared memory, each thread its own words: registers are short in the main loop)
+    __shared__ float rope_c[FUSED ? NT * 8 * 16 : 1], rope_s[FUSED ? NT * 8 * 16 : 1];
+    __shared__ long long rope_slot[FUSED ? NT * 8 * 16 : 1];
+    if (roped && threadIdx.x < NT * 8 * 16) {
+        float held_cos = 1.0f, held_sin = 0.0f;
+        long long held_slot = -1;
+        const int r = threadIdx.x & 15;
+        const int token = threadIdx.x >> 4;
+        if (token < M) {
+            const int column = column_of(r);
+            const int head = column / fusion.D;
+            const int pos = fusion.positions[token];
+            if (pos < 0 || pos >= fusion.rope_max_pos) {
+                if (fusion.flag) atomicOr(fusion.flag, KB_FLAG_BAD_POS);  // left unrotated and unwritten
+            } else {
+                if (head < fusion.Hq + fusion.Hkv) {
+                    const int i = column - head * fusion.D - ((r & 8) ? rope_half : 0);
+                    held_cos = fusion.rope_cos[(size_t)pos * rope_half + i];
+                    held_sin = fusion.rope_sin[(size_t)pos * rope_half + i];
+                }
+                if (head >= fusion.Hq && fusion.k_cache != nullptr) {
+                    const int row = fusion.row_ids[token];
+                    if (pos >= fusion.write_from[row]) {
+                        const int page_index = pos / fusion.page_size;
+                        const int page = page_index < fusion.max_pages ? fusion.block_table[(size_t)row * fusion.max_pages + page_index] : -1;
+                        if (page < 0 || page >= fusion.num_pages) {
+                            if (fusion.flag) atomicOr(fusion.flag, KB_FLAG_BAD_PAGE);
+                        } else {
+                            held_slot = (long long)page * fusion.page_size + (pos - page_index * fusion.page_size);
+                        }
+                    }
+                }
+            }
+        }
+        rope_c[threadIdx.x] = held_cos;
+        rope_s[threadIdx.x] = held_sin;
+        rope_slot[threadIdx.x] = held_slot;
+    }
     pdl_wait();
     load_tokens(0, step0);
     // scale: thread (chunk, token) adds every 16th block's partial sum of its token's row; the
@@ -197,7 +267,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     if (FUSED && fusion.residual != nullptr && threadIdx.x < NT * 8 * 16) {
         const int r = threadIdx.x & 15;
         const int token = threadIdx.x >> 4;
-        const int n = n0 + r;
+        const int n = column_of(r);
         if (token < M && r < rows_per_block && n < rows_out) {
             held_residual = fusion.residual[(size_t)token * fusion.ldr + n];
             held_weight = fusion.norm_w_bf16 ? __bfloat162float(((const __nv_bfloat16*)fusion.norm_w)[n]) : ((const float*)fusion.norm_w)[n];
@@ -240,7 +310,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
         const int token = idx >> 4;
         const int t = token >> 3;
         const int col = token & 7;
-        const int n = n0 + r;
+        const int n = column_of(r);
         const bool valid = token < M && r < rows_per_block && n < rows_out;
         float result = 0.0f;
         if (valid) {
@@ -256,6 +326,29 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
             }
             result = value[0];
             if (GATED) result = value[0] / (1.0f + expf(-value[0])) * value[HALVES - 1];
+        }
+        if (roped) {
+            // the other element of the rotated pair is eight rows on, in the same warp;
+            // rotate_half(u) = cat(-u[half:], u[:half])
+            const float partner = __shfl_xor_sync(0xffffffffu, result, 8);
+            const float held_cos = rope_c[idx], held_sin = rope_s[idx];  // idx == threadIdx.x: the loop runs once
+            const long long held_slot = rope_slot[idx];
+            const int head = n / fusion.D;
+            float rotated = result;
+            if (head < fusion.Hq + fusion.Hkv)
+                rotated = (r & 8) ? result * held_cos + partner * held_sin : result * held_cos - partner * held_sin;
+            if (valid) {
+                const __nv_bfloat16 rounded = __float2bfloat16_rn(rotated);
+                if (head < fusion.Hq) {
+                    reinterpret_cast<__nv_bfloat16*>(out)[(size_t)token * ldo + n] = rounded;
+                } else if (held_slot >= 0) {
+                    const bool is_k = head < fusion.Hq + fusion.Hkv;
+                    const int kvh = head - fusion.Hq - (is_k ? 0 : fusion.Hkv);
+                    __nv_bfloat16* cache = is_k ? fusion.k_cache : fusion.v_cache;
+                    cache[((size_t)held_slot * fusion.Hkv + kvh) * fusion.D + (n - head * fusion.D)] = rounded;
+                }
+            }
+            continue;
         }
         if (!FUSED || fusion.residual == nullptr) {
             if (valid) out[(size_t)token * ldo + n] = from_float<TO>(result);
@@ -323,8 +416,9 @@ static int launch_skinny(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w
     int rows_per_block;
     bool three;
     skinny_grid(rows_out, !GATED && NT == 1, GATED, rows_per_block, three);
+    if (fusion.rope_cos != nullptr) rows_per_block = 16;  // two runs of eight columns, half a head apart
     const int blocks = (rows_out + rows_per_block - 1) / rows_per_block;
-    const bool fused = fusion.in_sumsq != nullptr || fusion.residual != nullptr;
+    const bool fused = fusion.in_sumsq != nullptr || fusion.residual != nullptr || fusion.rope_cos != nullptr;
 #define GO(TO_, MINB_, F_) kb_launch(gemm_skinny_kernel<NT, GATED, TO_, MINB_, F_>, dim3(blocks), dim3(SK_THREADS), 0, stream, x, ldx, w, ldw, bias, (TO_*)out, ldo, M, N, K, rows_per_block, fusion)
 #define PICK(TO_) do { if (three) { if (fused) GO(TO_, 3, true); else GO(TO_, 3, false); } else { if (fused) GO(TO_, 2, true); else GO(TO_, 2, false); } } while (0)
     if (out_fp32) PICK(float); else PICK(__nv_bfloat16);
@@ -345,6 +439,11 @@ static int skinny_entry(const void* x, int ldx, const void* w, int ldw, const vo
     if (gated && N % 2 != 0) return KB_ERR_BAD_ARG;
     if (fusion.residual && (gated || !fusion.norm_w || !fusion.values || !fusion.out_sumsq)) return KB_ERR_BAD_ARG;
     if (fusion.in_sumsq && (fusion.in_blocks < 1 || fusion.in_blocks > SK_SUM_BLOCKS)) return KB_ERR_BAD_ARG;
+    if (fusion.rope_cos) {
+        if (gated || fusion.residual || out_fp32 || !out || !fusion.rope_sin || !fusion.positions) return KB_ERR_BAD_ARG;
+        if (fusion.D < 16 || fusion.D % 16 != 0 || fusion.Hq < 1 || fusion.Hkv < 1 || N != (fusion.Hq + 2 * fusion.Hkv) * fusion.D) return KB_ERR_UNSUPPORTED_SIZE;
+        if (fusion.k_cache && (!fusion.v_cache || !fusion.row_ids || !fusion.block_table || !fusion.write_from || fusion.page_size < 1)) return KB_ERR_BAD_ARG;
+    }
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
     const __nv_bfloat16* bb = (const __nv_bfloat16*)bias;
@@ -394,4 +493,40 @@ KB_EXPORT int kb_gemm_skinny_fused(const void* x, int ldx, const void* w, int ld
     fusion.ldv = ldv;
     fusion.out_sumsq = out_sumsq;
     return skinny_entry(x, ldx, w, ldw, bias, out, out_fp32, ldo, M, N, K, gated, fusion, stream);
+}
+
+// The q | k | v product of attention with the position encoding and the cache write in its epilogue
+// (SkinnyFusion: rope).  in_sumsq (or null) as in kb_gemm_skinny_fused.  cos, sin: [max_pos, D/2] fp32
+// (rotation over the whole head).  out: [M, N] bf16, of which the q columns are written; k and v go to
+// the caches ([num_pages, page_size, Hkv, D] bf16; null: not written) at the slots the tokens'
+// positions name in their rows' block tables.  Bad positions and pages set `flag` and are skipped.
+KB_EXPORT int kb_gemm_skinny_rope(const void* x, int ldx, const void* w, int ldw, const void* bias, void* out, int ldo,
+                                  int M, int N, int K, const float* in_sumsq, int in_blocks, int in_hidden, float in_eps,
+                                  const float* cos_table, const float* sin_table, int max_pos, int Hq, int Hkv, int D,
+                                  const int* positions, const int* row_ids, const int* block_table, int max_pages,
+                                  const int* write_from, void* k_cache, void* v_cache, int page_size, int num_pages,
+                                  int* flag, cudaStream_t stream) {
+    SkinnyFusion fusion = {};
+    fusion.in_sumsq = in_sumsq;
+    fusion.in_blocks = in_blocks;
+    fusion.in_inv_hidden = in_hidden > 0 ? 1.0f / (float)in_hidden : 0.0f;
+    fusion.in_eps = in_eps;
+    fusion.rope_cos = cos_table;
+    fusion.rope_sin = sin_table;
+    fusion.rope_max_pos = max_pos;
+    fusion.Hq = Hq;
+    fusion.Hkv = Hkv;
+    fusion.D = D;
+    fusion.positions = positions;
+    fusion.row_ids = row_ids;
+    fusion.block_table = block_table;
+    fusion.max_pages = max_pages;
+    fusion.write_from = write_from;
+    fusion.k_cache = (__nv_bfloat16*)k_cache;
+    fusion.v_cache = (__nv_bfloat16*)v_cache;
+    fusion.page_size = page_size;
+    fusion.num_pages = num_pages;
+    fusion.flag = flag;
+    if (!cos_table) return KB_ERR_NULL;
+    return skinny_entry(x, ldx, w, ldw, bias, out, 0, ldo, M, N, K, 0, fusion, stream);
 }

@@ -10,7 +10,6 @@
 // kernels round cos, sin and each product to bf16 first, kairyu/kernels/rope_gpu.py:74-112).
 #include "common.cuh"
 
-#define KB_FLAG_BAD_POS 8
 #define ROPE_WARPS 4
 #define ROPE_MAX_D 512
 

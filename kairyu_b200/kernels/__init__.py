@@ -621,6 +621,67 @@ def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     )
 
 
+def linear_rope_ok(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, num_q_heads: int,
+                   num_kv_heads: int, head_dim: int, cos: Optional[torch.Tensor], k_cache: Optional[torch.Tensor]) -> bool:
+    """Whether ``linear_rope`` takes this q | k | v product: bf16, at most 16 rows (the weight-streaming
+    kernel), a rotation over the whole head, bf16 caches."""
+    values = x.values if isinstance(x, PreNormed) else x
+    if cos is None or not values.is_cuda or values.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        return False
+    if head_dim % 16 or cos.dtype != torch.float32 or cos.dim() != 2 or cos.shape[1] * 2 != head_dim or not cos.is_contiguous():
+        return False
+    if weight.shape[0] != (num_q_heads + 2 * num_kv_heads) * head_dim or out.shape != (values.shape[0], weight.shape[0]):
+        return False
+    if k_cache is not None and (k_cache.dtype != torch.bfloat16 or not k_cache.is_contiguous()):
+        return False
+    return _skinny_ok(values, weight, bias, out)
+
+
+def linear_rope(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, num_q_heads: int, num_kv_heads: int,
+                head_dim: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor, row_ids: torch.Tensor,
+                block_table: Optional[torch.Tensor], write_from: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                v_cache: Optional[torch.Tensor], flag: Optional[torch.Tensor] = None) -> None:
+    """The q | k | v product of attention for a few rows with the position encoding and the cache
+    write in its epilogue (csrc/gemm_skinny.cu, rope): the q columns of ``out`` get the rotated
+    queries; rotated keys and the values go straight to their cache pages (``out``'s k and v
+    columns are left as they were).  ``x`` may be a :class:`PreNormed`.  Same arithmetic as
+    ``linear`` then ``qk_norm_rope_kv_write`` without per-head norms, except that the product is
+    not rounded to bf16 before it is rotated."""
+    scale_by = x if isinstance(x, PreNormed) else None
+    values = scale_by.values if scale_by is not None else x
+    _need_cuda("linear_rope", values, weight, bias, out, cos, sin, positions, row_ids, block_table, write_from, k_cache, v_cache, flag)
+    _need_i32("linear_rope", positions, row_ids, *(t for t in (block_table, write_from) if t is not None))
+    if not linear_rope_ok(x, weight, bias, out, num_q_heads=num_q_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, cos=cos, k_cache=k_cache):
+        raise KernelError("linear_rope: operands the fused kernel does not take (see linear_rope_ok)")
+    if sin.shape != cos.shape or sin.dtype != torch.float32 or not sin.is_contiguous():
+        raise KernelError("linear_rope: sin must match cos")
+    M, K = values.shape
+    if positions.numel() != M or row_ids.numel() != M:
+        raise KernelError("linear_rope: one position and one row id per token")
+    page_size = num_pages = max_pages = 0
+    if k_cache is not None:
+        if v_cache is None or block_table is None or write_from is None or v_cache.shape != k_cache.shape or v_cache.dtype != k_cache.dtype or not v_cache.is_contiguous():
+            raise KernelError("linear_rope: a cache write needs both caches, the block table and write_from")
+        if tuple(k_cache.shape[2:]) != (num_kv_heads, head_dim) or block_table.dim() != 2 or not block_table.is_contiguous():
+            raise KernelError("linear_rope: cache or block table layout")
+        num_pages, page_size = k_cache.shape[0], k_cache.shape[1]
+        max_pages = block_table.shape[1]
+    fn = _fn(
+        "gemm_skinny", "kb_gemm_skinny_rope",
+        [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float,
+         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+         c_void_p, c_void_p],
+    )
+    _check(
+        fn(values.data_ptr(), values.stride(0), weight.data_ptr(), weight.stride(0), _ptr(bias), out.data_ptr(), out.stride(0), M, weight.shape[0], K,
+           _ptr(scale_by.sumsq) if scale_by is not None else None, scale_by.sumsq.shape[0] if scale_by is not None else 0,
+           scale_by.hidden if scale_by is not None else 0, float(scale_by.eps) if scale_by is not None else 0.0,
+           cos.data_ptr(), sin.data_ptr(), cos.shape[0], num_q_heads, num_kv_heads, head_dim, positions.data_ptr(), row_ids.data_ptr(),
+           _ptr(block_table), max_pages, _ptr(write_from), _ptr(k_cache), _ptr(v_cache), page_size, num_pages, _ptr(flag), _stream()),
+        "linear_rope",
+    )
+
+
 # ---- RMSNorm inside the products around it (decode: a norm kernel of its own costs as much as
 # a third of the q/k/v product it feeds)
 
@@ -894,6 +955,8 @@ def sample(
 
 
 __all__ = [
+    "linear_rope",
+    "linear_rope_ok",
     "logprob_report",
     "KernelBuildError",
     "KernelError",

@@ -224,28 +224,36 @@ class GQAAttention(Mixer):
         tokens = x.shape[0]
         ws = ctx.workspace
         qkv = ws.buffer("attn.qkv", tokens, self.qkv_width, self.dtype)
-        kernels.linear(x, self.w_qkv, self.b_qkv, qkv)
         tables = self.position.rotary_tables() if self.position is not None else None
         cos, sin = tables if tables is not None else (None, None)
         writes = cache.writes
-        kernels.qk_norm_rope_kv_write(
-            qkv,
-            self.num_heads,
-            self.num_kv_heads,
-            self.head_dim,
+        placement = dict(
             positions=ctx.positions,
             row_ids=ctx.row_ids,
-            q_norm_weight=self.q_norm_weight,
-            k_norm_weight=self.k_norm_weight,
-            eps=self.norm_eps,
-            cos=cos,
-            sin=sin,
             block_table=ctx.block_tables[cache.group] if writes else None,
             write_from=ctx.write_from if writes else None,
             k_cache=cache.k if writes else None,
             v_cache=cache.v if writes else None,
             flag=ctx.error_flag,
         )
+        heads = dict(num_q_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+        if not self.qk_norm and kernels.linear_rope_ok(x, self.w_qkv, self.b_qkv, qkv, cos=cos, k_cache=placement["k_cache"], **heads):
+            # a few bf16 rows: the rotation and the cache write ride in the product's epilogue
+            kernels.linear_rope(x, self.w_qkv, self.b_qkv, qkv, cos=cos, sin=sin, **heads, **placement)
+        else:
+            kernels.linear(x, self.w_qkv, self.b_qkv, qkv)
+            kernels.qk_norm_rope_kv_write(
+                qkv,
+                self.num_heads,
+                self.num_kv_heads,
+                self.head_dim,
+                q_norm_weight=self.q_norm_weight,
+                k_norm_weight=self.k_norm_weight,
+                eps=self.norm_eps,
+                cos=cos,
+                sin=sin,
+                **placement,
+            )
         mixed = ws.buffer("attn.mixed", tokens, self.q_size, self.dtype)
         run_paged_attention(
             qkv,

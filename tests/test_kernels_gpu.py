@@ -311,6 +311,44 @@ def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, page_size, qk_norm, rot_dim, T
     assert torch.equal((kc.cpu().float().abs().sum(dim=(2, 3)) > 0), written)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D,page_size,K", [(4, 2, 16, 16, 64), (5, 1, 48, 16, 112), (32, 8, 128, 16, 4096), (3, 3, 80, 4, 96)])
+@pytest.mark.parametrize("T", [1, 8, 13])
+@pytest.mark.parametrize("bias", [False, True])
+def test_product_with_rotation_and_cache_write_in_its_epilogue(Hq, Hkv, D, page_size, K, T, bias):
+    """``linear_rope`` against the product in fp32, then the plain rotation and cache write: the q
+    columns of the output, the key and value pages, nothing written below ``write_from``."""
+    case = _rope_case(torch.bfloat16, T, Hq, Hkv, D, page_size, False, D, seed=30)
+    N = (Hq + 2 * Hkv) * D
+    x = rand(T, K, dtype=torch.bfloat16, seed=31)
+    w = rand(N, K, dtype=torch.bfloat16, seed=32, scale=0.05)
+    b = rand(N, dtype=torch.bfloat16, seed=33) if bias else None
+    product = x.float() @ w.float().t() + (b.float() if bias else 0)
+    kc_ref = torch.zeros(case["num_pages"], page_size, Hkv, D)
+    vc_ref = torch.zeros_like(kc_ref)
+    placement = dict(positions=case["positions"], row_ids=case["row_ids"], block_table=case["table"], write_from=case["write_from"])
+    ref.qk_norm_rope_kv_write(product, Hq, Hkv, D, cos=case["cos"], sin=case["sin"], k_cache=kc_ref, v_cache=vc_ref, **placement)
+    to = lambda t: None if t is None else t.to(DEV)
+    out = torch.full((T, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(kc_ref.shape, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    heads = dict(num_q_heads=Hq, num_kv_heads=Hkv, head_dim=D)
+    assert kernels().linear_rope_ok(to(x), to(w), to(b), out, cos=to(case["cos"]), k_cache=kc, **heads)
+    kernels().linear_rope(
+        to(x), to(w), to(b), out, cos=to(case["cos"]), sin=to(case["sin"]), k_cache=kc, v_cache=vc, flag=flag,
+        **heads, **{name: to(t) for name, t in placement.items()},
+    )
+    assert int(flag.item()) == 0
+    atol, rtol = 4e-3 * math.sqrt(K / 64) + 4e-3, 1e-2
+    close(out[:, : Hq * D], product[:, : Hq * D], atol, rtol)
+    assert bool((out[:, Hq * D :] == 7.0).all())  # k and v go to the cache only
+    close(kc, kc_ref, atol, rtol)
+    close(vc, vc_ref, atol, rtol)
+    written = kc_ref.abs().sum(dim=(2, 3)) > 0
+    assert torch.equal(kc.cpu().float().abs().sum(dim=(2, 3)) > 0, written)
+    assert torch.equal(vc.cpu().float().abs().sum(dim=(2, 3)) > 0, vc_ref.abs().sum(dim=(2, 3)) > 0)
+
+
 def test_rope_flags_a_position_outside_the_table():
     from kairyu_b200.parts.rope import rotary_tables
 

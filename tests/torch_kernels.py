@@ -223,10 +223,14 @@ def logprob_report(logits, rows, tokens, k, values, indices, *, tokens_by_row):
                 indices[r, place] = -1
 
 
+def linear_rope_ok(*args, **kwargs):
+    return False  # the CPU statements keep the product and the rotation apart
+
+
 _NAMES = [
     "embedding", "patch_tokens", "fused_norm_available", "rmsnorm", "swiglu", "gather_rows", "qk_norm_rope_kv_write", "paged_attention_generic",
     "attention_mma_supported", "attention_prefill_tile_rows", "attention_prefill_mma", "attention_decode_mma", "linear", "linear_swiglu", "argmax",
-    "edit_logits", "sample", "sample_work_floats", "logprob_report",
+    "edit_logits", "sample", "sample_work_floats", "logprob_report", "linear_rope_ok",
 ]
 
 
