@@ -27,7 +27,7 @@ gives pages back while the request runs, and state cannot be rebuilt from pages.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Hashable, Iterable, Mapping, Optional, Sequence
+from typing import Any, Hashable, Mapping, Optional, Sequence
 
 from kairyu_b200.cache.page_pool import OutOfPages, PagePool
 from kairyu_b200.cache.prefix import PrefixIndex, PrefixNode

@@ -6,7 +6,6 @@ kairyu/engine/kairyu_backend.py:467-1179, without tokenizer and server parts).
 
 from __future__ import annotations
 
-import json
 import dataclasses
 from collections import deque
 from dataclasses import dataclass

@@ -17,7 +17,6 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Hashable, Optional, Sequence
 
-import numpy as np
 import torch
 
 from kairyu_b200 import kernels

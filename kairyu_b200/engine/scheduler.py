@@ -51,7 +51,7 @@ from __future__ import annotations
 from collections import deque
 from dataclasses import dataclass, field
 from enum import Enum
-from typing import Hashable, Mapping, Optional, Sequence
+from typing import Mapping, Optional
 
 from kairyu_b200.cache.manager import CacheManager
 from kairyu_b200.cache.page_pool import OutOfPages

@@ -7,7 +7,7 @@ from __future__ import annotations
 import fnmatch
 import json
 from pathlib import Path
-from typing import Any, Mapping, Sequence
+from typing import Any, Sequence
 
 import torch
 

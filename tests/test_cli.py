@@ -4,7 +4,6 @@ import json
 
 import pytest
 
-import torch_kernels
 from tiny_configs import TINY_QWEN3
 
 from kairyu_b200.entrypoints import cli

@@ -10,7 +10,7 @@ from safetensors.torch import load_file, save_file
 from tiny_configs import TINY, TINY_LLAMA, TINY_QWEN3
 
 from kairyu_b200.config import ConfigError, EngineConfig, parse_dense_config
-from kairyu_b200.engine.engine import build_model, load_model
+from kairyu_b200.engine.engine import load_model
 from kairyu_b200.registry import architecture_of, register_architecture, supported_architectures, unregister_architecture
 from kairyu_b200.weights import WeightError, write_random_model
 

@@ -3,7 +3,6 @@ CPU with the kernels replaced by their torch statements: host-side decisions
 only.  The same workloads run on the GPU with the real kernels."""
 
 import pytest
-import torch
 
 import plain_model
 import torch_kernels

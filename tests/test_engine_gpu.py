@@ -6,7 +6,6 @@ import pytest
 import torch
 
 import plain_model
-from golden_inputs import golden_weights
 from tiny_configs import TINY
 
 pytestmark = pytest.mark.gpu

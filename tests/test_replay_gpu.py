@@ -3,10 +3,6 @@ one by one, in portions of changing size, and mixed with other requests over a
 pool so small that pages are used again; in 32-bit and in bfloat16; in process
 and through ``bin/trace_run``; all compared with the plain implementation."""
 
-import json
-import subprocess
-import sys
-
 import numpy as np
 import pytest
 import torch

@@ -7,7 +7,6 @@ import pytest
 from kairyu_b200.cache import CacheLayout, CacheManager
 from kairyu_b200.engine.scheduler import EngineRequest, Scheduler, Status
 from kairyu_b200.parts.base import PagedKVSpec
-from kairyu_b200.sampling.params import SamplingParams
 
 
 def make(num_pages=17, page_size=4, **kwargs):

@@ -5,7 +5,6 @@ themselves are checked on the GPU."""
 
 import numpy as np
 import pytest
-import torch
 
 import plain_model
 import torch_kernels

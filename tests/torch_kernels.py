@@ -7,8 +7,7 @@ They are test code: the package itself has no implementation but its kernels.
 
 from __future__ import annotations
 
-import math
-from typing import Optional
+
 
 import torch
 
