@@ -109,7 +109,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         *s_timeout = 0;
         fence_barrier_init();
     }
-    pdl_wait();
+    // What follows until the waits below reads only what the host's copy of the step wrote (rows,
+    // lengths, block tables) and keys and values of positions before the newest: none of it comes
+    // from the kernels this one may overlap with (the products just before it, which write the
+    // newest position only), so it need not wait for them.
 
     const int slot = blockIdx.x;
     const int kvh = blockIdx.y;
@@ -122,7 +125,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int key_lo = (window > 0 && qpos + 1 > window) ? qpos + 1 - window : 0;
     int t0, t1, per;
     split_range(key_lo / TILE_N, qpos / TILE_N, num_splits, split, t0, t1, per);
-    if (seq_len < 1 || t0 > t1) return;  // this split has no tile (the whole block leaves)
+    if (seq_len < 1 || t0 > t1) {  // this split has no tile (the whole block leaves)
+        pdl_wait();  // a block never ends before the kernels ahead have: those after this one count on that
+        return;
+    }
     const int* table = block_table + (size_t)row * max_pages;
     const int g = lane >> 2;
     const int tq = lane & 3;
@@ -138,8 +144,16 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int box_rows = page_size < TILE_N ? page_size : TILE_N;
         const int runs = TILE_N / box_rows;
         const int per_tile = 2 * HALVES * runs;
+        // The tile that holds the newest position is written by the kernel before this one; the tiles
+        // before it are not.  Up to a ring of those go out before the wait (no stage is reused yet,
+        // so nothing here waits on the consumers, who are waiting for their queries).
+        const int newest_tile = qpos / TILE_N;
+        int ahead = newest_tile - t0 < t1 - t0 + 1 ? newest_tile - t0 : t1 - t0 + 1;
+        ahead = ahead < STAGES ? ahead : STAGES;
+        if (ahead <= 0) pdl_wait();
         for (int kt = t0; kt <= t1; ++kt) {
             const int i = kt - t0;
+            if (ahead > 0 && i == ahead) pdl_wait();
             const int stage = i % STAGES;
             const int use = i / STAGES;
             if (use > 0 && !mbar_wait(empty_bar + stage, (use - 1) & 1)) {
@@ -167,8 +181,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 tma_load_4d(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, full_bar + stage);
             }
         }
+        if (ahead > 0 && t1 - t0 + 1 <= ahead) pdl_wait();  // every tile went out ahead of the wait
     } else {
         // ---------------- consumers
+        pdl_wait();  // the queries come from the kernel before this one
         for (int c = threadIdx.x; c < 16 * CH; c += CONSUMER_WARPS * 32) {
             const int r = c / CH;
             const int col = (c % CH) * 8;
