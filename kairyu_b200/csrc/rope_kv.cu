@@ -39,7 +39,8 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
                              const int* __restrict__ write_from, T* __restrict__ k_cache,
                              T* __restrict__ v_cache, int page_size, int num_pages, int* flag) {
     pdl_trigger();
-    pdl_wait();
+    // Positions, row ids, block tables and write_from come from the host's copy of the step, not from
+    // the kernel before this one: the look-ups below run ahead of the wait for that kernel's q | k | v.
     __shared__ float head_buf[ROPE_WARPS][ROPE_MAX_D];
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5;
@@ -53,6 +54,7 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
     const bool rotate = cos_table != nullptr && rot_half > 0;
     if (rotate && (pos < 0 || pos >= max_pos)) {
         if (lane == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+        pdl_wait();
         return;
     }
     const bool is_v = head >= Hq + Hkv;
@@ -69,6 +71,7 @@ qk_norm_rope_kv_write_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, int Hk
             slot = (long long)page * page_size + (pos % page_size);
         }
     }
+    pdl_wait();
     T* x = token + (size_t)head * D;
     if (is_v) {
         if (slot >= 0) {
