@@ -374,7 +374,8 @@ __global__ void attention_decode_tma_merge_kernel(const float* __restrict__ part
                                                   const int* __restrict__ seq_lens, const int* __restrict__ decode_rows,
                                                   const int* __restrict__ decode_tokens, __nv_bfloat16* __restrict__ out,
                                                   int out_stride, int Hq, int D, int window, int num_splits) {
-    pdl_wait();
+    pdl_trigger();  // the product after this one may fetch its first weights meanwhile
+    // rows and lengths come from the host's copy of the step: looked up ahead of the wait for the partial results
     const int slot = blockIdx.x;
     const int h = blockIdx.y;
     const int row = decode_rows[slot];
@@ -387,6 +388,7 @@ __global__ void attention_decode_tma_merge_kernel(const float* __restrict__ part
     const int tiles = seq_len < 1 ? 0 : qpos / TILE_N - key_lo / TILE_N + 1;
     const int used = (tiles + per - 1) / per;  // splits that had a tile
     const size_t base = ((size_t)slot * Hq + h) * num_splits;
+    pdl_wait();
     float big = -INFINITY;
     for (int s = 0; s < used; ++s) big = fmaxf(big, part_ml[(base + s) * 2]);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
