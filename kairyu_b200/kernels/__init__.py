@@ -517,7 +517,7 @@ def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[
     """out = x @ weight.T (+ bias).
 
     float32: this package's own FMA kernel (true 32-bit, fixed summation order).
-    bfloat16: the weight-streaming kernel up to 16 rows, else the library product (cuBLAS
+    bfloat16: the weight-streaming kernel up to 8 rows, else the library product (cuBLAS
     through torch), as the reference's ``F.linear`` is (kairyu/models/packed_linear.py:217);
     accumulation is fp32, ``out`` may be bfloat16 or float32.
 
@@ -559,7 +559,7 @@ def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[
         raise KernelError(f"linear: dtypes {x.dtype} / {weight.dtype} are not supported")
     if M == 0:
         return
-    if _skinny_ok(x, weight, bias, out):
+    if few_rows(M) and _skinny_ok(x, weight, bias, out):
         _gemm_skinny(x, weight, bias, out, gated=False)
         return
     if out.dtype == torch.bfloat16:
@@ -576,6 +576,15 @@ def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[
 
 
 SKINNY_MAX_ROWS = 16  # token rows the weight-streaming product takes (csrc/gemm_skinny.cu)
+# ... and up to which the engine uses it.  With two token tiles (9 to 16 rows) its main loop spills, and
+# the step is 5-7 % faster on the library product (plain) and the tcgen05 product (gated) with the
+# norms and the position encoding as kernels of their own (measured at 9, 12 and 16 rows).
+SKINNY_FAST_ROWS = 8
+
+
+def few_rows(rows: int) -> bool:
+    """Whether a step of this many token rows runs on the weight-streaming product and its fusions."""
+    return 1 <= rows <= SKINNY_FAST_ROWS
 
 
 def _skinny_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
@@ -619,6 +628,16 @@ def _gemm_skinny(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
            fold.sumsq.data_ptr() if fold is not None else None, _stream()),
         "gemm_skinny",
     )
+
+
+def linear_weight_streaming(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, gated: bool = False) -> None:
+    """The weight-streaming kernel itself, for up to 16 bf16 rows (``linear`` and ``linear_swiglu``
+    choose it up to ``SKINNY_FAST_ROWS``); ``gated``: out = silu(x.Wg^T) * (x.Wu^T)."""
+    _need_cuda("linear_weight_streaming", x, weight, bias, out)
+    n_out = weight.shape[0] // 2 if gated else weight.shape[0]
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or weight.shape[1] != x.shape[1] or out.shape != (x.shape[0], n_out) or not _skinny_ok(x, weight, bias, out):
+        raise KernelError("linear_weight_streaming: needs bf16 operands, at most 16 rows, sizes in steps of 16, 32-byte aligned rows")
+    _gemm_skinny(x, weight, bias, out, gated=gated)
 
 
 def linear_rope_ok(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, *, num_q_heads: int,
@@ -731,7 +750,7 @@ def skinny_blocks(rows: int, out_features: int, gated: bool = False) -> int:
 
 def fused_norm_shapes_ok(rows: int, *feature_sizes: int) -> bool:
     """Whether products over these inner and outer sizes can all take the fused path."""
-    return 1 <= rows <= SKINNY_MAX_ROWS and all(size % 16 == 0 for size in feature_sizes)
+    return few_rows(rows) and all(size % 16 == 0 for size in feature_sizes)
 
 
 TC5_MAX_ROWS = 64  # token rows the tcgen05 weight-streaming product takes (csrc/gemm_tc5.cu)
@@ -821,10 +840,10 @@ def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: o
     """out = silu(x @ Wg.T) * (x @ Wu.T) with ``weight_gate_up`` = [Wg; Wu] stacked by rows.
 
     For up to 64 bf16 token rows this is one weight-streaming kernel with the gate in its
-    epilogue: the mma.sync skinny kernel up to 16 rows (csrc/gemm_skinny.cu; measured on the
+    epilogue: the mma.sync skinny kernel up to 8 rows (csrc/gemm_skinny.cu; measured on the
     decode step at 8 rows it is 2 % of the step faster than the tcgen05 kernel, whose fixed
     costs - barrier and tensor-memory set-up, the accumulator read-back - weigh more on a 40 us
-    kernel), the tcgen05 + TMA kernel from 17 to 64 rows (csrc/gemm_tc5.cu); otherwise a product
+    kernel), the tcgen05 + TMA kernel from 9 to 64 rows (csrc/gemm_tc5.cu); otherwise a product
     into ``scratch.buffer(...)`` and the gate kernel.
     """
     if isinstance(x, PreNormed):  # its rows are scaled in the epilogue, before the gate
@@ -842,7 +861,7 @@ def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: o
     if M == 0:
         return
     if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-        if _skinny_ok(x, weight_gate_up, None, out):
+        if few_rows(M) and _skinny_ok(x, weight_gate_up, None, out):
             _gemm_skinny(x, weight_gate_up, None, out, gated=True)
             return
         if _tc5_ok(x, weight_gate_up, None, out):
@@ -955,6 +974,8 @@ def sample(
 
 
 __all__ = [
+    "few_rows",
+    "linear_weight_streaming",
     "linear_rope",
     "linear_rope_ok",
     "logprob_report",

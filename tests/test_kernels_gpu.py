@@ -182,10 +182,18 @@ def test_weight_streaming_product_for_few_rows(M, N, K, bias):
     launches = kernels().launch_count
     for dtype, atol, rtol in ((torch.float32, 2e-4 * math.sqrt(K / 64), 1e-4), (torch.bfloat16, 4e-3 * math.sqrt(K / 64), 1e-2)):
         out = torch.full((M, N), 7.0, dtype=dtype, device=DEV)
-        kernels().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out)
+        if K % 16 == 0:  # the kernel itself (``linear`` chooses it up to 8 rows)
+            kernels().linear_weight_streaming(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out)
+        else:
+            kernels().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, out)
         close(out, expected, atol, rtol)
+        if M <= 8:
+            again = torch.full((M, N), 7.0, dtype=dtype, device=DEV)
+            kernels().linear(x.to(DEV), w.to(DEV), b.to(DEV) if bias else None, again)
+            if K % 16 == 0:
+                assert torch.equal(again, out)  # ``linear`` ran the same kernel
     if K % 16 == 0:  # this package's kernel ran, not the library product (which takes the other sizes)
-        assert kernels().launch_count == launches + 2
+        assert kernels().launch_count == launches + (4 if M <= 8 else 2)
 
 
 @pytest.mark.parametrize("M", [1, 8, 13])
@@ -201,6 +209,10 @@ def test_weight_streaming_product_with_the_gate_fused(M, I, K):
 
     kernels().linear_swiglu(x.to(DEV), w.to(DEV), out, Workspace(DEV))
     close(out, expected, 4e-3 * math.sqrt(K / 64), 1e-2)
+    if K % 16 == 0:  # the weight-streaming kernel itself, which ``linear_swiglu`` chooses up to 8 rows
+        direct = torch.full((M, I), 7.0, dtype=torch.bfloat16, device=DEV)
+        kernels().linear_weight_streaming(x.to(DEV), w.to(DEV), None, direct, gated=True)
+        close(direct, expected, 4e-3 * math.sqrt(K / 64), 1e-2)
 
 
 def test_gated_product_for_many_rows_uses_the_two_kernel_path():
