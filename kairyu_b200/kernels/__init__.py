@@ -576,9 +576,10 @@ def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[
 
 
 SKINNY_MAX_ROWS = 16  # token rows the weight-streaming product takes (csrc/gemm_skinny.cu)
-# ... and up to which the engine uses it.  With two token tiles (9 to 16 rows) its main loop spills, and
-# the step is 5-7 % faster on the library product (plain) and the tcgen05 product (gated) with the
-# norms and the position encoding as kernels of their own (measured at 9, 12 and 16 rows).
+# ... and up to which the engine uses it.  With two token tiles (9 to 16 rows) the step is 5-7 % faster
+# on the library product (plain) and the tcgen05 product (gated) with the norms and the position
+# encoding as kernels of their own (measured at 9, 12 and 16 rows; a two-tile variant without
+# register spills, one k step a batch, was no faster).
 SKINNY_FAST_ROWS = 8
 
 
