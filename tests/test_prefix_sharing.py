@@ -348,3 +348,48 @@ def test_engine_with_prefix_caching_few_pages_and_depth_two(cpu_kernels):
         assert llm.engine.cache.live_requests == 0
     assert llm.engine.cache.prefix.counters["evicted_pages"] > 0
     assert llm.engine.scheduler.counters["cached_prompt_tokens"] > 0
+
+
+@pytest.mark.parametrize("seed", [3, 11, 29, 57])
+def test_everything_on_equals_everything_off_on_random_workloads(cpu_kernels, seed):
+    """Schedule-ahead, prefix caching and log-probability reports together, on prompts that share
+    stems, over pools so small that requests wait, are preempted and unread pages are taken back:
+    tokens, finish reasons and stop reasons are those of the plain configuration, twice in a row."""
+    rng = random.Random(seed)
+    name = rng.choice(["llama", "qwen3", "odd"])
+    config, model_seed, page_size = TINY[name]
+    count = rng.randint(3, 8)
+    stems = [prompts_of(config, [rng.randint(1, 40)], seed=1000 + seed * 7 + i)[0] for i in range(2)]
+    prompts = [rng.choice(stems) + prompts_of(config, [rng.randint(0, 25)], seed=2000 + seed * 11 + i)[0] for i in range(count)]
+    limits = [rng.randint(1, 14) for _ in range(count)]
+    options = dict(
+        num_pages=rng.randint(10, 20), max_num_batched_tokens=rng.choice([5, 16, 64]), max_num_seqs=rng.choice([2, 4, 8]), page_size=page_size
+    )
+    results = {}
+    stops = None
+    for variant in ("off", "on"):
+        extra = dict(pipeline_depth=1) if variant == "off" else dict(pipeline_depth=2, enable_prefix_caching=True)
+        llm = LLM.from_random(config, seed=model_seed, dtype="float32", device="cpu", **options, **extra)
+        if stops is None:  # tokens the free run produces, so that some requests stop early
+            free = llm.generate([TokensPrompt(tuple(p)) for p in prompts], [SamplingParams(temperature=0.0, max_tokens=m) for m in limits])
+            stops = [o.outputs[0].token_ids[len(o.outputs[0].token_ids) // 2] if i % 2 == 0 else None for i, o in enumerate(free)]
+        params = [
+            SamplingParams(
+                temperature=0.0 if i % 3 else 0.7, seed=5 + i, max_tokens=limits[i], stop_token_ids=[stops[i]] if stops[i] is not None else [],
+                logprobs=(i % 4 if variant == "on" and i % 2 else None),
+            )
+            for i in range(count)
+        ]
+        for round_ in range(2):  # the second round finds its prompts in the prefix tree
+            outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+            results[(variant, round_)] = [(o.outputs[0].token_ids, o.outputs[0].finish_reason, o.outputs[0].stop_reason) for o in outputs]
+            for output, asked in zip(outputs, params):
+                completion = output.outputs[0]
+                if asked.logprobs is None:
+                    assert completion.logprobs is None
+                else:
+                    assert len(completion.logprobs) == len(completion.token_ids)
+                    assert all(list(entry)[0] == token for entry, token in zip(completion.logprobs, completion.token_ids))
+            llm.engine.cache.check()
+            assert llm.engine.cache.live_requests == 0 and not llm.engine._pending and not llm.engine._logprobs
+    assert all(value == results[("off", 0)] for value in results.values())
