@@ -193,6 +193,11 @@ class Engine:
             self._stop_checks[request_id] = stop_check
 
     def abort(self, request_id: str) -> None:
+        """End a waiting or running request now (reason ``"abort"``); what it holds is given back, a
+        token of its that is still in flight is dropped when its step commits.  An id that is not
+        known, or has finished, is left alone."""
+        if not self.scheduler.is_unfinished(request_id):
+            return
         self.scheduler.abort(request_id)
         self._collect(request_id)
 

@@ -222,3 +222,30 @@ def test_logprobs_of_generated_tokens_match_plain(depth):
         check_logprobs(config, weights, prompts[index], outputs[index].outputs[0], params[index].logprobs)
     assert list(outputs[0].outputs[0].token_ids) == plain_generate(config, weights, prompts[0], 6)
     assert not llm.engine._logprobs
+
+
+@pytest.mark.parametrize("depth", [1, 2])
+def test_abort_in_the_middle_leaves_the_others_alone(depth):
+    """A request aborted while its step is in flight: its pages and slot go back, its late token is
+    dropped, the other requests' tokens are those of an undisturbed run."""
+    from kairyu_b200.sampling.params import SamplingParams as Params
+
+    llm, config = make_llm("llama", num_pages=40, max_num_batched_tokens=16, pipeline_depth=depth)
+    prompts = prompts_of(config, [20, 9, 33], seed=150)
+    params = Params(temperature=0.0, max_tokens=12, logprobs=1)
+    undisturbed = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params)
+    engine = llm.engine
+    for index, prompt in enumerate(prompts):
+        engine.add_request(f"r{index}", tuple(prompt), params)
+    for _ in range(4):
+        engine.step()
+    engine.abort("r1")
+    engine.abort("r1")  # already gone
+    engine.abort("nobody")
+    finished = engine.run_to_completion()
+    assert finished["r1"].finish_reason == "abort" and len(finished["r1"].output_token_ids) < 12
+    for index in (0, 2):
+        assert finished[f"r{index}"].output_token_ids == undisturbed[index].outputs[0].token_ids
+        assert len(finished[f"r{index}"].logprobs) == 12
+    engine.cache.check()
+    assert engine.cache.live_requests == 0 and not engine._pending and not engine._logprobs
