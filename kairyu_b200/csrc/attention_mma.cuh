@@ -748,7 +748,7 @@ static int padded_dim(int D) {
 }
 
 // Queries per tile of the prefill kernel for a head size: 128 up to a padded size of 128, else 64.
-static int prefill_tile_rows(int D) { return padded_dim(D) <= 128 ? 128 : 64; }
+static inline int prefill_tile_rows(int D) { return padded_dim(D) <= 128 ? 128 : 64; }
 
 template <int DP, int MT>
 static int launch_prefill(const __nv_bfloat16* q, int q_stride, __nv_bfloat16* out, int out_stride,

@@ -132,7 +132,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bflo
     const int rope_half = roped ? fusion.D >> 1 : 0;
     int rope_base = 0;
     if (roped) {
-        const int per_head = rope_half >> 3;  // blocks a head
+        const int per_head = rope_half >= 8 ? rope_half >> 3 : 1;  // blocks a head (the host refuses heads under 16)
         rope_base = (blockIdx.x / per_head) * fusion.D + (blockIdx.x % per_head) * 8;
     }
     auto column_of = [&](int r) { return roped ? rope_base + (r & 7) + ((r & 8) ? rope_half : 0) : n0 + r; };
