@@ -51,6 +51,9 @@ class EngineConfig:
     # Whole pages of finished and running requests stay matchable by their tokens; a request whose
     # tokens start the same way begins behind them (kairyu/engine/core/radix_kv.py:1-11).
     enable_prefix_caching: bool = False
+    # Waiting requests are admitted by (priority, arrival), the lower priority value first, instead
+    # of first come, first served (kairyu/engine/core/scheduler.py:191-199, without its aging).
+    priority_scheduling: bool = False
     seed: int = 0
 
     def __post_init__(self) -> None:

@@ -122,6 +122,7 @@ class Engine:
             max_num_partial_prefills=config.max_num_partial_prefills,
             max_model_len=self.max_model_len,
             prefill_chunk_size=config.prefill_chunk_size,
+            priority_scheduling=config.priority_scheduling,
         )
         self.sampler = Sampler(model.spec.vocab_size, self.device)
         self._finished: dict[str, FinishedRequest] = {}
@@ -167,7 +168,10 @@ class Engine:
         *,
         eos_token_ids: Sequence[int] = (),
         stop_check: Optional[Callable[[Sequence[int]], Optional[str]]] = None,
+        priority: int = 0,
     ) -> None:
+        if priority != 0 and not self.config.priority_scheduling:
+            raise ValueError("a priority needs an engine built with priority_scheduling=True")
         prompt = tuple(int(token) for token in prompt_token_ids)
         vocab = self.model.spec.vocab_size
         if any(not 0 <= token < vocab for token in prompt):
@@ -187,6 +191,7 @@ class Engine:
                 min_tokens=params.min_tokens,
                 ignore_eos=params.ignore_eos,
                 params=params,
+                priority=int(priority),
             )
         )
         if stop_check is not None:

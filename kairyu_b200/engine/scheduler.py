@@ -1,8 +1,8 @@
 """The scheduler: admits requests, cuts prompts into portions under a token
 budget, decodes, finishes and frees.  Pure policy over the cache manager; it
 never touches a tensor (kairyu/engine/core/scheduler.py:404-1770 is the
-reference; priorities, scheduling classes and speculative reservations are left
-out).
+reference; priority aging, scheduling classes and speculative reservations are
+left out).
 
 A request's work is ``prompt + outputs``; ``computed`` counts how many of those
 tokens have been fed.  While more than one token is left to feed the request
@@ -70,6 +70,7 @@ class EngineRequest:
     min_tokens: int = 0
     ignore_eos: bool = False
     params: SamplingParams = field(default_factory=lambda: SamplingParams(temperature=0.0))
+    priority: int = 0  # lower goes first when the scheduler orders by priority (scheduler.py:44, 191-199)
 
 
 MAX_WAITING_BYPASSES = 1  # kairyu/engine/core/scheduler.py:28
@@ -147,8 +148,10 @@ class Scheduler:
         max_num_partial_prefills: int = 2,
         max_model_len: Optional[int] = None,
         prefill_chunk_size: Optional[int] = None,
+        priority_scheduling: bool = False,
     ) -> None:
         self.cache = cache
+        self.priority_scheduling = priority_scheduling
         self.budget = max_num_batched_tokens
         self.max_num_seqs = max_num_seqs
         self.max_num_partial_prefills = max_num_partial_prefills
@@ -176,7 +179,27 @@ class Scheduler:
             )
         self._states[request.request_id] = RequestState(request, self._arrivals)
         self._arrivals += 1
-        self._waiting.append(request.request_id)
+        self._enqueue(request.request_id)
+
+    def _enqueue(self, request_id: str, front: bool = False) -> None:
+        """Put a request on the waiting queue: first come, first served (a preempted request goes
+        back to the front), or, with priority scheduling, by (priority, arrival), the lower first
+        (kairyu/engine/core/scheduler.py:191-199; a preempted request keeps its place by its arrival)."""
+        if not self.priority_scheduling:
+            if front:
+                self._waiting.appendleft(request_id)
+            else:
+                self._waiting.append(request_id)
+            return
+        key = self._queue_key(request_id)
+        place = 0
+        while place < len(self._waiting) and self._queue_key(self._waiting[place]) <= key:
+            place += 1
+        self._waiting.insert(place, request_id)
+
+    def _queue_key(self, request_id: str) -> tuple[int, int]:
+        state = self._states[request_id]
+        return state.request.priority, state.arrival
 
     def abort(self, request_id: str) -> None:
         state = self._states.get(request_id)
@@ -254,7 +277,7 @@ class Scheduler:
         state.computed = 0
         state.status = Status.WAITING
         state.preemptions += 1
-        self._waiting.appendleft(request_id)
+        self._enqueue(request_id, front=True)
         self.counters["preemptions"] += 1
 
     def _pick_victim(self, needy: str, taken: set[str]) -> Optional[str]:

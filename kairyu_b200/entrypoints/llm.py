@@ -153,7 +153,8 @@ class LLM:
                 if params.stop:
                     stop_check = self._stop_checker(params)
                 self.engine.add_request(
-                    child_id, token_ids, child_params, eos_token_ids=self.eos_token_ids, stop_check=stop_check
+                    child_id, token_ids, child_params, eos_token_ids=self.eos_token_ids, stop_check=stop_check,
+                    priority=priority[index] if priority is not None else 0,
                 )
                 children.append(child_id)
             submitted.append((request_id, children, tuple(token_ids), text, params))

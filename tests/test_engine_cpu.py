@@ -249,3 +249,27 @@ def test_abort_in_the_middle_leaves_the_others_alone(depth):
         assert len(finished[f"r{index}"].logprobs) == 12
     engine.cache.check()
     assert engine.cache.live_requests == 0 and not engine._pending and not engine._logprobs
+
+
+def test_priorities_through_the_entry_point():
+    llm, config = make_llm("llama", num_pages=40, max_num_batched_tokens=8, max_num_partial_prefills=1, priority_scheduling=True)
+    prompts = prompts_of(config, [8, 8, 8], seed=160)
+    params = SamplingParams(temperature=0.0, max_tokens=2)
+    started = []
+    real = llm.engine.scheduler._admit
+
+    def watch(request_id, *args, **kwargs):
+        used = real(request_id, *args, **kwargs)
+        if used is not None:
+            started.append(request_id.rsplit("-", 1)[1])
+        return used
+
+    llm.engine.scheduler._admit = watch
+    outputs = llm.generate([TokensPrompt(tuple(p)) for p in prompts], params, priority=[2, 0, 1])
+    assert started == ["1", "2", "0"]
+    assert [len(o.outputs[0].token_ids) for o in outputs] == [2, 2, 2]
+    plain, _ = make_llm("llama", num_pages=40)
+    with pytest.raises(ValueError, match="priority_scheduling"):
+        plain.generate([TokensPrompt(tuple(p)) for p in prompts], params, priority=[2, 0, 1])
+    with pytest.raises(ValueError, match="priority length"):
+        llm.generate([TokensPrompt(tuple(p)) for p in prompts], params, priority=[1])

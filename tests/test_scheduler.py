@@ -279,3 +279,37 @@ def test_nothing_passes_a_blocked_head_when_nothing_runs():
     scheduler.add_request(request("fits", 6, max_new=2))
     plan, _ = run_step(scheduler, cache)
     assert plan.rejected == ("too-big",) and [c.request_id for c in plan.scheduled] == ["fits"]
+
+
+def test_priority_scheduling_orders_the_waiting_queue():
+    """Lower priority values are admitted first, first come first served among equals; a preempted
+    request goes back to its place by its arrival (kairyu/engine/core/scheduler.py:191-199)."""
+    scheduler, cache = make(num_pages=40, max_num_batched_tokens=6, max_num_partial_prefills=1, priority_scheduling=True)
+    for name, priority in (("late-low", 5), ("first", 0), ("urgent", -1), ("second", 0)):
+        scheduler.add_request(EngineRequest(name, tuple(range(1, 7)), max_new_tokens=1, priority=priority))
+    order = []
+    for _ in range(8):
+        plan, _ = run_step(scheduler, cache)
+        order.extend(c.request_id for c in plan.scheduled if c.start == 0)
+    assert order == ["urgent", "first", "second", "late-low"]
+    # without the option the queue is first come, first served
+    scheduler, cache = make(num_pages=40, max_num_batched_tokens=6, max_num_partial_prefills=1)
+    for name, priority in (("a", 5), ("b", 0)):
+        scheduler.add_request(EngineRequest(name, tuple(range(1, 7)), max_new_tokens=1, priority=priority))
+    plan, _ = run_step(scheduler, cache)
+    assert plan.scheduled[0].request_id == "a"
+
+
+def test_preempted_request_keeps_its_place_under_priority_scheduling():
+    scheduler, cache = make(num_pages=6, page_size=4, max_num_batched_tokens=64, priority_scheduling=True)  # 5 pages
+    scheduler.add_request(EngineRequest("old", tuple(range(1, 8)), max_new_tokens=8, priority=1))
+    scheduler.add_request(EngineRequest("young", tuple(range(51, 60)), max_new_tokens=8, priority=1))
+    scheduler.add_request(EngineRequest("later-but-urgent", tuple(range(1, 4)), max_new_tokens=1, priority=0))
+    preempted = []
+    for _ in range(60):
+        if not scheduler.has_unfinished():
+            break
+        plan, _ = run_step(scheduler, cache)
+        preempted.extend(plan.preempted)
+    assert not scheduler.has_unfinished() and preempted
+    assert [len(scheduler.output_tokens(name)) for name in ("old", "young", "later-but-urgent")] == [8, 8, 1]
