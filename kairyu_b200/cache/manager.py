@@ -112,6 +112,10 @@ class CacheManager:
         self.pools = [PagePool(num_pages, reserved=reserved_pages) for _ in layout.groups]
         self.max_requests = max_requests
         self._free_state_slots = list(range(max_requests - 1, -1, -1))
+        # One state slot beyond the requests' own, as page 0 is reserved among the pages: the
+        # padding rows of a replayed decode graph read and write it, so that no live request's
+        # state is touched by a row that stands for nobody.
+        self.scratch_state_slot = max_requests
         self._requests: dict[Hashable, RequestCache] = {}
         self.fresh_state_slots: list[int] = []  # slots handed out since the storage last zeroed them
         self.prefix: Optional[PrefixIndex] = PrefixIndex(page_size) if prefix_sharing else None

@@ -16,7 +16,8 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 class CacheStorage:
     """K and V of group g: ``[slots_in_group, num_pages, page_size, kv_heads, head_dim]``.
     A page of one slot is a contiguous ``[page_size, kv_heads*head_dim]`` tile.
-    State tensors: ``[max_requests, *shape]`` each."""
+    State tensors: ``[max_requests + 1, *shape]`` each; the last row is the scratch slot that
+    padding rows of a decode graph use."""
 
     def __init__(
         self,
@@ -38,7 +39,7 @@ class CacheStorage:
             self.k.append(torch.zeros(shape, dtype=dtype, device=device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=device))
         self.states = [
-            torch.zeros((max_requests, *binding.spec.shape), dtype=_STATE_DTYPES[binding.spec.dtype], device=device)
+            torch.zeros((max_requests + 1, *binding.spec.shape), dtype=_STATE_DTYPES[binding.spec.dtype], device=device)
             for binding in layout.states
         ]
 

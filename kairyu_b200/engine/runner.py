@@ -252,10 +252,10 @@ class ModelRunner:
             qo_indptr.append(base + 1)
             seq_lens.append(1)
             write_from.append(0)
-            state_slots.append(0)
+            state_slots.append(self.cache.scratch_state_slot)
             decode_rows.append(row)
             decode_tokens.append(base)
-        needed_pages = max(-(-seq_len // page_size) for _, _, seq_len in rows)
+        needed_pages = max((-(-seq_len // page_size) for _, _, seq_len in rows), default=1)
         table_width = max_pages if max_pages is not None else needed_pages
         tables: list[int] = []
         for group in groups:
@@ -403,17 +403,18 @@ class ModelRunner:
         bucket, context_bucket = key
         held = self._graphs.get(key)
         if held is None or held.generation != self.graph_workspace.generation:
-            host, layout, facts = self._pack(
-                rows, pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
-            )
+            # The graph is captured over padding rows only (token 0 at position 0 of the reserved
+            # page, the scratch state slot), so that the capture's warm-up runs touch no request:
+            # a mixer with state of its own would otherwise see a request's token several times.
             # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
+            host, layout, facts = self._pack(
+                (), pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
+            )
             facts["max_seq_len"] = context_bucket
-            held = self._capture(key, host, layout, facts, sampled)
+            held = self._capture(key, host, layout, facts)
             held.mirror = host.numpy().copy()
             held.row_state = [None] * bucket
-            self._note_rows(held, rows)
-        else:
-            self._update_mirror(held, rows, bucket)
+        self._update_mirror(held, rows, bucket)
         self._upload(held)
         self._patch_tokens(held.meta, held.layout, sampled)
         held.graph.replay()
@@ -429,11 +430,6 @@ class ModelRunner:
 
     def _needed_pages(self, seq_len: int) -> int:
         return -(-seq_len // self.cache.page_size)
-
-    def _note_rows(self, held: _Graph, rows: Sequence[tuple[StepEntry, int, int]]) -> None:
-        groups = len(self.cache.layout.groups)
-        for row, (entry, _, seq_len) in enumerate(rows):
-            held.row_state[row] = (entry.request_id, [self._needed_pages(seq_len)] * groups)
 
     def _update_mirror(self, held: _Graph, rows: Sequence[tuple[StepEntry, int, int]], bucket: int) -> None:
         """Bring the host mirror of a graph's metadata to this step: per row the token, the
@@ -457,7 +453,10 @@ class ModelRunner:
             mirror[slot_at + row] = record.state_slot
             need = self._needed_pages(seq_len)
             state = held.row_state[row]
-            same = state is not None and state[0] == entry.request_id
+            # The row's pages may be topped up only for the same admission of the request: an id
+            # that was released and admitted again (a preempted request coming back, a reused id)
+            # has a new record and new pages, and its row is rewritten whole.
+            same = state is not None and state[0] is record
             for group in groups:
                 base = table_at + (group.index * bucket + row) * width
                 table = record.tables[group.index]
@@ -467,14 +466,14 @@ class ModelRunner:
                     mirror[base : base + need] = table[:need]
                 elif need > have:
                     mirror[base + have : base + need] = table[have:need]
-            held.row_state[row] = (entry.request_id, [need] * len(groups))
+            held.row_state[row] = (record, [need] * len(groups))
         for row in range(len(rows), bucket):
             if held.row_state[row] is not None:  # the row becomes padding: token 0 at position 0 of the reserved page
                 mirror[token_at + row] = 0
                 mirror[future_at + row] = -1
                 mirror[position_at + row] = 0
                 mirror[length_at + row] = 1
-                mirror[slot_at + row] = 0
+                mirror[slot_at + row] = self.cache.scratch_state_slot
                 for group in groups:
                     base = table_at + (group.index * bucket + row) * width
                     mirror[base : base + width] = 0
@@ -492,13 +491,11 @@ class ModelRunner:
         held.meta.copy_(pinned, non_blocking=True)
         event.record()
 
-    def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict,
-                 sampled: Optional[torch.Tensor] = None) -> _Graph:
+    def _capture(self, key: tuple[int, int], host: torch.Tensor, layout: dict, facts: dict) -> _Graph:
         bucket, _ = key
         workspace = self.graph_workspace
         meta = torch.zeros(host.numel(), dtype=torch.int32, device=self.device)
         meta.copy_(host)
-        self._patch_tokens(meta, layout, sampled)  # the warm-up runs below write keys and values of these tokens
         graph_layout = dict(layout)
         # inside the graph every row's single token gives logits
         want_all = torch.arange(bucket, dtype=torch.int32, device=self.device)

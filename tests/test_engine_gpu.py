@@ -329,3 +329,43 @@ def test_logprobs_of_generated_tokens(dtype, depth):
             total += entry[token]
             tokens.append(token)
         assert completion.cumulative_logprob == pytest.approx(total, abs=1e-4)
+
+
+@pytest.mark.parametrize("name", ["llama", "wide"])
+def test_decode_graphs_under_preemption_and_ids_used_again(name):
+    """Short prompts, long generations, a large token budget and few pages: requests are preempted
+    out of steps of single tokens and come back into them, into rows of graphs that showed their
+    old pages; then the same ids are submitted again.  fp32 greedy tokens are the plain model's in
+    both decode modes, and every kind of event is counted."""
+    from kairyu_b200 import SamplingParams
+    from kairyu_b200.config.engine_config import EngineConfig
+    from kairyu_b200.engine.engine import Engine
+
+    config, seed, page_size = TINY[name]
+    prompts = prompts_of(config, [3, 5, 2, 7, 4], seed=150)
+    new_tokens = [40, 55, 48, 36, 60]
+    results = {}
+    for mode in ("eager", "cuda_graph"):
+        options = EngineConfig.from_kwargs(
+            dtype="float32", seed=seed, page_size=page_size, num_pages=2 + 150 // page_size, max_num_seqs=4,
+            max_num_batched_tokens=256, decode_mode=mode,
+        )
+        engine = Engine.from_random(config, seed, options)
+        tokens = []
+        for turn in range(2):  # the second turn uses the ids of the first again
+            for index, prompt in enumerate(prompts):
+                engine.add_request(f"request-{index}", prompt, SamplingParams(temperature=0.0, max_tokens=new_tokens[index]))
+            finished = engine.run_to_completion()
+            tokens.append([finished[f"request-{index}"].output_token_ids for index in range(len(prompts))])
+            engine.cache.check()
+            assert engine.cache.live_requests == 0
+        engine.runner.check_errors()
+        assert engine.scheduler.counters["preemptions"] > 0
+        if mode == "cuda_graph":
+            assert engine.runner.counters["graph_replays"] > 50
+        results[mode] = tokens
+        weights = engine_weights(type("Holder", (), {"engine": engine}))
+    expected = [tuple(plain_generate(config, weights, prompt, count)) for prompt, count in zip(prompts, new_tokens)]
+    for mode, turns in results.items():
+        for turn in turns:
+            assert turn == expected, mode

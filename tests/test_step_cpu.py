@@ -172,3 +172,73 @@ def test_descriptor_table_never_frees_what_a_call_may_still_point_at(monkeypatch
         assert all(ref() is not None for ref in recent), step
     assert len(kernels._tensor_maps) <= 4 and len(kernels._tensor_maps_before) <= 4
     del ctypes
+
+
+def _padding_graph(runner, bucket):
+    """The host side of a captured decode graph (mirror, layout, row state) without a device."""
+    from kairyu_b200.engine.runner import _Graph
+
+    host, layout, _ = runner._pack((), pad_rows=bucket, max_pages=runner.max_pages_per_request, include_want=False)
+    held = _Graph(None, None, None, 0, layout)
+    held.mirror = host.numpy().copy()
+    held.row_state = [None] * bucket
+    return held
+
+
+def _mirror_table(runner, held, bucket, row, group=0):
+    width = runner.max_pages_per_request
+    base = held.layout["tables"][0] + (group * bucket + row) * width
+    return list(held.mirror[base : base + width])
+
+
+def _decode_rows(runner, names):
+    rows = []
+    for name in names:
+        start = runner.cache.get(name).num_tokens
+        assert runner.cache.ensure_capacity(name, start + 1, query_start=start)
+        rows.append((StepEntry(name, [1], (0,)), start, start + 1))
+    return rows
+
+
+def test_graph_mirror_follows_a_request_that_was_released_and_admitted_again():
+    """A request that comes back under the same id (after a preemption, or an id used again) holds
+    other pages; the row of the graph's metadata it lands on must show the new table, not the old
+    pages topped up."""
+    runner, _, _ = make_runner("llama", num_pages=12, page_size=4)
+    cache = runner.cache
+    bucket = 2
+    held = _padding_graph(runner, bucket)
+    assert _mirror_table(runner, held, bucket, 0) == [0] * runner.max_pages_per_request
+
+    def fill(name, tokens):
+        cache.admit(name)
+        assert cache.ensure_capacity(name, tokens, query_start=0)
+        cache.advance(name, tokens)
+
+    fill("a", 9)
+    fill("b", 5)
+    rows = _decode_rows(runner, ["a", "b"])
+    runner._update_mirror(held, rows, bucket)
+    for row, name in enumerate(["a", "b"]):
+        table = cache.block_table(name, 0)
+        assert _mirror_table(runner, held, bucket, row)[: len(table)] == table
+    first_pages = list(cache.block_table("a", 0))
+    cache.release("a")
+    fill("c", 7)  # takes some of a's pages
+    fill("a", 10)  # same id, other pages, same number of them
+    assert cache.block_table("a", 0) != first_pages
+    rows = _decode_rows(runner, ["a", "b"])
+    runner._update_mirror(held, rows, bucket)
+    table = cache.block_table("a", 0)
+    mirrored = _mirror_table(runner, held, bucket, 0)
+    assert mirrored[: len(table)] == table and set(mirrored[len(table) :]) == {-1}
+    # the same admission growing by a page is topped up in place
+    cache.advance("a", 12)
+    rows = _decode_rows(runner, ["a", "b"])
+    runner._update_mirror(held, rows, bucket)
+    table = cache.block_table("a", 0)
+    assert len(table) == 4 and _mirror_table(runner, held, bucket, 0)[:4] == table
+    # a row that empties becomes padding again: the reserved page and the scratch state slot
+    runner._update_mirror(held, _decode_rows(runner, ["b"]), bucket)
+    assert _mirror_table(runner, held, bucket, 1) == [0] * runner.max_pages_per_request
+    assert held.mirror[held.layout["state_slots"][0] + 1] == cache.scratch_state_slot

@@ -52,6 +52,13 @@ class DecayMixer(Mixer):
         assert cache.state is not None and cache.k is None
         out = torch.empty(x.shape[0], self.hidden_size, dtype=x.dtype, device=x.device)
         drive = x.float() @ self.w_in.float().t()
+        if ctx.num_tokens == ctx.num_rows:
+            # One token a row: everything on the device, so that a decode graph can replay it.
+            # Padding rows of a graph all name the scratch slot; what lands there is read by nobody.
+            slots = ctx.state_slots.long()
+            state = cache.state.index_select(0, slots) * DECAY + drive * (1 - DECAY)
+            cache.state.index_copy_(0, slots, state)
+            return (state @ self.w_out.float().t()).to(x.dtype)
         slots = ctx.state_slots.tolist()
         for row in range(len(ctx.host_qo_indptr) - 1):
             state = cache.state[slots[row]]
@@ -147,7 +154,7 @@ def plain_toy_logits(w: Mapping[str, torch.Tensor], tokens) -> torch.Tensor:
     return lin(plain_model.rms_norm(x, w["final_norm.weight"], EPS), w["head.weight"])
 
 
-def build(toy, device):
+def build(toy, device, decode_mode="eager"):
     model, _ = build_model(toy, dtype="float32", device=device)
     weights = random_tensors(model.tensor_specs(), seed=9, device="cpu")
     model.load({name: tensor.to(device) for name, tensor in weights.items()})
@@ -155,12 +162,12 @@ def build(toy, device):
     assert [g.slots for g in layout.groups] == [(0,)] and [b.slot for b in layout.states] == [1, 2]
     cache = CacheManager(layout, num_pages=24, page_size=8, max_requests=4)
     storage = CacheStorage(layout, num_pages=24, page_size=8, max_requests=4, dtype=model.dtype, device=device)
-    runner = ModelRunner(model, cache, storage, max_model_len=256, decode_mode="eager")
+    runner = ModelRunner(model, cache, storage, max_model_len=256, decode_mode=decode_mode, max_graph_batch=4)
     return runner, weights
 
 
-def check(toy, device):
-    runner, weights = build(toy, device)
+def check(toy, device, decode_mode="eager"):
+    runner, weights = build(toy, device, decode_mode)
     requests = traces.make_requests(VOCAB, [37, 20, 51, 9, 44, 30], seed=6)
     expected = {name: plain_toy_logits(weights, tokens).numpy() for name, tokens in requests.items()}
     for steps in (traces.trace_whole(requests), traces.trace_chunks(requests), traces.trace_mixed(requests, seed=2)):
@@ -177,6 +184,37 @@ def test_toy_architecture_on_cpu(toy, monkeypatch):
 @pytest.mark.gpu
 def test_toy_architecture_on_gpu(toy):
     check(toy, "cuda")
+
+
+@pytest.mark.gpu
+def test_toy_architecture_in_decode_graphs(toy):
+    """Steps of single tokens replay CUDA graphs.  A mixer with state must see every token of a
+    request once: the capture runs on padding rows only (they use a state slot no request
+    holds), and padding rows of a replay never touch a live request's state."""
+    runner, weights = build(toy, "cuda", "cuda_graph")
+    requests = traces.make_requests(VOCAB, [37, 20, 51, 9, 44, 30], seed=6)
+    expected = {name: plain_toy_logits(weights, tokens).numpy() for name, tokens in requests.items()}
+    # decode tails one request at a time (bucket 1), then three at a time in a bucket of four
+    # (one padding row), with requests of different lengths ending at different steps
+    steps = traces.trace_decode_tail(requests, 12)
+    result = traces.run_in_process(runner, steps)
+    worst = max(float(np.abs(row - expected[n][p]).max()) for (n, p), row in result.items())
+    assert worst < 3e-5, worst
+    names = list(requests)[:3]
+    head = 6
+    together = [{"step": 0, "entries": [{"id": n, "tokens": requests[n][:head], "want": []} for n in names], "end": []}]
+    longest = max(len(requests[n]) for n in names)
+    for index in range(head, longest):
+        live = [n for n in names if index < len(requests[n])]
+        together.append({
+            "step": len(together),
+            "entries": [{"id": n, "tokens": [requests[n][index]], "want": [0]} for n in live],
+            "end": [n for n in live if index == len(requests[n]) - 1],
+        })
+    result = traces.run_in_process(runner, together)
+    worst = max(float(np.abs(row - expected[n][p]).max()) for (n, p), row in result.items())
+    assert worst < 3e-5, worst
+    assert runner.counters["graph_replays"] > 40 and runner.counters["graph_captures"] >= 3
 
 
 # ------------------------------------------------------------------ a second toy: routing and another position encoding
