@@ -163,16 +163,28 @@ class CacheManager:
                 needed.append(max(0, last - first) - held)
         return needed
 
-    def can_hold(self, num_tokens: int) -> bool:
+    def peak_pages(self, num_tokens: int, portion: int = 1) -> list[int]:
+        """Per group, the most pages a request of ``num_tokens`` tokens holds at any time when it is
+        fed in portions of at most ``portion`` tokens.  A group that keeps every key holds them all;
+        a windowed group holds the window behind the portion's first query plus the portion itself
+        (one page more for a window that does not start on a page's edge)."""
+        whole = self.pages_for(num_tokens)
+        return [
+            whole if group.spec.window is None else min(whole, self.pages_for(group.spec.window + max(portion, 1)) + 1)
+            for group in self.layout.groups
+        ]
+
+    def can_hold(self, num_tokens: int, portion: int = 1) -> bool:
         """Whether an empty cache could ever hold a request of this many tokens."""
-        for group, pool in zip(self.layout.groups, self.pools):
-            if group.spec.window is None:
-                pages = self.pages_for(num_tokens)
-            else:
-                pages = min(self.pages_for(num_tokens), self.pages_for(group.spec.window) + 2)
-            if pages > pool.capacity:
-                return False
-        return True
+        return all(pages <= pool.capacity for pages, pool in zip(self.peak_pages(num_tokens, portion), self.pools))
+
+    def held_pages(self, request_id: Hashable) -> tuple[list[int], list[int]]:
+        """Per group: (pages the request's tables name, those of them that are its own, that is,
+        not read from the prefix tree)."""
+        record = self._requests[request_id]
+        named = [sum(1 for page in table if page >= 0) for table in record.tables]
+        own = [sum(1 for page in table[len(record.shared):] if page >= 0) for table in record.tables]
+        return named, own
 
     # ------------------------------------------------------------------ lifecycle
     def admit(self, request_id: Hashable, tokens: Optional[Sequence[int]] = None) -> RequestCache:

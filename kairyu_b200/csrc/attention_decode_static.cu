@@ -4,6 +4,8 @@
 
 #include "attention_mma.cuh"
 
+#include <cstdint>
+
 #define KB_MAX_DEVICES 64
 
 // The per-split partials of one call: first the unnormalised outputs
@@ -42,7 +44,12 @@ KB_EXPORT int kb_attention_decode_mma_static(const void* q, int q_stride, void* 
     if (num_rows == 0) return 0;
     if (!q || !out || !k_cache || !v_cache || !seq_lens || !block_table || !decode_rows || !decode_tokens) return KB_ERR_NULL;
     if (num_rows < 0 || max_seq_len < 1 || Hkv < 1 || Hq < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || Hkv > 65535) return KB_ERR_BAD_ARG;
-    if (q_stride % 8 != 0) return KB_ERR_BAD_ARG;
+    // What the Python wrapper of the ordinary entry point checks on tensors, a C caller has to
+    // be told here: the kernel copies 16 bytes at a time from q and from the cache pages.
+    if (q_stride % 8 != 0 || q_stride < Hq * D || out_stride < Hq * D) return KB_ERR_BAD_ARG;
+    if (page_size < 1 || max_pages < 1 || num_pages < 1 || window < 0 || D < 1) return KB_ERR_BAD_ARG;
+    if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) % 16 != 0) return KB_ERR_BAD_ARG;
+    if ((uintptr_t)out % 2 != 0 || ((uintptr_t)seq_lens | (uintptr_t)block_table | (uintptr_t)decode_rows | (uintptr_t)decode_tokens) % 4 != 0) return KB_ERR_BAD_ARG;
     const int dp = padded_dim(D);
     if (dp == 0) return KB_ERR_UNSUPPORTED_SIZE;
     const long long num_splits = ((long long)max_seq_len + DEC_SPLIT - 1) / DEC_SPLIT;

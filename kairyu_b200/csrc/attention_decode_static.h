@@ -50,6 +50,18 @@ extern "C" {
 //   k_cache, v_cache: [num_pages, page_size, Hkv, D] bf16
 //   seq_lens: [rows_total] int32; block_table: [rows_total, max_pages] int32
 //   decode_rows, decode_tokens: [num_rows] int32
+// Requirements, checked before anything is launched (KB_ERR_BAD_ARG, -1, if one fails;
+// KB_ERR_NULL, -3, for a null pointer; KB_ERR_UNSUPPORTED_SIZE, -2, for a head size that is
+// no multiple of 16 or beyond 256):
+//   - q, k_cache and v_cache start on 16-byte boundaries; q_stride is a multiple of 8
+//     elements; q_stride and out_stride are at least Hq * D; inner strides are 1;
+//   - the caches are contiguous in the layout above (a page of one cache is a contiguous
+//     [page_size, Hkv * D] tile);
+//   - page_size, max_pages, num_pages >= 1; window >= 0 (0: every key); Hq a multiple of
+//     Hkv with at most 16 query heads per KV head.
+// Not checked: that block_table entries lie in [0, num_pages).  A page outside the pool is
+// skipped (never read); the row's output then misses those keys, and this entry point has no
+// error word to report it in.  Keep tables valid.
 // Returns 0, a negative KB_ERR_* code, or a positive cudaError_t.
 int kb_attention_decode_mma_static(const void* q, int q_stride, void* out, int out_stride,
                                    const void* k_cache, const void* v_cache, const int* seq_lens,

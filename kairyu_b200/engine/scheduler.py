@@ -40,6 +40,13 @@ When pages run out:
   other running request is, outputs included (the reference raises here); the
   victim goes back to the front of the queue.  A request that is alone and
   still cannot grow is finished with reason ``"length"``;
+* a prompt is kept one token short of its end while finishing it could leave requests that
+  already decode without the pages they need to reach their limits: as long as it has not
+  sampled it is the cheap victim (nothing of its outputs is lost), once it decodes it is not
+  (scheduler.py:636-677, 719-730).  The spare pages are counted once a plan: free pages, plus
+  what unfinished prompts hold, minus what decoding requests still lack up to
+  ``prompt + max_new_tokens``; a prompt may finish if nothing decodes yet, if it will produce a
+  single token, or if the pages of its own whole life fit in that count;
 * a prefill portion that cannot get pages is skipped this step;
 * if a step would be empty while requests are unfinished, the youngest running
   request is preempted, or the stuck head is rejected
@@ -85,7 +92,7 @@ class Status(Enum):
 class RequestState:
     __slots__ = (
         "request", "status", "computed", "outputs", "in_flight", "finish_reason", "preemptions", "arrival",
-        "num_cached_tokens", "bypasses",
+        "num_cached_tokens", "bypasses", "decoding",
     )
 
     def __init__(self, request: EngineRequest, arrival: int) -> None:
@@ -99,6 +106,9 @@ class RequestState:
         self.arrival = arrival
         self.num_cached_tokens = 0  # tokens its first admission found in the prefix tree
         self.bypasses = 0  # times the request behind it was admitted while it waited for pages
+        # Since it was last admitted, a step has fed its last known token and sampled: from then on it
+        # is fed one token a step.  Until then it is a prompt (or a recomputation) under way.
+        self.decoding = False
 
     @property
     def total_tokens(self) -> int:
@@ -275,6 +285,7 @@ class Scheduler:
         if request_id in self.cache:
             self.cache.release(request_id)
         state.computed = 0
+        state.decoding = False
         state.status = Status.WAITING
         state.preemptions += 1
         self._enqueue(request_id, front=True)
@@ -302,7 +313,52 @@ class Scheduler:
             cap = min(cap, self.prefill_chunk_size)
         return cap
 
-    def _admit(self, request_id: str, budget: int, plan: list, taken: set) -> Optional[int]:
+    def _largest_portion(self) -> int:
+        return min(self.budget, self.prefill_chunk_size or self.budget)
+
+    # -- completion safety (kairyu/engine/core/scheduler.py:636-677, 719-730)
+    def _life_pages(self, state: RequestState) -> list[int]:
+        """Pages per group the request holds when it has produced its last token."""
+        return self.cache.peak_pages(len(state.request.prompt_token_ids) + state.request.max_new_tokens)
+
+    def _spare_pages(self) -> tuple[int, list[int]]:
+        """(requests that decode and will go on, pages per group that stay spare if each of them runs
+        to its limit): what is free or can be taken back, what unfinished prompts hold, less what the
+        decoding requests still lack."""
+        spare = [self.cache.available_pages(group.index) for group in self.cache.layout.groups]
+        decoders = 0
+        for request_id in self._running:
+            state = self._states[request_id]
+            named, own = self.cache.held_pages(request_id) if request_id in self.cache else ([0] * len(spare), [0] * len(spare))
+            if not state.decoding:
+                spare = [total + pages for total, pages in zip(spare, own)]
+            elif state.request.max_new_tokens > 1 and len(state.outputs) + state.in_flight < state.request.max_new_tokens:
+                decoders += 1
+                spare = [total - max(0, life - held) for total, life, held in zip(spare, self._life_pages(state), named)]
+        return decoders, spare
+
+    def _completion_cost(self, state: RequestState) -> list[int]:
+        """Pages per group that stop being spare when this prompt finishes: the ones it holds (they
+        can no longer be had back cheaply) and the ones it still lacks up to its limit."""
+        request_id = state.request.request_id
+        count = len(self.cache.layout.groups)
+        named, own = self.cache.held_pages(request_id) if request_id in self.cache else ([0] * count, [0] * count)
+        lacking = [max(0, life - held) for life, held in zip(self._life_pages(state), named)] if state.request.max_new_tokens > 1 else [0] * count
+        return [mine + more for mine, more in zip(own, lacking)]
+
+    def _may_complete(self, state: RequestState, safety: list) -> bool:
+        decoders, spare = safety
+        if state.request.max_new_tokens <= 1 or decoders < 1:
+            return True  # the first request to decode can have every unfinished prompt's pages
+        return all(cost <= room for cost, room in zip(self._completion_cost(state), spare))
+
+    def _note_completion(self, state: RequestState, safety: list) -> None:
+        safety[1] = [room - cost for room, cost in zip(safety[1], self._completion_cost(state))]
+        if state.request.max_new_tokens > 1:
+            safety[0] += 1
+        state.decoding = True
+
+    def _admit(self, request_id: str, budget: int, plan: list, taken: set, safety: list) -> Optional[int]:
         """Make a waiting request run if the pages its whole work needs are to be had: its first
         portion goes into ``plan``.  Returns the tokens it took from the budget, or None, with
         nothing changed, when it has to wait.  The caller takes it off the queue."""
@@ -311,13 +367,16 @@ class Scheduler:
             record = self.cache.admit(request_id, state.all_tokens())
         except OutOfPages:
             return None
-        needed = self.cache.pages_needed(request_id, state.total_tokens, record.num_tokens)
+        # every page of its work; a windowed group needs its window and one portion only
+        needed = [pages - len(record.shared) for pages in self.cache.peak_pages(state.total_tokens, self._largest_portion())]
         if any(count > self.cache.available_pages(group) for group, count in enumerate(needed)):
             self.cache.release(request_id)
             return None
         state.computed = record.num_tokens  # the pages the prefix tree already holds
         count = min(state.remaining, budget, self._chunk_cap(budget, 1))
-        if not self._grow(state, count):
+        if count == state.remaining and not self._may_complete(state, safety):
+            count -= 1  # stays one token short until the decoding requests are safe
+        if count < 1 or not self._grow(state, count):
             state.computed = 0
             self.cache.release(request_id)
             return None
@@ -330,7 +389,9 @@ class Scheduler:
         completes = count == state.remaining
         plan.append(ScheduledChunk(request_id, state.computed, count, count > 1 or not completes, completes))
         state.computed += count
-        state.in_flight += 1 if completes else 0
+        if completes:
+            state.in_flight += 1
+            self._note_completion(state, safety)
         taken.add(request_id)
         return count
 
@@ -366,7 +427,7 @@ class Scheduler:
             if budget < 1:
                 break
             state = self._states.get(request_id)
-            if state is None or state.status is not Status.RUNNING or state.remaining != 1:
+            if state is None or state.status is not Status.RUNNING or not state.decoding or state.remaining != 1:
                 continue
             if len(state.outputs) + state.in_flight >= state.request.max_new_tokens:
                 continue  # its last token is in flight
@@ -388,23 +449,29 @@ class Scheduler:
                 self._finish(state, "length")
                 rejected.append(request_id)
 
-        # 2. running prefills share what is left of the budget
+        # 2. running prefills share what is left of the budget.  Whether one may finish is judged
+        # against the requests that decode now (step 1 may have ended or preempted some).
+        safety = list(self._spare_pages())
         prefilling = [
             request_id
             for request_id in self._running
-            if self._states[request_id].remaining > 1 and request_id not in taken
+            if not self._states[request_id].decoding and self._states[request_id].remaining >= 1 and request_id not in taken
         ]
         for index, request_id in enumerate(prefilling):
             if budget < 1:
                 break
             state = self._states[request_id]
             count = min(state.remaining, budget, self._chunk_cap(budget, len(prefilling) - index))
+            if count == state.remaining and not self._may_complete(state, safety):
+                count -= 1  # stays one token short until the decoding requests are safe
             if count < 1 or not self._grow(state, count):
                 continue
             completes = count == state.remaining
-            plan.append(ScheduledChunk(request_id, state.computed, count, True, completes))
+            plan.append(ScheduledChunk(request_id, state.computed, count, count > 1 or not completes, completes))
             state.computed += count
-            state.in_flight += 1 if completes else 0
+            if completes:
+                state.in_flight += 1
+                self._note_completion(state, safety)
             taken.add(request_id)
             budget -= count
 
@@ -412,20 +479,20 @@ class Scheduler:
         while self._waiting and budget >= 1:
             if len(self._running) >= self.max_num_seqs:
                 break
-            partial = sum(1 for r in self._running if self._states[r].remaining > 1 and r not in taken) + sum(
+            partial = sum(1 for r in self._running if not self._states[r].decoding and r not in taken) + sum(
                 1 for chunk in plan if chunk.is_prefill and not chunk.samples
             )
             if partial >= self.max_num_partial_prefills:
                 break
             head = self._waiting[0]
             state = self._states[head]
-            if not self.cache.can_hold(state.total_tokens):
+            if not self.cache.can_hold(state.total_tokens, self._largest_portion()):
                 self._waiting.popleft()
                 self._finish(state, "length", in_running=False)
                 self.counters["rejections"] += 1
                 rejected.append(head)
                 continue
-            used = self._admit(head, budget, plan, taken)
+            used = self._admit(head, budget, plan, taken, safety)
             if used is not None:
                 self._waiting.popleft()
                 budget -= used
@@ -435,9 +502,9 @@ class Scheduler:
             if not self._running or state.bypasses >= MAX_WAITING_BYPASSES or len(self._waiting) < 2:
                 break
             successor = self._waiting[1]
-            if not self.cache.can_hold(self._states[successor].total_tokens):
+            if not self.cache.can_hold(self._states[successor].total_tokens, self._largest_portion()):
                 break
-            used = self._admit(successor, budget, plan, taken)
+            used = self._admit(successor, budget, plan, taken, safety)
             if used is None:
                 break
             state.bypasses += 1

@@ -333,21 +333,21 @@ def test_logprobs_of_generated_tokens(dtype, depth):
 
 @pytest.mark.parametrize("name", ["llama", "wide"])
 def test_decode_graphs_under_preemption_and_ids_used_again(name):
-    """Short prompts, long generations, a large token budget and few pages: requests are preempted
-    out of steps of single tokens and come back into them, into rows of graphs that showed their
-    old pages; then the same ids are submitted again.  fp32 greedy tokens are the plain model's in
+    """Long generations, a large token budget and few pages: prompts that wait one token short of
+    their end are preempted by decoding requests that need their pages, come back, and decode in
+    rows of graphs that showed other pages before; then the same ids are submitted again.  fp32 greedy tokens are the plain model's in
     both decode modes, and every kind of event is counted."""
     from kairyu_b200 import SamplingParams
     from kairyu_b200.config.engine_config import EngineConfig
     from kairyu_b200.engine.engine import Engine
 
     config, seed, page_size = TINY[name]
-    prompts = prompts_of(config, [3, 5, 2, 7, 4], seed=150)
+    prompts = prompts_of(config, [29, 31, 27, 30, 26], seed=150)
     new_tokens = [40, 55, 48, 36, 60]
     results = {}
     for mode in ("eager", "cuda_graph"):
         options = EngineConfig.from_kwargs(
-            dtype="float32", seed=seed, page_size=page_size, num_pages=2 + 150 // page_size, max_num_seqs=4,
+            dtype="float32", seed=seed, page_size=page_size, num_pages=1 + 192 // page_size, max_num_seqs=4,
             max_num_batched_tokens=256, decode_mode=mode,
         )
         engine = Engine.from_random(config, seed, options)

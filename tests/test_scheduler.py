@@ -313,3 +313,69 @@ def test_preempted_request_keeps_its_place_under_priority_scheduling():
         preempted.extend(plan.preempted)
     assert not scheduler.has_unfinished() and preempted
     assert [len(scheduler.output_tokens(name)) for name in ("old", "young", "later-but-urgent")] == [8, 8, 1]
+
+
+def test_a_prompt_stays_one_token_short_while_finishing_it_could_strand_running_decodes():
+    """kairyu/engine/core/scheduler.py:636-677.  Two requests decode and will need 4 pages each in
+    the end; 9 pages exist.  A third prompt fits beside them now, but as a decoding request it
+    could not be pushed out cheaply when they grow: it is fed up to its last token and waits
+    there, is the one to be preempted when a decode needs its page, and finishes its prompt once
+    a decoding request has ended."""
+    scheduler, cache = make(num_pages=10, page_size=4, max_num_batched_tokens=64)  # 9 usable pages
+    scheduler.add_request(request("a", 6, max_new=10))  # 16 tokens in the end: 4 pages
+    scheduler.add_request(request("b", 6, max_new=10))
+    plan, _ = run_step(scheduler, cache)
+    assert [(c.request_id, c.num_tokens, c.samples) for c in plan.scheduled] == [("a", 6, True), ("b", 6, True)]
+    scheduler.add_request(request("c", 7, max_new=6))  # 13 tokens in the end: 4 pages; 9 - 8 leave 1
+    plan, _ = run_step(scheduler, cache)
+    by_id = {c.request_id: c for c in plan.scheduled}
+    assert (by_id["c"].num_tokens, by_id["c"].samples, by_id["c"].is_prefill) == (6, False, True)
+    assert scheduler.state("c").remaining == 1 and not scheduler.state("c").decoding
+    waited = 0
+    preempted = []
+    finished_at = {}
+    for step in range(60):
+        if not scheduler.has_unfinished():
+            break
+        plan, finished = run_step(scheduler, cache)
+        preempted.extend(plan.preempted)
+        for name in finished:
+            finished_at[name] = step
+        if "c" in scheduler.running_ids() and not scheduler.state("c").decoding and not any(c.request_id == "c" for c in plan.scheduled):
+            waited += 1
+    assert waited > 0
+    assert set(preempted) <= {"c"}  # a and b never lose their outputs
+    assert scheduler.state("a").preemptions == 0 and scheduler.state("b").preemptions == 0
+    assert [len(scheduler.output_tokens(name)) for name in "abc"] == [10, 10, 6]
+    assert finished_at["c"] > min(finished_at["a"], finished_at["b"])
+    assert cache.live_requests == 0
+
+
+def test_a_prompt_may_finish_when_nothing_decodes_or_it_wants_one_token():
+    scheduler, cache = make(num_pages=5, page_size=4, max_num_batched_tokens=64)  # 4 usable pages
+    scheduler.add_request(request("a", 6, max_new=30))  # could never reach its limit; the first to decode goes on anyway
+    plan, _ = run_step(scheduler, cache)
+    assert plan.scheduled[0].samples
+    scheduler.add_request(request("one", 5, max_new=1))  # produces a single token: nothing to protect it from
+    plan, _ = run_step(scheduler, cache)
+    assert {c.request_id: c.samples for c in plan.scheduled} == {"a": True, "one": True}
+
+
+def test_a_windowed_group_admits_a_prompt_longer_than_its_pool():
+    """A group that keeps a window of keys needs the window and one portion, not the whole prompt:
+    a prompt of more tokens than the pool has room for is admitted and runs through."""
+    layout = CacheLayout.from_slot_specs({0: (PagedKVSpec(1, 16, 8),)})  # window of 8 tokens
+    cache = CacheManager(layout, num_pages=9, page_size=4, max_requests=4)  # 8 usable pages: 32 tokens
+    scheduler = Scheduler(cache, max_num_batched_tokens=8)
+    scheduler.add_request(request("long", 70, max_new=5))
+    steps = 0
+    while scheduler.has_unfinished() and steps < 100:
+        plan, _ = run_step(scheduler, cache)
+        assert plan.scheduled and not plan.rejected
+        steps += 1
+    assert scheduler.finish_reason("long") == "length" and len(scheduler.output_tokens("long")) == 5
+    # with portions larger than the pool can hold beside the window, the prompt is refused at the door
+    scheduler = Scheduler(cache, max_num_batched_tokens=64)
+    scheduler.add_request(request("hopeless", 70, max_new=5))
+    plan, _ = run_step(scheduler, cache)
+    assert plan.rejected == ("hopeless",)

@@ -1,7 +1,8 @@
 """The decode-attention entry point that allocates nothing
 (``kb_attention_decode_mma_static``, csrc/attention_decode_static.h), called
 through its exported C symbol the way a C host would, and compared with the
-ordinary entry point on two calls in a row.
+ordinary entry point and with attention written out in fp32 torch, on two calls
+in a row.
 
 The entry point is for callers that cannot allocate device memory around the
 call (all memory already given to a pool of their own, no allocator of the
@@ -18,6 +19,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
+ERR_BAD_ARG = -1
 ERR_SCRATCH_TOO_SMALL = -4
 BF16_TOLERANCE = 2e-2  # the bound the other bf16 attention tests use
 
@@ -37,6 +39,24 @@ def _case(seq_lens, Hq, Hkv, D, page_size, seed):
         rows=dev(torch.arange(rows, dtype=torch.int32)), tokens=dev(torch.arange(rows, dtype=torch.int32)),
         Hq=Hq, Hkv=Hkv, D=D, page_size=page_size, num_pages=num_pages, max_seq_len=max(seq_lens), count=rows,
     )
+
+
+def _plain_attention(case):
+    """softmax(q k^T / sqrt(D)) v per row and head over the row's pages, in fp32 torch."""
+    Hq, Hkv, D, page_size = case["Hq"], case["Hkv"], case["D"], case["page_size"]
+    group = Hq // Hkv
+    out = torch.zeros(case["count"], Hq * D)
+    k_all, v_all, table = case["k"].float().cpu(), case["v"].float().cpu(), case["table"].cpu()
+    q_all = case["q"].float().cpu()
+    for row, length in enumerate(case["seq_lens"].tolist()):
+        pages = table[row, : -(-length // page_size)].long()
+        keys = k_all[pages].reshape(-1, Hkv, D)[:length]
+        values = v_all[pages].reshape(-1, Hkv, D)[:length]
+        q = q_all[row, : Hq * D].view(Hq, D)
+        for head in range(Hq):
+            scores = keys[:, head // group] @ q[head] / math.sqrt(D)
+            out[row, head * D : (head + 1) * D] = torch.softmax(scores, dim=0) @ values[:, head // group]
+    return out
 
 
 def _static_entry():
@@ -86,6 +106,7 @@ def test_static_entry_matches_the_ordinary_one_twice_in_a_row():
         assert torch.cuda.memory_allocated() == before  # nothing was taken from torch's allocator either
         torch.cuda.synchronize()
         assert float((out.float() - expected.float()).abs().max()) <= BF16_TOLERANCE
+        assert float((out.float().cpu() - _plain_attention(case)).abs().max()) <= BF16_TOLERANCE
         assert float(out.float().abs().max()) > 0
 
 
@@ -99,3 +120,27 @@ def test_static_entry_refuses_what_its_scratch_cannot_hold():
     assert _call_static(function, case, out) == ERR_SCRATCH_TOO_SMALL
     torch.cuda.synchronize()
     assert float(out.float().abs().max()) == 0.0  # nothing ran
+
+
+def test_static_entry_refuses_bad_arguments_on_the_host():
+    """A C caller gets an error code, not a fault on the device: a pointer off its 16-byte
+    boundary, a page size of zero, an output narrower than its heads.  Nothing is launched."""
+    _, function = _static_entry()
+    case = _case([64] * 2, 4, 2, 32, 16, seed=4)
+    out = torch.zeros(case["count"], case["Hq"] * case["D"], dtype=torch.bfloat16, device="cuda")
+    good_q = case["q"]
+    padded = torch.zeros(good_q.numel() + 8, dtype=torch.bfloat16, device="cuda")
+    case["q"] = padded[1:][: good_q.numel()].view(good_q.shape)  # two bytes past a 16-byte boundary
+    assert case["q"].data_ptr() % 16 == 2
+    assert _call_static(function, case, out) == ERR_BAD_ARG
+    case["q"] = good_q
+    for key, value in (("page_size", 0), ("num_pages", 0)):
+        broken = dict(case, **{key: value})
+        assert _call_static(function, broken, out) == ERR_BAD_ARG
+    narrow = torch.zeros(case["count"], case["Hq"] * case["D"] - 8, dtype=torch.bfloat16, device="cuda")
+    assert _call_static(function, case, narrow) == ERR_BAD_ARG
+    torch.cuda.synchronize()
+    assert float(out.float().abs().max()) == 0.0
+    assert _call_static(function, case, out) == 0  # and the same arguments put right are accepted
+    torch.cuda.synchronize()
+    assert float((out.float().cpu() - _plain_attention(case)).abs().max()) <= BF16_TOLERANCE
