@@ -26,7 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Llama-3.1-8B shape
+# The headline configuration: the Llama-3.1-8B shape
 MODEL = {
     "architectures": ["LlamaForCausalLM"],
     "hidden_size": 4096,
@@ -57,8 +57,8 @@ GEN_LEN = 256
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
 
-# Further shapes (BASELINE.json configs[3] and [4]) for --shape; the default run and its JSON
-# contract are those of configs[2] above.
+# Further shapes (Qwen3-8B and Qwen3-32B) for --shape; the default run and its JSON
+# contract are those of the headline configuration above.
 SHAPES = {
     "llama31-8b": None,
     "qwen3-8b": dict(
@@ -271,12 +271,7 @@ def time_e2e(engine, batch: int, steps: int):
     from kairyu_b200 import SamplingParams, TokensPrompt
     from kairyu_b200.entrypoints.llm import LLM
 
-    llm = LLM.__new__(LLM)
-    llm.model = "random"
-    llm.seed = SEED
-    llm._model_dir = None
-    llm.engine = engine
-    llm._finish_init(None)
+    llm = LLM.from_engine(engine)
     prompts = [TokensPrompt(tuple(random_tokens(PROMPT_LEN, MODEL["vocab_size"], 200 + index))) for index in range(batch)]
 
     def run(max_tokens: int) -> float:
@@ -297,7 +292,7 @@ def time_e2e(engine, batch: int, steps: int):
 
 
 def time_mixed(layers: int) -> dict:
-    """BASELINE.json configs[3]'s workload through ``LLM.generate``: 32 requests with prompt lengths
+    """The mixed workload through ``LLM.generate``: 32 requests with prompt lengths
     uniform in [128, 4096], prompts cut into portions of 512 tokens beside the decodes of the others,
     128 generated tokens each.  Returns prompt+generated tokens a second and generated tokens a second."""
     import torch
@@ -317,9 +312,7 @@ def time_mixed(layers: int) -> dict:
         max_num_partial_prefills=1, pipeline_depth=2, seed=SEED,
     )
     engine = Engine.from_random(config, SEED, engine_config)
-    llm = LLM.__new__(LLM)
-    llm.model, llm.seed, llm._model_dir, llm.engine = "random", SEED, None, engine
-    llm._finish_init(None)
+    llm = LLM.from_engine(engine)
     prompts = [TokensPrompt(tuple(random_tokens(n, MODEL["vocab_size"], 300 + i))) for i, n in enumerate(lengths)]
     params = SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True)
     llm.generate(prompts[:4], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))  # warm
@@ -363,9 +356,7 @@ def time_shared_prefix(layers: int) -> dict:
             max_num_partial_prefills=1, pipeline_depth=2, enable_prefix_caching=caching, seed=SEED,
         )
         engine = Engine.from_random(config, SEED, engine_config)
-        llm = LLM.__new__(LLM)
-        llm.model, llm.seed, llm._model_dir, llm.engine = "random", SEED, None, engine
-        llm._finish_init(None)
+        llm = LLM.from_engine(engine)
         llm.generate(warm, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
         torch.cuda.synchronize()
         begin = time.perf_counter()

@@ -119,6 +119,10 @@ class CacheManager:
         self._requests: dict[Hashable, RequestCache] = {}
         self.fresh_state_slots: list[int] = []  # slots handed out since the storage last zeroed them
         self.prefix: Optional[PrefixIndex] = PrefixIndex(page_size) if prefix_sharing else None
+        # Debug aid: with ``log_freed_pages`` every page that goes back to a pool is noted, per
+        # group, until ``take_freed_pages`` is called (the step function can then overwrite them).
+        self.log_freed_pages = False
+        self._freed_log: list[list[int]] = [[] for _ in layout.groups]
 
     # ------------------------------------------------------------------ queries
     def __contains__(self, request_id: Hashable) -> bool:
@@ -264,14 +268,14 @@ class CacheManager:
                     stale.append(table[index])
                     table[index] = -1
             if stale:
-                pool.free(stale)
+                self._give_back(group.index, stale)
             record.first_live[group.index] = max(record.first_live[group.index], min(keep_from, len(table)))
 
     def _take_back(self, count: int) -> None:
         """Return ``count`` published pages that nobody reads to every pool."""
         for pages in self.prefix.evict(count):
-            for pool, page in zip(self.pools, pages):
-                pool.free([page])
+            for group, page in enumerate(pages):
+                self._give_back(group, [page])
 
     def publish(self, request_id: Hashable, tokens: Sequence[int]) -> int:
         """Make the whole pages this request has computed matchable; ``tokens`` are the tokens
@@ -301,14 +305,23 @@ class CacheManager:
         pools; the shared pages it read lose a reader and stay in the tree."""
         record = self._requests.pop(request_id)
         own_from = len(record.shared)
-        for table, pool in zip(record.tables, self.pools):
-            pool.free([page for page in table[own_from:] if page >= 0])
+        for group, table in enumerate(record.tables):
+            self._give_back(group, [page for page in table[own_from:] if page >= 0])
         if record.shared:
             self.prefix.drop(record.shared)
         self._free_state_slots.append(record.state_slot)
 
     def block_table(self, request_id: Hashable, group: int) -> list[int]:
         return self._requests[request_id].tables[group]
+
+    def _give_back(self, group: int, pages: Sequence[int]) -> None:
+        self.pools[group].free(pages)
+        if self.log_freed_pages:
+            self._freed_log[group].extend(pages)
+
+    def take_freed_pages(self) -> list[list[int]]:
+        freed, self._freed_log = self._freed_log, [[] for _ in self.layout.groups]
+        return freed
 
     def take_fresh_state_slots(self) -> list[int]:
         fresh, self.fresh_state_slots = self.fresh_state_slots, []

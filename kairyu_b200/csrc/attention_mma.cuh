@@ -47,7 +47,6 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // ---- mbarrier + bulk copy (the TMA unit moves whole key rows; one instruction per row)
 #define KB_FLAG_TIMEOUT 16
-#define MBAR_SPIN_LIMIT (1u << 20)
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
@@ -55,11 +54,14 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-// Waits for the phase with the given parity to complete; gives up after a bounded
-// number of polls and returns false (the caller raises a flag and leaves).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = MBAR_SPIN_LIMIT) {
+// Waits for the phase with the given parity to complete; gives up when the time limit
+// (KB_WAIT_LIMIT_NS) has passed and returns false (the caller raises a flag and leaves).
+// `polls` > 0 bounds the wait by that many polls instead: the brief waits of a block that is
+// leaving and only lets its copies in flight land.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t polls = 0) {
     const uint32_t addr = smem_u32(bar);
-    for (uint32_t spin = 0; spin < limit; ++spin) {
+    unsigned long long deadline = 0;
+    for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -67,8 +69,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
+        if (polls) {
+            if (spin + 1 >= polls) return false;
+        } else if ((spin & 63) == 63) {
+            const unsigned long long now = global_timer_ns();
+            if (deadline == 0) deadline = now + KB_WAIT_LIMIT_NS;
+            else if (now > deadline) return false;
+        }
     }
-    return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");

@@ -113,3 +113,13 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     total = warp_max(total);
     return total;
 }
+
+// Waits on barriers are bounded by time, not by a number of polls: two seconds on the GPU's
+// nanosecond timer, whatever the clocks are and however a profiler serialises the roles of a
+// block (a poll count that is generous at full speed ran out under a profiler's replay).
+#define KB_WAIT_LIMIT_NS 2000000000ull
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}

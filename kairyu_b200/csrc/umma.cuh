@@ -9,7 +9,6 @@
 
 #define KB_FLAG_TIMEOUT 16
 #define TC_BLOCK_ROWS 128  // rows of the M side of every tcgen05.mma issued here
-#define TC_SPIN_LIMIT (1u << 22)
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -20,10 +19,13 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait; also leaves when another role of the block has raised `abort`.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t limit = TC_SPIN_LIMIT) {
+// Bounded wait; also leaves when another role of the block has raised `abort`.  `polls` = 0:
+// bounded by time (KB_WAIT_LIMIT_NS); `polls` > 0: that many polls, for the brief waits of a
+// block that is leaving and only lets its copies in flight land.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, uint32_t polls = 0) {
     const uint32_t addr = smem_addr(bar);
-    for (uint32_t spin = 0; spin < limit; ++spin) {
+    unsigned long long deadline = 0;
+    for (uint32_t spin = 0;; ++spin) {
         uint32_t done;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -31,9 +33,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if ((spin & 63) == 63 && *abort) return false;
+        if (polls) {
+            if (spin + 1 >= polls) return false;
+        } else if ((spin & 63) == 63) {
+            if (*abort) return false;
+            const unsigned long long now = global_timer_ns();
+            if (deadline == 0) deadline = now + KB_WAIT_LIMIT_NS;
+            else if (now > deadline) return false;
+        }
     }
-    return false;
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {
     uint64_t p;

@@ -107,7 +107,13 @@ class ModelRunner:
         self.max_pages_per_request = -(-max_model_len // cache.page_size)
         self.decode_mode = decode_mode
         self.max_graph_batch = max_graph_batch
+        # Debug aid: pages that were given back since the last step are overwritten with a large
+        # finite value before the next one runs, so that a kernel that reads a page its request no
+        # longer (or not yet) holds gives logits far off, while keys that are read and masked,
+        # as the unwritten tail of a request's last page is, change nothing.
         self.debug_poison = debug_poison
+        if debug_poison:
+            cache.log_freed_pages = True
         # Per step, on the host: every page a row needs is there, and no page is named twice, in one
         # row or in two, except shared prefix pages, which no row may write
         # (kairyu/engine/core/prefill.py:105-178).  The cache manager guarantees this by
@@ -231,8 +237,11 @@ class ModelRunner:
             row_ids.extend([row] * count)
             qo_indptr.append(base + count)
             seq_lens.append(seq_len)
-            write_from.append(0)
-            state_slots.append(self.cache.get(entry.request_id).state_slot)
+            record = self.cache.get(entry.request_id)
+            # positions below this lie in pages the request only reads (its shared prefix): the
+            # kernels that write keys and values skip them, whatever the step's tokens say
+            write_from.append(len(record.shared) * page_size)
+            state_slots.append(record.state_slot)
             if include_want:
                 want.extend(base + place for place in entry.want)
             if count == 1:
@@ -356,6 +365,10 @@ class ModelRunner:
         else:
             self.counters["future_tokens"] += sum(1 for entry in entries if entry.future is not None)
         self.storage.zero_state_slots(self.cache.take_fresh_state_slots())
+        if self.debug_poison:
+            for group, pages in enumerate(self.cache.take_freed_pages()):
+                # a page that was handed out again since has not been written yet either
+                self.storage.poison_pages(group, pages, value=3.0e4)
         self.counters["steps"] += 1
         self.counters["tokens"] += sum(len(entry.tokens) for entry, _, _ in rows)
         pure_decode = all(len(entry.tokens) == 1 for entry, _, _ in rows)
@@ -441,6 +454,7 @@ class ModelRunner:
         position_at = layout["positions"][0]
         length_at = layout["seq_lens"][0]
         slot_at = layout["state_slots"][0]
+        write_at = layout["write_from"][0]
         table_at = layout["tables"][0]
         width = self.max_pages_per_request
         groups = self.cache.layout.groups
@@ -451,6 +465,7 @@ class ModelRunner:
             mirror[position_at + row] = start
             mirror[length_at + row] = seq_len
             mirror[slot_at + row] = record.state_slot
+            mirror[write_at + row] = len(record.shared) * self.cache.page_size
             need = self._needed_pages(seq_len)
             state = held.row_state[row]
             # The row's pages may be topped up only for the same admission of the request: an id
@@ -474,6 +489,7 @@ class ModelRunner:
                 mirror[position_at + row] = 0
                 mirror[length_at + row] = 1
                 mirror[slot_at + row] = self.cache.scratch_state_slot
+                mirror[write_at + row] = 0
                 for group in groups:
                     base = table_at + (group.index * bucket + row) * width
                     mirror[base : base + width] = 0

@@ -29,6 +29,7 @@ def _build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--prompt-token-ids", action="append", default=[], help="Comma-separated token ids; repeatable")
     generate.add_argument("--prompt-file", type=Path, default=None, help="JSON lines: a string or a list of token ids a line")
     generate.add_argument("--dtype", default="auto", choices=["auto", "bfloat16", "float32"])
+    generate.add_argument("--device", default="cuda", help="Device of the model and cache (the kernels need a CUDA device)")
     generate.add_argument("--seed", type=int, default=None)
     generate.add_argument("--temperature", type=float, default=1.0)
     generate.add_argument("--top-p", type=float, default=1.0)
@@ -91,7 +92,7 @@ def _generate(args: argparse.Namespace) -> int:
         max_tokens=args.max_tokens, min_tokens=args.min_tokens, ignore_eos=args.ignore_eos, logprobs=args.logprobs,
     )
     llm = LLM(
-        str(args.model), dtype=args.dtype, page_size=args.page_size, num_pages=args.num_pages,
+        str(args.model), dtype=args.dtype, device=args.device, page_size=args.page_size, num_pages=args.num_pages,
         max_num_batched_tokens=args.max_num_batched_tokens, max_num_seqs=args.max_num_seqs,
         max_model_len=args.max_model_len, decode_mode=args.decode_mode, pipeline_depth=args.pipeline_depth,
         enable_prefix_caching=args.enable_prefix_caching,
@@ -125,7 +126,10 @@ def _generate(args: argparse.Namespace) -> int:
 
 def _validate(args: argparse.Namespace) -> int:
     from kairyu_b200.engine.engine import build_model
+    import fnmatch
+
     from kairyu_b200.weights import CheckpointReader, WeightError, read_config
+    from kairyu_b200.weights.loading import IGNORED_TENSORS
 
     try:
         config = read_config(args.model)
@@ -136,8 +140,13 @@ def _validate(args: argparse.Namespace) -> int:
         wrong = [
             (s.name, reader.shape(s.name), tuple(s.shape)) for s in specs if s.name in reader and reader.shape(s.name) != tuple(s.shape)
         ]
-        if missing or wrong:
-            raise WeightError(str(args.model), missing, [], wrong, [])
+        known = {s.name for s in specs} | {s.alias_of for s in specs if s.alias_of}
+        unexpected = [
+            name for name in reader.names()
+            if name not in known and not any(fnmatch.fnmatch(name, pattern) for pattern in IGNORED_TENSORS)
+        ]
+        if missing or wrong or unexpected:
+            raise WeightError(str(args.model), missing, unexpected, wrong, [])
     except Exception as error:  # report, do not trace
         print(f"invalid: {error}")
         return 1

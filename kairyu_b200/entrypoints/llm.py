@@ -74,6 +74,17 @@ class LLM:
         self._finish_init(None)
         return self
 
+    @classmethod
+    def from_engine(cls, engine: Engine, *, model_dir: str | Path | None = None, tokenizer: str | None = None) -> "LLM":
+        """An LLM over an engine that was built elsewhere (its model, cache and options as they are)."""
+        self = cls.__new__(cls)
+        self.model = str(model_dir) if model_dir is not None else "engine"
+        self.seed = engine.config.seed
+        self._model_dir = Path(model_dir) if model_dir is not None else None
+        self.engine = engine
+        self._finish_init(tokenizer)
+        return self
+
     def _finish_init(self, tokenizer: str | None) -> None:
         self.eos_token_ids = _eos_token_ids(self._model_dir, self.engine.model_config)
         self._tokenizer = None

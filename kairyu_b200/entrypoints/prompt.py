@@ -7,9 +7,6 @@ from collections.abc import Mapping, Sequence
 from dataclasses import dataclass
 from typing import Union
 
-_MAX_TOKEN_ID = (1 << 64) - 1
-
-
 @dataclass(frozen=True)
 class TextPrompt:
     prompt: str
@@ -17,26 +14,28 @@ class TextPrompt:
 
 @dataclass(frozen=True)
 class TokensPrompt:
+    """Token ids given by the caller; ``prompt`` may carry the text they came from.  The ids are
+    kept as a tuple of true ints in [0, 2^64); anything else is refused at construction
+    (kairyu/engine/prompt.py:58-92 has the same rules)."""
+
     prompt_token_ids: tuple[int, ...]
     prompt: str | None = None
 
     def __post_init__(self) -> None:
-        token_ids = self.prompt_token_ids
-        if isinstance(token_ids, (str, bytes, bytearray)) or not isinstance(token_ids, Sequence):
-            raise TypeError("TokensPrompt.prompt_token_ids must be a sequence of integers")
-        copied = tuple(token_ids)
-        if not copied:
-            raise ValueError("TokensPrompt.prompt_token_ids must not be empty")
-        for token_id in copied:
-            if type(token_id) is not int:
-                raise TypeError(
-                    f"TokensPrompt.prompt_token_ids must contain integers, not {type(token_id).__name__}"
-                )
-            if not 0 <= token_id <= _MAX_TOKEN_ID:
-                raise ValueError("TokensPrompt.prompt_token_ids values must be non-negative")
-        if self.prompt is not None and type(self.prompt) is not str:
-            raise TypeError("TokensPrompt.prompt must be a string or None")
-        object.__setattr__(self, "prompt_token_ids", copied)
+        given = self.prompt_token_ids
+        if isinstance(given, (str, bytes, bytearray)) or not isinstance(given, Sequence):
+            raise TypeError(f"prompt_token_ids: a sequence of token ids is needed, got {type(given).__name__}")
+        ids = tuple(given)
+        strangers = sorted({type(item).__name__ for item in ids if type(item) is not int})
+        if strangers:
+            raise TypeError(f"prompt_token_ids: token ids are integers; found {', '.join(strangers)}")
+        if not ids:
+            raise ValueError("prompt_token_ids: at least one token is needed")
+        if min(ids) < 0 or max(ids) >= 2**64:
+            raise ValueError("prompt_token_ids: token ids lie in [0, 2^64)")
+        if not (self.prompt is None or type(self.prompt) is str):
+            raise TypeError("prompt: the text of a TokensPrompt is a str or None")
+        object.__setattr__(self, "prompt_token_ids", ids)
 
 
 PromptInput = Union[str, TextPrompt, TokensPrompt, Mapping]

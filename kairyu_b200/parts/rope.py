@@ -33,34 +33,36 @@ def _llama3_inv_freq(inv_freq: torch.Tensor, scaling: RopeScaling) -> torch.Tens
     return torch.where(medium, smoothed, scaled)
 
 
-def _yarn_mscale(scale: float, mscale: float = 1.0) -> float:
-    return 1.0 if scale <= 1.0 else 0.1 * mscale * math.log(scale) + 1.0
+def _yarn_amplitude(factor: float, mscale: float = 1.0) -> float:
+    """The factor yarn puts on cos and sin (it stands for a softmax temperature): 1 + 0.1 m ln(s)
+    for a context stretched s > 1 times."""
+    return 1.0 + 0.1 * mscale * math.log(factor) if factor > 1.0 else 1.0
 
 
 def _yarn_inv_freq(dim: int, theta: float, scaling: RopeScaling) -> tuple[torch.Tensor, float]:
-    """kairyu/models/layers.py:55-81."""
-    pos_freqs = theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim)
-    extrapolation = 1.0 / pos_freqs
-    interpolation = 1.0 / (scaling.factor * pos_freqs)
-    original = scaling.original_max_position_embeddings
+    """Yarn ("NTK by parts"): pairs of the head that turn often within the original context keep
+    their frequency, pairs that turn less than ``beta_slow`` times are slowed ``factor`` times
+    (positions interpolated), and the pairs between blend the two linearly in the pair index.
+    Pair i has frequency theta^(-2i/dim) and so makes L * theta^(-2i/dim) / 2 pi turns over the
+    original context L; solved for i, ``turns`` turns are made by pair
+    dim * ln(L / (2 pi turns)) / (2 ln theta).  The blend's ends are that index for ``beta_fast``
+    rounded down and for ``beta_slow`` rounded up, as kairyu/models/layers.py:55-81 has them."""
+    base = theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim)
+    kept, slowed = 1.0 / base, 1.0 / (scaling.factor * base)
+    context = scaling.original_max_position_embeddings
 
-    def correction_dim(rotations: float) -> float:
-        return (dim * math.log(original / (rotations * 2 * math.pi))) / (2 * math.log(theta))
+    def pair_with(turns: float) -> float:
+        return dim * math.log(context / (2 * math.pi * turns)) / (2 * math.log(theta))
 
-    low = max(math.floor(correction_dim(scaling.beta_fast)), 0)
-    high = min(math.ceil(correction_dim(scaling.beta_slow)), dim - 1)
-    if low == high:
-        high += 0.001
-    ramp = ((torch.arange(dim // 2).float() - low) / (high - low)).clamp(0, 1)
-    keep = 1.0 - ramp
-    inv_freq = interpolation * (1.0 - keep) + extrapolation * keep
+    first = max(math.floor(pair_with(scaling.beta_fast)), 0)
+    last = min(math.ceil(pair_with(scaling.beta_slow)), dim - 1)
+    span = last - first if last != first else 0.001
+    slowed_share = ((torch.arange(dim // 2).float() - first) / span).clamp(0, 1)
+    inv_freq = slowed * slowed_share + kept * (1.0 - slowed_share)
+    amplitude = _yarn_amplitude(scaling.factor)
     if scaling.mscale is not None and scaling.mscale_all_dim is not None:
-        factor = _yarn_mscale(scaling.factor, scaling.mscale) / _yarn_mscale(
-            scaling.factor, scaling.mscale_all_dim
-        )
-    else:
-        factor = _yarn_mscale(scaling.factor)
-    return inv_freq, factor
+        amplitude = _yarn_amplitude(scaling.factor, scaling.mscale) / _yarn_amplitude(scaling.factor, scaling.mscale_all_dim)
+    return inv_freq, amplitude
 
 
 def rotary_tables(

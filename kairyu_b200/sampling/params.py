@@ -9,17 +9,11 @@ import dataclasses
 from dataclasses import dataclass, field
 from typing import Sequence
 
-_INT64_MAX = (1 << 63) - 1
-_INT64_MIN = -(1 << 63)
-_UINT64_MAX = (1 << 64) - 1
+I64_LOW, I64_HIGH, U64_HIGH = -(2**63), 2**63 - 1, 2**64 - 1
 
 
-def _normalize_stop(stop: str | Sequence[str] | None) -> tuple[str, ...]:
-    if stop is None:
-        return ()
-    if isinstance(stop, str):
-        return (stop,)
-    return tuple(stop)
+def _is_int(value: object) -> bool:
+    return type(value) is int  # bool is not accepted as an integer
 
 
 @dataclass(frozen=True)
@@ -45,45 +39,51 @@ class SamplingParams:
     extra_args: dict = field(default_factory=dict, compare=False)
 
     def __post_init__(self) -> None:
-        object.__setattr__(self, "stop", _normalize_stop(self.stop))
-        object.__setattr__(self, "stop_token_ids", tuple(self.stop_token_ids) if self.stop_token_ids else ())
-        self._validate()
+        stop = self.stop
+        stop = () if stop is None else (stop,) if isinstance(stop, str) else tuple(stop)
+        object.__setattr__(self, "stop", stop)
+        object.__setattr__(self, "stop_token_ids", tuple(self.stop_token_ids or ()))
+        problems = self._problems()
+        if problems:
+            raise ValueError("; ".join(problems))
 
-    def _validate(self) -> None:
-        if self.seed is not None and (type(self.seed) is not int or not _INT64_MIN <= self.seed <= _UINT64_MAX):
-            raise ValueError("seed must fit signed or unsigned 64-bit range")
-        if type(self.top_k) is not int or self.top_k > _INT64_MAX:
-            raise ValueError("top_k must be a signed 64-bit integer")
-        if any(type(t) is not int or not 0 <= t <= _INT64_MAX for t in self.stop_token_ids):
-            raise ValueError("stop_token_ids must contain only non-negative 64-bit integers")
-        if self.n < 1:
-            raise ValueError(f"n must be >= 1, got {self.n}")
-        if self.temperature < 0.0:
-            raise ValueError(f"temperature must be >= 0, got {self.temperature}")
-        if not 0.0 < self.top_p <= 1.0:
-            raise ValueError(f"top_p must be in (0, 1], got {self.top_p}")
-        if self.top_k < -1 or self.top_k == 0:
-            raise ValueError(f"top_k must be -1 or >= 1, got {self.top_k}")
-        if not 0.0 <= self.min_p <= 1.0:
-            raise ValueError(f"min_p must be in [0, 1], got {self.min_p}")
-        if self.repetition_penalty <= 0.0:
-            raise ValueError(f"repetition_penalty must be > 0, got {self.repetition_penalty}")
-        if not -2.0 <= self.presence_penalty <= 2.0:
-            raise ValueError(f"presence_penalty must be in [-2, 2], got {self.presence_penalty}")
-        if not -2.0 <= self.frequency_penalty <= 2.0:
-            raise ValueError(f"frequency_penalty must be in [-2, 2], got {self.frequency_penalty}")
-        if self.max_tokens is not None and (type(self.max_tokens) is not int or not 1 <= self.max_tokens <= _INT64_MAX):
-            raise ValueError(f"max_tokens must be >= 1, got {self.max_tokens}")
-        if type(self.min_tokens) is not int or not 0 <= self.min_tokens <= _INT64_MAX:
-            raise ValueError(f"min_tokens must be >= 0, got {self.min_tokens}")
-        if self.max_tokens is not None and self.min_tokens > self.max_tokens:
-            raise ValueError(
-                f"min_tokens must be <= max_tokens, got min_tokens={self.min_tokens}, max_tokens={self.max_tokens}"
-            )
-        for name in ("logprobs", "prompt_logprobs"):
+    def _problems(self) -> list[str]:
+        """Everything wrong with the values, in words; empty when they are fine.  The rules are the
+        reference's (kairyu/sampling_params.py:222-313): integers are true ints within 64 bits, the
+        filters' ranges, min_tokens within max_tokens."""
+        found: list[str] = []
+
+        def integer(name: str, low: int, high: int, *, optional: bool = False) -> bool:
             value = getattr(self, name)
-            if value is not None and (type(value) is not int or not _INT64_MIN <= value <= _INT64_MAX):
-                raise ValueError(f"{name} must be a signed 64-bit integer or None")
+            if value is None and optional:
+                return False
+            if not _is_int(value) or not low <= value <= high:
+                found.append(f"{name}={value!r} is not an integer in [{low}, {high}]")
+                return False
+            return True
+
+        def real(name: str, ok: bool, rule: str) -> None:
+            if not ok:
+                found.append(f"{name}={getattr(self, name)!r} must be {rule}")
+
+        integer("seed", I64_LOW, U64_HIGH, optional=True)
+        integer("logprobs", I64_LOW, I64_HIGH, optional=True)
+        integer("prompt_logprobs", I64_LOW, I64_HIGH, optional=True)
+        if integer("top_k", -1, I64_HIGH) and self.top_k == 0:
+            found.append("top_k=0 keeps no token; use -1 for no limit or a count >= 1")
+        integer("n", 1, I64_HIGH)
+        has_max = integer("max_tokens", 1, I64_HIGH, optional=True)
+        if integer("min_tokens", 0, I64_HIGH) and has_max and self.min_tokens > self.max_tokens:
+            found.append(f"min_tokens={self.min_tokens} exceeds max_tokens={self.max_tokens}")
+        if not all(_is_int(token) and 0 <= token <= I64_HIGH for token in self.stop_token_ids):
+            found.append("stop_token_ids holds something that is not a token id (an integer in [0, 2^63))")
+        real("temperature", self.temperature >= 0.0, "0 (greedy) or positive")
+        real("top_p", 0.0 < self.top_p <= 1.0, "in (0, 1]")
+        real("min_p", 0.0 <= self.min_p <= 1.0, "in [0, 1]")
+        real("repetition_penalty", self.repetition_penalty > 0.0, "positive")
+        real("presence_penalty", -2.0 <= self.presence_penalty <= 2.0, "in [-2, 2]")
+        real("frequency_penalty", -2.0 <= self.frequency_penalty <= 2.0, "in [-2, 2]")
+        return found
 
     def clone(self, **overrides: object) -> "SamplingParams":
         return dataclasses.replace(self, **overrides)  # type: ignore[arg-type]

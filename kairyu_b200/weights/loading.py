@@ -1,6 +1,12 @@
 """Binds checkpoint tensors to a model's parts by name, with one error that
 says everything that is wrong with the file (kairyu/models/loader.py:106-265
-raises on the first missing tensor and ignores the rest)."""
+raises on the first missing tensor and ignores the rest).
+
+Tensors the model does not ask for are passed over, as the reference does
+(``strict=False``, kairyu/models/loader.py:250): exports carry stray buffers.
+They are still named in the error when something else is wrong, and
+``strict_unexpected=True`` (the ``validate`` command) makes them an error of
+their own."""
 
 from __future__ import annotations
 
@@ -74,7 +80,7 @@ def held_dtype(spec: TensorSpec, stored_tag: str, compute: torch.dtype) -> torch
     return compute
 
 
-def load_into(model: Any, model_dir: str | Path, *, strict_unexpected: bool = True) -> None:
+def load_into(model: Any, model_dir: str | Path, *, strict_unexpected: bool = False) -> None:
     """Fill every part of ``model`` (a DecoderModel) from ``model_dir``."""
     reader = CheckpointReader(model_dir)
     specs: list[TensorSpec] = model.tensor_specs()

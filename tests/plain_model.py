@@ -36,7 +36,7 @@ def plain_config(config: Mapping) -> dict:
         "eps": config.get("rms_norm_eps", 1e-6),
         "theta": float(config.get("rope_theta", rope.get("rope_theta", 10000.0))),
         "rope_kind": rope.get("rope_type", rope.get("type")),
-        "rope": rope,
+        "rope": {"original_max_position_embeddings": config.get("max_position_embeddings", 4096), **rope},
         "max_positions": config.get("max_position_embeddings", 4096),
         "tie": config.get("tie_word_embeddings", False),
         "bias": bool(config.get("attention_bias")),
@@ -75,13 +75,47 @@ def rope_cos_sin(cfg: Mapping, positions: torch.Tensor) -> tuple[torch.Tensor, t
     """kairyu/models/layers.py:113-152: fp32 table rows, [T, head_dim] (both halves)."""
     dim = cfg["head_dim"]
     inv_freq = 1.0 / (cfg["theta"] ** (torch.arange(0, dim, 2, dtype=torch.int64).to(torch.float32) / dim))
+    amplitude = 1.0
     if cfg["rope_kind"] == "llama3":
         inv_freq = llama3_inv_freq(inv_freq, cfg["rope"])
+    elif cfg["rope_kind"] == "yarn":
+        inv_freq, amplitude = yarn_inv_freq(dim, cfg["theta"], cfg["rope"])
     elif cfg["rope_kind"] not in (None, "default"):
         raise ValueError(f"plain model: rope type {cfg['rope_kind']!r} is not restated here")
     freqs = positions.to(torch.float32)[:, None] * inv_freq[None, :]
     emb = torch.cat((freqs, freqs), dim=-1)
-    return emb.cos(), emb.sin()
+    return emb.cos() * amplitude, emb.sin() * amplitude  # kairyu/models/layers.py:143-146
+
+
+def yarn_inv_freq(dim: int, theta: float, rope: Mapping) -> tuple[torch.Tensor, float]:
+    """kairyu/models/layers.py:48-81 and config.py:300-312 (defaults beta_fast 32, beta_slow 1,
+    original context = max_position_embeddings), pair by pair in a loop: pair i keeps
+    theta^(-2i/dim) up to index ``low``, is divided by ``factor`` from index ``high`` on, and
+    blends linearly in i between; cos and sin carry 0.1 ln(factor) + 1."""
+    factor = float(rope["factor"])
+    context = rope["original_max_position_embeddings"]  # plain_config fills the default in
+
+    def correction(rotations: float) -> float:
+        return dim * math.log(context / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+
+    low = max(math.floor(correction(float(rope.get("beta_fast", 32.0)))), 0)
+    high = min(math.ceil(correction(float(rope.get("beta_slow", 1.0)))), dim - 1)
+    if low == high:
+        high = high + 0.001
+    out = torch.empty(dim // 2, dtype=torch.float32)
+    pos_freqs = theta ** (torch.arange(0, dim, 2, dtype=torch.int64).float() / dim)
+    for i in range(dim // 2):
+        ramp = (torch.tensor(float(i) - low, dtype=torch.float32) / (high - low)).clamp(0, 1)
+        out[i] = (1.0 / (factor * pos_freqs[i])) * ramp + (1.0 / pos_freqs[i]) * (1.0 - ramp)
+
+    def mscale(scale: float, m: float = 1.0) -> float:
+        return 1.0 if scale <= 1.0 else 0.1 * m * math.log(scale) + 1.0
+
+    if rope.get("mscale") is not None and rope.get("mscale_all_dim") is not None:
+        amplitude = mscale(factor, rope["mscale"]) / mscale(factor, rope["mscale_all_dim"])
+    else:
+        amplitude = mscale(factor)
+    return out, amplitude
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:

@@ -100,7 +100,7 @@ def test_engine_config_validates_and_rejects_unknown_keys():
         EngineConfig.from_kwargs(num_page=3)
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide"])
+@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide", "yarn"])
 def test_random_folder_round_trip(name, tmp_path):
     config, seed, _ = TINY[name]
     folder = write_random_model(config, tmp_path / name, seed=seed, dtype="float32")
@@ -203,3 +203,22 @@ def test_tied_head_in_file_is_not_unexpected(tmp_path):
     save_file(tensors, str(path))
     model, _ = load_model(folder, dtype="float32", device="cpu")
     assert torch.equal(model.head.weight, tensors["model.embed_tokens.weight"])  # the tie wins, as in the reference
+
+
+def test_tensors_the_model_does_not_ask_for_are_passed_over_unless_strict(tmp_path):
+    """kairyu/models/loader.py:250 loads with strict=False: exports carry stray buffers."""
+    from kairyu_b200.engine.engine import build_model
+    from kairyu_b200.weights.loading import load_into
+
+    config, seed, _ = TINY["llama"]
+    folder = write_random_model(config, tmp_path / "m", seed=seed, dtype="float32")
+    path = folder / "model.safetensors"
+    tensors = {k: v.clone() for k, v in load_file(str(path)).items()}
+    tensors["model.layers.0.self_attn.stray_buffer"] = torch.zeros(3)
+    save_file(tensors, str(path))
+    model, _ = load_model(folder, dtype="float32", device="cpu")
+    assert torch.equal(model.embedding.weight, tensors["model.embed_tokens.weight"])
+    strict, _ = build_model(config, dtype="float32", device="cpu")
+    with pytest.raises(WeightError) as caught:
+        load_into(strict, folder, strict_unexpected=True)
+    assert caught.value.unexpected == ["model.layers.0.self_attn.stray_buffer"] and not caught.value.missing

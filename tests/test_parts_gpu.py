@@ -71,7 +71,7 @@ def close(got, expected, atol, rtol):
     assert bool((diff <= atol + rtol * expected.abs()).all()), f"max abs diff {diff.max().item():.3e}"
 
 
-CASES = [(n, d) for n in ("llama", "qwen3", "odd", "wide") for d in (torch.float32, torch.bfloat16)]
+CASES = [(n, d) for n in ("llama", "qwen3", "odd", "wide", "yarn") for d in (torch.float32, torch.bfloat16)]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -129,18 +129,3 @@ def test_parts_alone(name, dtype):
     head = load(HEADS.build(spec.head, **build), weights, dtype)
     head_weight = plain_weights["model.embed_tokens.weight"] if parsed.tie_word_embeddings else plain_weights["lm_head.weight"]
     close(head.forward(x_act.to(DEV), ctx), x_plain @ head_weight.t(), **bound(dtype))
-
-
-def test_llama3_and_yarn_tables():
-    from kairyu_b200.config import RopeScaling
-
-    config, parsed, *_ = setup("llama", torch.float32)
-    cos, _ = rotary_tables(parsed.head_dim, parsed.rope_theta, parsed.rope_scaling, 200)
-    plain_cos, _ = plain_model.rope_cos_sin(plain_model.plain_config(config), torch.arange(200))
-    assert torch.equal(cos, plain_cos[:, : parsed.head_dim // 2])
-    unscaled, _ = rotary_tables(parsed.head_dim, parsed.rope_theta, None, 200)
-    assert not torch.equal(cos, unscaled)
-    yarn = RopeScaling(kind="yarn", factor=4.0, original_max_position_embeddings=64)
-    ycos, ysin = rotary_tables(32, 10000.0, yarn, 300)
-    factor = 0.1 * math.log(4.0) + 1.0  # kairyu/models/layers.py:49-52 multiplies cos and sin by it
-    assert abs(float(ycos[0, 0]) - factor) < 1e-6 and float(ysin[0].abs().max()) == 0.0

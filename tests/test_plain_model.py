@@ -59,3 +59,36 @@ def test_plain_filters():
     assert (plain_model.filtered_probs(logits, 1.0, 2, 1.0, 0.0) > 0).tolist() == [True, True, False, False, False]
     assert (plain_model.filtered_probs(logits, 1.0, -1, 0.6, 0.0) > 0).tolist() == [True, True, False, False, False]
     assert (plain_model.filtered_probs(logits, 1.0, -1, 1.0, 0.25) > 0).tolist() == [True, True, True, False, False]
+
+
+def test_the_engine_tables_are_the_plain_ones_bit_for_bit():
+    """The engine's cos/sin tables (default, llama3, yarn) against the plain model's, which the
+    golden files anchor on the reference's own code; the yarn one also against its definition:
+    pair 0 keeps its frequency, the last pair is slowed ``factor`` times, cos and sin carry
+    0.1 ln(factor) + 1."""
+    import math
+
+    from kairyu_b200.models.llama import parse_llama as parse_config
+    from kairyu_b200.parts.rope import rotary_tables
+
+    for name in sorted(TINY):
+        config = TINY[name][0]
+        parsed = parse_config(config)
+        cfg = plain_model.plain_config(config)
+        cos, sin = rotary_tables(parsed.head_dim, parsed.rope_theta, parsed.rope_scaling, parsed.max_position_embeddings)
+        plain_cos, plain_sin = plain_model.rope_cos_sin(cfg, torch.arange(parsed.max_position_embeddings))
+        half = parsed.head_dim // 2
+        assert torch.equal(cos, plain_cos[:, :half]) and torch.equal(sin, plain_sin[:, :half]), name
+    config = TINY["yarn"][0]
+    parsed = parse_config(config)
+    assert parsed.rope_scaling.kind == "yarn" and parsed.rope_theta == 10000.0
+    cos, sin = rotary_tables(parsed.head_dim, parsed.rope_theta, parsed.rope_scaling, 256)
+    amplitude = 0.1 * math.log(4.0) + 1.0
+    assert abs(float(cos[0, 0]) - amplitude) < 1e-6 and float(sin[0].abs().max()) == 0.0
+    unscaled, _ = rotary_tables(parsed.head_dim, parsed.rope_theta, None, 256)
+    assert torch.allclose(cos[:, 0], unscaled[:, 0] * amplitude, atol=1e-6)  # the fastest pair is kept
+    last = parsed.head_dim // 2 - 1
+    slow = torch.cos(torch.arange(256, dtype=torch.float32) * (10000.0 ** (-2 * last / parsed.head_dim)) / 4.0) * amplitude
+    assert torch.allclose(cos[:, last], slow, atol=1e-5)  # the slowest pair sees positions divided by the factor
+    middle = 4  # between the ends, neither kept nor fully slowed
+    assert not torch.allclose(cos[:, middle], unscaled[:, middle] * amplitude, atol=1e-3)

@@ -29,7 +29,7 @@ def write_model(tmp_path_factory, name, dtype):
     return folder
 
 
-@pytest.fixture(scope="module", params=["llama", "qwen3", "odd", "wide"])
+@pytest.fixture(scope="module", params=["llama", "qwen3", "odd", "wide", "yarn"])
 def case(request, tmp_path_factory):
     name = request.param
     config, seed, page_size = TINY[name]
@@ -51,7 +51,7 @@ def make_runner(case, dtype, *, num_pages, decode_mode="eager"):
     layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
     cache = CacheManager(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8)
     storage = CacheStorage(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8, dtype=model.dtype, device="cuda")
-    return ModelRunner(model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode, max_graph_batch=8, check_tables=True)
+    return ModelRunner(model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode, max_graph_batch=8, check_tables=True, debug_poison=True)
 
 
 def worst(result, expected):

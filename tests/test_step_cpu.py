@@ -27,7 +27,7 @@ def make_runner(name, *, num_pages, page_size=None, dtype="float32", max_request
     layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
     cache = CacheManager(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests)
     storage = CacheStorage(layout, num_pages=num_pages, page_size=page_size, max_requests=max_requests, dtype=model.dtype, device="cpu")
-    runner = ModelRunner(model, cache, storage, max_model_len=config["max_position_embeddings"], decode_mode="eager", check_tables=True)
+    runner = ModelRunner(model, cache, storage, max_model_len=config["max_position_embeddings"], decode_mode="eager", check_tables=True, debug_poison=True)
     return runner, config, weights
 
 
@@ -48,7 +48,7 @@ def cpu_kernels(monkeypatch):
     torch_kernels.install(monkeypatch)
 
 
-@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide"])
+@pytest.mark.parametrize("name", ["llama", "qwen3", "odd", "wide", "yarn"])
 def test_whole_prompts_match_plain(name):
     runner, config, weights = make_runner(name, num_pages=40)
     requests = traces.make_requests(config["vocab_size"], [1, 7, 33, 50], seed=11)

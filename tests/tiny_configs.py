@@ -81,6 +81,34 @@ TINY_WIDE = {
     "hidden_act": "silu",
 }
 
+# A fifth for yarn position scaling, written in the newer config generation (``rope_parameters``
+# with theta nested in it): context stretched 4 times over an original 64 positions, with
+# beta_fast/beta_slow such that the head's pairs fall into all three ranges (kept, blended,
+# slowed); every query head with a KV head of its own, three layers, a tied head.
+TINY_YARN = {
+    "architectures": ["LlamaForCausalLM"],
+    "hidden_size": 80,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 4,
+    "head_dim": 48,
+    "intermediate_size": 112,
+    "vocab_size": 149,
+    "rope_parameters": {
+        "rope_type": "yarn",
+        "rope_theta": 10000.0,
+        "factor": 4.0,
+        "beta_fast": 8.0,
+        "beta_slow": 0.5,
+        "original_max_position_embeddings": 64,
+    },
+    "max_position_embeddings": 256,
+    "rms_norm_eps": 1e-5,
+    "tie_word_embeddings": True,
+    "hidden_act": "silu",
+}
+
 TINY = {  # config, seed, page size
     "llama": (TINY_LLAMA, 0, 16), "qwen3": (TINY_QWEN3, 1, 8), "odd": (TINY_ODD, 5, 16), "wide": (TINY_WIDE, 7, 8),
+    "yarn": (TINY_YARN, 9, 4),
 }
