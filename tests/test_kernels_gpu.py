@@ -794,3 +794,20 @@ def test_sample_frequencies_follow_the_distribution():
     counts = torch.bincount(out.cpu().long(), minlength=V).float() / n
     assert (counts[:4] - probs[:4]).abs().max() < 0.03
     assert counts[4:].sum() == 0
+
+
+def test_sampling_kernels_draw_what_the_reference_sampler_drew():
+    """tests/golden/sampler.pt: tokens the reference's own ``Sampler.sample`` drew for 56 cases of
+    temperature, top-k, top-p, min-p, seeds, positions and penalties; the device pipeline (logit
+    edits, radix-descent filters, Gumbel arg-max) draws the same tokens."""
+    from pathlib import Path
+
+    from kairyu_b200.sampling import Sampler
+    from test_sampling_cpu import sampler_rows_of
+
+    cases = torch.load(Path(__file__).resolve().parent / "golden" / "sampler.pt")
+    for vocab, entries in sampler_rows_of(cases).items():
+        sampler = Sampler(vocab, DEV)
+        logits = torch.stack([entry[1] for entry in entries]).to(DEV)
+        got = sampler.sample(logits, [entry[0] for entry in entries]).tolist()
+        assert got == [entry[2] for entry in entries], vocab

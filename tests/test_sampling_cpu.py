@@ -83,3 +83,51 @@ def test_request_without_a_seed_draws_from_its_id():
     b = sampler.sample(logits.clone(), [SamplingRow("y", params, 0), SamplingRow("x", params, 0)]).tolist()
     assert a == b[::-1]  # a draw belongs to (request, position), not to the row it sits in
     assert a[0] == plain_model.sample_token(logits[0], temperature=1.0, base_seed=stable_request_seed("x"), position=0)
+
+
+def _golden_draws():
+    from pathlib import Path
+
+    return torch.load(Path(__file__).resolve().parent / "golden" / "sampler.pt")
+
+
+def test_plain_sampler_draws_what_the_reference_sampler_drew():
+    """tests/golden/sampler.pt holds tokens drawn by the reference's own ``Sampler.sample``
+    (script beside it): the plain restatement of its filters, noise and penalties gives the same
+    token in every case."""
+    cases = _golden_draws()
+    assert len(cases) >= 50 and sum(1 for case in cases if case["temperature"] > 0) >= 30
+    for index, case in enumerate(cases):
+        logits = plain_model.apply_penalties(
+            case["logits"], case["prompt"], case["outputs"], repetition=case["repetition_penalty"],
+            frequency=case["frequency_penalty"], presence=case["presence_penalty"],
+        )
+        token = plain_model.sample_token(
+            logits, temperature=case["temperature"], top_k=case["top_k"], top_p=case["top_p"], min_p=case["min_p"],
+            base_seed=case["seed"], position=case["position"],
+        )
+        assert token == case["token"], index
+
+
+def sampler_rows_of(cases):
+    """The golden cases as rows of this package's sampler, grouped by vocabulary size."""
+    by_vocab = {}
+    for index, case in enumerate(cases):
+        params = SamplingParams(
+            temperature=case["temperature"], top_k=min(case["top_k"], case["logits"].numel()) if case["top_k"] > 0 else -1,
+            top_p=case["top_p"], min_p=case["min_p"], seed=case["seed"], repetition_penalty=case["repetition_penalty"],
+            frequency_penalty=case["frequency_penalty"], presence_penalty=case["presence_penalty"],
+        )
+        row = SamplingRow(f"case-{index}", params, case["position"], list(case["prompt"]), list(case["outputs"]))
+        by_vocab.setdefault(case["logits"].numel(), []).append((row, case["logits"], case["token"]))
+    return by_vocab
+
+
+def test_the_sampler_pipeline_draws_what_the_reference_sampler_drew():
+    """The same cases through ``sampling.Sampler`` (host side: which logits to edit, which seeds),
+    with the torch statements of the kernels."""
+    for vocab, entries in sampler_rows_of(_golden_draws()).items():
+        sampler = Sampler(vocab, "cpu")
+        logits = torch.stack([entry[1] for entry in entries])
+        got = sampler.sample(logits.clone(), [entry[0] for entry in entries]).tolist()
+        assert got == [entry[2] for entry in entries], vocab
