@@ -30,3 +30,11 @@ def as_held_in_bf16(weights: Mapping[str, torch.Tensor]) -> dict[str, torch.Tens
         keep = tensor.ndim == 1 and name.endswith("norm.weight")
         held[name] = tensor if keep else tensor.to(torch.bfloat16).float()
     return held
+
+
+def golden_weights_on(config: Mapping, seed: int, device: str) -> dict[str, torch.Tensor]:
+    """As ``golden_weights`` but drawn on ``device`` (a device has its own random stream: these
+    are the values ``init_random`` gives a model built there with the same seed)."""
+    architecture = architecture_of(config)
+    spec = architecture.build_spec(architecture.parse_config(config))
+    return random_tensors(_specs_without_building(spec), seed, device=device)

@@ -82,9 +82,9 @@ def rope_cos_sin(cfg: Mapping, positions: torch.Tensor) -> tuple[torch.Tensor, t
         inv_freq, amplitude = yarn_inv_freq(dim, cfg["theta"], cfg["rope"])
     elif cfg["rope_kind"] not in (None, "default"):
         raise ValueError(f"plain model: rope type {cfg['rope_kind']!r} is not restated here")
-    freqs = positions.to(torch.float32)[:, None] * inv_freq[None, :]
+    freqs = positions.cpu().to(torch.float32)[:, None] * inv_freq[None, :]  # the table is made on the CPU, wherever the model runs
     emb = torch.cat((freqs, freqs), dim=-1)
-    return emb.cos() * amplitude, emb.sin() * amplitude  # kairyu/models/layers.py:143-146
+    return (emb.cos() * amplitude).to(positions.device), (emb.sin() * amplitude).to(positions.device)  # kairyu/models/layers.py:143-146
 
 
 def yarn_inv_freq(dim: int, theta: float, rope: Mapping) -> tuple[torch.Tensor, float]:
@@ -144,8 +144,8 @@ def causal_attention(
     v = v.repeat_interleave(group, dim=1)
     scale = 1.0 / math.sqrt(dim) if scale is None else scale
     scores = torch.einsum("qhd,khd->hqk", q.float(), k.float()) * scale
-    i = torch.arange(T)[:, None]
-    j = torch.arange(T)[None, :]
+    i = torch.arange(T, device=q.device)[:, None]
+    j = torch.arange(T, device=q.device)[None, :]
     mask = j <= i
     if window is not None:
         mask = mask & (j > i - window)
@@ -192,8 +192,9 @@ def forward_logits(config: Mapping, weights: Mapping[str, torch.Tensor], token_i
     """Logits [T, vocab] at every position of one whole sequence
     (kairyu/models/llama.py:309-329 and 612-614)."""
     cfg = plain_config(config)
-    tokens = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(tokens.numel())
+    device = weights["model.embed_tokens.weight"].device  # the CPU in most tests; a GPU for the shapes too large for it
+    tokens = torch.as_tensor(token_ids, dtype=torch.long, device=device)
+    positions = torch.arange(tokens.numel(), device=device)
     x = weights["model.embed_tokens.weight"][tokens]
     for index in range(cfg["layers"]):
         x = decoder_layer(cfg, weights, index, x, positions)

@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+import parity
 import plain_model
 import traces
 from golden_inputs import as_held_in_bf16, golden_weights
@@ -16,6 +17,11 @@ pytestmark = pytest.mark.gpu
 
 FP32_TOL = 2e-5
 BF16_TOL = 2e-2  # absolute, on logits of magnitude ~1 (the reference's own bf16 bound, tests/gpu/test_tensor_decode_gpu.py:62-87)
+# These models' logits are smaller than 1 (standard deviation about 0.2), so bfloat16 results are
+# also held to what bfloat16 rounding costs the plain model itself: the engine, which keeps the
+# residual and the statistics in 32-bit, may be this many times as far from the 32-bit result as the
+# plain model is when every operation's result is rounded to bfloat16.
+BF16_FACTOR = 1.5
 
 LENGTHS = [70, 45, 101, 38, 64, 83, 90, 55]
 
@@ -39,19 +45,47 @@ def case(request, tmp_path_factory):
     expected32 = {n: plain_model.forward_logits(config, weights, t).numpy() for n, t in requests.items()}
     rounded = as_held_in_bf16(weights)
     expected16 = {n: plain_model.forward_logits(config, rounded, t).numpy() for n, t in requests.items()}
-    return dict(name=name, config=config, folder=folder, page_size=page_size, requests=requests, expected={"float32": expected32, "bfloat16": expected16})
+    in_bf16 = parity.in_bf16(weights, keep_norms_in_fp32=True)  # the model folder stores 32-bit: norm weights stay so
+    plain16 = {n: plain_model.forward_logits(config, in_bf16, t).float().numpy() for n, t in requests.items()}
+    plain16_error = max(float(np.abs(plain16[n] - expected16[n]).max()) for n in requests)
+    return dict(
+        name=name, config=config, seed=seed, folder=folder, page_size=page_size, requests=requests, weights=weights,
+        expected={"float32": expected32, "bfloat16": expected16}, plain_bf16_error=plain16_error,
+    )
 
 
-def make_runner(case, dtype, *, num_pages, decode_mode="eager"):
+def bound_of(case, dtype):
+    return FP32_TOL if dtype == "float32" else min(BF16_TOL, BF16_FACTOR * case["plain_bf16_error"])
+
+
+def kernels_in_use(runner):
+    """For a failure's message: which attention kernels this runner's shapes select."""
+    import kairyu_b200.kernels as kernels
+
+    k, v = runner.storage.k[0][0], runner.storage.v[0][0]
+    head_dim, page_size = k.shape[-1], k.shape[1]
+    try:
+        decode = "tma ring" if kernels._decode_tma_ok(k, v) else "row copy (mma.sync)"
+    except Exception as error:  # the private check moved: say so instead of hiding the failure it decorates
+        decode = f"unknown ({error})"
+    prefill = "tcgen05" if k.dtype == torch.bfloat16 and head_dim in (64, 128) and page_size >= 8 and page_size & (page_size - 1) == 0 else "mma.sync or fp32"
+    return dict(dtype=str(k.dtype), head_dim=head_dim, page_size=page_size, decode_attention=decode, prefill_attention=prefill, decode_mode=runner.decode_mode)
+
+
+def make_runner(case, dtype, *, num_pages, decode_mode="eager", max_graph_batch=8):
     from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
     from kairyu_b200.engine.engine import load_model
     from kairyu_b200.engine.runner import ModelRunner
 
     model, _ = load_model(case["folder"], dtype=dtype, device="cuda")
     layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
-    cache = CacheManager(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8)
-    storage = CacheStorage(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=8, dtype=model.dtype, device="cuda")
-    return ModelRunner(model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode, max_graph_batch=8, check_tables=True, debug_poison=True)
+    live = max(8, max_graph_batch)
+    cache = CacheManager(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=live)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=case["page_size"], max_requests=live, dtype=model.dtype, device="cuda")
+    return ModelRunner(
+        model, cache, storage, max_model_len=case["config"]["max_position_embeddings"], decode_mode=decode_mode,
+        max_graph_batch=max_graph_batch, check_tables=True, debug_poison=True,
+    )
 
 
 def worst(result, expected):
@@ -74,10 +108,11 @@ def cuts(case):
     }
 
 
-@pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("decode_mode", ["eager", "cuda_graph"])
-def test_every_cut_matches_plain(case, dtype, tolerance, decode_mode):
+def test_every_cut_matches_plain(case, dtype, decode_mode):
     all_cuts = cuts(case)
+    tolerance = bound_of(case, dtype)
     small_pool = traces.peak_tokens(all_cuts["mixed"]) // case["page_size"] + 1
     total = sum(len(t) for t in case["requests"].values())
     assert small_pool * case["page_size"] < total + case["page_size"]
@@ -86,7 +121,9 @@ def test_every_cut_matches_plain(case, dtype, tolerance, decode_mode):
     for cut, steps in all_cuts.items():
         results[cut] = traces.run_in_process(runner, steps)
         assert len(results[cut]) == total
-        assert worst(results[cut], case["expected"][dtype]) < tolerance, (cut, off_rows(results[cut], case["expected"][dtype], tolerance))
+        error = worst(results[cut], case["expected"][dtype])
+        print(f"[parity] {case['name']} {dtype} {decode_mode} {cut}: {error:.3e} bound {tolerance:.3e} plain-bf16 {case['plain_bf16_error']:.3e}")
+        assert error < tolerance, (cut, error, tolerance, off_rows(results[cut], case["expected"][dtype], tolerance), kernels_in_use(runner))
     if decode_mode == "cuda_graph":
         assert runner.counters["graph_replays"] > 0
     if dtype == "float32":
@@ -95,10 +132,94 @@ def test_every_cut_matches_plain(case, dtype, tolerance, decode_mode):
         for cut in ("tail", "chunks", "mixed"):
             for key, row in results["whole"].items():
                 assert np.array_equal(row, results[cut][key]), (cut, key)
+    else:
+        # bfloat16 kernels depend on the cut, but not on the run: a second engine over the same
+        # steps gives the same bits, or something in a kernel depends on timing (a race shows here
+        # on every run that has it, where a bound shows it only when the damage is large)
+        again = make_runner(case, dtype, num_pages=max(small_pool, 8), decode_mode=decode_mode)
+        for cut, steps in all_cuts.items():
+            repeat = traces.run_in_process(again, steps)
+            different = [key for key, row in results[cut].items() if not np.array_equal(row, repeat[key])]
+            assert not different, (cut, different[:12], kernels_in_use(runner))
 
 
-@pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
-def test_trace_run_program(case, dtype, tolerance, tmp_path):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("decode_mode", ["eager", "cuda_graph"])
+def test_decode_steps_of_many_rows(case, dtype, decode_mode):
+    """12, 16, 24 and 64 live requests decoded together (kairyu tests/unit/test_batched_decode.py:40,92):
+    graphs of every batch bucket up to 64, and the kernels that take over beyond 8 rows."""
+    config = case["config"]
+    tail = 6
+    runner = make_runner(case, dtype, num_pages=64 * (-(-72 // case["page_size"])) + 1, decode_mode=decode_mode, max_graph_batch=64)
+    weights = case["weights"] if dtype == "float32" else as_held_in_bf16(case["weights"])
+    for rows in (12, 16, 24, 64):
+        lengths = torch.randint(tail + 1, 70, (rows,), generator=torch.Generator().manual_seed(rows)).tolist()
+        requests = {f"m{rows}-{i}": t for i, t in enumerate(traces.make_requests(config["vocab_size"], lengths, seed=60 + rows).values())}
+        keep = {name: list(range(len(tokens) - tail - 1, len(tokens))) for name, tokens in requests.items()}
+        expected = parity.plain_rows(config, weights, requests, keep)
+        bound = FP32_TOL
+        if dtype == "bfloat16":
+            rounded = parity.plain_rows(config, parity.in_bf16(case["weights"], True), requests, keep)
+            bound = min(BF16_TOL, BF16_FACTOR * parity.worst_error(rounded, expected))
+        before = runner.counters["graph_replays"]
+        result = traces.run_in_process(runner, parity.trace_many_rows(requests, tail))
+        assert runner.counters["graph_replays"] - before == (tail if decode_mode == "cuda_graph" else 0)
+        assert result.keys() == expected.keys()
+        error = parity.worst_error(result, expected)
+        print(f"[parity] {case['name']} {dtype} {decode_mode} {rows} rows: {error:.3e} bound {bound:.3e}")
+        assert error < bound, (rows, error, bound, parity.rows_beyond(result, expected, bound), kernels_in_use(runner))
+
+
+def test_a_wrong_page_is_far_beyond_the_bfloat16_bound(case):
+    """What the bound is for.  A request's block table is corrupted between its prompt and its
+    next token: four of its pages are replaced by its first one, so attention finds the wrong keys
+    in most places.  With random weights attention is nearly uniform and hardly cares which keys it
+    averages, so the queries and keys are scaled up first (by powers of two: exact in bfloat16)
+    until single scores stand out.  The right table stays within the bound that bfloat16 rounding
+    of the plain model gives for these weights; the wrong one leaves it by a clear margin."""
+    from kairyu_b200.engine.runner import StepEntry
+
+    config, page_size = case["config"], case["page_size"]
+    qk_norm = config["architectures"][0] == "Qwen3ForCausalLM"
+    weights = dict(case["weights"])
+    for name in weights:
+        if qk_norm and name.endswith(("q_norm.weight", "k_norm.weight")):
+            weights[name] = weights[name] * 4.0
+        elif not qk_norm and (".q_proj." in name or ".k_proj." in name):
+            weights[name] = weights[name] * 16.0
+    tokens = case["requests"]["r2"]  # 101 tokens
+    head = 5 * page_size + 3
+    sequence = tokens[: head + 1]
+    expected = plain_model.forward_logits(config, as_held_in_bf16(weights), sequence)[head].numpy()
+    rounded = plain_model.forward_logits(config, parity.in_bf16(weights, True), sequence)[head].float().numpy()
+    bound = BF16_FACTOR * float(np.abs(rounded - expected).max())
+    errors = {}
+    for corrupt in (False, True):
+        runner = make_runner(case, "bfloat16", num_pages=16)
+        runner.check_tables = False
+        for block in runner.model.blocks:
+            mixer = block.mixer
+            if qk_norm:
+                mixer.q_norm_weight.mul_(4.0)
+                mixer.k_norm_weight.mul_(4.0)
+            else:
+                mixer.w_qkv[: mixer.q_size + mixer.kv_size].mul_(16.0)
+                if mixer.b_qkv is not None:
+                    mixer.b_qkv[: mixer.q_size + mixer.kv_size].mul_(16.0)
+        runner.step([StepEntry("a", tokens[:head], ())])
+        if corrupt:
+            table = runner.cache.get("a").tables[0]
+            table[1:5] = [table[0]] * 4
+        logits = runner.step([StepEntry("a", tokens[head : head + 1], (0,))]).float().cpu().numpy()
+        errors[corrupt] = float(np.abs(logits[0] - expected).max())
+    print(f"[parity] {case['name']} wrong pages: {errors} bound {bound:.3e}")
+    assert errors[False] < bound, (errors, bound)
+    assert errors[True] > 3 * bound, (errors, bound)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(case, dtype, tmp_path):
+    tolerance = bound_of(case, dtype)
     steps = traces.trace_mixed(case["requests"], seed=8)
     result = traces.run_program(
         case["folder"], tmp_path, steps, dtype=dtype, max_tokens=traces.peak_tokens(steps), vocab=case["config"]["vocab_size"],
@@ -138,8 +259,8 @@ def test_first_tokens_of_a_sequence(case):
     assert np.abs(two - expected[1:3]).max() < FP32_TOL
 
 
-@pytest.mark.parametrize("dtype,tolerance", [("float32", FP32_TOL), ("bfloat16", BF16_TOL)])
-def test_long_decoding(case, dtype, tolerance):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(case, dtype):
     """One request decoded token by token over many pages (and, for bf16, past a split of the decode kernel)."""
     config = case["config"]
     length = min(config["max_position_embeddings"], 300)
@@ -151,7 +272,12 @@ def test_long_decoding(case, dtype, tolerance):
     runner = make_runner(case, dtype, num_pages=length // case["page_size"] + 3, decode_mode="cuda_graph")
     steps = traces.trace_decode_tail({"r0": tokens}, tail=length - 3)
     result = traces.run_in_process(runner, steps)
-    assert worst(result, {"r0": expected}) < tolerance
+    bound = FP32_TOL
+    if dtype == "bfloat16":
+        rounded = plain_model.forward_logits(config, parity.in_bf16(golden_weights(config, TINY[case["name"]][1]), True), tokens).float().numpy()
+        bound = min(BF16_TOL, BF16_FACTOR * float(np.abs(rounded - expected).max()))
+    error = worst(result, {"r0": expected})
+    assert error < bound, (error, bound, kernels_in_use(runner))
 
 
 def test_graph_replays_of_several_rows_survive_other_work_between_steps(case):
