@@ -377,25 +377,27 @@ def time_shared_prefix(layers: int) -> dict:
 
 
 def reference_arm(args) -> int:
-    """The unmodified reference through its own public API, if it is installed under baseline/_ref."""
+    """The unmodified reference through its own public API, from the copy of its package under
+    baseline/_ref (``baseline/reference_bench.py`` drives it; nothing of this package is imported
+    on that path)."""
     ref_root = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "kairyu")):
-        print(
-            json.dumps(
-                {
-                    "impl": "reference",
-                    "unavailable": "ytworks/kairyu is not installed under baseline/_ref: its offline pip install fails "
-                    "(build backend hatchling is neither installed nor in the wheelhouse)",
-                }
-            )
-        )
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "no copy of ytworks/kairyu under baseline/_ref (pip cannot build it offline: its build backend, "
+            "hatchling, is not in the wheelhouse; the package is pure Python, so copying its kairyu/ folder there installs it)",
+        }))
         return 0
     try:
         from baseline.reference_bench import run_reference
 
-        line = run_reference(args, MODEL, dict(prompt_len=PROMPT_LEN, gen_len=GEN_LEN, page_size=PAGE_SIZE, context_len=CONTEXT_LEN, seed=SEED))
+        workload = dict(
+            name=MODEL_NAME, prompt_len=PROMPT_LEN, gen_len=GEN_LEN, page_size=PAGE_SIZE, context_len=CONTEXT_LEN, seed=SEED,
+            ref_root=ref_root, layers=args.layers, layers_full=FULL_LAYERS, clock_sampler=ClockSampler,
+        )
+        line = run_reference(args, MODEL, workload)
     except Exception as error:  # the reference arm must never take the driver down
-        line = {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:200]}"}
+        line = {"impl": "reference", "unavailable": f"{type(error).__name__}: {str(error)[:300]}"}
     print(json.dumps(line))
     return 0
 
