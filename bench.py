@@ -376,6 +376,135 @@ def time_shared_prefix(layers: int) -> dict:
     return result
 
 
+def time_kernels(engine, config: dict, batch: int, peaks: dict) -> dict:
+    """The step's dominant kernels, each timed alone: one launch per layer of the model (every layer
+    has weights and cache pages of its own, 0.4 GB a layer, so no launch finds its operands in the
+    126 MB L2), the launches of one kernel captured in a CUDA graph and timed with CUDA events.
+    Decode products and decode attention are judged by the bytes they have to read over the measured
+    copy bandwidth, prefill attention and the prefill products by their FLOPs over the measured
+    library product peak."""
+    import torch
+
+    import kairyu_b200.kernels as kernels
+    from kairyu_b200.engine.workspace import Workspace
+
+    device = engine.device
+    blocks = engine.model.blocks
+    hidden, inter = config["hidden_size"], config["intermediate_size"]
+    heads, kv_heads, dim = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    page = engine.page_size
+    workspace = Workspace(device)
+    bf16 = torch.bfloat16
+
+    def rand(*shape):
+        return (torch.randn(*shape, device=device, dtype=torch.float32) * 0.5).to(bf16)
+
+    def timed(launch, repeats: int = 3) -> float:
+        """Median microseconds of one launch: ``launch(layer)`` for every layer, in a graph."""
+        for layer in range(min(2, len(blocks))):
+            launch(layer)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.cuda.graph(graph):
+            for layer in range(len(blocks)):
+                launch(layer)
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(repeats):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            times.append(start.elapsed_time(stop) * 1e3 / len(blocks))
+        return statistics.median(times)
+
+    def by_bytes(us: float, count: float) -> dict:
+        achieved = count / (us * 1e-6) / 1e9
+        return {"us": us, "achieved": achieved, "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"]}
+
+    def by_flops(us: float, count: float, library: bool = False) -> dict:
+        achieved = count / (us * 1e-6) / 1e12
+        entry = {"us": us, "achieved": achieved, "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"]}
+        if library:
+            entry["library"] = True  # the product is the library's (cuBLAS through torch), as the reference's is
+        return entry
+
+    result = {}
+    q_size, kv_size = heads * dim, kv_heads * dim
+    qkv_width = q_size + 2 * kv_size
+    # ---- decode products at the headline batch (weights streamed once)
+    x_h, x_q, x_i = rand(batch, hidden), rand(batch, q_size), rand(batch, inter)
+    out_qkv = torch.empty(batch, qkv_width, device=device, dtype=bf16)
+    out_h = torch.empty(batch, hidden, device=device, dtype=bf16)
+    out_i = torch.empty(batch, inter, device=device, dtype=bf16)
+    result["qkv_product_decode"] = by_bytes(timed(lambda l: kernels.linear(x_h, blocks[l].mixer.w_qkv, None, out_qkv)), qkv_width * hidden * 2)
+    result["o_product_decode"] = by_bytes(timed(lambda l: kernels.linear(x_q, blocks[l].mixer.w_o, None, out_h)), hidden * q_size * 2)
+    result["gate_up_product_decode"] = by_bytes(
+        timed(lambda l: kernels.linear_swiglu(x_h, blocks[l].ffn.w_gate_up, out_i, workspace)), 2 * inter * hidden * 2)
+    result["down_product_decode"] = by_bytes(timed(lambda l: kernels.linear(x_i, blocks[l].ffn.w_down, None, out_h)), hidden * inter * 2)
+    head_weight = engine.model.head.weight
+    logits = torch.empty(batch, head_weight.shape[0], device=device, dtype=torch.float32)
+    head_us = timed(lambda l: kernels.linear(x_h, head_weight, None, logits)) if head_weight.numel() * 2 > 200e6 else None
+    if head_us is not None:  # one weight, but eight times the L2: every launch streams it whole
+        result["lm_head_decode"] = by_bytes(head_us, head_weight.numel() * 2)
+    # ---- decode attention: ``batch`` rows of PROMPT_LEN + 15 keys each over this layer's pages
+    context = PROMPT_LEN + 15
+    pages_per_row = -(-context // page)
+    usable = engine.num_pages - 1
+    if batch * pages_per_row <= usable:
+        table = (torch.arange(batch * pages_per_row, device=device, dtype=torch.int32) + 1).view(batch, pages_per_row).contiguous()
+        seq_lens = torch.full((batch,), context, device=device, dtype=torch.int32)
+        rows = torch.arange(batch, device=device, dtype=torch.int32)
+        q = rand(batch, qkv_width)
+        mixed = torch.empty(batch, q_size, device=device, dtype=bf16)
+        k_all, v_all = engine.storage.k[0], engine.storage.v[0]
+        scale = dim ** -0.5
+
+        def decode_attention(l):
+            kernels.attention_decode_mma(
+                q, mixed, k_all[l], v_all[l], seq_lens=seq_lens, block_table=table, decode_rows=rows, decode_tokens=rows,
+                num_rows=batch, max_seq_len=context, num_q_heads=heads, scale=scale, workspace=workspace,
+            )
+
+        result["attention_decode"] = by_bytes(timed(decode_attention), batch * context * kv_size * 2 * 2)
+        # ---- prefill attention: one row of PREFILL_TOKENS tokens
+        tokens = PREFILL_TOKENS
+        if -(-tokens // page) <= usable:
+            tile = kernels.attention_prefill_tile_rows(dim)
+            tiles = -(-tokens // tile)
+            table1 = (torch.arange(-(-tokens // page), device=device, dtype=torch.int32) + 1).view(1, -1).contiguous()
+            qo = torch.tensor([0, tokens], device=device, dtype=torch.int32)
+            lens1 = torch.tensor([tokens], device=device, dtype=torch.int32)
+            tile_rows = torch.zeros(tiles, device=device, dtype=torch.int32)
+            tile_starts = torch.arange(tiles, device=device, dtype=torch.int32) * tile
+            q_many = rand(tokens, qkv_width)
+            mixed_many = torch.empty(tokens, q_size, device=device, dtype=bf16)
+
+            def prefill_attention(l):
+                kernels.attention_prefill_mma(
+                    q_many, mixed_many, k_all[l], v_all[l], qo_indptr=qo, seq_lens=lens1, block_table=table1, tile_rows=tile_rows,
+                    tile_starts=tile_starts, num_tiles=tiles, num_q_heads=heads, scale=scale,
+                )
+
+            result["attention_prefill"] = by_flops(timed(prefill_attention), 4.0 * heads * dim * tokens * (tokens + 1) / 2)
+            # ---- prefill products (the library's)
+            xm_h, xm_q, xm_i = rand(tokens, hidden), rand(tokens, q_size), rand(tokens, inter)
+            om_qkv = torch.empty(tokens, qkv_width, device=device, dtype=bf16)
+            om_h = torch.empty(tokens, hidden, device=device, dtype=bf16)
+            om_gu = torch.empty(tokens, 2 * inter, device=device, dtype=bf16)
+            result["qkv_product_prefill"] = by_flops(timed(lambda l: kernels.linear(xm_h, blocks[l].mixer.w_qkv, None, om_qkv)), 2.0 * tokens * hidden * qkv_width, True)
+            result["o_product_prefill"] = by_flops(timed(lambda l: kernels.linear(xm_q, blocks[l].mixer.w_o, None, om_h)), 2.0 * tokens * hidden * q_size, True)
+            result["gate_up_product_prefill"] = by_flops(timed(lambda l: kernels.linear(xm_h, blocks[l].ffn.w_gate_up, None, om_gu)), 2.0 * tokens * hidden * 2 * inter, True)
+            result["down_product_prefill"] = by_flops(timed(lambda l: kernels.linear(xm_i, blocks[l].ffn.w_down, None, om_h)), 2.0 * tokens * hidden * inter, True)
+    torch.cuda.synchronize()
+    return result
+
+
 def reference_arm(args) -> int:
     """The unmodified reference through its own public API, from the copy of its package under
     baseline/_ref (``baseline/reference_bench.py`` drives it; nothing of this package is imported
@@ -471,11 +600,25 @@ def main() -> int:
 
     points = {}
     e2e = None
+    kernel_block = None
+
+    def roofline_point(batch: int, step_ms: float, tokens_held: float) -> dict:
+        moved = weight_bytes + batch * tokens_held * kv_bytes_per_token
+        rate = moved / (step_ms / 1e3) / 1e9
+        return {"batch": batch, "ms_per_step": step_ms, "gbytes": moved / 1e9, "achieved": rate, "frac": rate / peaks["hbm_gbs"]}
+
+    roofline_points = {f"decode_b{args.batch}": roofline_point(args.batch, ms_per_step, context)}
     if not args.no_points:
-        for batch, key in ((1, "decode_b1"), (64, "decode_b64")):
+        for batch in (1, 16, 32, 64):
+            if batch == args.batch:
+                continue
             steps = max(16, min(args.steps, 64))
-            ms, _, _, _ = time_decode(engine, batch, steps, args.warmup, False)
-            points[key] = batch * steps / (ms / 1e3)
+            ms, _, _, held = time_decode(engine, batch, steps, args.warmup, False)
+            key = f"decode_b{batch}"
+            if batch in (1, 64):
+                points[key] = batch * steps / (ms / 1e3)
+            roofline_points[key] = roofline_point(batch, ms / steps, held)
+        kernel_block = time_kernels(engine, config, args.batch, peaks)
         rate, h2d, d2h = time_e2e(engine, args.batch, min(args.steps, 64))
         e2e = {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
     if args.mixed:
@@ -530,12 +673,15 @@ def main() -> int:
             "unit": "GB/s",
             "frac": achieved / peaks["hbm_gbs"],
         },
+        "roofline_points": roofline_points,
         "points": points,
         "clocks": clocks,
         "gpu_launches": launches,
     }
     if e2e is not None:
         line["e2e"] = e2e
+    if kernel_block is not None:
+        line["kernels"] = kernel_block
     print(json.dumps(line))
     return 0
 
