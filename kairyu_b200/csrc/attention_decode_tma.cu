@@ -1,12 +1,17 @@
 // Split-KV decode attention whose key and value tiles come in through tiled TMA copies.
 //
 // The cache is [pages, page_size, kv_heads, head_dim]: the 64 keys of a tile that belong to
-// one KV head are page_size-long runs of rows, 2 * kv_heads * head_dim bytes apart.  A 4-D
-// tensor map (head_dim, kv_heads, page_size, pages) lets ONE cp.async.bulk.tensor bring a whole
-// run of rows (box = 64 columns x 1 head x min(page_size, 64) positions x 1 page), so a tile
-// costs a handful of copies instead of one per key row.  The copies use the 128-byte swizzle;
-// ldmatrix reads the tiles with the same XOR, which keeps unpadded 128-byte rows free of bank
-// conflicts.
+// one KV head are page_size-long runs of rows, 2 * kv_heads * head_dim bytes apart.  A 5-D
+// tensor map (64 columns, kv_heads, page_size, head_dim / 64 bands of columns, pages) lets ONE
+// cp.async.bulk.tensor bring a whole run of rows with all their columns (box = 64 columns x 1 head
+// x min(page_size, 64) positions x all bands x 1 page: 4 KB for 16 positions of 128 columns), so a
+// tile costs a few copies instead of one per key row.  How many copies an SM can issue, not how many
+// bytes they move, bounds this kernel at small pages (measured: about 50 to 75 ns a copy; with one
+// 2 KB copy per band a tile of 16-position pages took 16 copies and the kernel stood at 40 GB/s an
+// SM), which is why the bands, a dimension of their own with the smallest stride, travel in one
+// copy.  The copies use the 128-byte swizzle; ldmatrix reads the tiles with the same XOR, which
+// keeps unpadded 128-byte rows free of bank conflicts.  In shared memory a tile is
+// [run of positions][band][position in the run][64 columns].
 //
 // Grid (rows, kv_heads, splits).  The visible tiles of a row are divided evenly over the
 // splits, so a block streams a run of consecutive tiles through a ring of shared-memory
@@ -14,11 +19,15 @@
 // the copies; four consumer warps (16 keys of every tile each) wait for the stage to fill,
 // compute, and release it.  The number of splits is chosen so that the grid fills the SMs
 // once; a block pays its start-up latency and its epilogue once, however long the context.
-// Partial results (unnormalised O, running max, running sum) go to scratch and a merge
-// kernel combines a row's splits in order.  (Letting the block that finishes last among a
-// row's splits do the combination saves the launch but was slower on the decode step: its
-// fence, its counter and its dependent loads all sit on the critical path of the kernel's
-// end.)  Sizes: head_dim a multiple of 64 up to 256, page_size a power of two from 8 up;
+// With one split the block writes the normalised output itself.  With more, partial results
+// (unnormalised O, running max, running sum) go to scratch and a merge kernel combines a row's
+// splits in order.  (Two other ways to combine were measured and dropped.  Letting the block that
+// finishes last among a row's splits combine through global memory: its fence, its counter and its
+// dependent loads all sit on the critical path of the kernel's end.  Making the splits of a (row,
+// KV head) a thread-block cluster that combines through distributed shared memory: the kernel
+// alone was as fast as kernel + merge, 17.2 against 17.3 us at 8 rows, but the decode step was
+// 0.5 % slower, because the merge kernel's early trigger lets the output projection fetch its
+// first weights while the merge runs.)  Sizes: head_dim a multiple of 64 up to 256, page_size a power of two from 8 up;
 // anything else goes to the row-copy kernel of attention_mma.cuh.
 #include "attention_mma.cuh"
 
@@ -31,14 +40,17 @@ constexpr int HALF_ELEMS = TILE_N * 64;  // one 64-column band of a tile: 64 row
 constexpr int CONSUMER_WARPS = 4;
 constexpr int KB_FLAG_TIMEOUT_DECODE = 64;  // this kernel's own bit, beside the common KB_FLAG_TIMEOUT
 constexpr int MAX_SPLITS = 256;
+// how a row's splits are combined (the kernel's `combine` argument)
+constexpr int COMBINE_SCRATCH = 0;  // partial results to global scratch, a merge kernel follows
+constexpr int COMBINE_DIRECT = 1;   // one split: the block writes the output
 constexpr int MIN_TILES_PER_SPLIT = 4;   // shorter splits cost more in the combination than they save
 constexpr int TMA_THREADS = (CONSUMER_WARPS + 1) * 32;  // the last warp is the producer
 
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint64_t* bar) {
+__device__ __forceinline__ void tma_load_5d(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
     asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n" ::"r"(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::"r"(
             smem_u32(dst)),
-        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
@@ -49,8 +61,14 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;\n" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
-// Element offset of (row, 8-column chunk) inside a swizzled 64-row band.
-__device__ __forceinline__ int swz(int row, int chunk) { return row * 64 + ((chunk ^ (row & 7)) << 3); }
+// Element offset of (key of the tile, band, 8-column chunk of the band) in a tile laid out
+// [run][band][position in the run][64 columns] with the 128-byte swizzle; a run has 1 << run_shift
+// positions (a multiple of 8, so the swizzle's row index is the key's lowest three bits).
+template <int HALVES>
+__device__ __forceinline__ int tile_offset(int key, int band, int chunk, int run_shift) {
+    const int row = ((((key >> run_shift) * HALVES + band) << run_shift) + (key & ((1 << run_shift) - 1)));
+    return row * 64 + ((chunk ^ (key & 7)) << 3);
+}
 
 template <int D>
 struct TmaSmem {
@@ -80,7 +98,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ decode_rows,
                             const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size, int page_shift,
                             int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, int* flag) {
+                            float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
     using S = TmaSmem<D>;
     constexpr int HALVES = S::HALVES;
     constexpr int STAGES = S::STAGES;
@@ -127,9 +145,14 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     split_range(key_lo / TILE_N, qpos / TILE_N, num_splits, split, t0, t1, per);
     if (seq_len < 1 || t0 > t1) {  // this split has no tile (the whole block leaves)
         pdl_wait();  // a block never ends before the kernels ahead have: those after this one count on that
+        // without a merge kernel behind it, the block of an empty row writes the row's zeros
+        if (combine == COMBINE_DIRECT && seq_len < 1)
+            for (int idx = threadIdx.x; idx < (Hq / Hkv) * D; idx += TMA_THREADS)
+                out[(size_t)token * out_stride + (size_t)(kvh * (Hq / Hkv) + idx / D) * D + idx % D] = __float2bfloat16_rn(0.0f);
         return;
     }
     const int* table = block_table + (size_t)row * max_pages;
+    const int run_shift = page_shift < 6 ? page_shift : 6;  // a copy brings min(page_size, 64) positions
     const int g = lane >> 2;
     const int tq = lane & 3;
     __syncthreads();  // the barriers are initialised
@@ -143,7 +166,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // ---------------- producer: one copy per (K or V, 64-column band, run of rows on one page)
         const int box_rows = page_size < TILE_N ? page_size : TILE_N;
         const int runs = TILE_N / box_rows;
-        const int per_tile = 2 * HALVES * runs;
+        const int per_tile = 2 * runs;
         // The tile that holds the newest position is written by the kernel before this one; the tiles
         // before it are not.  Up to a ring of those go out before the wait (no stage is reused yet,
         // so nothing here waits on the consumers, who are waiting for their queries).
@@ -163,10 +186,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             if (lane == 0) mbar_arrive_expect_tx(full_bar + stage, (uint32_t)(S::STAGE_ELEMS * sizeof(__nv_bfloat16)));
             __syncwarp();
             for (int op = lane; op < per_tile; op += 32) {
-                const int is_v = op / (HALVES * runs);
-                const int rest = op % (HALVES * runs);
-                const int band = rest / runs;
-                const int run = rest % runs;
+                const int is_v = op / runs;
+                const int run = op % runs;
                 const int key = kt * TILE_N + run * box_rows;
                 const int page_index = key >> page_shift;
                 int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
@@ -177,8 +198,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         within = key - (page_index << page_shift);
                     }
                 }
-                __nv_bfloat16* dst = ring + stage * S::STAGE_ELEMS + is_v * S::TILE_ELEMS + band * HALF_ELEMS + run * box_rows * 64;
-                tma_load_4d(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, full_bar + stage);
+                __nv_bfloat16* dst = ring + stage * S::STAGE_ELEMS + is_v * S::TILE_ELEMS + run * HALVES * box_rows * 64;
+                tma_load_5d(dst, is_v ? &map_v : &map_k, 0, kvh, within, 0, page, full_bar + stage);
             }
         }
         if (ahead > 0 && t1 - t0 + 1 <= ahead) pdl_wait();  // every tile went out ahead of the wait
@@ -224,7 +245,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     const int c = idx % (HALVES * 8);
                     const int key = tile_key0 + r;
                     if (key < key_lo || key >= seq_len)
-                        *reinterpret_cast<uint4*>(tV + (c >> 3) * HALF_ELEMS + r * 64 + (c & 7) * 8) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(tV + tile_offset<HALVES>(r, c >> 3, c & 7, run_shift)) = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();  // these writes stay ordered before the copy that refills the stage
                 __syncwarp();
@@ -238,7 +259,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int m = lane >> 3;
                 const int key = warp * 16 + (m >> 1) * 8 + (lane & 7);
                 const int chunk = (ks * 2 + (m & 1)) & 7;
-                ldmatrix_x4(b, tK + (ks >> 2) * HALF_ELEMS + swz(key, chunk));
+                ldmatrix_x4(b, tK + tile_offset<HALVES>(key, ks >> 2, chunk, run_shift));
                 mma_16816(s[0], qf[ks], b[0], b[1]);
                 mma_16816(s[1], qf[ks], b[2], b[3]);
             }
@@ -298,7 +319,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int m = lane >> 3;
                 const int key = warp * 16 + (m & 1) * 8 + (lane & 7);
                 const int chunk = (dp * 2 + (m >> 1)) & 7;
-                ldmatrix_x4_trans(b, tV + (dp >> 2) * HALF_ELEMS + swz(key, chunk));
+                ldmatrix_x4_trans(b, tV + tile_offset<HALVES>(key, dp >> 2, chunk, run_shift));
                 mma_16816(o[2 * dp], a, b[0], b[1]);
                 mma_16816(o[2 * dp + 1], a, b[2], b[3]);
             }
@@ -359,6 +380,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             const float f = mw == -INFINITY ? 0.0f : exp2f(mw - big);
             acc += sO[((size_t)w * 16 + r) * OSTRIDE + d] * f;
             den += sL[w * 16 + r] * f;
+        }
+        if (combine == COMBINE_DIRECT) {  // the only split of its row: what the merge kernel would make of it
+            out[(size_t)token * out_stride + (size_t)(kvh * G + r) * D + d] = __float2bfloat16_rn(den > 0.0f ? acc / den : 0.0f);
+            continue;
         }
         const size_t pidx = ((size_t)slot * Hq + (kvh * G + r)) * num_splits + split;
         part_o[pidx * D + d] = acc;
@@ -444,7 +469,7 @@ template <int D>
 int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q, int q_stride, const int* seq_lens,
            const int* block_table, int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows, int Hq,
            int Hkv, int page_size, int num_pages, float scale, int window, int num_splits, float* part_o, float* part_ml,
-           int* flag, cudaStream_t stream) {
+           __nv_bfloat16* out, int out_stride, int combine, int* flag, cudaStream_t stream) {
     const size_t smem = TmaSmem<D>::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -453,7 +478,7 @@ int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q,
     dim3 grid(num_rows, Hkv, num_splits);
     kb_launch(attention_decode_tma_kernel<D>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
               block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, shift, num_pages, scale,
-              window, num_splits, part_o, part_ml, flag);
+              window, num_splits, part_o, part_ml, out, out_stride, combine, flag);
     return kb_launch_result();
 }
 
@@ -485,35 +510,53 @@ KB_EXPORT int kb_attention_decode_tma_splits(int num_rows, int Hkv, int D, int m
 
 // Writes a 128-byte tensor map (host memory, 64-byte aligned) for a bf16 cache
 // [num_pages, page_size, kv_heads, head_dim] with the given strides in elements (head_dim
-// contiguous).  Boxes are 64 columns x 1 head x min(page_size, 64) positions x 1 page, 128-byte swizzle.
+// contiguous).  ``bands`` = 0: four dimensions (head_dim, kv_heads, page_size, pages), boxes of 64
+// columns x 1 head x min(page_size, 64) positions x 1 page (the prefill kernel's copies, one per
+// 64-column band).  ``bands`` = 1: five dimensions (64 columns, kv_heads, page_size, head_dim / 64
+// bands, pages), boxes that take every band at once (this kernel's copies).  128-byte swizzle.
 KB_EXPORT int kb_attention_encode_cache_map(void* map_out, const void* base, long long num_pages, int page_size, int Hkv, int D,
-                                            long long stride_page, long long stride_pos, long long stride_head) {
+                                            long long stride_page, long long stride_pos, long long stride_head, int bands) {
     if (!map_out || !base) return KB_ERR_NULL;
     if (((uintptr_t)map_out % 64) != 0 || ((uintptr_t)base % 16) != 0) return KB_ERR_BAD_ARG;
     if (!kb_attention_decode_tma_supported(D, page_size) || num_pages < 1 || Hkv < 1) return KB_ERR_UNSUPPORTED_SIZE;
     if ((stride_page * 2) % 16 != 0 || (stride_pos * 2) % 16 != 0 || (stride_head * 2) % 16 != 0) return KB_ERR_UNSUPPORTED_SIZE;
     const int rc = get_encoder();
     if (rc != 0) return rc;
-    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)page_size, (cuuint64_t)num_pages};
-    cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_pos * 2, (cuuint64_t)stride_page * 2};
-    cuuint32_t box[4] = {64, 1, (cuuint32_t)(page_size < TILE_N ? page_size : TILE_N), 1};
-    cuuint32_t elem[4] = {1, 1, 1, 1};
-    CUresult r = g_encode((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const cuuint32_t box_rows = (cuuint32_t)(page_size < TILE_N ? page_size : TILE_N);
+    CUresult r;
+    if (bands) {
+        cuuint64_t dims[5] = {64, (cuuint64_t)Hkv, (cuuint64_t)page_size, (cuuint64_t)(D / 64), (cuuint64_t)num_pages};
+        cuuint64_t strides[4] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_pos * 2, 128, (cuuint64_t)stride_page * 2};
+        cuuint32_t box[5] = {64, 1, box_rows, (cuuint32_t)(D / 64), 1};
+        cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+        r = g_encode((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)page_size, (cuuint64_t)num_pages};
+        cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_pos * 2, (cuuint64_t)stride_page * 2};
+        cuuint32_t box[4] = {64, 1, box_rows, 1};
+        cuuint32_t elem[4] = {1, 1, 1, 1};
+        r = g_encode((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-// map_k, map_v: host pointers to tensor maps made by kb_attention_encode_cache_map.
+// map_k, map_v: host pointers to tensor maps made by kb_attention_encode_cache_map with bands = 1.
 // num_splits: any value from 1 up (kb_attention_decode_tma_splits gives a good one).
-// part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch).
+// part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch; only read
+// and written with more than one split).
 KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, const void* q, int q_stride, void* out, int out_stride,
                                       const int* seq_lens, const int* block_table, int max_pages, const int* decode_rows,
                                       const int* decode_tokens, int num_rows, int Hq, int Hkv, int D, int page_size, int num_pages,
                                       float scale, int window, int num_splits, float* part_o, float* part_ml, int* flag,
                                       cudaStream_t stream) {
     if (num_rows == 0) return 0;
-    if (!map_k || !map_v || !q || !out || !seq_lens || !block_table || !decode_rows || !decode_tokens || !part_o || !part_ml) return KB_ERR_NULL;
+    if (!map_k || !map_v || !q || !out || !seq_lens || !block_table || !decode_rows || !decode_tokens) return KB_ERR_NULL;
+    const int combine = num_splits == 1 ? COMBINE_DIRECT : COMBINE_SCRATCH;
+    if (combine == COMBINE_SCRATCH && (!part_o || !part_ml)) return KB_ERR_NULL;
     if (out_stride % 2 != 0) return KB_ERR_BAD_ARG;
     if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > 16 || Hkv > 65535 || num_splits < 1 || num_splits > MAX_SPLITS) return KB_ERR_BAD_ARG;
     if (q_stride % 8 != 0) return KB_ERR_BAD_ARG;
@@ -522,7 +565,7 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
     const CUtensorMap* mv = (const CUtensorMap*)map_v;
     int rc;
 #define ARGS mk, mv, (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, \
-             Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, flag, stream
+             Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, (__nv_bfloat16*)out, out_stride, combine, flag, stream
     switch (D) {
         case 64: rc = launch<64>(ARGS); break;
         case 128: rc = launch<128>(ARGS); break;
@@ -530,9 +573,12 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
         default: rc = launch<256>(ARGS); break;
     }
 #undef ARGS
-    if (rc != 0) return rc;
+    if (rc != 0 || combine != COMBINE_SCRATCH) return rc;
     dim3 grid(num_rows, Hq);
     kb_launch(attention_decode_tma_merge_kernel, dim3(grid), dim3(128), 0, stream, part_o, part_ml, seq_lens, decode_rows,
               decode_tokens, (__nv_bfloat16*)out, out_stride, Hq, D, window, num_splits);
     return kb_launch_result();
 }
+
+// Launches kb_attention_decode_tma makes for this many splits: 1, or 2 when a merge kernel follows.
+KB_EXPORT int kb_attention_decode_tma_launches(int num_splits) { return num_splits > 1 ? 2 : 1; }

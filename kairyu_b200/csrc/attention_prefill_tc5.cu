@@ -6,7 +6,7 @@
 // A block owns 128 queries of one head (a tile of the tile list) and walks the keys it may see
 // in tiles of 64.  Roles (192 threads):
 //   warp 0     producer: TMA copies of the Q tile (2-D map over the packed qkv rows) and of
-//              every K and V tile (4-D map over the cache: a copy brings a page's run of rows
+//              every K and V tile (a map over the cache: a copy brings a page's run of rows
 //              for one KV head), two stages ahead of their use;
 //   warp 1     one thread issues tcgen05.mma: S = Q K^T into one of two buffers of 64 TMEM
 //              columns, O += P V into head_dim TMEM columns.  Q K^T runs two tiles ahead of
@@ -21,6 +21,16 @@
 // MN-major operand, read straight from the [key][dim] rows the cache holds.
 // Two blocks share an SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory), so one block's
 // softmax overlaps the other's products.
+//
+// How many copies an SM can issue bounds this kernel before the tensor cores do (about 50 to
+// 75 ns a copy were measured; a 64-key tile of 16-position pages and 128 columns is 16 copies of
+// 2 KB with one copy per 64-column band, 1 us a tile, against 0.28 us of products).  So for
+// head_dim 128 and pages of 16 positions or more the copies of V take both bands at once
+// (`merged`: a 5-D map whose band dimension has the smallest stride; 12 copies a tile).  A V tile
+// then lies in shared memory as [run of positions][band][position][64 columns]; P V, whose steps
+// are 16 keys anyway, only takes other strides.  K keeps a copy per band: as a K-major operand it
+// needs its 8-row groups evenly spaced over all 64 keys, and issuing Q K^T run by run instead
+// (N = 16) cost more on the tensor cores than the copies saved (104 against 71 us for 2,048 tokens).
 //
 // Every wait on an mbarrier is bounded: a role that gives up raises KB_FLAG_TIMEOUT, lets the
 // other roles leave through a shared abort word, and the block frees its TMEM and returns.
@@ -87,7 +97,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
                              const int* __restrict__ tile_starts, int Hq, int Hkv, int page_size, int page_shift, int num_pages,
-                             float scale, int window, int* flag) {
+                             float scale, int window, int merged, int* flag) {
     using Cfg = FaCfg<D>;
     constexpr int BANDS = Cfg::BANDS;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -156,6 +166,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int first_kt = key_lo / FA_BN;
     const int last_kt = (key_end - 1) / FA_BN;
     const int num_kt = last_kt - first_kt + 1;
+    // Layout of a V tile: rows of a band lie `run_rows` x 128 bytes from the next band's, and a run
+    // of positions BANDS x run_rows x 128 bytes from the next run (not merged: one run of 64, as K).
+    const int box_rows = page_size < FA_BN ? page_size : FA_BN;
+    const int run_rows = merged ? box_rows : FA_BN;
+    const int band_bytes = run_rows * 128;
+    const int run_bytes = BANDS * band_bytes;
 
     if (*abort_word) {
         // fall through to the common exit
@@ -168,9 +184,9 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 tma_load_2d_plain(sQ + band * Cfg::Q_BAND, &map_q, h * D + band * 64, tok0 + q0, q_full);
         }
         const int* table = block_table + (size_t)row * max_pages;
-        const int box_rows = page_size < FA_BN ? page_size : FA_BN;
         const int runs = FA_BN / box_rows;
-        const int per_kind = BANDS * runs;  // copies of a K (or V) tile
+        const int per_k = BANDS * runs;                     // copies of a K tile
+        const int per_v = merged ? runs : BANDS * runs;     // copies of a V tile
         bool ok = true;
         for (int j = 0; j < num_kt && ok; ++j) {
             const int st = j % FA_STAGES;
@@ -187,8 +203,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 uint64_t* bar = (is_v ? v_full : k_full) + st;
                 if (lane == 0) mbar_arrive_expect_tx(bar, Cfg::KV_BYTES);
                 __syncwarp();
-                for (int op = lane; op < per_kind; op += 32) {
-                    const int band = op / runs;
+                for (int op = lane; op < (is_v ? per_v : per_k); op += 32) {
+                    const int band = op / runs;  // 0 when the copy takes every band
                     const int run = op % runs;
                     const int key = (first_kt + j) * FA_BN + run * box_rows;
                     const int page_index = key >> page_shift;
@@ -200,8 +216,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                             within = key - (page_index << page_shift);
                         }
                     }
-                    unsigned char* dst = (is_v ? sV : sK) + st * Cfg::KV_BYTES + band * Cfg::KV_BAND + run * box_rows * 128;
-                    tma_load_4d_plain(dst, is_v ? &map_v : &map_k, band * 64, kvh, within, page, bar);
+                    unsigned char* tile_base = (is_v ? sV : sK) + st * Cfg::KV_BYTES;
+                    if (is_v && merged)
+                        tma_load_5d_plain(tile_base + run * run_bytes, &map_v, 0, kvh, within, 0, page, bar);
+                    else
+                        tma_load_4d_plain(tile_base + band * Cfg::KV_BAND + run * box_rows * 128, is_v ? &map_v : &map_k, band * 64, kvh, within, page, bar);
                 }
             }
         }
@@ -214,7 +233,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // one of each kind and add offsets.
             const uint64_t q_desc = umma_desc_sw128(smem_addr(sQ));
             const uint64_t k_desc = umma_desc_sw128(smem_addr(sK));
-            const uint64_t v_desc = umma_desc_mn_sw128(smem_addr(sV), Cfg::KV_BAND, 1024);
+            const uint64_t v_desc = umma_desc_mn_sw128(smem_addr(sV), (uint32_t)band_bytes, 1024);
             bool ok = true;
             auto give_up = [&]() {
                 if (!*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
@@ -255,9 +274,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 tc_fence_after();
                 const uint64_t v_tile = v_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
 #pragma unroll
-                for (int ks = 0; ks < FA_BN / 16; ++ks)  // 16 keys: 8 columns of P in tensor memory, 16 rows of V
+                for (int ks = 0; ks < FA_BN / 16; ++ks) {  // 16 keys: 8 columns of P in tensor memory, 16 rows of V
+                    const int key = ks * 16;
+                    const int v_offset = (key / run_rows) * run_bytes + (key % run_rows) * 128;
                     umma_bf16_a_tmem(tmem_base + Cfg::O_COL, tmem_base + Cfg::S_COL + (j & 1) * FA_BN + ks * 8,
-                                     v_tile + (uint64_t)((ks * 16 * 128) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                                     v_tile + (uint64_t)(v_offset >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                }
                 umma_commit(v_empty + st);  // the slot may be refilled once these products have read it
                 umma_commit(pv_done);
                 if (j + 2 < num_kt) {
@@ -366,7 +388,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     const int vr = idx / (BANDS * 8);
                     const int c = idx % (BANDS * 8);
                     if (key0 + vr >= key_end)
-                        *reinterpret_cast<uint4*>(v_tile + (c >> 3) * Cfg::KV_BAND + vr * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(v_tile + (vr / run_rows) * run_bytes + (c >> 3) * band_bytes + (vr % run_rows) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async_smem();
             }
@@ -424,7 +446,7 @@ template <int D>
 static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, __nv_bfloat16* out, int out_stride,
                      const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages, const int* tile_rows,
                      const int* tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int num_pages, float scale, int window,
-                     int* flag, cudaStream_t stream) {
+                     int merged, int* flag, cudaStream_t stream) {
     const size_t smem = FaCfg<D>::SMEM;
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -432,7 +454,7 @@ static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtenso
     while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
     dim3 grid(Hq, num_tiles);
     kb_launch(attention_prefill_tc5_kernel<D>, dim3(grid), dim3(FA_THREADS), smem, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
-              seq_lens, block_table, max_pages, tile_rows, tile_starts, Hq, Hkv, page_size, shift, num_pages, scale, window, flag);
+              seq_lens, block_table, max_pages, tile_rows, tile_starts, Hq, Hkv, page_size, shift, num_pages, scale, window, merged, flag);
     return kb_launch_result();
 }
 
@@ -443,10 +465,15 @@ KB_EXPORT int kb_attention_prefill_tc5_supported(int D, int page_size) {
     return 1;
 }
 
+// 1 when the kernel wants a map of V whose boxes take every 64-column band at once
+// (kb_attention_encode_cache_map with bands = 1) for this head_dim and page size.
+KB_EXPORT int kb_attention_prefill_tc5_merged(int D, int page_size) { return D > 64 && page_size >= 16 ? 1 : 0; }
+
 // map_q: 2-D map over the packed qkv rows [tokens, q_stride] with boxes of [128 rows, 64 columns];
-// map_k, map_v: 4-D maps over the caches [pages, page_size, kv_heads, head_dim] with boxes of
-// 64 columns x 1 head x min(page_size, 64) positions x 1 page; all with the 128-byte swizzle
-// (host pointers).  The tile list holds 128 queries per tile.
+// map_k, map_v: maps over the caches [pages, page_size, kv_heads, head_dim]: 4-D with boxes of
+// 64 columns x 1 head x min(page_size, 64) positions x 1 page; map_v, where
+// kb_attention_prefill_tc5_merged says so, 5-D with every band in a box; all with the 128-byte
+// swizzle (host pointers).  The tile list holds 128 queries per tile.
 KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, const void* map_v, void* out, int out_stride,
                                        const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages,
                                        const int* tile_rows, const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
@@ -457,7 +484,8 @@ KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, con
     if (out_stride % 8 != 0 || ((uintptr_t)out % 16) != 0) return KB_ERR_BAD_ARG;  // 16-byte stores of whole rows
     if (!kb_attention_prefill_tc5_supported(D, page_size)) return KB_ERR_UNSUPPORTED_SIZE;
 #define ARGS (const CUtensorMap*)map_q, (const CUtensorMap*)map_k, (const CUtensorMap*)map_v, (__nv_bfloat16*)out, out_stride, qo_indptr, \
-             seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, num_pages, scale, window, flag, stream
+             seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, num_pages, scale, window,            \
+             kb_attention_prefill_tc5_merged(D, page_size), flag, stream
     if (D == 64) return launch_fa<64>(ARGS);
     return launch_fa<128>(ARGS);
 #undef ARGS

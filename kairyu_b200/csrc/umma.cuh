@@ -134,6 +134,13 @@ __device__ __forceinline__ void tma_load_4d_plain(void* dst, const CUtensorMap* 
         "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_5d_plain(void* dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, int c4, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];\n" ::"r"(
+            smem_addr(dst)),
+        "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
 // 32 consecutive 32-bit columns of this warp's 32 TMEM lanes; the caller waits (tmem_wait_ld).
 __device__ __forceinline__ void tmem_load32_nowait(uint32_t address, uint32_t (&r)[32]) {
     asm volatile(

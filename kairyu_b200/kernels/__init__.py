@@ -371,9 +371,10 @@ def attention_prefill_mma(
             "kb_attention_prefill_tc5",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
         )
+        merged = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_merged", [c_int, c_int])(head_dim, page_size))
         _check(
             fn(
-                _tensor_map(q, 128), _cache_map(k_cache), _cache_map(v_cache), out.data_ptr(), out.stride(0),
+                _tensor_map(q, 128), _cache_map(k_cache), _cache_map(v_cache, bands=merged), out.data_ptr(), out.stride(0),
                 qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
                 tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
                 page_size, num_pages, float(scale), int(window), _ptr(flag), _stream(),
@@ -444,13 +445,13 @@ def attention_decode_mma(
         )
         _check(
             fn(
-                _cache_map(k_cache), _cache_map(v_cache), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+                _cache_map(k_cache, bands=True), _cache_map(v_cache, bands=True), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
                 seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
                 decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
                 float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(flag), _stream(),
             ),
             what,
-            launches=2,
+            launches=_fn("attention_decode_tma", "kb_attention_decode_tma_launches", [c_int])(num_splits),
         )
         return
     num_splits = max(1, -(-int(max_seq_len) // DECODE_SPLIT))
@@ -492,17 +493,18 @@ def _decode_tma_ok(k_cache: torch.Tensor, v_cache: torch.Tensor) -> bool:
     )
 
 
-def _cache_map(cache: torch.Tensor) -> int:
-    """Host address of a cached TMA descriptor of one layer's key (or value) pages."""
-    key = ("cache", cache.data_ptr(), tuple(cache.shape), tuple(cache.stride()))
+def _cache_map(cache: torch.Tensor, bands: bool = False) -> int:
+    """Host address of a cached TMA descriptor of one layer's key (or value) pages: boxes of one
+    64-column band (the prefill kernel's), or with ``bands`` of every band at once (the decode kernel's)."""
+    key = ("cache", cache.data_ptr(), tuple(cache.shape), tuple(cache.stride()), bands)
     held = _held_map(key)
     if held is None:
         held = ctypes.create_string_buffer(128 + 64)
         address = (ctypes.addressof(held) + 63) & ~63
         ll = ctypes.c_longlong
-        fn = _fn("attention_decode_tma", "kb_attention_encode_cache_map", [c_void_p, c_void_p, ll, c_int, c_int, c_int, ll, ll, ll])
+        fn = _fn("attention_decode_tma", "kb_attention_encode_cache_map", [c_void_p, c_void_p, ll, c_int, c_int, c_int, ll, ll, ll, c_int])
         num_pages, page_size, num_kv_heads, head_dim = cache.shape
-        code = fn(address, cache.data_ptr(), num_pages, page_size, num_kv_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2))
+        code = fn(address, cache.data_ptr(), num_pages, page_size, num_kv_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2), 1 if bands else 0)
         if code != 0:
             raise KernelError(f"tensor map encoding of the cache failed with code {code}")
         _keep_map(key, held)

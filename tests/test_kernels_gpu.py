@@ -574,7 +574,7 @@ def test_mma_attention_random(Hq, Hkv, D, page_size, window, workspace):
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page_size", [(8, 2, 64, 16), (32, 8, 128, 16), (6, 2, 192, 8), (2, 1, 256, 64)])
-@pytest.mark.parametrize("num_splits", [1, 2, 3, 7])
+@pytest.mark.parametrize("num_splits", [1, 2, 3, 7, 8, 9, 16])
 @pytest.mark.parametrize("window", [0, 333])
 def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_size, num_splits, window, workspace):
     """Few splits and long rows: every block of the TMA-fed kernel refills its stages several times."""
