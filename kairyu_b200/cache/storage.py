@@ -14,7 +14,8 @@ _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": 
 
 
 class CacheStorage:
-    """K and V of group g: ``[slots_in_group, num_pages, page_size, kv_heads, head_dim]``.
+    """K and V of group g: ``[slots_in_group, num_pages, page_size, kv_heads, head_dim]``
+    (V with the spec's value width where that differs).
     A page of one slot is a contiguous ``[page_size, kv_heads*head_dim]`` tile.
     State tensors: ``[max_requests + 1, *shape]`` each; the last row is the scratch slot that
     padding rows of a decode graph use."""
@@ -35,9 +36,9 @@ class CacheStorage:
         self.k: list[torch.Tensor] = []
         self.v: list[torch.Tensor] = []
         for group in layout.groups:
-            shape = (len(group.slots), num_pages, page_size, group.spec.num_kv_heads, group.spec.head_dim)
-            self.k.append(torch.zeros(shape, dtype=dtype, device=device))
-            self.v.append(torch.zeros(shape, dtype=dtype, device=device))
+            shape = (len(group.slots), num_pages, page_size, group.spec.num_kv_heads)
+            self.k.append(torch.zeros((*shape, group.spec.head_dim), dtype=dtype, device=device))
+            self.v.append(torch.zeros((*shape, group.spec.value_dim), dtype=dtype, device=device))
         self.states = [
             torch.zeros((max_requests + 1, *binding.spec.shape), dtype=_STATE_DTYPES[binding.spec.dtype], device=device)
             for binding in layout.states
@@ -46,7 +47,7 @@ class CacheStorage:
     @staticmethod
     def bytes_per_page(layout: CacheLayout, page_size: int, element_size: int) -> int:
         return sum(
-            2 * len(group.slots) * page_size * group.spec.num_kv_heads * group.spec.head_dim * element_size
+            len(group.slots) * page_size * group.spec.num_kv_heads * (group.spec.head_dim + group.spec.value_dim) * element_size
             for group in layout.groups
         )
 

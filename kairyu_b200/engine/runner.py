@@ -26,8 +26,6 @@ from kairyu_b200.cache.storage import CacheStorage
 from kairyu_b200.engine.workspace import Workspace
 from kairyu_b200.parts.base import CacheView, StepContext
 
-ATTENTION_TILE_SIZES = (64, 128)  # query-tile granularities the attention kernels may ask for
-
 
 @dataclass
 class StepEntry:
@@ -123,6 +121,10 @@ class ModelRunner:
         self.graph_workspace = Workspace(self.device)
         self._is_cuda = str(self.device).startswith("cuda")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # query-tile sizes the model's mixers want listed with every step (each names its own)
+        self._tile_sizes = tuple(sorted({
+            int(size) for block in getattr(model, "blocks", ()) for size in getattr(getattr(block, "mixer", None), "query_tile_sizes", lambda: ())()
+        }))
         self._views: dict[tuple[int, bool], CacheView] = {}
         for call in model.schedule:
             key = (call.cache_slot, call.writes_cache)
@@ -224,8 +226,8 @@ class ModelRunner:
         state_slots: list[int] = []
         want: list[int] = []
         future_src: list[int] = []
-        tile_rows: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
-        tile_starts: dict[int, list[int]] = {size: [] for size in ATTENTION_TILE_SIZES}
+        tile_rows: dict[int, list[int]] = {size: [] for size in self._tile_sizes}
+        tile_starts: dict[int, list[int]] = {size: [] for size in self._tile_sizes}
         decode_rows: list[int] = []
         decode_tokens: list[int] = []
         for row, (entry, start, seq_len) in enumerate(rows):
@@ -248,7 +250,7 @@ class ModelRunner:
                 decode_rows.append(row)
                 decode_tokens.append(base)
             else:
-                for size in ATTENTION_TILE_SIZES:
+                for size in self._tile_sizes:
                     for tile_start in range(0, count, size):
                         tile_rows[size].append(row)
                         tile_starts[size].append(tile_start)
@@ -285,8 +287,8 @@ class ModelRunner:
             "write_from": write_from,
             "state_slots": state_slots,
             "want": want,
-            **{f"tile_rows{size}": tile_rows[size] for size in ATTENTION_TILE_SIZES},
-            **{f"tile_starts{size}": tile_starts[size] for size in ATTENTION_TILE_SIZES},
+            **{f"tile_rows{size}": tile_rows[size] for size in self._tile_sizes},
+            **{f"tile_starts{size}": tile_starts[size] for size in self._tile_sizes},
             "decode_rows": decode_rows,
             "decode_tokens": decode_tokens,
             "tables": tables,
@@ -339,7 +341,7 @@ class ModelRunner:
             host_seq_lens=facts["host_seq_lens"],
             tiles={
                 size: (layout[f"tile_rows{size}"][1], part(f"tile_rows{size}"), part(f"tile_starts{size}"))
-                for size in ATTENTION_TILE_SIZES
+                for size in self._tile_sizes
             },
             num_decode_rows=layout["decode_rows"][1],
             decode_rows=part("decode_rows"),

@@ -213,6 +213,9 @@ class GQAAttention(Mixer):
     def cache_specs(self) -> tuple[Any, ...]:
         return (PagedKVSpec(self.num_kv_heads, self.head_dim, self.window),)
 
+    def query_tile_sizes(self) -> tuple[int, ...]:
+        return (kernels.attention_prefill_tile_rows(self.head_dim),)
+
     # -- compute
     def fusable_norm(self, tokens: int) -> bool:
         """Whether the q/k/v and the output product can take the norms around them into their epilogues."""

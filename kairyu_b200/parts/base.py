@@ -115,11 +115,19 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values in pages: ``window=None`` keeps every key, an integer
-    keeps the last ``window`` positions (older pages go back to the pool)."""
+    keeps the last ``window`` positions (older pages go back to the pool).
+    ``v_head_dim``: the width of a value row where it differs from a key row's
+    (a mixer whose values are narrower than its keys; None: the same).  Slots
+    whose specs are equal share a group: pages of one geometry, one block table."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -135,7 +143,7 @@ class CacheView:
     """What one call's mixer sees of the cache."""
 
     k: torch.Tensor | None = None  # [num_pages, page_size, kv_heads, head_dim]
-    v: torch.Tensor | None = None
+    v: torch.Tensor | None = None  # [num_pages, page_size, kv_heads, value_dim]
     page_size: int = 0
     group: int = -1  # which block table of the step belongs to this slot
     state: torch.Tensor | None = None  # [num_state_slots, *StateSpec.shape]
@@ -150,9 +158,10 @@ class StepContext:
     """Device-side description of one step's batch, shared by every layer.
 
     Rows are requests; tokens are flat over rows.  ``tiles[n]`` describes the
-    n-query tiles (n = 64, 128) of rows that carry more than one token (prompt
-    portions) as (count, row of each tile, offset of each tile within the row's
-    tokens); ``decode_*`` list rows that carry exactly one token.
+    n-query tiles of rows that carry more than one token (prompt portions) as
+    (count, row of each tile, offset of each tile within the row's tokens), for
+    every n some mixer of the model asked for (``Mixer.query_tile_sizes``);
+    ``decode_*`` list rows that carry exactly one token.
     """
 
     num_tokens: int
@@ -225,6 +234,11 @@ class PositionEncoding(Part):
 class Mixer(Part):
     def cache_specs(self) -> tuple[Any, ...]:
         """What this mixer keeps between steps: PagedKVSpec and/or StateSpec."""
+        return ()
+
+    def query_tile_sizes(self) -> tuple[int, ...]:
+        """Query-tile sizes this mixer's kernels want listed in the step's description
+        (``ctx.tiles[n]``): the step function packs a list for every size a mixer names."""
         return ()
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:

@@ -7,7 +7,6 @@ from typing import Mapping, Optional
 import torch
 
 from kairyu_b200 import kernels
-from kairyu_b200.parts.norm import RMSNorm
 from kairyu_b200.parts.base import (
     BLOCKS,
     FEED_FORWARDS,
@@ -16,6 +15,7 @@ from kairyu_b200.parts.base import (
     Block,
     CacheView,
     LayerSpec,
+    Norm,
     StepContext,
     TensorSpec,
 )
@@ -31,8 +31,8 @@ class PreNormBlock(Block):
     For a few bf16 rows (decode) the norms have no kernel of their own: the product before a
     norm adds its result to the residual and leaves the rows weighted and their sums of squares
     (``kernels.ResidualNorm``), the product after it scales by the root mean square
-    (``kernels.PreNormed``).  That needs RMSNorms and a mixer and feed-forward that offer
-    ``fusable_norm``; any other part gets the plain flow.
+    (``kernels.PreNormed``).  That needs norms that offer ``fold_target`` (RMSNorm does) and a
+    mixer and feed-forward that offer ``fusable_norm``; any other part gets the plain flow.
     """
 
     takes_next_norm = True  # forward accepts the norm of the block that runs next
@@ -58,13 +58,13 @@ class PreNormBlock(Block):
     def _fused(self, ctx: StepContext) -> bool:
         if ctx.dtype != torch.bfloat16 or not kernels.fused_norm_available():
             return False
-        if not (isinstance(self.mixer_norm, RMSNorm) and isinstance(self.ffn_norm, RMSNorm)):
-            return False
+        if not (hasattr(self.mixer_norm, "fold_target") and hasattr(self.ffn_norm, "fold_target")):
+            return False  # a norm offers ``fold_target`` when the products around it can take its two halves
         mixer_ok = getattr(self.mixer, "fusable_norm", None)
         ffn_ok = getattr(self.ffn, "fusable_norm", None)
         return bool(mixer_ok and ffn_ok and mixer_ok(ctx.num_tokens) and ffn_ok(ctx.num_tokens))
 
-    def prenorm_target(self, ctx: StepContext) -> Optional[RMSNorm]:
+    def prenorm_target(self, ctx: StepContext) -> Optional[Norm]:
         """The norm the block before this one may fold into its last product, or None."""
         return self.mixer_norm if self._fused(ctx) else None
 
@@ -74,7 +74,7 @@ class PreNormBlock(Block):
         delta,
         ctx: StepContext,
         cache: CacheView,
-        next_norm: Optional[RMSNorm] = None,
+        next_norm: Optional[Norm] = None,
     ):
         if isinstance(delta, kernels.PreNormed):  # the block before has added its output and begun our norm
             normed = delta

@@ -147,3 +147,20 @@ def test_random_orders_never_lose_or_share_a_page(seed):
         cache.release(name)
     cache.check()
     assert all(pool.num_held == 0 for pool in cache.pools)
+
+
+def test_values_may_be_narrower_than_keys_and_get_pages_of_their_own_shape():
+    """A mixer describes what it keeps: keys of one width, values of another.  Slots whose needs
+    are equal share a group (one geometry, one block table); the storage gives K and V their own shapes."""
+    import torch
+
+    from kairyu_b200.cache import CacheStorage
+
+    narrow = PagedKVSpec(2, 24, None, v_head_dim=8)
+    layout = CacheLayout.from_slot_specs({0: (PagedKVSpec(2, 16),), 1: (narrow,), 2: (narrow,)})
+    assert [group.slots for group in layout.groups] == [(0,), (1, 2)]
+    storage = CacheStorage(layout, num_pages=5, page_size=4, max_requests=2, dtype=torch.float32, device="cpu")
+    assert tuple(storage.k[1].shape) == (2, 5, 4, 2, 24) and tuple(storage.v[1].shape) == (2, 5, 4, 2, 8)
+    view = storage.view(2, writes=True)
+    assert tuple(view.k.shape) == (5, 4, 2, 24) and tuple(view.v.shape) == (5, 4, 2, 8) and view.group == 1
+    assert CacheStorage.bytes_per_page(layout, 4, 4) == 4 * 2 * 4 * (2 * 16 + 2 * (24 + 8))
