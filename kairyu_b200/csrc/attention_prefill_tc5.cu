@@ -3,8 +3,14 @@
 //
 //     S = Q K^T * scale (causal, optional window),  P = softmax rows online,  O = P V.
 //
-// A block owns 128 queries of one head (a tile of the tile list) and walks the keys it may see
-// in tiles of 64.  Roles (192 threads):
+// A block owns a tile of 128 queries of one head, or two, one after the other.  Later tiles of a
+// portion see more keys.  With many tiles, blocks take one tile each, the longest first, and the
+// short ones fill the tail of the grid.  When all blocks fit the device at once even at two tiles
+// each (a prompt of 2,048 tokens: 16 tiles x 32 heads), a block takes tile T-1-y of the list and
+// then tile y, so that every block of a prompt does the same work (34 key tiles each) instead of
+// the longest walking its 32 key tiles alone at the end (2,048 tokens: 63 -> 59 us; at 8,192
+// tokens equal blocks would fill their last wave badly: 629 -> 707 us, so there they stay single).
+// For a tile the block walks the keys it may see in tiles of 64.  Roles (192 threads):
 //   warp 0     producer: TMA copies of the Q tile (2-D map over the packed qkv rows) and of
 //              every K and V tile (a map over the cache: a copy brings a page's run of rows
 //              for one KV head), two stages ahead of their use;
@@ -82,7 +88,7 @@ struct FaCfg {
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + FA_STAGES * KV_BYTES;
     static constexpr int OFF_BAR = OFF_V + FA_STAGES * KV_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 2;
+    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 2 + 1;
     static constexpr size_t SMEM = OFF_BAR + NUM_BARS * 8 + 16;
     static constexpr int S_COL = 0;          // two S buffers of FA_BN columns each; P (bf16 pairs) overwrites the first half of its S
     static constexpr int O_COL = 2 * FA_BN;
@@ -96,8 +102,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out, int out_stride,
                              const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
-                             const int* __restrict__ tile_starts, int Hq, int Hkv, int page_size, int page_shift, int num_pages,
-                             float scale, int window, int merged, int* flag) {
+                             const int* __restrict__ tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int page_shift,
+                             int num_pages, float scale, int window, int merged, int paired, int* flag) {
     using Cfg = FaCfg<D>;
     constexpr int BANDS = Cfg::BANDS;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -113,6 +119,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* s_full = v_empty + FA_STAGES;  // one per S buffer
     uint64_t* p_full = s_full + 2;
     uint64_t* pv_done = p_full + 1;
+    uint64_t* q_empty = pv_done + 1;  // every Q K^T of a query tile has read the queries' buffer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -133,6 +140,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         mbar_init(s_full + 1, 1);
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
+        mbar_init(q_empty, 1);
         *abort_word = 0;
         if ((smem_addr(smem) & 1023u) != 0) {  // the swizzled layouts below assume it
             if (flag) atomicOr(flag, KB_FLAG_MISALIGNED);
@@ -148,24 +156,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const uint32_t tmem_base = *tmem_slot;
     pdl_wait();
 
-    // Later tiles of a portion see more keys and run longer: hand them out first.
-    const int tile = gridDim.y - 1 - blockIdx.y;
+    // The block's two tiles: a long one first (later tiles of a portion see more keys), then the short
+    // one from the other end of the list.  Barrier phases run on through both: `g` counts key tiles
+    // since the block began.
     const int h = blockIdx.x;
     const int kvh = h / (Hq / Hkv);
-    const int row = tile_rows[tile];
-    const int q0 = tile_starts[tile];
-    const int tok0 = qo_indptr[row];
-    const int chunk_len = qo_indptr[row + 1] - tok0;
-    const int seq_len = seq_lens[row];
-    const int chunk_pos = seq_len - chunk_len;  // absolute position of the portion's first token
-    const int rows_here = min(FA_BM, chunk_len - q0);
-    const int first_pos = chunk_pos + q0;
-    const int last_pos = first_pos + rows_here - 1;
-    const int key_end = last_pos + 1;  // causal bound of the tile (<= seq_len)
-    const int key_lo = (window > 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
-    const int first_kt = key_lo / FA_BN;
-    const int last_kt = (key_end - 1) / FA_BN;
-    const int num_kt = last_kt - first_kt + 1;
+    const int num_parts = (paired && (int)blockIdx.y != num_tiles - 1 - (int)blockIdx.y) ? 2 : 1;
     // Layout of a V tile: rows of a band lie `run_rows` x 128 bytes from the next band's, and a run
     // of positions BANDS x run_rows x 128 bytes from the next run (not merged: one run of 64, as K).
     const int box_rows = page_size < FA_BN ? page_size : FA_BN;
@@ -173,56 +169,90 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int band_bytes = run_rows * 128;
     const int run_bytes = BANDS * band_bytes;
 
+    struct TileInfo {
+        int row, q0, tok0, rows_here, first_pos, last_pos, key_end, key_lo, first_kt, num_kt;
+    };
+    auto tile_info = [&](int part) {
+        TileInfo t;
+        const int tile = part == 0 ? num_tiles - 1 - (int)blockIdx.y : (int)blockIdx.y;
+        t.row = tile_rows[tile];
+        t.q0 = tile_starts[tile];
+        t.tok0 = qo_indptr[t.row];
+        const int chunk_len = qo_indptr[t.row + 1] - t.tok0;
+        const int seq_len = seq_lens[t.row];
+        const int chunk_pos = seq_len - chunk_len;  // absolute position of the portion's first token
+        t.rows_here = min(FA_BM, chunk_len - t.q0);
+        t.first_pos = chunk_pos + t.q0;
+        t.last_pos = t.first_pos + t.rows_here - 1;
+        t.key_end = t.last_pos + 1;  // causal bound of the tile (<= seq_len)
+        t.key_lo = (window > 0 && t.first_pos + 1 > window) ? t.first_pos + 1 - window : 0;
+        t.first_kt = t.key_lo / FA_BN;
+        t.num_kt = (t.key_end - 1) / FA_BN - t.first_kt + 1;
+        return t;
+    };
+
     if (*abort_word) {
         // fall through to the common exit
     } else if (warp == 0) {
         // ---------------- producer
-        if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
-#pragma unroll
-            for (int band = 0; band < BANDS; ++band)
-                tma_load_2d_plain(sQ + band * Cfg::Q_BAND, &map_q, h * D + band * 64, tok0 + q0, q_full);
-        }
-        const int* table = block_table + (size_t)row * max_pages;
         const int runs = FA_BN / box_rows;
         const int per_k = BANDS * runs;                     // copies of a K tile
         const int per_v = merged ? runs : BANDS * runs;     // copies of a V tile
         bool ok = true;
-        for (int j = 0; j < num_kt && ok; ++j) {
-            const int st = j % FA_STAGES;
-            const int use = j / FA_STAGES;
+        int g0 = 0;
+        for (int part = 0; part < num_parts && ok; ++part) {
+            const TileInfo t = tile_info(part);
+            // the queries' buffer is free once every Q K^T of the tile before has read it
+            if (part > 0 && !mbar_wait(q_empty, (part - 1) & 1, abort_word)) {
+                if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
+                *abort_word = 1;
+                break;
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(q_full, Cfg::Q_BYTES);
 #pragma unroll
-            for (int is_v = 0; is_v < 2; ++is_v) {
-                // K's slot is free once Q K^T of the tile that used it is done, V's once its P V is done
-                if (use > 0 && !mbar_wait((is_v ? v_empty : k_empty) + st, (use - 1) & 1, abort_word)) {
-                    if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
-                    *abort_word = 1;
-                    ok = false;
-                    break;
-                }
-                uint64_t* bar = (is_v ? v_full : k_full) + st;
-                if (lane == 0) mbar_arrive_expect_tx(bar, Cfg::KV_BYTES);
-                __syncwarp();
-                for (int op = lane; op < (is_v ? per_v : per_k); op += 32) {
-                    const int band = op / runs;  // 0 when the copy takes every band
-                    const int run = op % runs;
-                    const int key = (first_kt + j) * FA_BN + run * box_rows;
-                    const int page_index = key >> page_shift;
-                    int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
-                    if (key < key_end && key + box_rows > key_lo && page_index < max_pages) {
-                        const int p = table[page_index];
-                        if (p >= 0 && p < num_pages) {
-                            page = p;
-                            within = key - (page_index << page_shift);
-                        }
+                for (int band = 0; band < BANDS; ++band)
+                    tma_load_2d_plain(sQ + band * Cfg::Q_BAND, &map_q, h * D + band * 64, t.tok0 + t.q0, q_full);
+            }
+            const int* table = block_table + (size_t)t.row * max_pages;
+            for (int j = 0; j < t.num_kt && ok; ++j) {
+                const int g = g0 + j;
+                const int st = g % FA_STAGES;
+                const int use = g / FA_STAGES;
+#pragma unroll
+                for (int is_v = 0; is_v < 2; ++is_v) {
+                    // K's slot is free once Q K^T of the tile that used it is done, V's once its P V is done
+                    if (use > 0 && !mbar_wait((is_v ? v_empty : k_empty) + st, (use - 1) & 1, abort_word)) {
+                        if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
+                        *abort_word = 1;
+                        ok = false;
+                        break;
                     }
-                    unsigned char* tile_base = (is_v ? sV : sK) + st * Cfg::KV_BYTES;
-                    if (is_v && merged)
-                        tma_load_5d_plain(tile_base + run * run_bytes, &map_v, 0, kvh, within, 0, page, bar);
-                    else
-                        tma_load_4d_plain(tile_base + band * Cfg::KV_BAND + run * box_rows * 128, is_v ? &map_v : &map_k, band * 64, kvh, within, page, bar);
+                    uint64_t* bar = (is_v ? v_full : k_full) + st;
+                    if (lane == 0) mbar_arrive_expect_tx(bar, Cfg::KV_BYTES);
+                    __syncwarp();
+                    for (int op = lane; op < (is_v ? per_v : per_k); op += 32) {
+                        const int band = op / runs;  // 0 when the copy takes every band
+                        const int run = op % runs;
+                        const int key = (t.first_kt + j) * FA_BN + run * box_rows;
+                        const int page_index = key >> page_shift;
+                        int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
+                        if (key < t.key_end && key + box_rows > t.key_lo && page_index < max_pages) {
+                            const int p = table[page_index];
+                            if (p >= 0 && p < num_pages) {
+                                page = p;
+                                within = key - (page_index << page_shift);
+                            }
+                        }
+                        unsigned char* tile_base = (is_v ? sV : sK) + st * Cfg::KV_BYTES;
+                        if (is_v && merged)
+                            tma_load_5d_plain(tile_base + run * run_bytes, &map_v, 0, kvh, within, 0, page, bar);
+                        else
+                            tma_load_4d_plain(tile_base + band * Cfg::KV_BAND + run * box_rows * 128, is_v ? &map_v : &map_k, band * 64, kvh, within, page, bar);
+                    }
                 }
             }
+            g0 += t.num_kt;
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (one thread)
@@ -240,57 +270,66 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 *abort_word = 1;
                 ok = false;
             };
-            // S[j % 2] = Q K_j^T; releases K's slot and tells the softmax warps
-            auto issue_qk = [&](int j) {
-                const int st = j % FA_STAGES;
+            // S[g % 2] = Q K_g^T; releases K's slot and tells the softmax warps
+            auto issue_qk = [&](int g, bool last_of_tile) {
+                const int st = g % FA_STAGES;
                 const uint64_t k_tile = k_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
 #pragma unroll
                 for (int band = 0; band < BANDS; ++band)
 #pragma unroll
                     for (int k = 0; k < 4; ++k)  // 16 of the head dimension = 32 bytes along the swizzled row
-                        umma_bf16(tmem_base + Cfg::S_COL + (j & 1) * FA_BN, q_desc + (uint64_t)((band * Cfg::Q_BAND + k * 32) >> 4),
+                        umma_bf16(tmem_base + Cfg::S_COL + (g & 1) * FA_BN, q_desc + (uint64_t)((band * Cfg::Q_BAND + k * 32) >> 4),
                                   k_tile + (uint64_t)((band * Cfg::KV_BAND + k * 32) >> 4), idesc_qk, (band > 0 || k > 0) ? 1u : 0u);
                 umma_commit(k_empty + st);
-                umma_commit(s_full + (j & 1));
+                umma_commit(s_full + (g & 1));
+                if (last_of_tile) umma_commit(q_empty);  // the queries' buffer may take the next tile's
             };
-            if (!mbar_wait(q_full, 0, abort_word) || !mbar_wait(k_full, 0, abort_word)) give_up();
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            if (ok && num_kt > 1) {
-                if (!mbar_wait(k_full + 1, 0, abort_word)) give_up();
+            int g0 = 0;
+            for (int part = 0; part < num_parts && ok; ++part) {
+                const int num_kt = tile_info(part).num_kt;
+                // Q K^T runs two key tiles ahead of P V.  (The two S buffers are free here: the products that
+                // read the tile before's last P were issued before these, and the tensor pipe keeps the order.)
+                if (!mbar_wait(q_full, part & 1, abort_word) || !mbar_wait(k_full + g0 % FA_STAGES, (g0 / FA_STAGES) & 1, abort_word)) give_up();
                 if (ok) {
                     tc_fence_after();
-                    issue_qk(1);
+                    issue_qk(g0, num_kt == 1);
                 }
-            }
-            for (int j = 0; j < num_kt && ok; ++j) {
-                const int st = j % FA_STAGES;
-                if (!mbar_wait(p_full, j & 1, abort_word) || !mbar_wait(v_full + st, (j / FA_STAGES) & 1, abort_word)) {
-                    give_up();
-                    break;
+                if (ok && num_kt > 1) {
+                    if (!mbar_wait(k_full + (g0 + 1) % FA_STAGES, ((g0 + 1) / FA_STAGES) & 1, abort_word)) give_up();
+                    if (ok) {
+                        tc_fence_after();
+                        issue_qk(g0 + 1, num_kt == 2);
+                    }
                 }
-                tc_fence_after();
-                const uint64_t v_tile = v_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
-#pragma unroll
-                for (int ks = 0; ks < FA_BN / 16; ++ks) {  // 16 keys: 8 columns of P in tensor memory, 16 rows of V
-                    const int key = ks * 16;
-                    const int v_offset = (key / run_rows) * run_bytes + (key % run_rows) * 128;
-                    umma_bf16_a_tmem(tmem_base + Cfg::O_COL, tmem_base + Cfg::S_COL + (j & 1) * FA_BN + ks * 8,
-                                     v_tile + (uint64_t)(v_offset >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-                }
-                umma_commit(v_empty + st);  // the slot may be refilled once these products have read it
-                umma_commit(pv_done);
-                if (j + 2 < num_kt) {
-                    // the softmax warps hold S_j in registers (they have written P_j): its buffer takes tile j + 2
-                    if (!mbar_wait(k_full + st, ((j + 2) / FA_STAGES) & 1, abort_word)) {
+                for (int j = 0; j < num_kt && ok; ++j) {
+                    const int g = g0 + j;
+                    const int st = g % FA_STAGES;
+                    if (!mbar_wait(p_full, g & 1, abort_word) || !mbar_wait(v_full + st, (g / FA_STAGES) & 1, abort_word)) {
                         give_up();
                         break;
                     }
                     tc_fence_after();
-                    issue_qk(j + 2);
+                    const uint64_t v_tile = v_desc + (uint64_t)((st * Cfg::KV_BYTES) >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < FA_BN / 16; ++ks) {  // 16 keys: 8 columns of P in tensor memory, 16 rows of V
+                        const int key = ks * 16;
+                        const int v_offset = (key / run_rows) * run_bytes + (key % run_rows) * 128;
+                        umma_bf16_a_tmem(tmem_base + Cfg::O_COL, tmem_base + Cfg::S_COL + (g & 1) * FA_BN + ks * 8,
+                                         v_tile + (uint64_t)(v_offset >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                    }
+                    umma_commit(v_empty + st);  // the slot may be refilled once these products have read it
+                    umma_commit(pv_done);
+                    if (j + 2 < num_kt) {
+                        // the softmax warps hold S_g in registers (they have written P_g): its buffer takes tile g + 2
+                        if (!mbar_wait(k_full + st, ((g + 2) / FA_STAGES) & 1, abort_word)) {
+                            give_up();
+                            break;
+                        }
+                        tc_fence_after();
+                        issue_qk(g + 2, j + 3 == num_kt);
+                    }
                 }
+                g0 += num_kt;
             }
         }
     } else {
@@ -298,112 +337,115 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         const int quarter = warp & 3;  // the TMEM lanes this warp may touch
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const bool valid = r < rows_here;
-        const int pos = valid ? first_pos + r : last_pos;
-        const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
-        const int lo_last = (window > 0 && last_pos + 1 > window) ? last_pos + 1 - window : 0;
         const int soft_tid = threadIdx.x - 64;  // 0..127
         const float sl2 = scale * FA_LOG2E;
-        float m_ref = -INFINITY;  // the maximum the row's P and O are scaled by
-        float l = 0.0f;
         bool ok = true;
-        for (int j = 0; j < num_kt; ++j) {
-            const int key0 = (first_kt + j) * FA_BN;
-            if (!mbar_wait(s_full + (j & 1), (j >> 1) & 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            uint32_t raw[2][32];
-            tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN, raw[0]);
-            tmem_load32_nowait(lane_base + Cfg::S_COL + (j & 1) * FA_BN + 32, raw[1]);
-            tmem_wait_ld();
-            // Work on the raw scores: the row maximum is taken before the scale (scale > 0), and
-            // scale and reference enter the exponent's argument as one fused multiply-add.
-            float t[FA_BN];
-#pragma unroll
-            for (int c = 0; c < FA_BN; ++c) t[c] = __uint_as_float(raw[c >> 5][c & 31]);
-            if (key0 + FA_BN - 1 > first_pos || key0 < lo_last) {  // the diagonal or the window's edge crosses this tile
-#pragma unroll
-                for (int c = 0; c < FA_BN; ++c) {
-                    const int key = key0 + c;
-                    t[c] = (key <= pos && key >= lo) ? t[c] : -INFINITY;
-                }
-            }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int c = 0; c < FA_BN; c += 8) {
-                mx4[0] = max3(mx4[0], t[c], t[c + 1]);
-                mx4[1] = max3(mx4[1], t[c + 2], t[c + 3]);
-                mx4[2] = max3(mx4[2], t[c + 4], t[c + 5]);
-                mx4[3] = max3(mx4[3], t[c + 6], t[c + 7]);
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // -inf stays -inf
-            float alpha = 1.0f;
-            if (m_ref == -INFINITY) {
-                m_ref = mx;  // nothing accumulated for this row yet
-            } else if (mx > m_ref + FA_RESCALE_STEP) {
-                alpha = exp2f(m_ref - mx);
-                m_ref = mx;
-            }
-            // Every phase of pv_done is observed (a parity wait cannot tell a phase from the one two
-            // before it); P V of the tile before must also be complete before O is rescaled.
-            if (j > 0 && !mbar_wait(pv_done, (j - 1) & 1, abort_word)) { ok = false; break; }
-            if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        int g0 = 0;
+        for (int part = 0; part < num_parts && ok; ++part) {
+            const TileInfo t = tile_info(part);
+            const int num_kt = t.num_kt, first_kt = t.first_kt, first_pos = t.first_pos, last_pos = t.last_pos, key_end = t.key_end;
+            const bool valid = r < t.rows_here;
+            const int pos = valid ? first_pos + r : last_pos;
+            const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
+            const int lo_last = (window > 0 && last_pos + 1 > window) ? last_pos + 1 - window : 0;
+            float m_ref = -INFINITY;  // the maximum the row's P and O are scaled by
+            float l = 0.0f;
+            for (int j = 0; j < num_kt; ++j) {
+                const int g = g0 + j;
+                const int key0 = (first_kt + j) * FA_BN;
+                if (!mbar_wait(s_full + (g & 1), (g >> 1) & 1, abort_word)) { ok = false; break; }
                 tc_fence_after();
+                uint32_t raw[2][32];
+                tmem_load32_nowait(lane_base + Cfg::S_COL + (g & 1) * FA_BN, raw[0]);
+                tmem_load32_nowait(lane_base + Cfg::S_COL + (g & 1) * FA_BN + 32, raw[1]);
+                tmem_wait_ld();
+                // Work on the raw scores: the row maximum is taken before the scale (scale > 0), and
+                // scale and reference enter the exponent's argument as one fused multiply-add.
+                float tt[FA_BN];
 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_load32_nowait(lane_base + Cfg::O_COL + c * 32, o);
-                    tmem_wait_ld();
+                for (int c = 0; c < FA_BN; ++c) tt[c] = __uint_as_float(raw[c >> 5][c & 31]);
+                if (key0 + FA_BN - 1 > first_pos || key0 < lo_last) {  // the diagonal or the window's edge crosses this tile
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_store32(lane_base + Cfg::O_COL + c * 32, o);
+                    for (int c = 0; c < FA_BN; ++c) {
+                        const int key = key0 + c;
+                        tt[c] = (key <= pos && key >= lo) ? tt[c] : -INFINITY;
+                    }
                 }
+                float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < FA_BN; c += 8) {
+                    mx4[0] = max3(mx4[0], tt[c], tt[c + 1]);
+                    mx4[1] = max3(mx4[1], tt[c + 2], tt[c + 3]);
+                    mx4[2] = max3(mx4[2], tt[c + 4], tt[c + 5]);
+                    mx4[3] = max3(mx4[3], tt[c + 6], tt[c + 7]);
+                }
+                const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // -inf stays -inf
+                float alpha = 1.0f;
+                if (m_ref == -INFINITY) {
+                    m_ref = mx;  // nothing accumulated for this row yet
+                } else if (mx > m_ref + FA_RESCALE_STEP) {
+                    alpha = exp2f(m_ref - mx);
+                    m_ref = mx;
+                }
+                // Every phase of pv_done is observed (a parity wait cannot tell a phase from the one two
+                // before it); P V of the tile before must also be complete before O is rescaled.  (The
+                // last phase of a query tile is observed by its epilogue.)
+                if (j > 0 && !mbar_wait(pv_done, (g - 1) & 1, abort_word)) { ok = false; break; }
+                if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_load32_nowait(lane_base + Cfg::O_COL + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_store32(lane_base + Cfg::O_COL + c * 32, o);
+                    }
+                    tmem_wait_st();
+                    l *= alpha;
+                }
+                const float neg_base = m_ref == -INFINITY ? 0.0f : -m_ref;
+                const float2 scale2 = make_float2(sl2, sl2);
+                const float2 base2 = make_float2(neg_base, neg_base);
+                float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+                uint32_t packed[FA_BN / 2];
+#pragma unroll
+                for (int c = 0; c < FA_BN; c += 2) {
+                    const float2 arg = ffma2(make_float2(tt[c], tt[c + 1]), scale2, base2);  // (-inf) * scale + base = -inf
+                    const float2 p = make_float2(ex2_ftz(arg.x), ex2_ftz(arg.y));
+                    sum2[(c >> 1) & 1] = fadd2(sum2[(c >> 1) & 1], p);
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
+                    packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                const float sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+                l += sum;
+                // P_g takes the place of the first half of S_g: this thread's own row, which it holds in registers
+                tmem_store32(lane_base + Cfg::S_COL + (g & 1) * FA_BN, packed);
                 tmem_wait_st();
-                l *= alpha;
-            }
-            const float neg_base = m_ref == -INFINITY ? 0.0f : -m_ref;
-            const float2 scale2 = make_float2(sl2, sl2);
-            const float2 base2 = make_float2(neg_base, neg_base);
-            float2 sum2[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
-            uint32_t packed[FA_BN / 2];
-#pragma unroll
-            for (int c = 0; c < FA_BN; c += 2) {
-                const float2 arg = ffma2(make_float2(t[c], t[c + 1]), scale2, base2);  // (-inf) * scale + base = -inf
-                const float2 p = make_float2(ex2_ftz(arg.x), ex2_ftz(arg.y));
-                sum2[(c >> 1) & 1] = fadd2(sum2[(c >> 1) & 1], p);
-                __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
-                packed[c >> 1] = *reinterpret_cast<uint32_t*>(&pair);
-            }
-            const float sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
-            l += sum;
-            // P_j takes the place of the first half of S_j: this thread's own row, which it holds in registers
-            tmem_store32(lane_base + Cfg::S_COL + (j & 1) * FA_BN, packed);
-            tmem_wait_st();
-            if (key0 + FA_BN > key_end) {
-                // Keys beyond the last query have probability 0, but 0 * NaN is NaN and what lies
-                // beyond a request's length may be anything: clear those rows of V.
-                const int st = j % FA_STAGES;
-                if (!mbar_wait(v_full + st, (j / FA_STAGES) & 1, abort_word)) { ok = false; break; }
-                unsigned char* v_tile = sV + st * Cfg::KV_BYTES;
-                for (int idx = soft_tid; idx < FA_BN * BANDS * 8; idx += 128) {
-                    const int vr = idx / (BANDS * 8);
-                    const int c = idx % (BANDS * 8);
-                    if (key0 + vr >= key_end)
-                        *reinterpret_cast<uint4*>(v_tile + (vr / run_rows) * run_bytes + (c >> 3) * band_bytes + (vr % run_rows) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                if (key0 + FA_BN > key_end) {
+                    // Keys beyond the last query have probability 0, but 0 * NaN is NaN and what lies
+                    // beyond a request's length may be anything: clear those rows of V.
+                    const int st = g % FA_STAGES;
+                    if (!mbar_wait(v_full + st, (g / FA_STAGES) & 1, abort_word)) { ok = false; break; }
+                    unsigned char* v_tile = sV + st * Cfg::KV_BYTES;
+                    for (int idx = soft_tid; idx < FA_BN * BANDS * 8; idx += 128) {
+                        const int vr = idx / (BANDS * 8);
+                        const int c = idx % (BANDS * 8);
+                        if (key0 + vr >= key_end)
+                            *reinterpret_cast<uint4*>(v_tile + (vr / run_rows) * run_bytes + (c >> 3) * band_bytes + (vr % run_rows) * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    fence_proxy_async_smem();
                 }
-                fence_proxy_async_smem();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
-        }
-        if (ok && !mbar_wait(pv_done, (num_kt - 1) & 1, abort_word)) ok = false;
-        if (!ok) {
-            if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
-            *abort_word = 1;
-        } else {
+            if (ok && !mbar_wait(pv_done, (g0 + num_kt - 1) & 1, abort_word)) ok = false;
+            if (!ok) break;
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D;
+            __nv_bfloat16* dst = out + (size_t)(t.tok0 + t.q0 + r) * out_stride + (size_t)h * D;
 #pragma unroll
             for (int c = 0; c < D / 32; ++c) {
                 uint32_t o[32];
@@ -423,6 +465,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     }
                 }
             }
+            tc_fence_before();  // the reads of O are done before this thread's next arrival lets the next tile's P V overwrite it
+            g0 += num_kt;
+        }
+        if (!ok) {
+            if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
+            *abort_word = 1;
         }
     }
     tc_fence_before();
@@ -452,9 +500,18 @@ static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtenso
     if (e != cudaSuccess) return (int)e;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
-    dim3 grid(Hq, num_tiles);
+    // two tiles a block (one from each end of the list) when the blocks then all run at once
+    static int resident = 0;
+    if (resident == 0) {
+        int device = 0, sms = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+        resident = sms * FaCfg<D>::BLOCKS_PER_SM;
+    }
+    const int paired = num_tiles > 1 && (long long)Hq * ((num_tiles + 1) / 2) <= resident ? 1 : 0;
+    dim3 grid(Hq, paired ? (num_tiles + 1) / 2 : num_tiles);
     kb_launch(attention_prefill_tc5_kernel<D>, dim3(grid), dim3(FA_THREADS), smem, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
-              seq_lens, block_table, max_pages, tile_rows, tile_starts, Hq, Hkv, page_size, shift, num_pages, scale, window, merged, flag);
+              seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, shift, num_pages, scale, window, merged,
+              paired, flag);
     return kb_launch_result();
 }
 

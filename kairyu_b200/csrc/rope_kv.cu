@@ -288,6 +288,140 @@ qk_norm_rope_kv_write_many_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, i
     }
 }
 
+// Many bf16 tokens with heads of 128 that rotate whole: eight lanes take one token and walk a slice
+// of its heads, sixteen bytes a lane at a time (eight elements of the first half and their partners
+// of the second), so a token's cos and sin rows are fetched once for all its heads and every access
+// is 16 bytes wide.  All loads of a lane's heads go out before the first result is stored.  Same
+// arithmetic as the kernels above.
+#define ROPE_WIDE_TOKENS 4   // tokens a block of 256 threads takes: eight 8-lane groups a token
+#define ROPE_WIDE_HEADS 8    // heads a group may be dealt: (Hq + 2 Hkv) <= 8 * 8
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, int Hq, int Hkv,
+                                  const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
+                                  const float* __restrict__ cos_table, const float* __restrict__ sin_table, int max_pos,
+                                  const int* __restrict__ positions, const int* __restrict__ row_ids,
+                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ write_from,
+                                  __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int page_size,
+                                  int num_pages, int tokens, int* flag) {
+    pdl_trigger();
+    constexpr int D = 128, HALF = 64;
+    const int group = threadIdx.x >> 3;   // 32 groups of eight lanes
+    const int sub = threadIdx.x & 7;      // this lane's 8 elements of each half
+    const int t = blockIdx.x * ROPE_WIDE_TOKENS + (group >> 3);
+    const int slice = group & 7;          // heads slice, slice + 8, ...
+    const int heads = Hq + 2 * Hkv;
+    // the step's description comes from the host's copy, not from the kernel before: looked up ahead of the wait
+    int pos = 0;
+    long long slot = -1;
+    bool ok = t < tokens;
+    if (ok) {
+        pos = positions[t];
+        if (pos < 0 || pos >= max_pos) {
+            if (sub == 0 && slice == 0 && flag) atomicOr(flag, KB_FLAG_BAD_POS);
+            ok = false;
+        }
+    }
+    if (ok && k_cache != nullptr) {
+        const int row = row_ids[t];
+        if (pos >= write_from[row]) {
+            const int page_index = pos / page_size;
+            const int page = page_index < max_pages ? block_table[(size_t)row * max_pages + page_index] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (sub == 0 && slice == 0 && flag) atomicOr(flag, KB_FLAG_BAD_PAGE);
+            } else {
+                slot = (long long)page * page_size + (pos % page_size);
+            }
+        }
+    }
+    float c[8], sn[8];
+    if (ok) {
+        const float4* cr = reinterpret_cast<const float4*>(cos_table + (size_t)pos * HALF + sub * 8);
+        const float4* sr = reinterpret_cast<const float4*>(sin_table + (size_t)pos * HALF + sub * 8);
+        const float4 c0 = cr[0], c1 = cr[1], s0 = sr[0], s1 = sr[1];
+        c[0] = c0.x; c[1] = c0.y; c[2] = c0.z; c[3] = c0.w; c[4] = c1.x; c[5] = c1.y; c[6] = c1.z; c[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    pdl_wait();
+    if (!ok) return;
+    __nv_bfloat16* token = qkv + (size_t)t * qkv_stride;
+    uint4 lo_raw[ROPE_WIDE_HEADS], hi_raw[ROPE_WIDE_HEADS];
+#pragma unroll
+    for (int n = 0; n < ROPE_WIDE_HEADS; ++n) {
+        const int head = slice + 8 * n;
+        if (head < heads) {
+            lo_raw[n] = *reinterpret_cast<const uint4*>(token + (size_t)head * D + sub * 8);
+            hi_raw[n] = *reinterpret_cast<const uint4*>(token + (size_t)head * D + HALF + sub * 8);
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < ROPE_WIDE_HEADS; ++n) {
+        const int head = slice + 8 * n;
+        if (head >= heads) break;
+        if (head >= Hq + Hkv) {  // a value head: copied as it is
+            if (slot >= 0) {
+                __nv_bfloat16* vdst = v_cache + ((size_t)slot * Hkv + (head - Hq - Hkv)) * D;
+                *reinterpret_cast<uint4*>(vdst + sub * 8) = lo_raw[n];
+                *reinterpret_cast<uint4*>(vdst + HALF + sub * 8) = hi_raw[n];
+            }
+            continue;
+        }
+        const bool is_k = head >= Hq;
+        float a[8], b[8];
+        unpack8(lo_raw[n], a);
+        unpack8(hi_raw[n], b);
+        const TW* w = is_k ? k_norm_w : q_norm_w;
+        if (w != nullptr) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
+            // the head's eight lanes only: the other groups of the warp may be at other heads, or gone
+            const unsigned mates = 0xffu << ((threadIdx.x & 31) & ~7);
+            ss += __shfl_xor_sync(mates, ss, 1);
+            ss += __shfl_xor_sync(mates, ss, 2);
+            ss += __shfl_xor_sync(mates, ss, 4);
+            const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                a[i] = a[i] * inv * to_float(w[sub * 8 + i]);
+                b[i] = b[i] * inv * to_float(w[HALF + sub * 8 + i]);
+            }
+        }
+        float lo[8], hi[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {  // rotate_half(u) = cat(-u[half:], u[:half])
+            lo[i] = a[i] * c[i] - b[i] * sn[i];
+            hi[i] = b[i] * c[i] + a[i] * sn[i];
+        }
+        const uint4 lo_out = pack8(lo), hi_out = pack8(hi);
+        *reinterpret_cast<uint4*>(token + (size_t)head * D + sub * 8) = lo_out;
+        *reinterpret_cast<uint4*>(token + (size_t)head * D + HALF + sub * 8) = hi_out;
+        if (is_k && slot >= 0) {
+            __nv_bfloat16* kdst = k_cache + ((size_t)slot * Hkv + (head - Hq)) * D;
+            *reinterpret_cast<uint4*>(kdst + sub * 8) = lo_out;
+            *reinterpret_cast<uint4*>(kdst + HALF + sub * 8) = hi_out;
+        }
+    }
+}
+
 // qkv: [T, qkv_stride] with q | k | v packed per token, head-major.
 // *_norm_w: [D] (both or neither), norm_w_bf16 says which type.
 // cos/sin: [max_pos, rot_half] fp32 or null.  caches: [num_pages, page_size, Hkv, D] or null.
@@ -314,6 +448,20 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
                         (D * elem) % 16 == 0 && ((size_t)qkv_stride * elem) % 16 == 0 && ((uintptr_t)qkv % 16) == 0 &&
                         ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
                         ((uintptr_t)cos_table % 8) == 0 && ((uintptr_t)sin_table % 8) == 0;
+    // many bf16 tokens, heads of 128: eight lanes a token, 16 bytes a lane, cos and sin fetched once a token
+    if (paired && is_bf16 && D == 128 && T >= 256 && Hq + 2 * Hkv <= 8 * ROPE_WIDE_HEADS && ((uintptr_t)cos_table % 16) == 0 &&
+        ((uintptr_t)sin_table % 16) == 0) {
+        dim3 wide((T + ROPE_WIDE_TOKENS - 1) / ROPE_WIDE_TOKENS);
+#define WIDE(TW_)                                                                                              \
+    kb_launch(qk_norm_rope_kv_write_wide_kernel<TW_>, dim3(wide), dim3(256), 0, stream, (__nv_bfloat16*)qkv,   \
+        qkv_stride, Hq, Hkv, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps, cos_table, sin_table, max_pos,   \
+        positions, row_ids, block_table, max_pages, write_from, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
+        page_size, num_pages, T, flag)
+        if (norm_w_bf16) WIDE(__nv_bfloat16);
+        else WIDE(float);
+#undef WIDE
+        return kb_launch_result();
+    }
     // many tokens, heads of up to 128: four tokens a warp, their memory round trips overlapped
     if (paired && D <= 128 && T >= 256) {
         constexpr int TPW = 4;

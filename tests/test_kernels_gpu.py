@@ -288,9 +288,11 @@ def _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize(
     "Hq,Hkv,D,page_size,qk_norm,rot_dim",
-    [(4, 2, 16, 16, False, 16), (6, 3, 32, 8, True, 32), (5, 1, 48, 16, True, 48), (32, 8, 128, 16, False, 128), (3, 3, 80, 4, True, 32)],
+    [(4, 2, 16, 16, False, 16), (6, 3, 32, 8, True, 32), (5, 1, 48, 16, True, 48), (32, 8, 128, 16, False, 128), (3, 3, 80, 4, True, 32),
+     # heads of 128 in bf16 with many tokens: the kernel that gives a token eight lanes of 16 bytes
+     (32, 8, 128, 16, True, 128), (5, 1, 128, 8, True, 128), (9, 3, 128, 32, False, 128)],
 )
-@pytest.mark.parametrize("T", [37, 301])  # 301: the four-tokens-a-warp kernel (full rotation, heads up to 128), with a ragged end
+@pytest.mark.parametrize("T", [37, 301])  # 301: the many-token kernels (full rotation, heads up to 128), with a ragged end
 def test_qk_norm_rope_kv_write(dtype, Hq, Hkv, D, page_size, qk_norm, rot_dim, T):
     case = _rope_case(dtype, T, Hq, Hkv, D, page_size, qk_norm, rot_dim, seed=20)
     kc_ref = torch.zeros(case["num_pages"], page_size, Hkv, D, dtype=dtype)
