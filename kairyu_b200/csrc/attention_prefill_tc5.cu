@@ -22,7 +22,8 @@
 //              pairs back into tensor memory over its row of S (tcgen05.st), from where the
 //              tensor core reads it as the A operand of P V; and rescales O in TMEM only when
 //              the row maximum has grown by more than 2^8 since the reference it scales by
-//              (P stays below 256, sums stay exact enough in fp32).
+//              (P stays below 256, sums stay exact enough in fp32).  Only then does it wait
+//              for the P V before to finish; otherwise it goes straight on to the next S.
 // V is the B operand of O += P V with its N index (the head dimension) contiguous: an
 // MN-major operand, read straight from the [key][dim] rows the cache holds.
 // Two blocks share an SM (2 x 256 TMEM columns, 2 x 97 KB of shared memory), so one block's
@@ -88,7 +89,7 @@ struct FaCfg {
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + FA_STAGES * KV_BYTES;
     static constexpr int OFF_BAR = OFF_V + FA_STAGES * KV_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 2 + 1;
+    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 1 + 2 + 1;
     static constexpr size_t SMEM = OFF_BAR + NUM_BARS * 8 + 16;
     static constexpr int S_COL = 0;          // two S buffers of FA_BN columns each; P (bf16 pairs) overwrites the first half of its S
     static constexpr int O_COL = 2 * FA_BN;
@@ -118,8 +119,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* v_empty = k_empty + FA_STAGES;
     uint64_t* s_full = v_empty + FA_STAGES;  // one per S buffer
     uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 1;
-    uint64_t* q_empty = pv_done + 1;  // every Q K^T of a query tile has read the queries' buffer
+    uint64_t* pv_done = p_full + 1;   // two, used in turn by the key tiles: P V of tile g completes pv_done[g % 2]
+    uint64_t* q_empty = pv_done + 2;  // every Q K^T of a query tile has read the queries' buffer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -140,6 +141,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         mbar_init(s_full + 1, 1);
         mbar_init(p_full, 4);
         mbar_init(pv_done, 1);
+        mbar_init(pv_done + 1, 1);
         mbar_init(q_empty, 1);
         *abort_word = 0;
         if ((smem_addr(smem) & 1023u) != 0) {  // the swizzled layouts below assume it
@@ -318,7 +320,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                                          v_tile + (uint64_t)(v_offset >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     }
                     umma_commit(v_empty + st);  // the slot may be refilled once these products have read it
-                    umma_commit(pv_done);
+                    umma_commit(pv_done + (g & 1));
                     if (j + 2 < num_kt) {
                         // the softmax warps hold S_g in registers (they have written P_g): its buffer takes tile g + 2
                         if (!mbar_wait(k_full + st, ((g + 2) / FA_STAGES) & 1, abort_word)) {
@@ -387,11 +389,13 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     alpha = exp2f(m_ref - mx);
                     m_ref = mx;
                 }
-                // Every phase of pv_done is observed (a parity wait cannot tell a phase from the one two
-                // before it); P V of the tile before must also be complete before O is rescaled.  (The
-                // last phase of a query tile is observed by its epilogue.)
-                if (j > 0 && !mbar_wait(pv_done, (g - 1) & 1, abort_word)) { ok = false; break; }
+                // The softmax does not wait for P V of the tile before: only a rescale of O needs it complete,
+                // and that is rare.  Every phase of the two pv_done barriers is still observed, in order and
+                // two tiles late (a parity wait cannot tell a phase from the one two before it); a query
+                // tile's last two phases are observed by its epilogue.
+                if (j > 1 && !mbar_wait(pv_done + (g & 1), ((g - 2) >> 1) & 1, abort_word)) { ok = false; break; }
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    if (j > 0 && !mbar_wait(pv_done + ((g - 1) & 1), ((g - 1) >> 1) & 1, abort_word)) { ok = false; break; }
                     tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
@@ -413,6 +417,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                 for (int c = 0; c < FA_BN; c += 2) {
                     const float2 arg = ffma2(make_float2(tt[c], tt[c + 1]), scale2, base2);  // (-inf) * scale + base = -inf
+                    // (A cubic for 2^x on the FMA pipes for every fourth pair, to spare the special-function unit,
+                    // made the kernel slower, 54 -> 57 us at 2,048 tokens: the exponentials are not what it waits for.)
                     const float2 p = make_float2(ex2_ftz(arg.x), ex2_ftz(arg.y));
                     sum2[(c >> 1) & 1] = fadd2(sum2[(c >> 1) & 1], p);
                     __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
@@ -441,7 +447,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
             }
-            if (ok && !mbar_wait(pv_done, (g0 + num_kt - 1) & 1, abort_word)) ok = false;
+            if (ok && num_kt > 1 && !mbar_wait(pv_done + ((g0 + num_kt - 2) & 1), ((g0 + num_kt - 2) >> 1) & 1, abort_word)) ok = false;
+            if (ok && !mbar_wait(pv_done + ((g0 + num_kt - 1) & 1), ((g0 + num_kt - 1) >> 1) & 1, abort_word)) ok = false;
             if (!ok) break;
             tc_fence_after();
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
