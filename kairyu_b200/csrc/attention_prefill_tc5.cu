@@ -89,7 +89,7 @@ struct FaCfg {
     static constexpr int OFF_K = Q_BYTES;
     static constexpr int OFF_V = OFF_K + FA_STAGES * KV_BYTES;
     static constexpr int OFF_BAR = OFF_V + FA_STAGES * KV_BYTES;
-    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 1 + 2 + 1;
+    static constexpr int NUM_BARS = 1 + 4 * FA_STAGES + 2 + 2 + 2 + 1;
     static constexpr size_t SMEM = OFF_BAR + NUM_BARS * 8 + 16;
     static constexpr int S_COL = 0;          // two S buffers of FA_BN columns each; P (bf16 pairs) overwrites the first half of its S
     static constexpr int O_COL = 2 * FA_BN;
@@ -118,8 +118,11 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* k_empty = v_full + FA_STAGES;
     uint64_t* v_empty = k_empty + FA_STAGES;
     uint64_t* s_full = v_empty + FA_STAGES;  // one per S buffer
+    // p_full and pv_done: two each, used in turn by the key tiles (tile g uses [g % 2]).  The softmax may
+    // be a tile ahead of the thread that issues the products (it needs no P V to go on), and one barrier
+    // whose phase is told by its parity cannot be two phases ahead of who waits on it.
     uint64_t* p_full = s_full + 2;
-    uint64_t* pv_done = p_full + 1;   // two, used in turn by the key tiles: P V of tile g completes pv_done[g % 2]
+    uint64_t* pv_done = p_full + 2;
     uint64_t* q_empty = pv_done + 2;  // every Q K^T of a query tile has read the queries' buffer
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NUM_BARS);
     volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -140,6 +143,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         mbar_init(s_full, 1);
         mbar_init(s_full + 1, 1);
         mbar_init(p_full, 4);
+        mbar_init(p_full + 1, 4);
         mbar_init(pv_done, 1);
         mbar_init(pv_done + 1, 1);
         mbar_init(q_empty, 1);
@@ -306,7 +310,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 for (int j = 0; j < num_kt && ok; ++j) {
                     const int g = g0 + j;
                     const int st = g % FA_STAGES;
-                    if (!mbar_wait(p_full, g & 1, abort_word) || !mbar_wait(v_full + st, (g / FA_STAGES) & 1, abort_word)) {
+                    if (!mbar_wait(p_full + (g & 1), (g >> 1) & 1, abort_word) || !mbar_wait(v_full + st, (g / FA_STAGES) & 1, abort_word)) {
                         give_up();
                         break;
                     }
@@ -445,7 +449,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(p_full);
+                if (lane == 0) mbar_arrive(p_full + (g & 1));
             }
             if (ok && num_kt > 1 && !mbar_wait(pv_done + ((g0 + num_kt - 2) & 1), ((g0 + num_kt - 2) >> 1) & 1, abort_word)) ok = false;
             if (ok && !mbar_wait(pv_done + ((g0 + num_kt - 1) & 1), ((g0 + num_kt - 1) >> 1) & 1, abort_word)) ok = false;
