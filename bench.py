@@ -77,6 +77,42 @@ SHAPES = {
         },
         name="Qwen3-32B shape", seed=4, prompt_len=1024, gen_len=128, context_len=8192,
     ),
+    # Further sizes of the two families: a head size of 64 with tied embeddings, small widths where
+    # launches weigh more, and 70B-sized layers (fewer of them than the model has, named in config).
+    "llama32-1b": dict(
+        model={
+            "architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 16, "num_attention_heads": 32,
+            "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256, "rope_theta": 500000.0,
+            "rope_scaling": dict(MODEL["rope_scaling"], factor=32.0), "max_position_embeddings": 131072, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": True, "hidden_act": "silu",
+        },
+        name="Llama-3.2-1B shape", seed=5, prompt_len=2048, gen_len=256, context_len=8192,
+    ),
+    "qwen3-1.7b": dict(
+        model={
+            "architectures": ["Qwen3ForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 28, "num_attention_heads": 16,
+            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 6144, "vocab_size": 151936, "rope_theta": 1000000.0,
+            "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "hidden_act": "silu",
+        },
+        name="Qwen3-1.7B shape", seed=6, prompt_len=2048, gen_len=256, context_len=8192,
+    ),
+    "qwen3-14b": dict(
+        model={
+            "architectures": ["Qwen3ForCausalLM"], "hidden_size": 5120, "num_hidden_layers": 40, "num_attention_heads": 40,
+            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 17408, "vocab_size": 151936, "rope_theta": 1000000.0,
+            "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
+        },
+        name="Qwen3-14B shape", seed=7, prompt_len=2048, gen_len=256, context_len=8192,
+    ),
+    "llama31-70b": dict(
+        model={
+            "architectures": ["LlamaForCausalLM"], "hidden_size": 8192, "num_hidden_layers": 80, "num_attention_heads": 64,
+            "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 28672, "vocab_size": 128256, "rope_theta": 500000.0,
+            "rope_scaling": dict(MODEL["rope_scaling"]), "max_position_embeddings": 131072, "rms_norm_eps": 1e-5,
+            "tie_word_embeddings": False, "hidden_act": "silu",
+        },
+        name="Llama-3.1-70B shape", seed=8, prompt_len=1024, gen_len=128, context_len=8192,
+    ),
 }
 MODEL_NAME = "Llama-3.1-8B shape"
 

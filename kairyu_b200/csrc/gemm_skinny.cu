@@ -471,6 +471,10 @@ KB_EXPORT int kb_gemm_skinny_blocks(int M, int N, int gated) {
     return (rows_out + rows_per_block - 1) / rows_per_block;
 }
 
+// Partial sums per row a scaling epilogue can add up: a folding product launched with more blocks
+// than this (an output wider than 6,144 columns) cannot feed one, and the caller keeps the norm kernel.
+KB_EXPORT int kb_gemm_skinny_max_sum_blocks() { return SK_SUM_BLOCKS; }
+
 // The product with RMSNorm work in its epilogue (see the top of the file).
 // in_sumsq (or null): the producer's partial sums [in_blocks, 16]; rows are scaled by
 //   rsqrt(sum / in_hidden + in_eps) before bias and gate.

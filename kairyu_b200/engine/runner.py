@@ -17,6 +17,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Hashable, Optional, Sequence
 
+import numpy as np
 import torch
 
 from kairyu_b200 import kernels
@@ -217,26 +218,30 @@ class ModelRunner:
         groups = self.cache.layout.groups
         num_rows = len(rows)
         padded_rows = pad_rows if pad_rows is not None else num_rows
-        token_ids: list[int] = []
-        positions: list[int] = []
-        row_ids: list[int] = []
+        # The per-token arrays are filled as numpy slices (a 2,048-token portion is four slice
+        # assignments, not 8,192 list items); the per-row and per-tile arrays are short lists.
+        num_tokens = sum(len(entry.tokens) for entry, _, _ in rows) + (padded_rows - num_rows)
+        token_ids = np.zeros(num_tokens, dtype=np.int32)
+        future_src = np.full(num_tokens, -1, dtype=np.int32)
+        positions = np.zeros(num_tokens, dtype=np.int32)
+        row_ids = np.zeros(num_tokens, dtype=np.int32)
         qo_indptr = [0]
         seq_lens: list[int] = []
         write_from: list[int] = []
         state_slots: list[int] = []
         want: list[int] = []
-        future_src: list[int] = []
         tile_rows: dict[int, list[int]] = {size: [] for size in self._tile_sizes}
         tile_starts: dict[int, list[int]] = {size: [] for size in self._tile_sizes}
         decode_rows: list[int] = []
         decode_tokens: list[int] = []
+        base = 0
         for row, (entry, start, seq_len) in enumerate(rows):
             count = len(entry.tokens)
-            base = len(token_ids)
-            token_ids.extend(entry.tokens)
-            future_src.extend([-1] * count if entry.future is None else [entry.future])
-            positions.extend(range(start, seq_len))
-            row_ids.extend([row] * count)
+            token_ids[base : base + count] = entry.tokens
+            if entry.future is not None:
+                future_src[base] = entry.future
+            positions[base : base + count] = np.arange(start, seq_len, dtype=np.int32)
+            row_ids[base : base + count] = row
             qo_indptr.append(base + count)
             seq_lens.append(seq_len)
             record = self.cache.get(entry.request_id)
@@ -251,32 +256,27 @@ class ModelRunner:
                 decode_tokens.append(base)
             else:
                 for size in self._tile_sizes:
-                    for tile_start in range(0, count, size):
-                        tile_rows[size].append(row)
-                        tile_starts[size].append(tile_start)
-        for row in range(num_rows, padded_rows):  # padding rows of a replayed graph
-            base = len(token_ids)
-            token_ids.append(0)
-            future_src.append(-1)
-            positions.append(0)
-            row_ids.append(row)
+                    starts = range(0, count, size)
+                    tile_rows[size].extend([row] * len(starts))
+                    tile_starts[size].extend(starts)
+            base += count
+        for row in range(num_rows, padded_rows):  # padding rows of a replayed graph: token 0 at position 0
+            row_ids[base] = row
             qo_indptr.append(base + 1)
             seq_lens.append(1)
             write_from.append(0)
             state_slots.append(self.cache.scratch_state_slot)
             decode_rows.append(row)
             decode_tokens.append(base)
+            base += 1
         needed_pages = max((-(-seq_len // page_size) for _, _, seq_len in rows), default=1)
         table_width = max_pages if max_pages is not None else needed_pages
-        tables: list[int] = []
-        for group in groups:
-            for entry, _, seq_len in rows:
-                table = self.cache.block_table(entry.request_id, group.index)
-                pages = table[: -(-seq_len // page_size)]
-                tables.extend(pages)
-                tables.extend([-1] * (table_width - len(pages)))
-            for _ in range(num_rows, padded_rows):
-                tables.extend([0] * table_width)  # the reserved page
+        tables = np.full((len(groups), padded_rows, table_width), -1, dtype=np.int32)
+        for place, group in enumerate(groups):
+            for row, (entry, _, seq_len) in enumerate(rows):
+                pages = self.cache.block_table(entry.request_id, group.index)[: -(-seq_len // page_size)]
+                tables[place, row, : len(pages)] = pages
+            tables[place, num_rows:, :] = 0  # the reserved page
         arrays = {
             "token_ids": token_ids,
             "future_src": future_src,
@@ -291,18 +291,21 @@ class ModelRunner:
             **{f"tile_starts{size}": tile_starts[size] for size in self._tile_sizes},
             "decode_rows": decode_rows,
             "decode_tokens": decode_tokens,
-            "tables": tables,
+            "tables": tables.reshape(-1),
         }
         layout: dict[str, tuple[int, int]] = {}
-        flat: list[int] = []
+        total = 0
         for name, values in arrays.items():
-            layout[name] = (len(flat), len(values))
-            flat.extend(values)
-        host = torch.tensor(flat, dtype=torch.int32)
-        if self._is_cuda:
-            host = host.pin_memory()
+            layout[name] = (total, len(values))
+            total += len(values)
+        host = torch.empty(total, dtype=torch.int32, pin_memory=self._is_cuda)
+        flat = host.numpy()
+        for name, values in arrays.items():
+            offset, length = layout[name]
+            if length:
+                flat[offset : offset + length] = values
         facts = {
-            "num_tokens": len(token_ids),
+            "num_tokens": num_tokens,
             "num_rows": padded_rows,
             "table_width": table_width,
             "max_seq_len": max(seq_lens),

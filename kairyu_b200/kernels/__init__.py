@@ -751,9 +751,21 @@ def skinny_blocks(rows: int, out_features: int, gated: bool = False) -> int:
     return int(fn(int(rows), int(out_features), 1 if gated else 0))
 
 
-def fused_norm_shapes_ok(rows: int, *feature_sizes: int) -> bool:
-    """Whether products over these inner and outer sizes can all take the fused path."""
-    return few_rows(rows) and all(size % 16 == 0 for size in feature_sizes)
+def fused_norm_shapes_ok(rows: int, hidden: int, *feature_sizes: int) -> bool:
+    """Whether products between ``hidden`` (the width of the residual, which the folding products
+    write) and these other sizes can all take the fused path.  The product that scales adds one
+    partial sum per block of the product that folded: a residual so wide that the folding product
+    is launched with more blocks than it can add up keeps the norm kernel."""
+    if not few_rows(rows) or hidden % 16 != 0 or any(size % 16 != 0 for size in feature_sizes):
+        return False
+    fits = _fold_fits.get((rows, hidden))
+    if fits is None:
+        limit = int(_fn("gemm_skinny", "kb_gemm_skinny_max_sum_blocks", [])())
+        fits = _fold_fits[(rows, hidden)] = skinny_blocks(rows, hidden) <= limit
+    return fits
+
+
+_fold_fits: dict[tuple[int, int], bool] = {}
 
 
 TC5_MAX_ROWS = 64  # token rows the tcgen05 weight-streaming product takes (csrc/gemm_tc5.cu)

@@ -35,7 +35,16 @@ QWEN3_8B = {
     "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
     "max_position_embeddings": 40960, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
 }
-SHAPES = {"llama31_8b": (LLAMA31_8B, 2), "qwen3_8b": (QWEN3_8B, 3)}
+# The width and head count of Llama-3.1-70B (8192, 64 query heads on 8 KV heads) with a narrower
+# feed-forward and vocabulary: products that write the residual are launched with more blocks than
+# a scaling epilogue adds up, so these steps take the norm kernels at every row count.
+WIDE_70B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 8192, "num_hidden_layers": 2, "num_attention_heads": 64,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 7168, "vocab_size": 32000, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+SHAPES = {"llama31_8b": (LLAMA31_8B, 2), "qwen3_8b": (QWEN3_8B, 3), "width_8192": (WIDE_70B, 4)}
 
 # Every bound is what the same arithmetic costs the plain model itself.
 # 32-bit: the truth is the plain model in 64-bit; the plain model in 32-bit is a few 1e-5 from it on
