@@ -352,6 +352,7 @@ def time_mixed(layers: int) -> dict:
     prompts = [TokensPrompt(tuple(random_tokens(n, MODEL["vocab_size"], 300 + i))) for i, n in enumerate(lengths)]
     params = SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True)
     llm.generate(prompts[:4], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))  # warm
+    engine.warm_up(32, max(lengths) + 128)  # a serving engine's decode graphs exist before its first request
     torch.cuda.synchronize()
     begin = time.perf_counter()
     outputs = llm.generate(prompts, params)
@@ -394,6 +395,7 @@ def time_shared_prefix(layers: int) -> dict:
         engine = Engine.from_random(config, SEED, engine_config)
         llm = LLM.from_engine(engine)
         llm.generate(warm, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+        engine.warm_up(16, 2048 + 128 + 64)
         torch.cuda.synchronize()
         begin = time.perf_counter()
         outputs = llm.generate(prompts, params)

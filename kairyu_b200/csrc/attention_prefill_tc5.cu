@@ -104,7 +104,8 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const int* __restrict__ qo_indptr, const int* __restrict__ seq_lens,
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ tile_rows,
                              const int* __restrict__ tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int page_shift,
-                             int num_pages, float scale, int window, int merged, int paired, int* flag) {
+                             int num_pages, float scale, int window, int merged, int paired, int splits, float* __restrict__ part_o,
+                             float* __restrict__ part_ml, int* flag) {
     using Cfg = FaCfg<D>;
     constexpr int BANDS = Cfg::BANDS;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -176,11 +177,12 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int run_bytes = BANDS * band_bytes;
 
     struct TileInfo {
-        int row, q0, tok0, rows_here, first_pos, last_pos, key_end, key_lo, first_kt, num_kt;
+        int tile, row, q0, tok0, rows_here, first_pos, last_pos, key_end, key_lo, first_kt, num_kt;
     };
     auto tile_info = [&](int part) {
         TileInfo t;
         const int tile = part == 0 ? num_tiles - 1 - (int)blockIdx.y : (int)blockIdx.y;
+        t.tile = tile;
         t.row = tile_rows[tile];
         t.q0 = tile_starts[tile];
         t.tok0 = qo_indptr[t.row];
@@ -194,6 +196,15 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         t.key_lo = (window > 0 && t.first_pos + 1 > window) ? t.first_pos + 1 - window : 0;
         t.first_kt = t.key_lo / FA_BN;
         t.num_kt = (t.key_end - 1) / FA_BN - t.first_kt + 1;
+        if (splits > 1) {
+            // this block's share of the tile's keys: split z takes key tiles [z * per, (z + 1) * per); a
+            // short tile leaves the last splits without any (num_kt <= 0: the block only says so)
+            const int per = (t.num_kt + splits - 1) / splits;
+            const int begin = (int)blockIdx.z * per;
+            const int end = min(begin + per, t.num_kt);
+            t.first_kt += begin;
+            t.num_kt = end - begin;
+        }
         return t;
     };
 
@@ -208,6 +219,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         int g0 = 0;
         for (int part = 0; part < num_parts && ok; ++part) {
             const TileInfo t = tile_info(part);
+            if (t.num_kt <= 0) break;  // a split without keys (splits > 1: one part a block)
             // the queries' buffer is free once every Q K^T of the tile before has read it
             if (part > 0 && !mbar_wait(q_empty, (part - 1) & 1, abort_word)) {
                 if (lane == 0 && !*abort_word && flag) atomicOr(flag, KB_FLAG_TIMEOUT | KB_FLAG_TIMEOUT_PREFILL);
@@ -293,6 +305,7 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             int g0 = 0;
             for (int part = 0; part < num_parts && ok; ++part) {
                 const int num_kt = tile_info(part).num_kt;
+                if (num_kt <= 0) break;  // a split without keys
                 // Q K^T runs two key tiles ahead of P V.  (The two S buffers are free here: the products that
                 // read the tile before's last P were issued before these, and the tensor pipe keeps the order.)
                 if (!mbar_wait(q_full, part & 1, abort_word) || !mbar_wait(k_full + g0 % FA_STAGES, (g0 / FA_STAGES) & 1, abort_word)) give_up();
@@ -351,6 +364,15 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             const TileInfo t = tile_info(part);
             const int num_kt = t.num_kt, first_kt = t.first_kt, first_pos = t.first_pos, last_pos = t.last_pos, key_end = t.key_end;
             const bool valid = r < t.rows_here;
+            // with the keys split over blocks: where this block's unnormalised O, reference maximum and sum go
+            const size_t part_slot = (((size_t)blockIdx.z * num_tiles + t.tile) * FA_BM + r) * Hq + h;
+            if (num_kt <= 0) {
+                if (valid) {
+                    part_ml[part_slot * 2] = -INFINITY;
+                    part_ml[part_slot * 2 + 1] = 0.0f;
+                }
+                break;
+            }
             const int pos = valid ? first_pos + r : last_pos;
             const int lo = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
             const int lo_last = (window > 0 && last_pos + 1 > window) ? last_pos + 1 - window : 0;
@@ -455,6 +477,28 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (ok && !mbar_wait(pv_done + ((g0 + num_kt - 1) & 1), ((g0 + num_kt - 1) >> 1) & 1, abort_word)) ok = false;
             if (!ok) break;
             tc_fence_after();
+            if (splits > 1) {
+                // the merge kernel divides: O as accumulated (scaled by 2^-m_ref), m_ref and the sum
+                float* dst_o = part_o + part_slot * D;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_load32_nowait(lane_base + Cfg::O_COL + c * 32, o);
+                    tmem_wait_ld();
+                    if (valid) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            *reinterpret_cast<uint4*>(dst_o + c * 32 + i * 4) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+                    }
+                }
+                if (valid) {
+                    part_ml[part_slot * 2] = m_ref;
+                    part_ml[part_slot * 2 + 1] = l;
+                }
+                tc_fence_before();
+                g0 += num_kt;
+                continue;
+            }
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             __nv_bfloat16* dst = out + (size_t)(t.tok0 + t.q0 + r) * out_stride + (size_t)h * D;
 #pragma unroll
@@ -501,28 +545,110 @@ attention_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     }
 }
 
+// Combines the splits of the keys: a warp per (query, head); lane i owns D / 32 columns.
+// part_o: [splits, tiles * 128, Hq, D] as the blocks accumulated it, part_ml: the same slots x (reference
+// maximum, sum).  out = sum_z 2^(m_z - M) O_z / sum_z 2^(m_z - M) l_z, in split order.
+template <int D>
+__global__ void attention_prefill_tc5_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                   const int* __restrict__ qo_indptr, const int* __restrict__ tile_rows,
+                                                   const int* __restrict__ tile_starts, int num_tiles, int Hq, int splits,
+                                                   __nv_bfloat16* __restrict__ out, int out_stride) {
+    constexpr int PER = D / 32;
+    pdl_trigger();
+    const int lane = threadIdx.x & 31;
+    const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);  // (tile, row of the tile, head)
+    const long long slots = (long long)num_tiles * FA_BM;
+    if (pair >= slots * Hq) return;
+    const int h = (int)(pair % Hq);
+    const int slot = (int)(pair / Hq);
+    const int tile = slot / FA_BM, r = slot % FA_BM;
+    const int row = tile_rows[tile];
+    const int tok0 = qo_indptr[row];
+    const int q0 = tile_starts[tile];
+    if (q0 + r >= qo_indptr[row + 1] - tok0) return;  // the tile's last rows lie beyond the portion
+    pdl_wait();
+    float big = -INFINITY;
+    for (int z = 0; z < splits; ++z) big = fmaxf(big, part_ml[(((size_t)z * slots + slot) * Hq + h) * 2]);
+    float acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.0f;
+    float den = 0.0f;
+    for (int z = 0; z < splits; ++z) {
+        const size_t at = ((size_t)z * slots + slot) * Hq + h;
+        const float m = part_ml[at * 2];
+        if (m == -INFINITY) continue;  // a split without keys this row may see: its O was not written or is all zero
+        const float f = exp2f(m - big);
+        den += part_ml[at * 2 + 1] * f;
+        float part[PER];
+        if (PER == 4)
+            *reinterpret_cast<float4*>(part) = *reinterpret_cast<const float4*>(part_o + at * D + lane * PER);
+        else
+            *reinterpret_cast<float2*>(part) = *reinterpret_cast<const float2*>(part_o + at * D + lane * PER);
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] += part[i] * f;
+    }
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    __nv_bfloat16* dst = out + (size_t)(tok0 + q0 + r) * out_stride + (size_t)h * D + lane * PER;
+    uint32_t packed[PER / 2];
+#pragma unroll
+    for (int i = 0; i < PER; i += 2) {
+        __nv_bfloat162 two = __floats2bfloat162_rn(acc[i] * inv, acc[i + 1] * inv);
+        packed[i / 2] = *reinterpret_cast<uint32_t*>(&two);
+    }
+    if (PER == 4)
+        *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[PER / 2 - 1]);
+    else
+        *reinterpret_cast<uint32_t*>(dst) = packed[0];
+}
+
+static int fa_resident(int blocks_per_sm) {
+    static int sms = 0;
+    if (sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
+    }
+    return sms * blocks_per_sm;
+}
+
+// Blocks that share a query tile's keys: more than one when a step's tiles (a short portion of a
+// long prompt: 4 tiles x 32 heads) would leave most of the device idle.  Every split gets at least
+// four key tiles of the longest row; at most eight splits.
+KB_EXPORT int kb_attention_prefill_tc5_splits(int D, int Hq, int num_tiles, int max_seq_len) {
+    if (D != 64 && D != 128) return 1;
+    const long long blocks = (long long)Hq * num_tiles;
+    if (blocks < 1) return 1;
+    const int resident = fa_resident(FaCfg<128>::BLOCKS_PER_SM);
+    long long splits = resident / blocks;
+    const int key_tiles = (max_seq_len + FA_BN - 1) / FA_BN;
+    if (splits > key_tiles / 4) splits = key_tiles / 4;
+    if (splits > 8) splits = 8;
+    return splits < 2 ? 1 : (int)splits;
+}
+
 template <int D>
 static int launch_fa(const CUtensorMap* mq, const CUtensorMap* mk, const CUtensorMap* mv, __nv_bfloat16* out, int out_stride,
                      const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages, const int* tile_rows,
                      const int* tile_starts, int num_tiles, int Hq, int Hkv, int page_size, int num_pages, float scale, int window,
-                     int merged, int* flag, cudaStream_t stream) {
+                     int merged, int splits, float* part_o, float* part_ml, int* flag, cudaStream_t stream) {
     const size_t smem = FaCfg<D>::SMEM;
     cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc5_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
-    // two tiles a block (one from each end of the list) when the blocks then all run at once
-    static int resident = 0;
-    if (resident == 0) {
-        int device = 0, sms = 0;
-        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 148;
-        resident = sms * FaCfg<D>::BLOCKS_PER_SM;
-    }
-    const int paired = num_tiles > 1 && (long long)Hq * ((num_tiles + 1) / 2) <= resident ? 1 : 0;
-    dim3 grid(Hq, paired ? (num_tiles + 1) / 2 : num_tiles);
+    // Two tiles a block (one from each end of the list) when one tile a block would not run all at
+    // once but two tiles a block do; with the keys split over blocks, one tile a block.
+    const int resident = fa_resident(FaCfg<D>::BLOCKS_PER_SM);
+    const long long single = (long long)Hq * num_tiles;
+    const int paired = splits == 1 && num_tiles > 1 && single > resident && (long long)Hq * ((num_tiles + 1) / 2) <= resident ? 1 : 0;
+    dim3 grid(Hq, paired ? (num_tiles + 1) / 2 : num_tiles, splits);
     kb_launch(attention_prefill_tc5_kernel<D>, dim3(grid), dim3(FA_THREADS), smem, stream, *mq, *mk, *mv, out, out_stride, qo_indptr,
               seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, shift, num_pages, scale, window, merged,
-              paired, flag);
+              paired, splits, part_o, part_ml, flag);
+    int rc = kb_launch_result();
+    if (rc != 0 || splits == 1) return rc;
+    const long long pairs = (long long)num_tiles * FA_BM * Hq;
+    kb_launch(attention_prefill_tc5_merge_kernel<D>, dim3((unsigned)((pairs + 3) / 4)), dim3(128), 0, stream, (const float*)part_o,
+              (const float*)part_ml, qo_indptr, tile_rows, tile_starts, num_tiles, Hq, splits, out, out_stride);
     return kb_launch_result();
 }
 
@@ -541,19 +667,24 @@ KB_EXPORT int kb_attention_prefill_tc5_merged(int D, int page_size) { return D >
 // map_k, map_v: maps over the caches [pages, page_size, kv_heads, head_dim]: 4-D with boxes of
 // 64 columns x 1 head x min(page_size, 64) positions x 1 page; map_v, where
 // kb_attention_prefill_tc5_merged says so, 5-D with every band in a box; all with the 128-byte
-// swizzle (host pointers).  The tile list holds 128 queries per tile.
+// swizzle (host pointers).  The tile list holds 128 queries per tile.  splits (1, or what
+// kb_attention_prefill_tc5_splits gives): blocks that share a tile's keys; with more than one,
+// part_o [splits, tiles * 128, Hq, D] and part_ml [splits, tiles * 128, Hq, 2] floats hold their results
+// until a second kernel combines them.
 KB_EXPORT int kb_attention_prefill_tc5(const void* map_q, const void* map_k, const void* map_v, void* out, int out_stride,
                                        const int* qo_indptr, const int* seq_lens, const int* block_table, int max_pages,
                                        const int* tile_rows, const int* tile_starts, int num_tiles, int Hq, int Hkv, int D,
-                                       int page_size, int num_pages, float scale, int window, int* flag, cudaStream_t stream) {
+                                       int page_size, int num_pages, float scale, int window, int splits, float* part_o,
+                                       float* part_ml, int* flag, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
+    if (splits < 1 || splits > 8 || (splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o % 16) != 0))) return KB_ERR_BAD_ARG;
     if (!map_q || !map_k || !map_v || !out || !qo_indptr || !seq_lens || !block_table || !tile_rows || !tile_starts) return KB_ERR_NULL;
     if (Hkv < 1 || Hq % Hkv != 0 || num_tiles > 65535) return KB_ERR_BAD_ARG;
     if (out_stride % 8 != 0 || ((uintptr_t)out % 16) != 0) return KB_ERR_BAD_ARG;  // 16-byte stores of whole rows
     if (!kb_attention_prefill_tc5_supported(D, page_size)) return KB_ERR_UNSUPPORTED_SIZE;
 #define ARGS (const CUtensorMap*)map_q, (const CUtensorMap*)map_k, (const CUtensorMap*)map_v, (__nv_bfloat16*)out, out_stride, qo_indptr, \
              seq_lens, block_table, max_pages, tile_rows, tile_starts, num_tiles, Hq, Hkv, page_size, num_pages, scale, window,            \
-             kb_attention_prefill_tc5_merged(D, page_size), flag, stream
+             kb_attention_prefill_tc5_merged(D, page_size), splits, part_o, part_ml, flag, stream
     if (D == 64) return launch_fa<64>(ARGS);
     return launch_fa<128>(ARGS);
 #undef ARGS

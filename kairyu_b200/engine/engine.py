@@ -159,6 +159,15 @@ class Engine:
             return int(min(wanted, fit))
         return int(min(wanted, 4096))
 
+    def warm_up(self, max_batch: Optional[int] = None, max_context: Optional[int] = None) -> int:
+        """Capture the decode graphs for up to ``max_batch`` rows (default: max_num_seqs) of up to
+        ``max_context`` tokens (default: max_model_len) before the first request, so that no step of
+        a serving engine pays for a capture.  Returns the number of graphs captured."""
+        return self.runner.capture_decode_graphs(
+            self.config.max_num_seqs if max_batch is None else max_batch,
+            self.runner.max_model_len if max_context is None else max_context,
+        )
+
     # ------------------------------------------------------------------ requests
     def add_request(
         self,

@@ -309,6 +309,7 @@ class ModelRunner:
             "num_rows": padded_rows,
             "table_width": table_width,
             "max_seq_len": max(seq_lens),
+            "max_portion_seq_len": max((seq_len for (entry, _, seq_len) in rows if len(entry.tokens) > 1), default=0),
             "host_qo_indptr": tuple(qo_indptr),
             "host_seq_lens": tuple(seq_lens),
         }
@@ -350,6 +351,7 @@ class ModelRunner:
             decode_rows=part("decode_rows"),
             decode_tokens=part("decode_tokens"),
             max_seq_len=facts["max_seq_len"],
+            max_portion_seq_len=facts["max_portion_seq_len"],
             workspace=workspace,
             error_flag=self.error_flag,
         )
@@ -421,17 +423,7 @@ class ModelRunner:
         bucket, context_bucket = key
         held = self._graphs.get(key)
         if held is None or held.generation != self.graph_workspace.generation:
-            # The graph is captured over padding rows only (token 0 at position 0 of the reserved
-            # page, the scratch state slot), so that the capture's warm-up runs touch no request:
-            # a mixer with state of its own would otherwise see a request's token several times.
-            # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
-            host, layout, facts = self._pack(
-                (), pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False
-            )
-            facts["max_seq_len"] = context_bucket
-            held = self._capture(key, host, layout, facts)
-            held.mirror = host.numpy().copy()
-            held.row_state = [None] * bucket
+            held = self._capture_padding_graph(key)
         self._update_mirror(held, rows, bucket)
         self._upload(held)
         self._patch_tokens(held.meta, held.layout, sampled)
@@ -445,6 +437,42 @@ class ModelRunner:
             return held.logits[:num_rows]
         index = torch.tensor(wanted_rows, dtype=torch.long, device=self.device)
         return held.logits.index_select(0, index)
+
+    def capture_decode_graphs(self, max_batch: int, max_context: int) -> int:
+        """Capture, ahead of the first request, the decode graphs of every batch bucket up to
+        ``max_batch`` rows and every context bucket up to ``max_context`` tokens, so that no step of
+        a running engine pays for a capture (a capture runs the step two to three times).
+        Returns how many graphs were captured."""
+        if self.decode_mode != "cuda_graph" or not self._is_cuda:
+            return 0
+        captured = 0
+        top = min(max_context, self.max_model_len)
+        contexts = sorted({self._graph_key(1, length)[1] for length in list(range(1, top + 1, 64)) + [top]})
+        limit = max(1, min(max_batch, self.max_graph_batch))
+        buckets = [size for size in self._buckets if size < limit] + [next(size for size in self._buckets if size >= limit)]
+        # the largest first: its buffers are the workspace's final size, and a workspace that grows
+        # afterwards would retire the graphs captured before (the second pass finds nothing to do then)
+        for _ in range(2):
+            for bucket in reversed(buckets):
+                for context in reversed(contexts):
+                    held = self._graphs.get((bucket, context))
+                    if held is None or held.generation != self.graph_workspace.generation:
+                        self._capture_padding_graph((bucket, context))
+                        captured += 1
+        return captured
+
+    def _capture_padding_graph(self, key: tuple[int, int]) -> _Graph:
+        # The graph is captured over padding rows only (token 0 at position 0 of the reserved
+        # page, the scratch state slot), so that the capture's warm-up runs touch no request:
+        # a mixer with state of its own would otherwise see a request's token several times.
+        # Every padded row is "wanted" inside the graph; the caller's wants are picked after.
+        bucket, context = key
+        host, layout, facts = self._pack((), pad_rows=bucket, max_pages=self.max_pages_per_request, include_want=False)
+        facts["max_seq_len"] = context
+        held = self._capture(key, host, layout, facts)
+        held.mirror = host.numpy().copy()
+        held.row_state = [None] * bucket
+        return held
 
     def _needed_pages(self, seq_len: int) -> int:
         return -(-seq_len // self.cache.page_size)

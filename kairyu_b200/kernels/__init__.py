@@ -355,9 +355,17 @@ def attention_prefill_mma(
     scale: float,
     window: int = 0,
     flag: Optional[torch.Tensor] = None,
+    max_seq_len: int = 0,
+    workspace: object = None,
+    num_splits: Optional[int] = None,
 ) -> None:
     """Flash attention over query tiles (``attention_prefill_tile_rows`` queries each) of
-    rows with several tokens (bf16)."""
+    rows with several tokens (bf16).
+
+    With ``workspace`` and ``max_seq_len`` (a bound on the rows' lengths) given, the tcgen05 kernel
+    may share a tile's keys among several blocks when the tiles alone would leave most of the device
+    idle (a short portion of a long prompt); their results meet in fp32 scratch of the workspace and a
+    second kernel combines them.  ``num_splits`` overrides the choice (tests)."""
     what = "attention_prefill_mma"
     _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
     _need_i32(what, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
@@ -369,17 +377,30 @@ def attention_prefill_mma(
         fn = _fn(
             "attention_prefill_tc5",
             "kb_attention_prefill_tc5",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         )
         merged = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_merged", [c_int, c_int])(head_dim, page_size))
+        splits = 1
+        if workspace is not None and num_tiles > 0:
+            if num_splits is not None:
+                splits = int(num_splits)
+            elif max_seq_len > 0:
+                longest = min(int(max_seq_len), int(window) + 128) if window > 0 else int(max_seq_len)
+                splits = _fn("attention_prefill_tc5", "kb_attention_prefill_tc5_splits", [c_int, c_int, c_int, c_int])(head_dim, num_q_heads, int(num_tiles), longest)
+        part_o = part_ml = None
+        if splits > 1:
+            slots = splits * int(num_tiles) * 128 * num_q_heads
+            part_o = workspace.flat("attn.prefill.part_o", slots * head_dim, torch.float32)
+            part_ml = workspace.flat("attn.prefill.part_ml", slots * 2, torch.float32)
         _check(
             fn(
                 _tensor_map(q, 128), _cache_map(k_cache), _cache_map(v_cache, bands=merged), out.data_ptr(), out.stride(0),
                 qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
                 tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
-                page_size, num_pages, float(scale), int(window), _ptr(flag), _stream(),
+                page_size, num_pages, float(scale), int(window), splits, _ptr(part_o), _ptr(part_ml), _ptr(flag), _stream(),
             ),
             what,
+            launches=2 if splits > 1 else 1,
         )
         return
     fn = _fn(

@@ -9,6 +9,7 @@ encoding are constructor arguments; the part does not know its model.
 
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Any, Mapping, Optional
 
@@ -25,6 +26,28 @@ from kairyu_b200.parts.base import (
     StepContext,
     TensorSpec,
 )
+
+
+OVERLAP_MIXED_ATTENTION = True
+
+
+class _SideStream:
+    """A second stream for work that may run beside the step's own, and the two events that fence it."""
+
+    def __init__(self, device: torch.device) -> None:
+        self.stream = torch.cuda.Stream(device=device)
+        self.fork = torch.cuda.Event()
+        self.join = torch.cuda.Event()
+
+
+_side_streams: dict[torch.device, _SideStream] = {}
+
+
+def _side_stream(device: torch.device) -> _SideStream:
+    held = _side_streams.get(device)
+    if held is None:
+        held = _side_streams[device] = _SideStream(device)
+    return held
 
 
 def run_paged_attention(
@@ -68,6 +91,15 @@ def run_paged_attention(
         )
         return
     num_tiles, tile_rows, tile_starts = ctx.tiles[kernels.attention_prefill_tile_rows(head_dim)]
+    # A step with prompt portions beside decoded tokens: the two kernels read the same q|k|v rows and
+    # write different rows of `out`, and neither fills the device alone (a 512-token portion is 256
+    # blocks of tensor-core work, sixteen decode rows a memory-bound stream), so the single-token rows
+    # go to a second stream between two events.
+    beside = None
+    if OVERLAP_MIXED_ATTENTION and num_tiles and ctx.num_decode_rows and qkv.is_cuda and not torch.cuda.is_current_stream_capturing():
+        beside = _side_stream(qkv.device)
+        beside.fork.record()
+        beside.stream.wait_event(beside.fork)
     if num_tiles:
         kernels.attention_prefill_mma(
             qkv,
@@ -84,25 +116,32 @@ def run_paged_attention(
             scale=scale,
             window=window,
             flag=ctx.error_flag,
+            max_seq_len=ctx.max_portion_seq_len,
+            workspace=ctx.workspace,
         )
     if ctx.num_decode_rows:
-        kernels.attention_decode_mma(
-            qkv,
-            out,
-            cache.k,
-            cache.v,
-            seq_lens=ctx.seq_lens,
-            block_table=block_table,
-            decode_rows=ctx.decode_rows,
-            decode_tokens=ctx.decode_tokens,
-            num_rows=ctx.num_decode_rows,
-            max_seq_len=ctx.max_seq_len,
-            num_q_heads=num_q_heads,
-            scale=scale,
-            window=window,
-            workspace=ctx.workspace,
-            flag=ctx.error_flag,
-        )
+        with torch.cuda.stream(beside.stream) if beside is not None else contextlib.nullcontext():
+            kernels.attention_decode_mma(
+                qkv,
+                out,
+                cache.k,
+                cache.v,
+                seq_lens=ctx.seq_lens,
+                block_table=block_table,
+                decode_rows=ctx.decode_rows,
+                decode_tokens=ctx.decode_tokens,
+                num_rows=ctx.num_decode_rows,
+                max_seq_len=ctx.max_seq_len,
+                num_q_heads=num_q_heads,
+                scale=scale,
+                window=window,
+                workspace=ctx.workspace,
+                flag=ctx.error_flag,
+            )
+            if beside is not None:
+                beside.join.record()
+        if beside is not None:
+            torch.cuda.current_stream().wait_event(beside.join)
 
 
 @MIXERS.register("gqa_attention")

@@ -183,6 +183,7 @@ class StepContext:
     decode_rows: torch.Tensor | None = None  # [n] i32 row ids of 1-token rows
     decode_tokens: torch.Tensor | None = None  # [n] i32 flat token index of each
     max_seq_len: int = 0  # host upper bound over rows (sizes split-KV grids)
+    max_portion_seq_len: int = 0  # the same over rows that carry several tokens (prompt portions)
     workspace: Any = None
     error_flag: torch.Tensor | None = None  # [1] i32, set by kernels on bad indices
     extras: dict[str, Any] = field(default_factory=dict)

@@ -369,3 +369,33 @@ def test_decode_graphs_under_preemption_and_ids_used_again(name):
     for mode, turns in results.items():
         for turn in turns:
             assert turn == expected, mode
+
+
+def test_warm_up_captures_every_decode_graph_ahead():
+    """After ``warm_up`` a workload of every batch size up to the limit captures nothing more, and its
+    fp32 greedy tokens are the plain model's."""
+    from kairyu_b200 import SamplingParams
+    from kairyu_b200.config.engine_config import EngineConfig
+    from kairyu_b200.engine.engine import Engine
+
+    config, seed, page_size = TINY["llama"]
+    options = EngineConfig.from_kwargs(
+        dtype="float32", seed=seed, page_size=page_size, num_pages=1 + 2048 // page_size, max_num_seqs=6,
+        max_num_batched_tokens=256, decode_mode="cuda_graph",
+    )
+    engine = Engine.from_random(config, seed, options)
+    captured = engine.warm_up(max_batch=6)
+    # batch buckets 1, 2, 4 and 6 (the engine's limit); one context bucket (the model's 256 positions)
+    assert captured == 4 and engine.runner.counters["graph_captures"] == 4
+    assert engine.warm_up(max_batch=6) == 0
+    prompts = prompts_of(config, [40, 3, 77, 150, 9, 61], seed=160)
+    new_tokens = [30, 12, 40, 100, 25, 33]
+    for index, prompt in enumerate(prompts):
+        engine.add_request(f"request-{index}", prompt, SamplingParams(temperature=0.0, max_tokens=new_tokens[index]))
+    finished = engine.run_to_completion()
+    engine.runner.check_errors()
+    assert engine.runner.counters["graph_captures"] == 4
+    assert engine.runner.counters["graph_replays"] > 50
+    weights = engine_weights(type("Holder", (), {"engine": engine}))
+    for index, (prompt, count) in enumerate(zip(prompts, new_tokens)):
+        assert finished[f"request-{index}"].output_token_ids == tuple(plain_generate(config, weights, prompt, count))

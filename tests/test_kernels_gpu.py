@@ -5,6 +5,7 @@ random data would hide a fault the inputs are built so that it shows (one key
 among hundreds carries the whole softmax; keys at page, tile and split edges)."""
 
 import math
+from ctypes import c_int
 
 import pytest
 import torch
@@ -594,6 +595,59 @@ def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_s
     )
     assert int(flag.item()) == 0
     close(out, expected, 2e-2)
+
+
+def _run_prefill(case, Hq, scale, window, workspace, num_splits, max_seq_len=0):
+    k = kernels()
+    qo = case["qo"].tolist()
+    tile_rows, tile_starts = [], []
+    for r in range(len(qo) - 1):
+        for start in range(0, qo[r + 1] - qo[r], k.attention_prefill_tile_rows(case["kc"].shape[-1])):
+            tile_rows.append(r)
+            tile_starts.append(start)
+    dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.attention_prefill_mma(
+        case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), qo_indptr=case["qo"].to(DEV), seq_lens=case["seq_lens"].to(DEV),
+        block_table=case["table"].to(DEV), tile_rows=dev(tile_rows), tile_starts=dev(tile_starts), num_tiles=len(tile_rows),
+        num_q_heads=Hq, scale=scale, window=window, flag=flag, workspace=workspace, num_splits=num_splits, max_seq_len=max_seq_len,
+    )
+    assert int(flag.item()) == 0
+    return out
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,page_size", [(8, 2, 64, 16), (32, 8, 128, 16), (4, 1, 128, 64), (6, 3, 64, 8)])
+@pytest.mark.parametrize("num_splits", [2, 3, 8])
+@pytest.mark.parametrize("window", [0, 333])
+def test_prefill_attention_with_the_keys_split_over_blocks(Hq, Hkv, D, page_size, num_splits, window, workspace):
+    """Portions of long requests whose keys several blocks share: a portion deep in a request, one
+    whose last tile is ragged, a fresh short prompt (fewer key tiles than splits: blocks without
+    keys), a 2-token portion."""
+    seq_lens = [900, 1300, 150, 700]
+    chunk_lens = [200, 131, 150, 2]
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, chunk_lens, seed=37)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    out = _run_prefill(case, Hq, scale, window, workspace, num_splits)
+    close(out, expected, 2e-2)
+    again = _run_prefill(case, Hq, scale, window, workspace, num_splits)
+    assert torch.equal(out, again)  # the splits are combined in order, not as they arrive
+
+
+@pytest.mark.parametrize("hot_key", [0, 63, 64, 500, 1023, 1024, 1900])
+def test_prefill_attention_split_finds_one_far_key(hot_key, workspace):
+    """One key among 2,000 carries the softmax of a 128-token portion, whichever block's share it lies in;
+    the number of splits is the kernel's own choice (a lone tile of few heads: as many as it takes)."""
+    Hq, Hkv, D, page_size = 8, 2, 128, 16
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, [2000], [128], seed=38, hot=(0, hot_key))
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, 0)
+    visible = [t for t in range(128) if 2000 - 128 + t >= hot_key]
+    assert float(expected[visible].min()) > 24.0  # the reference itself is dominated by that key
+    assert kernels()._fn("attention_prefill_tc5", "kb_attention_prefill_tc5_splits", [c_int] * 4)(D, Hq, 1, 2000) > 1
+    out = _run_prefill(case, Hq, scale, 0, workspace, None, max_seq_len=2000)
+    close(out, expected, 2e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("num_splits", [None, 1, 5])
