@@ -584,6 +584,7 @@ def main() -> int:
     parser.add_argument("--shared-prefix", action="store_true", help="add the shared-stem workload of 16 requests, prefix caching off and on")
     parser.add_argument("--prompt-len", type=int, default=None, help="another prompt length than the shape's (with --gen-len, within the context length)")
     parser.add_argument("--gen-len", type=int, default=None)
+    parser.add_argument("--context-len", type=int, default=None, help="another context length than the shape's (longer prompts)")
     args = parser.parse_args()
     if SHAPES[args.shape] is not None:
         shape = SHAPES[args.shape]
@@ -592,6 +593,9 @@ def main() -> int:
         if args.layers == FULL_LAYERS:
             args.layers = MODEL["num_hidden_layers"]
         FULL_LAYERS = MODEL["num_hidden_layers"]
+    if args.context_len is not None:
+        CONTEXT_LEN = args.context_len
+        MODEL = dict(MODEL, max_position_embeddings=max(MODEL["max_position_embeddings"], CONTEXT_LEN))
     if args.prompt_len is not None:
         PROMPT_LEN = args.prompt_len
     if args.gen_len is not None:

@@ -328,6 +328,13 @@ def attention_prefill_tile_rows(head_dim: int) -> int:
     return 128 if head_dim <= 128 else 64
 
 
+def attention_prefill_wide_tile_rows(head_dim: int) -> Optional[int]:
+    """Queries per tile of the second list the prefill attention takes for long portions (the kernel
+    that walks two 128-query tiles a block, csrc/attention_prefill_tc5.cu), or None for head sizes
+    it does not cover."""
+    return 256 if head_dim == 128 else None
+
+
 def _check_mma_common(what: str, q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError(f"{what}: bf16 only")
@@ -358,6 +365,8 @@ def attention_prefill_mma(
     max_seq_len: int = 0,
     workspace: object = None,
     num_splits: Optional[int] = None,
+    wide_tiles: Optional[tuple[int, torch.Tensor, torch.Tensor]] = None,
+    two_tiles: Optional[bool] = None,
 ) -> None:
     """Flash attention over query tiles (``attention_prefill_tile_rows`` queries each) of
     rows with several tokens (bf16).
@@ -365,7 +374,11 @@ def attention_prefill_mma(
     With ``workspace`` and ``max_seq_len`` (a bound on the rows' lengths) given, the tcgen05 kernel
     may share a tile's keys among several blocks when the tiles alone would leave most of the device
     idle (a short portion of a long prompt); their results meet in fp32 scratch of the workspace and a
-    second kernel combines them.  ``num_splits`` overrides the choice (tests)."""
+    second kernel combines them.  ``num_splits`` overrides the choice (tests).
+
+    ``wide_tiles`` (count, rows, starts of tiles of ``attention_prefill_wide_tile_rows`` queries over the
+    same portions): long portions of head size 128 go to the kernel that takes two query tiles a block
+    when its grid makes two waves or more; ``two_tiles`` overrides that choice (tests)."""
     what = "attention_prefill_mma"
     _need_cuda(what, q, out, k_cache, v_cache, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
     _need_i32(what, qo_indptr, seq_lens, block_table, tile_rows, tile_starts)
@@ -377,7 +390,7 @@ def attention_prefill_mma(
         fn = _fn(
             "attention_prefill_tc5",
             "kb_attention_prefill_tc5",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p],
         )
         merged = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_merged", [c_int, c_int])(head_dim, page_size))
         splits = 1
@@ -387,6 +400,15 @@ def attention_prefill_mma(
             elif max_seq_len > 0:
                 longest = min(int(max_seq_len), int(window) + 128) if window > 0 else int(max_seq_len)
                 splits = _fn("attention_prefill_tc5", "kb_attention_prefill_tc5_splits", [c_int, c_int, c_int, c_int])(head_dim, num_q_heads, int(num_tiles), longest)
+        use_two = False
+        if wide_tiles is not None and wide_tiles[0] > 0 and head_dim == 128 and splits == 1:
+            if two_tiles is None:
+                use_two = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_two_tiles", [c_int, c_int, c_int])(head_dim, num_q_heads, int(wide_tiles[0])))
+            else:
+                use_two = bool(two_tiles)
+            if use_two:
+                _need_cuda(what, wide_tiles[1], wide_tiles[2])
+                _need_i32(what, wide_tiles[1], wide_tiles[2])
         part_o = part_ml = None
         if splits > 1:
             slots = splits * int(num_tiles) * 128 * num_q_heads
@@ -397,7 +419,9 @@ def attention_prefill_mma(
                 _tensor_map(q, 128), _cache_map(k_cache), _cache_map(v_cache, bands=merged), out.data_ptr(), out.stride(0),
                 qo_indptr.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1],
                 tile_rows.data_ptr(), tile_starts.data_ptr(), int(num_tiles), num_q_heads, num_kv_heads, head_dim,
-                page_size, num_pages, float(scale), int(window), splits, _ptr(part_o), _ptr(part_ml), _ptr(flag), _stream(),
+                page_size, num_pages, float(scale), int(window), splits, _ptr(part_o), _ptr(part_ml),
+                wide_tiles[1].data_ptr() if use_two else None, wide_tiles[2].data_ptr() if use_two else None,
+                int(wide_tiles[0]) if use_two else 0, 1 if use_two else 0, _ptr(flag), _stream(),
             ),
             what,
             launches=2 if splits > 1 else 1,
@@ -1023,6 +1047,7 @@ __all__ = [
     "attention_decode_mma",
     "attention_mma_supported",
     "attention_prefill_tile_rows",
+    "attention_prefill_wide_tile_rows",
     "attention_prefill_mma",
     "edit_logits",
     "embedding",

@@ -118,6 +118,7 @@ def run_paged_attention(
             flag=ctx.error_flag,
             max_seq_len=ctx.max_portion_seq_len,
             workspace=ctx.workspace,
+            wide_tiles=ctx.tiles.get(kernels.attention_prefill_wide_tile_rows(head_dim)),
         )
     if ctx.num_decode_rows:
         with torch.cuda.stream(beside.stream) if beside is not None else contextlib.nullcontext():
@@ -253,7 +254,8 @@ class GQAAttention(Mixer):
         return (PagedKVSpec(self.num_kv_heads, self.head_dim, self.window),)
 
     def query_tile_sizes(self) -> tuple[int, ...]:
-        return (kernels.attention_prefill_tile_rows(self.head_dim),)
+        wide = kernels.attention_prefill_wide_tile_rows(self.head_dim)
+        return (kernels.attention_prefill_tile_rows(self.head_dim),) + ((wide,) if wide else ())
 
     # -- compute
     def fusable_norm(self, tokens: int) -> bool:
