@@ -3,13 +3,18 @@
 //
 //     S = Q K^T * scale (causal, optional window),  P = softmax rows online,  O = P V.
 //
-// A block owns a tile of 128 queries of one head, or two, one after the other.  Later tiles of a
-// portion see more keys.  With many tiles, blocks take one tile each, the longest first, and the
-// short ones fill the tail of the grid.  When all blocks fit the device at once even at two tiles
-// each (a prompt of 2,048 tokens: 16 tiles x 32 heads), a block takes tile T-1-y of the list and
-// then tile y, so that every block of a prompt does the same work (34 key tiles each) instead of
-// the longest walking its 32 key tiles alone at the end (2,048 tokens: 63 -> 59 us; at 8,192
-// tokens equal blocks would fill their last wave badly: 629 -> 707 us, so there they stay single).
+// Three ways to spread a step's query tiles over the device, chosen on the host:
+//  * one tile of 128 queries a block, the longest first (later tiles of a portion see more keys),
+//    when the blocks fit the device at once, or are far too many to;
+//  * two tiles a block, tile T-1-y and then tile y, when one tile a block would not all run at once
+//    but two a block do (a prompt of 2,048 tokens: 16 tiles x 32 heads): every block then does the
+//    same work (34 key tiles) instead of the longest walking its 32 key tiles alone at the end
+//    (2,048 tokens: 63 -> 59 us; at 8,192 tokens equal blocks would fill their last wave badly);
+//  * several blocks a tile, each with a share of the tile's keys, when the tiles alone would leave
+//    most of the device idle (a 512-token portion at the end of 8,192 tokens is 128 tiles x heads:
+//    312 -> 102 us); the blocks leave unnormalised O, their reference maximum and their sum in
+//    fp32 scratch, and a second kernel combines them in split order.
+// Long portions of head_dim 128 go to a second kernel further down, which walks two tiles side by side.
 // For a tile the block walks the keys it may see in tiles of 64.  Roles (192 threads):
 //   warp 0     producer: TMA copies of the Q tile (2-D map over the packed qkv rows) and of
 //              every K and V tile (a map over the cache: a copy brings a page's run of rows
@@ -1098,10 +1103,16 @@ static int launch_two(const CUtensorMap* mq, const CUtensorMap* mk, const CUtens
 }
 
 // Whether a step's portions go to the kernel that takes two query tiles a block (head_dim 128,
-// lists of 256-query tiles given): when its blocks, one an SM, make two waves or more.
-KB_EXPORT int kb_attention_prefill_tc5_two_tiles(int D, int Hq, int num_wide) {
-    if (D != 128 || num_wide < 1) return 0;
-    return (long long)Hq * num_wide >= 2LL * fa_resident(1) ? 1 : 0;
+// lists of 256-query tiles given): when its blocks, one an SM, make two waves or more, or one wave
+// over long rows.  Measured on 32 heads, pages of 16 (us a layer, one tile a block / two):
+// 2,048 tokens 55.5 / 57.0; 4,096: 177 / 169; 8,192: 596 / 555; 2,048 tokens at the end of 8,192:
+// 318 / 273; 16,384: 2,250 / 2,242.  With pages of 64 positions the one-tile kernel needs few copies
+// and stays ahead (8,192 tokens: 529 / 555).
+KB_EXPORT int kb_attention_prefill_tc5_two_tiles(int D, int Hq, int num_wide, int page_size, int max_seq_len) {
+    if (D != 128 || num_wide < 1 || page_size >= 64) return 0;
+    const long long blocks = (long long)Hq * num_wide;
+    const long long wave = fa_resident(1);
+    return (blocks >= 2 * wave || (blocks >= wave && max_seq_len >= 4096)) ? 1 : 0;
 }
 
 // 1 when (head_dim, page_size) fit this kernel.

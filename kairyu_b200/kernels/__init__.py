@@ -403,7 +403,8 @@ def attention_prefill_mma(
         use_two = False
         if wide_tiles is not None and wide_tiles[0] > 0 and head_dim == 128 and splits == 1:
             if two_tiles is None:
-                use_two = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_two_tiles", [c_int, c_int, c_int])(head_dim, num_q_heads, int(wide_tiles[0])))
+                use_two = bool(_fn("attention_prefill_tc5", "kb_attention_prefill_tc5_two_tiles", [c_int] * 5)(
+                    head_dim, num_q_heads, int(wide_tiles[0]), page_size, int(max_seq_len)))
             else:
                 use_two = bool(two_tiles)
             if use_two:

@@ -597,24 +597,60 @@ def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_s
     close(out, expected, 2e-2)
 
 
-def _run_prefill(case, Hq, scale, window, workspace, num_splits, max_seq_len=0):
+def _run_prefill(case, Hq, scale, window, workspace, num_splits, max_seq_len=0, two_tiles=None):
     k = kernels()
     qo = case["qo"].tolist()
-    tile_rows, tile_starts = [], []
+    tile_rows, tile_starts, wide_rows, wide_starts = [], [], [], []
     for r in range(len(qo) - 1):
         for start in range(0, qo[r + 1] - qo[r], k.attention_prefill_tile_rows(case["kc"].shape[-1])):
             tile_rows.append(r)
             tile_starts.append(start)
+        for start in range(0, qo[r + 1] - qo[r], 256):
+            wide_rows.append(r)
+            wide_starts.append(start)
     dev = lambda values: torch.tensor(values, dtype=torch.int32, device=DEV)
+    wide = (len(wide_rows), dev(wide_rows), dev(wide_starts)) if two_tiles is not None else None
     out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
     flag = torch.zeros(1, dtype=torch.int32, device=DEV)
     k.attention_prefill_mma(
         case["q"].to(DEV), out, case["kc"].to(DEV), case["vc"].to(DEV), qo_indptr=case["qo"].to(DEV), seq_lens=case["seq_lens"].to(DEV),
         block_table=case["table"].to(DEV), tile_rows=dev(tile_rows), tile_starts=dev(tile_starts), num_tiles=len(tile_rows),
         num_q_heads=Hq, scale=scale, window=window, flag=flag, workspace=workspace, num_splits=num_splits, max_seq_len=max_seq_len,
+        wide_tiles=wide, two_tiles=two_tiles,
     )
     assert int(flag.item()) == 0
     return out
+
+
+@pytest.mark.parametrize("Hq,Hkv,page_size", [(8, 2, 16), (32, 8, 16), (4, 4, 8), (6, 1, 32), (4, 2, 128)])
+@pytest.mark.parametrize("window", [0, 37, 333])
+def test_prefill_attention_two_query_tiles_a_block(Hq, Hkv, page_size, window, workspace):
+    """The kernel that walks two 128-query tiles over 128-key tiles: a whole prompt of five tiles (the
+    last block has one tile, and that ragged), a portion that starts at an odd position deep in a
+    request, a portion of exactly 256, a short one and a 2-token one; with windows shorter and longer
+    than a key tile (tile B starts later than tile A, whole key tiles lie before the window)."""
+    D = 128
+    seq_lens = [600, 1301, 256, 777, 300]
+    chunk_lens = [600, 391, 256, 100, 2]
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, chunk_lens, seed=39)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    out = _run_prefill(case, Hq, scale, window, workspace, 1, two_tiles=True)
+    close(out, expected, 2e-2)
+    assert torch.equal(out, _run_prefill(case, Hq, scale, window, workspace, 1, two_tiles=True))
+
+
+@pytest.mark.parametrize("hot_key", [0, 127, 128, 129, 700, 1023, 1024, 1150, 1279])
+def test_prefill_attention_two_tiles_finds_one_far_key(hot_key, workspace):
+    """One key among 1,280 carries the softmax of the last 300 queries, wherever it lies in a key tile."""
+    Hq, Hkv, D, page_size = 8, 2, 128, 16
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, [1280], [300], seed=40, hot=(0, hot_key))
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, 0)
+    visible = [t for t in range(300) if 1280 - 300 + t >= hot_key]
+    assert float(expected[visible].min()) > 24.0
+    out = _run_prefill(case, Hq, scale, 0, workspace, 1, two_tiles=True)
+    close(out, expected, 2e-2, rtol=1e-2)
 
 
 @pytest.mark.parametrize("Hq,Hkv,D,page_size", [(8, 2, 64, 16), (32, 8, 128, 16), (4, 1, 128, 64), (6, 3, 64, 8)])

@@ -99,7 +99,7 @@ def truth_and_bound(case, dtype, requests=None, keep=None):
     return truth, bound
 
 
-def make_runner(case, dtype, *, num_pages, max_graph_batch=8, decode_mode="cuda_graph"):
+def make_runner(case, dtype, *, num_pages, max_graph_batch=8, decode_mode="cuda_graph", max_model_len=2048):
     from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
     from kairyu_b200.engine.engine import random_model
     from kairyu_b200.engine.runner import ModelRunner
@@ -110,7 +110,7 @@ def make_runner(case, dtype, *, num_pages, max_graph_batch=8, decode_mode="cuda_
     cache = CacheManager(layout, num_pages=num_pages, page_size=PAGE, max_requests=requests_at_once)
     storage = CacheStorage(layout, num_pages=num_pages, page_size=PAGE, max_requests=requests_at_once, dtype=model.dtype, device="cuda")
     return ModelRunner(
-        model, cache, storage, max_model_len=2048, decode_mode=decode_mode, max_graph_batch=max_graph_batch,
+        model, cache, storage, max_model_len=max_model_len, decode_mode=decode_mode, max_graph_batch=max_graph_batch,
         check_tables=True, debug_poison=True,
     )
 
@@ -166,3 +166,37 @@ def test_decode_steps_of_many_rows_at_real_layer_sizes(shape, dtype):
         error = parity.worst_error(result, expected)
         print(f"[parity] {shape['name']} {dtype} {rows} rows: worst error {error:.3e}, bound {bound:.3e}")
         assert error < bound, (rows, error, bound, parity.rows_beyond(result, expected, bound))
+
+
+def test_a_long_prompt_at_real_layer_sizes(shape):
+    """One prompt of 4,300 tokens in bfloat16, whole (its attention goes to the kernel that takes two
+    query tiles a block), in portions of 1,024 (one tile a block) and of 512 and less (the later
+    portions' keys are shared among blocks), with the last tokens decoded: every cut within the bound."""
+    from ctypes import c_int
+
+    import kairyu_b200.kernels as kernels
+
+    config = shape["config"]
+    if config["hidden_size"] != 4096:
+        pytest.skip("one width is enough here")
+    length = 4300
+    heads = config["num_attention_heads"]
+    assert kernels._fn("attention_prefill_tc5", "kb_attention_prefill_tc5_two_tiles", [c_int] * 5)(128, heads, -(-length // 256), PAGE, length) == 1
+    assert kernels._fn("attention_prefill_tc5", "kb_attention_prefill_tc5_splits", [c_int] * 4)(128, heads, 4, 4000) > 1
+    requests = traces.make_requests(config["vocab_size"], [length], seed=77)
+    keep = {name: sorted(set(range(0, length, 389)) | set(range(length - 6, length))) for name in requests}
+    expected, bound = truth_and_bound(shape, "bfloat16", requests, keep)
+    cuts = {
+        "whole": traces.trace_whole(requests),
+        "portions of 1024": traces.trace_chunks(requests, sizes=(1024,)),
+        "portions of 512 and less": traces.trace_chunks(requests, sizes=(512, 300, 512, 128, 512, 2, 512)),
+        "tail decoded": traces.trace_decode_tail(requests, 5),
+    }
+    runner = make_runner(shape, "bfloat16", num_pages=length // PAGE + 3, max_model_len=4608)
+    for cut, steps in cuts.items():
+        result = traces.run_in_process(runner, parity.thin_wants(steps, keep))
+        assert result.keys() == expected.keys()
+        error = parity.worst_error(result, expected)
+        print(f"[parity] {shape['name']} long prompt, {cut}: worst error {error:.3e}, bound {bound:.3e}")
+        assert error < bound, (cut, error, bound, parity.rows_beyond(result, expected, bound))
+    runner.check_errors()
