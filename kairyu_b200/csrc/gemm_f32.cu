@@ -1,13 +1,15 @@
 // y[M,N] = x[M,K] . W[N,K]^T (+ bias[N]) in true fp32: plain FMA on CUDA cores,
-// no tensor cores and no reduced-precision mode.  Each output element is one
-// accumulator running over k = 0..K-1 in order, so a row's result does not
-// depend on M or on which tile it falls in: the 32-bit path is bit-stable
-// however a prompt is cut into steps.
+// no tensor cores and no reduced-precision mode.  Each output element adds its terms
+// in order of k, 256 at a time into one accumulator whose sums are then added in
+// order into a second (a sum of 8,192 terms carries the rounding of 256 + 32
+// additions, not of 8,192), so a row's result does not depend on M or on which tile
+// it falls in: the 32-bit path is bit-stable however a prompt is cut into steps.
 #include "common.cuh"
 
 #define F32_BM 64
 #define F32_BN 64
 #define F32_BK 16
+#define F32_SUM_BLOCK 256  // terms a first-level accumulator takes before it is added to the second
 
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ w, int ldw,
@@ -21,13 +23,22 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
     const int m0 = blockIdx.y * F32_BM;
     const int n0 = blockIdx.x * F32_BN;
 
-    float acc[4][4];
+    float acc[4][4], total[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; ++j) acc[i][j] = total[i][j] = 0.0f;
 
     for (int k0 = 0; k0 < K; k0 += F32_BK) {
+        if (k0 > 0 && k0 % F32_SUM_BLOCK == 0) {  // a block of 256 terms is complete
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    total[i][j] += acc[i][j];
+                    acc[i][j] = 0.0f;
+                }
+        }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int idx = tid + i * 256;
@@ -62,7 +73,7 @@ gemm_f32_kernel(const float* __restrict__ x, int ldx, const float* __restrict__ 
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
-            float v = acc[i][j];
+            float v = total[i][j] + acc[i][j];
             if (bias) v += bias[n];
             y[(size_t)m * ldy + n] = v;
         }
