@@ -1,0 +1,122 @@
+"""Long prompts cut at random, in bfloat16, on a small model whose attention has the head size
+(128) and head count (16 query heads on 4 KV heads) that send its prompt portions through every
+way the tcgen05 prefill attention spreads its query tiles: one tile a block, a long and a short
+tile a block, two tiles side by side over 128-key tiles, and a tile's keys shared among blocks.
+
+Each seed draws a few requests of up to 6,000 tokens and cuts them into portions drawn from
+sizes between 2 tokens and the whole prompt, with decoded tokens of other requests beside them
+and a pool so small that pages are used again.  Logits at chosen positions are compared with the
+plain model (kairyu tests/unit/test_model_parity.py:78-114 compares whole against chunked the
+same way); the bound is what rounding every operation to bfloat16 costs the plain model itself.
+"""
+
+import random
+
+import pytest
+import torch
+
+import parity
+import traces
+
+pytestmark = pytest.mark.gpu
+
+PAGE = 16
+CONFIG = {
+    "architectures": ["Qwen3ForCausalLM"], "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 16,
+    "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 384, "vocab_size": 512, "rope_theta": 1000000.0,
+    "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "hidden_act": "silu",
+}
+SEED = 9
+SIZES = (2, 17, 64, 128, 129, 300, 512, 1024, 2048, 10_000)
+BF16_FACTOR = 1.25
+
+
+def random_cut(requests, rng):
+    """Steps in which one request brings a portion of random size while up to three others, whose
+    prompts are done but for their last eight tokens, bring one token each."""
+    steps = []
+    decoding: dict[str, int] = {}
+    for name, tokens in requests.items():
+        head = len(tokens) - 8
+        start = 0
+        while start < head:
+            size = min(rng.choice(SIZES), head - start)
+            entries = [{"id": name, "tokens": tokens[start : start + size], "want": list(range(size))}]
+            ended = []
+            for other in list(decoding):
+                if rng.random() < 0.6:
+                    place = decoding[other]
+                    entries.append({"id": other, "tokens": [requests[other][place]], "want": [0]})
+                    decoding[other] = place + 1
+                    if place + 1 == len(requests[other]):
+                        ended.append(other)
+                        del decoding[other]
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+            start += size
+        decoding[name] = head
+        if len(decoding) > 3:  # finish the oldest before the next prompt starts
+            oldest = next(iter(decoding))
+            while oldest in decoding:
+                place = decoding[oldest]
+                last = place + 1 == len(requests[oldest])
+                steps.append({"step": len(steps), "entries": [{"id": oldest, "tokens": [requests[oldest][place]], "want": [0]}], "end": [oldest] if last else []})
+                decoding[oldest] = place + 1
+                if last:
+                    del decoding[oldest]
+    while decoding:
+        entries, ended = [], []
+        for other in list(decoding):
+            place = decoding[other]
+            entries.append({"id": other, "tokens": [requests[other][place]], "want": [0]})
+            decoding[other] = place + 1
+            if place + 1 == len(requests[other]):
+                ended.append(other)
+                del decoding[other]
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+    return steps
+
+
+@pytest.fixture(scope="module")
+def model():
+    from golden_inputs import golden_weights_on
+    from kairyu_b200.engine.engine import random_model
+
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.set_float32_matmul_precision("highest")
+    weights = golden_weights_on(CONFIG, SEED, "cuda")
+    held = {k: v.float() for k, v in parity.in_bf16(weights, False).items()}
+    built, _ = random_model(CONFIG, SEED, dtype="bfloat16", device="cuda")
+    return {"weights": weights, "held": held, "model": built}
+
+
+def make_runner(built, num_pages):
+    from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+    from kairyu_b200.engine.runner import ModelRunner
+
+    layout = CacheLayout.from_slot_specs(built.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=num_pages, page_size=PAGE, max_requests=8)
+    storage = CacheStorage(layout, num_pages=num_pages, page_size=PAGE, max_requests=8, dtype=built.dtype, device="cuda")
+    return ModelRunner(built, cache, storage, max_model_len=8192, decode_mode="cuda_graph", max_graph_batch=8, check_tables=True, debug_poison=True)
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_long_prompts_cut_at_random(model, seed):
+    rng = random.Random(seed)
+    lengths = [rng.choice((rng.randint(2000, 6000), rng.randint(300, 1500), rng.randint(20, 200))) for _ in range(rng.randint(3, 5))]
+    lengths[0] = rng.randint(4200, 6000)  # one that is long enough for every kernel
+    requests = traces.make_requests(CONFIG["vocab_size"], lengths, seed=500 + seed)
+    keep = {name: parity.keep_positions(len(tokens), spread=12, tail=10) for name, tokens in requests.items()}
+    truth = parity.plain_rows(CONFIG, model["held"], requests, keep)
+    rounded = parity.plain_rows(CONFIG, parity.in_bf16(model["weights"], False), requests, keep)
+    bound = BF16_FACTOR * parity.worst_error(rounded, truth)
+    steps = random_cut(requests, rng)
+    pool = traces.peak_tokens(steps) // PAGE + 2
+    runner = make_runner(model["model"], pool)
+    result = traces.run_in_process(runner, parity.thin_wants(steps, keep))
+    runner.check_errors()
+    assert result.keys() == truth.keys()
+    error = parity.worst_error(result, truth)
+    print(f"[parity] long prompts, seed {seed}, lengths {lengths}, {len(steps)} steps: worst error {error:.3e}, bound {bound:.3e}")
+    assert error < bound, (error, bound, parity.rows_beyond(result, truth, bound))
+    whole = traces.run_in_process(make_runner(model["model"], sum(lengths) // PAGE + 8), parity.thin_wants(traces.trace_whole(requests), keep))
+    assert parity.worst_error(whole, truth) < bound
