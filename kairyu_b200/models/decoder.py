@@ -113,5 +113,5 @@ class DecoderModel:
                 residual, delta = block.forward(residual, delta, ctx, view)
         if want_rows is None or want_rows.numel() == 0:
             return None
-        hidden = self.final_norm.apply(residual, delta, ctx, rows=want_rows, tag="final_norm.out")
+        hidden = self.final_norm.apply(residual, delta, ctx, rows=want_rows)
         return self.head.forward(hidden, ctx)

@@ -38,10 +38,10 @@ class RMSNorm(Norm):
         ctx: StepContext,
         *,
         rows: Optional[torch.Tensor] = None,
-        tag: str = "norm.out",
     ) -> torch.Tensor:
         count = rows.numel() if rows is not None else residual.shape[0]
-        out = ctx.workspace.buffer(tag, count, self.size, self.dtype)
+        # a subset of rows (the model's last norm, at the wanted places) has a buffer of its own
+        out = ctx.workspace.buffer("norm.out" if rows is None else "norm.rows.out", count, self.size, self.dtype)
         kernels.rmsnorm(residual, self.weight, self.eps, out, delta=delta, rows=rows)
         return out
 

@@ -363,3 +363,148 @@ def test_routed_toy_architecture_on_cpu(routed, monkeypatch):
 @pytest.mark.gpu
 def test_routed_toy_architecture_on_gpu(routed):
     check_routed(routed, "cuda")
+
+
+# ------------------------------------------------------------------ a third toy: another norm and another block arrangement
+# A LayerNorm with a bias and a block in which the mixer and the feed-forward read the same normed
+# rows and their outputs are added together (a parallel residual), both defined here; attention
+# and the feed-forward are the package's.
+
+from kairyu_b200.parts import BLOCKS, NORMS, Block, Norm  # noqa: E402
+
+P_HIDDEN, P_INTER, P_VOCAB, P_HEADS, P_KV, P_HEAD = 56, 40, 83, 4, 2, 16
+P_EPS = 1e-4
+
+
+class ToyLayerNorm(Norm):
+    """(x - mean) / sqrt(var + eps) * weight + bias, statistics in 32-bit; adds the pending delta first."""
+
+    def __init__(self, *, name, size, eps, dtype, device, **_):
+        self.name, self.size, self.eps, self.dtype = name, size, eps, dtype
+        self.weight = self.bias = None
+
+    def tensor_specs(self):
+        return [TensorSpec(f"{self.name}.weight", (self.size,), role="vector", init="norm"), TensorSpec(f"{self.name}.bias", (self.size,), role="vector")]
+
+    def load(self, tensors):
+        self.weight, self.bias = tensors[f"{self.name}.weight"], tensors[f"{self.name}.bias"]
+
+    def apply(self, residual, delta, ctx, *, rows=None):
+        if rows is None:
+            if delta is not None:
+                residual.add_(delta.float())
+            x = residual
+        else:
+            x = residual.index_select(0, rows.long())
+            if delta is not None:
+                x = x + delta.index_select(0, rows.long()).float()
+        y = torch.nn.functional.layer_norm(x.float(), (self.size,), self.weight.float(), self.bias.float(), self.eps)
+        return y.to(self.dtype)
+
+
+class ParallelBlock(Block):
+    """x += mixer(norm(x)) + ffn(norm(x)): one norm, both branches read it."""
+
+    def __init__(self, *, layer, dtype, device, shared, **_):
+        from kairyu_b200.parts import FEED_FORWARDS as feed_forwards
+
+        context = dict(dtype=dtype, device=device, shared=shared)
+        self.norm = NORMS.build(layer.mixer_norm, **context)
+        self.mixer = MIXERS.build(layer.mixer, **context)
+        self.ffn = feed_forwards.build(layer.ffn, **context)
+        self._parts = (self.norm, self.mixer, self.ffn)
+
+    def tensor_specs(self):
+        return [spec for part in self._parts for spec in part.tensor_specs()]
+
+    def load(self, tensors):
+        for part in self._parts:
+            part.load(tensors)
+
+    def forward(self, residual, delta, ctx, cache):
+        normed = self.norm.apply(residual, delta, ctx)
+        return residual, self.mixer.forward(normed, ctx, cache) + self.ffn.forward(normed, ctx)
+
+
+def parallel_spec(config) -> ModelSpec:
+    def norm(name):
+        return PartSpec("toy_layer_norm", name=name, size=P_HIDDEN, eps=P_EPS)
+
+    position = PartSpec("rope", rotary_dim=P_HEAD, theta=5000.0, scaling=None, max_positions=192)
+    layers = tuple(
+        LayerSpec(
+            f"layers.{i}", "toy_parallel",
+            PartSpec("gqa_attention", prefix=f"layers.{i}.attn", hidden_size=P_HIDDEN, num_heads=P_HEADS, num_kv_heads=P_KV, head_dim=P_HEAD,
+                     qk_norm=False, norm_eps=P_EPS, qkv_bias=False, o_bias=False, position=position),
+            PartSpec("swiglu", prefix=f"layers.{i}.mlp", hidden_size=P_HIDDEN, intermediate_size=P_INTER, activation="silu"),
+            norm(f"layers.{i}.ln"), norm(f"layers.{i}.unused"),
+        )
+        for i in range(2)
+    )
+    return ModelSpec(
+        embedding=PartSpec("token_embedding", name="embed.weight", vocab_size=P_VOCAB, hidden_size=P_HIDDEN),
+        layers=layers, schedule=(LayerCall(0, cache_slot=0), LayerCall(1, cache_slot=1)), final_norm=norm("final_ln"),
+        head=PartSpec("linear_head", name="head.weight", vocab_size=P_VOCAB, hidden_size=P_HIDDEN, tied_to=None),
+        vocab_size=P_VOCAB, hidden_size=P_HIDDEN, max_position_embeddings=192,
+    )
+
+
+@pytest.fixture
+def parallel():
+    NORMS.register("toy_layer_norm")(ToyLayerNorm)
+    BLOCKS.register("toy_parallel")(ParallelBlock)
+    register_architecture("ToyParallelForCausalLM", lambda config: dict(config), parallel_spec)
+    yield {"architectures": ["ToyParallelForCausalLM"]}
+    unregister_architecture("ToyParallelForCausalLM")
+    BLOCKS.unregister("toy_parallel")
+    NORMS.unregister("toy_layer_norm")
+
+
+def plain_parallel_logits(w, tokens):
+    lin = torch.nn.functional.linear
+    cfg = {"head_dim": P_HEAD, "theta": 5000.0, "rope_kind": None, "rope": {}}
+    T = len(tokens)
+    cos, sin = plain_model.rope_cos_sin(cfg, torch.arange(T))
+
+    def ln(x, name):
+        return torch.nn.functional.layer_norm(x, (P_HIDDEN,), w[f"{name}.weight"], w[f"{name}.bias"], P_EPS)
+
+    x = w["embed.weight"][torch.tensor(tokens)]
+    for i in range(2):
+        h = ln(x, f"layers.{i}.ln")
+        q = lin(h, w[f"layers.{i}.attn.q_proj.weight"]).view(T, P_HEADS, P_HEAD)
+        k = lin(h, w[f"layers.{i}.attn.k_proj.weight"]).view(T, P_KV, P_HEAD)
+        v = lin(h, w[f"layers.{i}.attn.v_proj.weight"]).view(T, P_KV, P_HEAD)
+        q, k = plain_model.apply_rope(q, k, cos, sin)
+        x = x + lin(plain_model.causal_attention(q, k, v), w[f"layers.{i}.attn.o_proj.weight"]) + plain_model.swiglu_mlp(w, f"layers.{i}.mlp", h)
+    return lin(ln(x, "final_ln"), w["head.weight"])
+
+
+def check_parallel(config, device):
+    model, _ = build_model(config, dtype="float32", device=device)
+    weights = random_tensors(model.tensor_specs(), seed=15, device="cpu")
+    for name in list(weights):
+        if name.endswith(".bias"):  # biases that matter
+            weights[name] = torch.randn(weights[name].shape, generator=torch.Generator().manual_seed(len(name))) * 0.3
+    model.load({name: tensor.to(device) for name, tensor in weights.items()})
+    assert not any("unused" in spec.name for spec in model.tensor_specs())  # the block builds what it uses
+    layout = CacheLayout.from_slot_specs(model.cache_slot_specs())
+    cache = CacheManager(layout, num_pages=24, page_size=8, max_requests=4)
+    storage = CacheStorage(layout, num_pages=24, page_size=8, max_requests=4, dtype=model.dtype, device=device)
+    runner = ModelRunner(model, cache, storage, max_model_len=192, decode_mode="eager")
+    requests = traces.make_requests(P_VOCAB, [37, 20, 51, 9, 44, 30], seed=10)
+    expected = {name: plain_parallel_logits(weights, tokens).numpy() for name, tokens in requests.items()}
+    for steps in (traces.trace_whole(requests), traces.trace_chunks(requests), traces.trace_mixed(requests, seed=5)):
+        result = traces.run_in_process(runner, steps)
+        worst = max(float(np.abs(row - expected[n][p]).max()) for (n, p), row in result.items())
+        assert worst < 3e-5, worst
+
+
+def test_parallel_toy_architecture_on_cpu(parallel, monkeypatch):
+    torch_kernels.install(monkeypatch)
+    check_parallel(parallel, "cpu")
+
+
+@pytest.mark.gpu
+def test_parallel_toy_architecture_on_gpu(parallel):
+    check_parallel(parallel, "cuda")
