@@ -290,6 +290,28 @@ def time_prefill(engine, iterations: int = 5, warmup: int = 3):
     return statistics.median(times)
 
 
+def time_short_prefill(engine, tokens: int = 128, iterations: int = 5, warmup: int = 4) -> float:
+    """Wall-clock milliseconds from a short prompt's step call to its logits on the device (what a first
+    token waits for): below a few hundred tokens the step is a replayed graph once its shape has come
+    three times, which the warm-up steps see to."""
+    import torch
+
+    from kairyu_b200.engine.runner import StepEntry
+
+    runner, cache = engine.runner, engine.cache
+    prompt = random_tokens(tokens, MODEL["vocab_size"], 11)
+    times = []
+    for index in range(warmup + iterations):
+        torch.cuda.synchronize()
+        begin = time.perf_counter()
+        runner.step([StepEntry("short", prompt, (tokens - 1,))])
+        torch.cuda.synchronize()
+        if index >= warmup:
+            times.append((time.perf_counter() - begin) * 1e3)
+        cache.release("short")
+    return statistics.median(times)
+
+
 def prefill_flops(config: dict, tokens: int) -> float:
     hidden, inter = config["hidden_size"], config["intermediate_size"]
     heads, kv_heads, dim = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
@@ -660,6 +682,7 @@ def main() -> int:
             if batch in (1, 64):
                 points[key] = batch * steps / (ms / 1e3)
             roofline_points[key] = roofline_point(batch, ms / steps, held)
+        points["prefill_128_tokens_ms"] = time_short_prefill(engine)
         kernel_block = time_kernels(engine, config, args.batch, peaks)
         rate, h2d, d2h = time_e2e(engine, args.batch, min(args.steps, 64))
         e2e = {"value": rate, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}

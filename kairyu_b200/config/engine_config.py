@@ -45,6 +45,8 @@ class EngineConfig:
     gpu_memory_utilization: float = 0.9
     decode_mode: str | None = None  # None -> "cuda_graph" on CUDA, "eager" elsewhere
     cuda_graph_max_batch: int | None = None
+    # capture steps that hold prompt portions once their shape has come twice (None: where decode graphs are on)
+    portion_graphs: bool | None = None
     # Steps that may be launched before the oldest one's tokens are read (the reference's option
     # of this name, default 1 there too): 2 plans and launches step N+1 while step N runs.
     pipeline_depth: int = 1

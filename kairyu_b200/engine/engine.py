@@ -114,6 +114,7 @@ class Engine:
             max_model_len=self.max_model_len,
             decode_mode=decode_mode,
             max_graph_batch=config.cuda_graph_max_batch or min(config.max_num_seqs, 256),
+            portion_graphs=config.portion_graphs,
         )
         self.scheduler = Scheduler(
             self.cache,

@@ -14,6 +14,7 @@ kairyu/engine/core/step_executor.py:591-934 does with its buckets.
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Any, Hashable, Optional, Sequence
 
@@ -42,6 +43,11 @@ class StepEntry:
 
 class StepError(RuntimeError):
     pass
+
+
+PORTION_PAD = 16           # a captured step's tokens are padded to a multiple of this (of the page size, if that is smaller)
+MAX_PORTION_GRAPHS = 64    # captured shapes of steps kept; the least recently used goes first
+PORTION_CAPTURE_AT = 3     # a shape of step is captured when it comes for this many-th time (a capture costs a dozen replays' gain)
 
 
 def context_bucket(max_seq_len: int) -> int:
@@ -97,6 +103,8 @@ class ModelRunner:
         max_graph_batch: int = 256,
         debug_poison: bool = False,
         check_tables: bool = False,
+        portion_graphs: Optional[bool] = None,
+        portion_graph_max_tokens: int = 256,
     ) -> None:
         self.model = model
         self.cache = cache
@@ -134,9 +142,25 @@ class ModelRunner:
         self._graphs: dict[tuple[int, int], _Graph] = {}
         self._graph_pool = None
         self._buckets = decode_buckets(max_graph_batch)
+        # Steps that hold prompt portions of up to a few hundred tokens are captured too, once the same shape
+        # of step has come for the third time: such a step's launches take the host longer (4 ms for 32
+        # layers) than the device takes to run them, while a larger step keeps the device busy for longer
+        # than the host needs, and a capture (the step once more, and a wait for the device) would only cost.  What a captured step takes from
+        # the host is its shape alone: tokens (padded to a multiple of 16 with a filler row on the reserved
+        # page), rows, tiles, single-token rows, wanted places, context bucket; everything else is in the
+        # device-side description, which is copied before every replay.
+        safe = getattr(model, "graph_safe", None)
+        capable = self._is_cuda and decode_mode == "cuda_graph" and bool(safe and safe())
+        self._portion_pad = min(PORTION_PAD, cache.page_size)  # the filler row lies on the one reserved page
+        self.portion_graphs = capable if portion_graphs is None else (bool(portion_graphs) and capable)
+        self.portion_graph_max_tokens = portion_graph_max_tokens
+        self.portion_workspace = Workspace(self.device)
+        self._portion_graphs: "OrderedDict[tuple, _Graph]" = OrderedDict()
+        self._portion_seen: dict[tuple, int] = {}
         self.counters = {
             "steps": 0, "graph_replays": 0, "graph_captures": 0, "eager_steps": 0, "tokens": 0, "kernel_launches": 0,
             "future_tokens": 0,  # tokens taken from the device because the host had not seen them yet
+            "portion_graph_captures": 0, "portion_graph_replays": 0,
         }
 
     # ------------------------------------------------------------------ host-side packing
@@ -211,6 +235,7 @@ class ModelRunner:
         pad_rows: Optional[int] = None,
         max_pages: Optional[int] = None,
         include_want: bool = True,
+        pad_portion: int = 0,
     ) -> tuple[torch.Tensor, dict[str, tuple[int, int]], dict[str, Any]]:
         """One int32 host tensor holding every index array of the step, the
         (offset, length) of each array, and host-side facts."""
@@ -218,9 +243,11 @@ class ModelRunner:
         groups = self.cache.layout.groups
         num_rows = len(rows)
         padded_rows = pad_rows if pad_rows is not None else num_rows
+        if pad_portion:  # one more row of that many tokens at positions 0.. of the reserved page (a captured step's filler)
+            padded_rows += 1
         # The per-token arrays are filled as numpy slices (a 2,048-token portion is four slice
         # assignments, not 8,192 list items); the per-row and per-tile arrays are short lists.
-        num_tokens = sum(len(entry.tokens) for entry, _, _ in rows) + (padded_rows - num_rows)
+        num_tokens = sum(len(entry.tokens) for entry, _, _ in rows) + (padded_rows - num_rows) + max(pad_portion - 1, 0)
         token_ids = np.zeros(num_tokens, dtype=np.int32)
         future_src = np.full(num_tokens, -1, dtype=np.int32)
         positions = np.zeros(num_tokens, dtype=np.int32)
@@ -261,14 +288,22 @@ class ModelRunner:
                     tile_starts[size].extend(starts)
             base += count
         for row in range(num_rows, padded_rows):  # padding rows of a replayed graph: token 0 at position 0
-            row_ids[base] = row
-            qo_indptr.append(base + 1)
-            seq_lens.append(1)
+            count = pad_portion if pad_portion and row == padded_rows - 1 else 1
+            row_ids[base : base + count] = row
+            positions[base : base + count] = np.arange(count, dtype=np.int32)
+            qo_indptr.append(base + count)
+            seq_lens.append(count)
             write_from.append(0)
             state_slots.append(self.cache.scratch_state_slot)
-            decode_rows.append(row)
-            decode_tokens.append(base)
-            base += 1
+            if count == 1:
+                decode_rows.append(row)
+                decode_tokens.append(base)
+            else:
+                for size in self._tile_sizes:
+                    starts = range(0, count, size)
+                    tile_rows[size].extend([row] * len(starts))
+                    tile_starts[size].extend(starts)
+            base += count
         needed_pages = max((-(-seq_len // page_size) for _, _, seq_len in rows), default=1)
         table_width = max_pages if max_pages is not None else needed_pages
         tables = np.full((len(groups), padded_rows, table_width), -1, dtype=np.int32)
@@ -386,6 +421,8 @@ class ModelRunner:
             and len(rows) <= self.max_graph_batch
         ):
             logits = self._graph_step(rows, sampled)
+        elif self.portion_graphs and sum(len(entry.tokens) for entry, _, _ in rows) <= self.portion_graph_max_tokens:
+            logits = self._portion_step(rows, sampled)
         else:
             logits = self._eager_step(rows, sampled)
         for entry, _, seq_len in rows:
@@ -399,8 +436,19 @@ class ModelRunner:
         source_at, _ = layout["future_src"]
         kernels.patch_tokens(meta[offset : offset + length], meta[source_at : source_at + length], sampled, self.error_flag)
 
-    def _eager_step(self, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-        host, layout, facts = self._pack(rows)
+    def _eager_step(self, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor] = None,
+                    as_captured: Optional[tuple[int, int, int]] = None) -> Optional[torch.Tensor]:
+        """``as_captured`` = (filler tokens, context bucket, table width): launch the step exactly as a graph
+        of its shape would run it (same filler row, same bounds), so that the first time a shape comes and
+        every later time give the same bits."""
+        if as_captured is None:
+            host, layout, facts = self._pack(rows)
+        else:
+            pad, bucket, width = as_captured
+            host, layout, facts = self._pack(rows, pad_portion=pad, max_pages=width)
+            facts["max_seq_len"] = bucket
+            if facts["max_portion_seq_len"]:
+                facts["max_portion_seq_len"] = bucket
         meta = self.workspace.flat("meta", host.numel(), torch.int32)
         meta.copy_(host, non_blocking=True)
         self._patch_tokens(meta, layout, sampled)
@@ -409,6 +457,91 @@ class ModelRunner:
         before = kernels.launch_count
         logits = self.model.forward(ctx, self._views, want)
         self.counters["kernel_launches"] += kernels.launch_count - before
+        return logits
+
+    # ------------------------------------------------------------------ captured steps of prompt portions
+    def _portion_shape(self, rows: Sequence[tuple[StepEntry, int, int]]) -> tuple[tuple, int, int, int]:
+        """(what a captured step takes from the host, filler tokens, context bucket, table width)."""
+        counts = [len(entry.tokens) for entry, _, _ in rows]
+        tokens = sum(counts)
+        pad = -tokens % self._portion_pad
+        if pad:
+            counts.append(pad)
+        tiles = tuple(sum(-(-count // size) for count in counts if count > 1) for size in self._tile_sizes)
+        singles = sum(1 for count in counts if count == 1)
+        wanted = sum(len(entry.want) for entry, _, _ in rows)
+        bucket = min(context_bucket(max(seq_len for _, _, seq_len in rows)), max(self.max_model_len, 256))
+        width = min(self._needed_pages(bucket), self.max_pages_per_request)
+        return (tokens + pad, len(counts), tiles, singles, wanted, bucket), pad, bucket, width
+
+    def _portion_step(self, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        shape, pad, bucket, width = self._portion_shape(rows)
+        held = self._portion_graphs.get(shape)
+        if held is not None and held.generation != self.portion_workspace.generation:
+            del self._portion_graphs[shape]  # the workspace has grown since: its buffers are not the ones the graph reads
+            held = None
+        if held is None:
+            seen = self._portion_seen.get(shape, 0) + 1
+            if len(self._portion_seen) > 4096:
+                self._portion_seen.clear()
+            self._portion_seen[shape] = seen
+            if seen < PORTION_CAPTURE_AT:
+                return self._eager_step(rows, sampled, as_captured=(pad, bucket, width))
+            return self._capture_portion(shape, rows, sampled, pad, bucket, width)
+        self._portion_graphs.move_to_end(shape)
+        host, layout, _ = self._pack(rows, pad_portion=pad, max_pages=width)
+        if layout != held.layout:
+            raise StepError("a captured step's description is laid out differently from the one it was captured with")
+        held.meta.copy_(host, non_blocking=True)
+        self._patch_tokens(held.meta, held.layout, sampled)
+        held.graph.replay()
+        self.counters["portion_graph_replays"] += 1
+        self.counters["kernel_launches"] += held.launches
+        return held.logits
+
+    def _capture_portion(self, shape: tuple, rows: Sequence[tuple[StepEntry, int, int]], sampled: Optional[torch.Tensor],
+                         pad: int, bucket: int, width: int) -> Optional[torch.Tensor]:
+        """Run the step once with the buffers a graph of it will use (that run is the step), then capture it."""
+        host, layout, facts = self._pack(rows, pad_portion=pad, max_pages=width)
+        facts["max_seq_len"] = bucket
+        if facts["max_portion_seq_len"]:
+            facts["max_portion_seq_len"] = bucket
+        workspace = self.portion_workspace
+        meta = torch.zeros(host.numel(), dtype=torch.int32, device=self.device)
+        meta.copy_(host, non_blocking=True)
+        self._patch_tokens(meta, layout, sampled)
+        ctx, want = self._context(meta, layout, facts, workspace)
+
+        def run() -> Optional[torch.Tensor]:
+            return self.model.forward(ctx, self._views, want)
+
+        before = kernels.launch_count
+        logits = run()
+        launches = kernels.launch_count - before
+        self.counters["eager_steps"] += 1
+        self.counters["kernel_launches"] += launches
+        generation = workspace.generation
+        torch.cuda.current_stream().synchronize()
+        workspace.freeze(True)
+        try:
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                captured = run()
+        finally:
+            workspace.freeze(False)
+        if generation != workspace.generation:
+            raise StepError("the workspace of captured steps changed during capture")
+        if (logits is None) != (captured is None) or (logits is not None and captured.data_ptr() != logits.data_ptr()):
+            raise StepError("a captured step does not leave its logits where the step before it did")
+        # graphs captured against buffers that have been replaced since are of no use
+        for key in [k for k, g in self._portion_graphs.items() if g.generation != generation]:
+            del self._portion_graphs[key]
+        while len(self._portion_graphs) >= MAX_PORTION_GRAPHS:
+            self._portion_graphs.popitem(last=False)
+        self._portion_graphs[shape] = _Graph(graph, meta, logits, generation, dict(layout), launches=launches, keepalive=(ctx, want))
+        self.counters["portion_graph_captures"] += 1
         return logits
 
     # ------------------------------------------------------------------ graphs

@@ -10,6 +10,9 @@ class Workspace:
     def __init__(self, device: str) -> None:
         self.device = device
         self._buffers: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
+        # the views handed out, by (buffer, rows): a step asks for the same few hundred views every time, and
+        # slicing a tensor costs as much host time as a third of a kernel launch
+        self._views: dict[tuple, torch.Tensor] = {}
         self._frozen = False
         self.generation = 0  # bumps whenever a buffer is (re)allocated
 
@@ -17,6 +20,9 @@ class Workspace:
         """A ``[rows, cols]`` view of the buffer named ``tag``; grows (by
         reallocation) when more rows are asked for than ever before."""
         key = (tag, cols, dtype)
+        view = self._views.get((key, rows))
+        if view is not None:
+            return view
         held = self._buffers.get(key)
         if held is None or held.shape[0] < rows:
             if self._frozen:
@@ -28,12 +34,16 @@ class Workspace:
                 capacity = max(capacity, 2 * held.shape[0])
             held = torch.empty((capacity, cols), dtype=dtype, device=self.device)
             self._buffers[key] = held
+            self._drop_views(key)
             self.generation += 1
-        return held[:rows]
+        return self._remember((key, rows), held[:rows])
 
     def flat(self, tag: str, count: int, dtype: torch.dtype) -> torch.Tensor:
         """A 1-D buffer of ``count`` elements named ``tag``."""
         key = (tag, -1, dtype)
+        view = self._views.get((key, count))
+        if view is not None:
+            return view
         held = self._buffers.get(key)
         if held is None or held.numel() < count:
             if self._frozen:
@@ -43,8 +53,20 @@ class Workspace:
                 capacity = max(capacity, 2 * held.numel())
             held = torch.empty((capacity,), dtype=dtype, device=self.device)
             self._buffers[key] = held
+            self._drop_views(key)
             self.generation += 1
-        return held[:count]
+        return self._remember((key, count), held[:count])
+
+    def _remember(self, key: tuple, view: torch.Tensor) -> torch.Tensor:
+        if len(self._views) >= 4096:  # many sizes over a long run: start over rather than grow without end
+            self._views.clear()
+        self._views[key] = view
+        return view
+
+    def _drop_views(self, key: tuple) -> None:
+        """Views of a buffer that has just been replaced point at the old memory."""
+        for stale in [k for k in self._views if k[0] == key]:
+            del self._views[stale]
 
     def freeze(self, frozen: bool = True) -> None:
         self._frozen = frozen

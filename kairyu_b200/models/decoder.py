@@ -62,6 +62,16 @@ class DecoderModel:
                 )
 
     # -- weights
+    def graph_safe(self) -> bool:
+        """Whether a step of prompt portions can be captured in a CUDA graph: every part says so of itself,
+        and a block also of the parts it built."""
+        def safe(part: Any) -> bool:
+            if not getattr(part, "graph_safe", False):
+                return False
+            return all(safe(inner) for inner in getattr(part, "_parts", ()))
+
+        return all(safe(part) for part in self.parts())
+
     def parts(self) -> list[Any]:
         extra = [self.embedding_position] if self.embedding_position is not None else []
         return [self.embedding, *extra, *self.blocks, self.final_norm, self.head]

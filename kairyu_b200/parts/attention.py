@@ -147,6 +147,8 @@ def run_paged_attention(
 
 @MIXERS.register("gqa_attention")
 class GQAAttention(Mixer):
+    graph_safe = True
+
     def __init__(
         self,
         *,

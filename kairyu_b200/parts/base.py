@@ -195,6 +195,12 @@ class StepContext:
 class Part:
     """Anything with weights.  ``prefix`` is the tensor-name prefix it binds under."""
 
+    # Whether the part's work for a step of prompt portions can be captured in a CUDA graph: every
+    # launch takes what changes from step to step (tokens, positions, rows, lengths, pages) from the
+    # step's device-side description, nothing from the host.  A part that loops over rows on the host
+    # or reads a tensor back leaves this False, and steps of its model are launched one by one.
+    graph_safe: bool = False
+
     def tensor_specs(self) -> list[TensorSpec]:
         return []
 

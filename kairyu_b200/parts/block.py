@@ -35,6 +35,8 @@ class PreNormBlock(Block):
     mixer and feed-forward that offer ``fusable_norm``; any other part gets the plain flow.
     """
 
+    graph_safe = True
+
     takes_next_norm = True  # forward accepts the norm of the block that runs next
 
     def __init__(self, *, layer: LayerSpec, dtype: torch.dtype, device: str, shared: dict, **_: object) -> None:

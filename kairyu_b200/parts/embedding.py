@@ -14,6 +14,8 @@ from kairyu_b200.parts.base import EMBEDDINGS, HEADS, Part, StepContext, TensorS
 class TokenEmbedding(Part):
     """``x = E[token_ids]``, no scaling; the residual it starts is fp32."""
 
+    graph_safe = True
+
     def __init__(self, *, name: str, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: str, **_: object) -> None:
         self.name = name
         self.vocab_size = vocab_size
@@ -36,6 +38,8 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     """``logits = h @ W^T`` in fp32 output; ``tied_to`` names the embedding
     tensor to share when the file has no head tensor of its own."""
+
+    graph_safe = True
 
     def __init__(
         self,

@@ -14,6 +14,8 @@ from kairyu_b200.parts.base import FEED_FORWARDS, FeedForward, StepContext, Tens
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(
         self,
         *,

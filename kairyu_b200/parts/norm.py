@@ -14,6 +14,8 @@ from kairyu_b200.parts.base import NORMS, Norm, StepContext, TensorSpec
 class RMSNorm(Norm):
     """``y = x * rsqrt(mean(x^2) + eps) * weight`` with fp32 statistics."""
 
+    graph_safe = True
+
     def __init__(self, *, name: str, size: int, eps: float, dtype: torch.dtype, device: str, **_: object) -> None:
         self.name = name  # full tensor name of the weight
         self.size = size

@@ -83,6 +83,8 @@ def rotary_tables(
 
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(
         self,
         *,

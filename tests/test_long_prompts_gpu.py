@@ -120,3 +120,77 @@ def test_long_prompts_cut_at_random(model, seed):
     assert error < bound, (error, bound, parity.rows_beyond(result, truth, bound))
     whole = traces.run_in_process(make_runner(model["model"], sum(lengths) // PAGE + 8), parity.thin_wants(traces.trace_whole(requests), keep))
     assert parity.worst_error(whole, truth) < bound
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_of_portions_are_captured_and_replayed(dtype):
+    """The same shapes of step come again and again (portions of 48 and 100 tokens, with and without
+    decoded tokens beside them): the third time a shape comes it is captured, from then on replayed.  Every
+    logits row equals, bit for bit, what a runner that launches every step kernel by kernel gives
+    in 32-bit (the kernels are the same, and a captured step's filler row touches no request), and
+    stays within the bfloat16 bound of the plain model."""
+    from golden_inputs import golden_weights_on
+    from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+    from kairyu_b200.engine.engine import random_model
+    from kairyu_b200.engine.runner import ModelRunner
+
+    built, _ = random_model(CONFIG, SEED, dtype=dtype, device="cuda")
+    weights = golden_weights_on(CONFIG, SEED, "cuda")
+    requests = traces.make_requests(CONFIG["vocab_size"], [400, 333, 290, 410, 377, 305], seed=900)
+    steps = []
+    names = list(requests)
+    live: dict[str, int] = {}
+    for index, name in enumerate(names):
+        tokens = requests[name]
+        start = 0
+        while start < len(tokens) - 4:
+            size = min(48 if (start // 48) % 2 == 0 else 100, len(tokens) - 4 - start)
+            entries = [{"id": name, "tokens": tokens[start : start + size], "want": [size - 1]}]
+            ended = []
+            for other, place in list(live.items()):
+                entries.append({"id": other, "tokens": [requests[other][place]], "want": [0]})
+                live[other] = place + 1
+                if place + 1 == len(requests[other]):
+                    ended.append(other)
+                    del live[other]
+            steps.append({"step": len(steps), "entries": entries, "end": ended})
+            start += size
+        live[name] = len(tokens) - 4
+    while live:
+        entries, ended = [], []
+        for other, place in list(live.items()):
+            entries.append({"id": other, "tokens": [requests[other][place]], "want": [0]})
+            live[other] = place + 1
+            if place + 1 == len(requests[other]):
+                ended.append(other)
+                del live[other]
+        steps.append({"step": len(steps), "entries": entries, "end": ended})
+
+    def runner_with(portion_graphs):
+        layout = CacheLayout.from_slot_specs(built.cache_slot_specs())
+        cache = CacheManager(layout, num_pages=160, page_size=PAGE, max_requests=8)
+        storage = CacheStorage(layout, num_pages=160, page_size=PAGE, max_requests=8, dtype=built.dtype, device="cuda")
+        return ModelRunner(built, cache, storage, max_model_len=1024, decode_mode="cuda_graph", max_graph_batch=8,
+                           check_tables=True, debug_poison=True, portion_graphs=portion_graphs)
+
+    captured = runner_with(True)
+    assert captured.portion_graphs
+    result = traces.run_in_process(captured, steps)
+    captured.check_errors()
+    assert captured.counters["portion_graph_captures"] >= 2 and captured.counters["portion_graph_replays"] >= 4
+    plain_runner = runner_with(False)
+    assert not plain_runner.portion_graphs
+    launched = traces.run_in_process(plain_runner, steps)
+    assert plain_runner.counters["portion_graph_captures"] == 0
+    if dtype == "float32":
+        parity.assert_same_bits(result, launched, "captured against launched")
+    held = {k: v.float() for k, v in parity.in_bf16(weights, False).items()} if dtype == "bfloat16" else weights
+    truth = parity.plain_rows(CONFIG, held, requests)
+    truth = {key: row for key, row in truth.items() if key in result}
+    bound = 2e-5 if dtype == "float32" else BF16_FACTOR * parity.worst_error(
+        {k: v for k, v in parity.plain_rows(CONFIG, parity.in_bf16(weights, False), requests).items() if k in result}, truth)
+    for rows in (result, launched):
+        assert rows.keys() == truth.keys()
+        assert parity.worst_error(rows, truth) < bound, (parity.worst_error(rows, truth), bound)
+    # the same steps again on the runner that has its graphs: the same bits
+    parity.assert_same_bits(result, traces.run_in_process(captured, steps), "a second pass over the captured steps")
