@@ -163,6 +163,7 @@ def build(toy, device, decode_mode="eager"):
     cache = CacheManager(layout, num_pages=24, page_size=8, max_requests=4)
     storage = CacheStorage(layout, num_pages=24, page_size=8, max_requests=4, dtype=model.dtype, device=device)
     runner = ModelRunner(model, cache, storage, max_model_len=256, decode_mode=decode_mode, max_graph_batch=4)
+    assert not runner.portion_graphs  # the toy mixer loops over rows on the host: its portions are launched one by one
     return runner, weights
 
 
