@@ -129,23 +129,31 @@ struct Vec4<__nv_bfloat16> {
     }
 };
 
+// The sum of a row's squares is added in one order whatever the block's size: chunk by chunk (four
+// elements each), then group g = 0..G-1 adds the partial sums of chunks g, g + G, g + 2G, g + 3G in that
+// order (G = `groups`: the thread count of the block that holds every chunk a thread may), then the groups'
+// sums go through block_sum as the values of threads 0..G-1.  A block of G threads has all of a group's
+// chunks in one thread; a larger block (a few rows: every load in flight at once) passes the chunks' sums
+// through shared memory.  Either way a row's result depends on its width alone.
 template <typename TX, typename TA, typename TW>
 __global__ void rmsnorm_vec_kernel(TX* __restrict__ x, const TA* __restrict__ delta,
                                    const TW* __restrict__ w, TA* __restrict__ out,
-                                   const int* __restrict__ rows, int H, float eps, int write_back) {
+                                   const int* __restrict__ rows, int H, float eps, int write_back, int groups) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[32];
+    __shared__ float chunk_sums[NORM_MAX_CHUNKS * 1024];
     const int r = blockIdx.x;
     const int s = rows ? rows[r] : r;
     TX* xr = x + (size_t)s * H;
     const TA* dr = delta ? delta + (size_t)s * H : nullptr;
     const int chunks = H >> 2;
     float v[NORM_MAX_CHUNKS][4];
-    float ss = 0.0f;
+    float part[NORM_MAX_CHUNKS];
 #pragma unroll
     for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
         const int chunk = threadIdx.x + c * blockDim.x;
+        part[c] = 0.0f;
         if (chunk < chunks) {
             Vec4<TX>::load(xr + 4 * chunk, v[c]);
             if (dr) {
@@ -155,8 +163,26 @@ __global__ void rmsnorm_vec_kernel(TX* __restrict__ x, const TA* __restrict__ de
                 for (int e = 0; e < 4; ++e) v[c][e] += d[e];
                 if (write_back) Vec4<TX>::store(xr + 4 * chunk, v[c]);
             }
+            part[c] = ((v[c][0] * v[c][0] + v[c][1] * v[c][1]) + v[c][2] * v[c][2]) + v[c][3] * v[c][3];
+        }
+    }
+    float ss = 0.0f;
+    if ((int)blockDim.x == groups) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) ss += v[c][e] * v[c][e];
+        for (int c = 0; c < NORM_MAX_CHUNKS; ++c) ss += part[c];  // chunks t, t + G, t + 2G, t + 3G: this thread's own
+    } else {
+#pragma unroll
+        for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+            const int chunk = threadIdx.x + c * blockDim.x;
+            if (chunk < NORM_MAX_CHUNKS * 1024) chunk_sums[chunk] = part[c];
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < groups) {
+#pragma unroll
+            for (int c = 0; c < NORM_MAX_CHUNKS; ++c) {
+                const int chunk = threadIdx.x + c * groups;
+                ss += chunk < chunks ? chunk_sums[chunk] : 0.0f;
+            }
         }
     }
     const float total = block_sum(ss, scratch);
@@ -182,19 +208,25 @@ static int rmsnorm_dispatch_w(void* x, const void* delta, const void* w, int w_b
     const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
                          (delta == nullptr || (uintptr_t)delta % 16 == 0);
     if (H % 4 == 0 && H <= 16 * 1024 && aligned) {
-        // Every chunk a thread may hold, whatever the number of rows (the order of a row's sum then depends
-        // on its width alone): for a prompt portion an SM has eight small blocks in different phases (loads,
-        // the sum, stores) instead of two large ones in step (2,048 rows of 4,096: 21.5 -> 18.1 us; 8,192
-        // rows: 75 -> 63 us), and a few rows take the same 3.5 us either way.
-        int threads_v = ((H / 4 + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS + 31) / 32 * 32;
-        if (threads_v < 128) threads_v = 128;
-        if (threads_v > 1024) threads_v = 1024;
+        // Many rows (a prompt portion): blocks that hold every chunk a thread may, so that an SM has eight
+        // small blocks in different phases (loads, the sum, stores) instead of two large ones in step (2,048
+        // rows of 4,096: 21.5 -> 18.1 us; 8,192 rows: 75 -> 63 us).  A few rows (decode): a chunk a thread,
+        // every load in flight at once (in a decode step of 16 rows the small blocks cost 2 us a norm).
+        int groups = ((H / 4 + NORM_MAX_CHUNKS - 1) / NORM_MAX_CHUNKS + 31) / 32 * 32;
+        if (groups < 128) groups = 128;
+        if (groups > 1024) groups = 1024;
+        int threads_v = groups;
+        if (R < 256) {
+            threads_v = ((H / 4 + 31) / 32) * 32;
+            if (threads_v > 1024) threads_v = 1024;
+            if (threads_v < groups) threads_v = groups;
+        }
         if (w_bf16)
             kb_launch(rmsnorm_vec_kernel<TX, TA, __nv_bfloat16>, dim3(R), dim3(threads_v), 0, stream, 
-                (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back);
+                (TX*)x, (const TA*)delta, (const __nv_bfloat16*)w, (TA*)out, rows, H, eps, write_back, groups);
         else
             kb_launch(rmsnorm_vec_kernel<TX, TA, float>, dim3(R), dim3(threads_v), 0, stream, 
-                (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back);
+                (TX*)x, (const TA*)delta, (const float*)w, (TA*)out, rows, H, eps, write_back, groups);
         return kb_launch_result();
     }
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);

@@ -84,6 +84,22 @@ def test_rmsnorm_with_residual_sum(act, wdtype, H, T, eps):
     close(out2, out_ref, 2e-6 if act == torch.float32 else 0.0, rtol=0.0 if act == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("H", [96, 4096, 5120, 8192, 16384])
+@pytest.mark.parametrize("act", [torch.float32, torch.bfloat16])
+def test_rmsnorm_rows_do_not_depend_on_how_many_there_are(H, act):
+    """A few rows take larger blocks than many rows do; the sum of a row's squares is added in one order
+    either way, so a row normed among 300 has the bits it has among 5."""
+    x = rand(300, H, seed=8, scale=3.0)
+    delta = rand(300, H, dtype=act, seed=9)
+    w = (1 + 0.1 * rand(H, seed=10)).to(DEV)
+    many_x, few_x = x.to(DEV), x[:5].to(DEV)
+    many = torch.empty(300, H, dtype=act, device=DEV)
+    few = torch.empty(5, H, dtype=act, device=DEV)
+    kernels().rmsnorm(many_x, w, 1e-5, many, delta=delta.to(DEV))
+    kernels().rmsnorm(few_x, w, 1e-5, few, delta=delta[:5].to(DEV))
+    assert torch.equal(many[:5], few) and torch.equal(many_x[:5], few_x)
+
+
 def test_rmsnorm_rows_leave_the_residual_alone():
     T, H = 12, 200
     x = rand(T, H, seed=4)
