@@ -198,6 +198,35 @@ def run_reference(args: Any, model: Mapping[str, Any], workload: Mapping[str, An
             except Exception as error:
                 points["error"] = f"{type(error).__name__}: {str(error)[:160]}"
             line["points"] = points
+        if getattr(args, "mixed", False):
+            # The mixed workload of bench.py's own arm: 32 requests, prompt lengths uniform in [128, 4096] from
+            # the same seeded draw, a token budget of 512 + 32 so that prompts are cut into portions that share
+            # steps with the decodes of the others, 128 generated tokens each.  The warm-up prompts are others
+            # than the timed ones: the reference keeps the pages of prompts it has seen.
+            del llm, backend
+            torch.cuda.empty_cache()
+            generator = torch.Generator().manual_seed(int(workload["seed"]))
+            lengths = torch.randint(128, 4097, (32,), generator=generator).tolist()
+            mixed = KairyuBackend(
+                model_path=scratch, num_pages=sum(-(-(n + 128 + 16) // page_size) for n in lengths) + 1, page_size=page_size,
+                max_num_batched_tokens=512 + 32, max_num_seqs=32, max_model_len=workload["context_len"], max_num_partial_prefills=1,
+                pipeline_depth=2, decode_mode="cuda_graph",
+            )
+            llm = LLM(model=scratch, backend=mixed)
+            prompts = [TokensPrompt(prompt_token_ids=_random_tokens(n, vocab, 300 + i)) for i, n in enumerate(lengths)]
+            warm = [TokensPrompt(prompt_token_ids=_random_tokens(600, vocab, 350 + i)) for i in range(4)]
+            llm.generate(warm, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            outputs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=128, ignore_eos=True))
+            torch.cuda.synchronize()
+            seconds = time.perf_counter() - begin
+            generated = sum(len(output.outputs[0].token_ids) for output in outputs)
+            line.setdefault("points", {}).update({
+                "mixed_b32_total_tok_s": (sum(lengths) + generated) / seconds,
+                "mixed_b32_generated_tok_s": generated / seconds,
+                "mixed_b32_seconds": seconds,
+            })
         return line
     finally:
         shutil.rmtree(scratch, ignore_errors=True)
