@@ -47,6 +47,7 @@ class StepError(RuntimeError):
 
 PORTION_PAD = 16           # a captured step's tokens are padded to a multiple of this (of the page size, if that is smaller)
 MAX_PORTION_GRAPHS = 64    # captured shapes of steps kept; the least recently used goes first
+PORTION_EVICT_AFTER = 256  # a kept shape gives way to a new one only if it has not come for this many steps
 PORTION_CAPTURE_AT = 3     # a shape of step is captured when it comes for this many-th time (a capture costs a dozen replays' gain)
 
 
@@ -89,6 +90,7 @@ class _Graph:
     row_state: list = field(default_factory=list)
     staging: list = field(default_factory=list)
     next_staging: int = 0
+    last_used: int = 0  # the step that last replayed it (captured steps of prompt portions)
 
 
 class ModelRunner:
@@ -154,7 +156,7 @@ class ModelRunner:
         self._portion_pad = min(PORTION_PAD, cache.page_size)  # the filler row lies on the one reserved page
         self.portion_graphs = capable if portion_graphs is None else (bool(portion_graphs) and capable)
         self.portion_graph_max_tokens = portion_graph_max_tokens
-        self.portion_workspace = Workspace(self.device)
+        self.portion_workspace = Workspace(self.device, min_rows=portion_graph_max_tokens + PORTION_PAD)
         self._portion_graphs: "OrderedDict[tuple, _Graph]" = OrderedDict()
         self._portion_seen: dict[tuple, int] = {}
         self.counters = {
@@ -485,10 +487,15 @@ class ModelRunner:
             if len(self._portion_seen) > 4096:
                 self._portion_seen.clear()
             self._portion_seen[shape] = seen
-            if seen < PORTION_CAPTURE_AT:
+            full = len(self._portion_graphs) >= MAX_PORTION_GRAPHS
+            if full:  # the least recently used shape goes only if it has not come for a while: shapes that take turns would evict one another for ever
+                oldest = next(iter(self._portion_graphs.values()))
+                full = self.counters["steps"] - oldest.last_used < PORTION_EVICT_AFTER
+            if seen < PORTION_CAPTURE_AT or full:
                 return self._eager_step(rows, sampled, as_captured=(pad, bucket, width))
             return self._capture_portion(shape, rows, sampled, pad, bucket, width)
         self._portion_graphs.move_to_end(shape)
+        held.last_used = self.counters["steps"]
         host, layout, _ = self._pack(rows, pad_portion=pad, max_pages=width)
         if layout != held.layout:
             raise StepError("a captured step's description is laid out differently from the one it was captured with")
@@ -540,7 +547,8 @@ class ModelRunner:
             del self._portion_graphs[key]
         while len(self._portion_graphs) >= MAX_PORTION_GRAPHS:
             self._portion_graphs.popitem(last=False)
-        self._portion_graphs[shape] = _Graph(graph, meta, logits, generation, dict(layout), launches=launches, keepalive=(ctx, want))
+        self._portion_graphs[shape] = _Graph(graph, meta, logits, generation, dict(layout), launches=launches, keepalive=(ctx, want),
+                                             last_used=self.counters["steps"])
         self.counters["portion_graph_captures"] += 1
         return logits
 

@@ -7,8 +7,11 @@ import torch
 
 
 class Workspace:
-    def __init__(self, device: str) -> None:
+    def __init__(self, device: str, min_rows: int = 0) -> None:
+        """``min_rows``: what a row buffer holds at least from its first allocation on (a workspace whose
+        buffers captured graphs point at should not have to grow with the first larger step)."""
         self.device = device
+        self.min_rows = min_rows
         self._buffers: dict[tuple[str, int, torch.dtype], torch.Tensor] = {}
         # the views handed out, by (buffer, rows): a step asks for the same few hundred views every time, and
         # slicing a tensor costs as much host time as a third of a kernel launch
@@ -29,7 +32,7 @@ class Workspace:
                 raise RuntimeError(
                     f"workspace buffer {tag!r} would have to grow to {rows} rows while a graph is being captured"
                 )
-            capacity = max(rows, 1)
+            capacity = max(rows, 1, self.min_rows)
             if held is not None:
                 capacity = max(capacity, 2 * held.shape[0])
             held = torch.empty((capacity, cols), dtype=dtype, device=self.device)

@@ -194,3 +194,49 @@ def test_steps_of_portions_are_captured_and_replayed(dtype):
         assert parity.worst_error(rows, truth) < bound, (parity.worst_error(rows, truth), bound)
     # the same steps again on the runner that has its graphs: the same bits
     parity.assert_same_bits(result, traces.run_in_process(captured, steps), "a second pass over the captured steps")
+
+
+def test_captured_shapes_are_bounded(monkeypatch):
+    """More shapes of step than the runner keeps graphs for, taking turns: the first three stay (a kept
+    shape gives way only after it has not come for a while, or shapes that take turns would evict one
+    another for ever), the others are launched kernel by kernel; once the kept ones have gone unused for
+    long enough, new shapes take their places.  Every step gives the bits of a runner that launches
+    kernel by kernel (32-bit)."""
+    import kairyu_b200.engine.runner as runner_module
+    from kairyu_b200.cache import CacheLayout, CacheManager, CacheStorage
+    from kairyu_b200.engine.engine import random_model
+    from kairyu_b200.engine.runner import ModelRunner, StepEntry
+
+    monkeypatch.setattr(runner_module, "MAX_PORTION_GRAPHS", 3)
+    monkeypatch.setattr(runner_module, "PORTION_EVICT_AFTER", 12)
+    built, _ = random_model(CONFIG, SEED, dtype="float32", device="cuda")
+
+    def runner_with(portion_graphs):
+        layout = CacheLayout.from_slot_specs(built.cache_slot_specs())
+        cache = CacheManager(layout, num_pages=64, page_size=PAGE, max_requests=4)
+        storage = CacheStorage(layout, num_pages=64, page_size=PAGE, max_requests=4, dtype=built.dtype, device="cuda")
+        return ModelRunner(built, cache, storage, max_model_len=512, decode_mode="cuda_graph", max_graph_batch=4, portion_graphs=portion_graphs)
+
+    captured, launched = runner_with(True), runner_with(False)
+    generator = torch.Generator().manual_seed(4)
+
+    def run(sizes, turns):
+        for turn in range(turns):
+            for size in sizes:
+                tokens = torch.randint(0, CONFIG["vocab_size"], (size,), generator=generator).tolist()
+                rows = []
+                for runner in (captured, launched):
+                    logits = runner.step([StepEntry("p", tokens, (size - 1,))])
+                    rows.append(logits.clone())
+                    runner.cache.release("p")
+                assert torch.equal(rows[0], rows[1]), (turn, size)
+                assert len(captured._portion_graphs) <= 3
+
+    run([16, 32, 48, 64, 80], 5)  # five shapes take turns: three are kept
+    assert captured.counters["portion_graph_captures"] == 3
+    replays = captured.counters["portion_graph_replays"]
+    assert replays >= 6
+    run([96, 112], 12)  # the kept ones go unused: the new shapes take their places
+    assert captured.counters["portion_graph_captures"] == 5
+    assert captured.counters["portion_graph_replays"] > replays
+    captured.check_errors()
