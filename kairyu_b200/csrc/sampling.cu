@@ -271,20 +271,35 @@ struct ClusterScratch {
     float vals[2][16];  // this block's partial result of the reduction in progress
     int index[2];       // (argmax) the index that goes with vals[.][0]
     int turn;           // which slot the next reduction uses (the same in every block)
+    float combined[16]; // the reduction's result, read from the other blocks by a few threads for all of this block's
+    unsigned long long hist[2][256];  // (threshold search) this block's histogram of the round in progress, two slots as vals
+    unsigned long long total[256];    // the cluster's histogram of the round
+    unsigned long long above;         // the search's running weight above the prefix
+    int digit;                        // the digit the round chose
 };
 
 // Every block calls this with its partial results in mine->vals[0..count); on return all[k] holds
-// op over the ranks, in rank order, the same in every block.  Two cluster barriers.
+// op over the ranks, in rank order, the same in every block.  One cluster barrier and one of the block
+// (the result's buffer is free again by then: the next reduction writes it behind its own cluster barrier).
 template <int COUNT, typename Op>
 __device__ __forceinline__ void cluster_combine(cg::cluster_group& cluster, ClusterScratch* mine, int slot, float (&all)[COUNT], Op op) {
     cluster.sync();  // every block's partials are in its shared memory
+    // Thread k fetches value k of every rank (in rank order) and leaves the result in this block's own
+    // shared memory; with every thread fetching every value, a block made 57,000 remote loads a round.
+    if (threadIdx.x < COUNT) {
+        float theirs[SAMPLE_CLUSTER];  // the loads go out together; the values are combined in rank order after
 #pragma unroll
-    for (int k = 0; k < COUNT; ++k) all[k] = cluster.map_shared_rank(mine, 0)->vals[slot][k];
-    for (unsigned rank = 1; rank < cluster.num_blocks(); ++rank) {
-        const ClusterScratch* theirs = cluster.map_shared_rank(mine, rank);
+        for (unsigned rank = 0; rank < SAMPLE_CLUSTER; ++rank)
+            theirs[rank] = rank < cluster.num_blocks() ? cluster.map_shared_rank(mine, rank)->vals[slot][threadIdx.x] : 0.0f;
+        float acc = theirs[0];
 #pragma unroll
-        for (int k = 0; k < COUNT; ++k) all[k] = op(all[k], theirs->vals[slot][k]);
+        for (unsigned rank = 1; rank < SAMPLE_CLUSTER; ++rank)
+            if (rank < cluster.num_blocks()) acc = op(acc, theirs[rank]);
+        mine->combined[threadIdx.x] = acc;
     }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < COUNT; ++k) all[k] = mine->combined[k];
 }
 // The slot this reduction uses; every thread of every block sees the same sequence of slots.
 __device__ __forceinline__ int next_slot(int& turn) {
@@ -324,64 +339,136 @@ __device__ __forceinline__ int cluster_argmax(cg::cluster_group& cluster, Cluste
     return best.i;
 }
 
-// Sums 16 per-thread values over the block in a fixed order, then over the cluster; result in totals[16].
-__device__ __forceinline__ void cluster_sum16(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, float (&local)[16],
-                                              float (*s_part)[16], float (&totals)[16]) {
+// Exact sum of one 64-bit integer per thread over the block and the cluster (through the histogram's bins 0..warps).
+__device__ __forceinline__ unsigned long long cluster_sum_units(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, unsigned long long v) {
     const int slot = next_slot(turn);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int d = 0; d < 16; ++d) local[d] = warp_sum(local[d]);
+    unsigned long long* bins = mine->hist[slot];
+    if (threadIdx.x == 0) bins[0] = 0;
     __syncthreads();
-    if (lane == 0) {
 #pragma unroll
-        for (int d = 0; d < 16; ++d) s_part[warp][d] = local[d];
-    }
-    __syncthreads();
-    if (threadIdx.x < 16) {
-        float total = 0.0f;
-        for (int w = 0; w < STAGE1_WARPS; ++w) total += s_part[w][threadIdx.x];
-        mine->vals[slot][threadIdx.x] = total;
-    }
-    cluster_combine(cluster, mine, slot, totals, [](float a, float b) { return a + b; });
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    if ((threadIdx.x & 31) == 0) atomicAdd(&bins[0], v);
+    cluster.sync();
+    unsigned long long sum = 0;
+    for (unsigned rank = 0; rank < cluster.num_blocks(); ++rank) sum += cluster.map_shared_rank(mine, rank)->hist[slot][0];
+    return sum;
 }
+
+// Weights of the threshold search are integers, so that no order of addition matters: a count is 1, a
+// probability is its value in units of 2^-40 (a row's sum stays far below 2^64).
+__device__ __forceinline__ unsigned long long mass_units(float pv) { return (unsigned long long)(pv * 1099511627776.0f); }  // a power of two: exact
 
 // Smallest 32-bit key u such that weight{ key_i > u, key_i >= lo_key } < target,
 // where key_i are the bits of the non-negative floats p_i and weight is a count
-// (use_sum = 0) or the sum of p_i (use_sum = 1).  Radix descent, 4 bits a round; every block
-// scans its slice [begin, end) and all of them return the same u.  Requires target > 0.
+// (use_sum = 0) or the sum of p_i in units of 2^-40 (use_sum = 1).  Radix descent, 8 bits a round (four
+// rounds): every block builds the histogram of its slice [begin, end) in shared memory (lanes with the
+// same digit add up in the warp first: most of a row shares a few exponents), thread t adds up bin t
+// of all the cluster's blocks, one thread walks the 256 bins from the top, and all blocks return the same
+// u.  Requires target > 0 and a block of at least 256 threads.
 __device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, const float* __restrict__ p, int begin,
-                                   int end, unsigned int lo_key, float target, int use_sum, float (*s_part)[16]) {
+                                   int end, unsigned int lo_key, unsigned long long target, int use_sum,
+                                   unsigned long long (*warp_hist)[256]) {
     unsigned int prefix = 0;
-    float above = 0.0f;
-    for (int shift = 28; shift >= 0; shift -= 4) {
-        float local[16];
+    if (threadIdx.x == 0) mine->above = 0;
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        const int slot = next_slot(turn);
+        // a histogram a warp: its lanes with the same digit add up among themselves and one of them adds the
+        // sum to the warp's bin, so no two threads ever meet at a bin (most of a row shares a few exponents,
+        // and atomics on those few bins took most of a round)
+        unsigned long long* hist = warp_hist[warp];
+        for (int d = lane; d < 256; d += 32) hist[d] = 0;
+        __syncwarp();
+        const unsigned int high_mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        // eight of a thread's values are loaded together and then taken in turn: a load between the turns
+        // would wait behind the warp's meeting points, one memory round trip a value
+        constexpr int BATCH = 8;
+        for (int base = begin + (int)threadIdx.x; base - (int)threadIdx.x < end; base += BATCH * (int)blockDim.x) {  // every lane of a warp makes the same turns
+            float batch[BATCH];
 #pragma unroll
-        for (int d = 0; d < 16; ++d) local[d] = 0.0f;
-        const unsigned int high_mask = shift == 28 ? 0u : (0xffffffffu << (shift + 4));
-        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-            const float pv = p[i];
-            const unsigned int key = __float_as_uint(pv);
-            if (key < lo_key) continue;
-            if ((key & high_mask) != (prefix & high_mask)) continue;
-            const int digit = (key >> shift) & 15;
-            const float wgt = use_sum ? pv : 1.0f;
+            for (int u = 0; u < BATCH; ++u) {
+                const int i = base + u * (int)blockDim.x;
+                batch[u] = i < end ? p[i] : 0.0f;
+            }
 #pragma unroll
-            for (int d = 0; d < 16; ++d)
-                if (d == digit) local[d] += wgt;
+            for (int u = 0; u < BATCH; ++u) {
+                const int i = base + u * (int)blockDim.x;
+                const float pv = batch[u];
+                const unsigned int key = __float_as_uint(pv);
+                const bool in = i < end && key >= lo_key && (key & high_mask) == (prefix & high_mask);
+                const unsigned int taking = __ballot_sync(0xffffffffu, in);
+                if (taking == 0) continue;
+                if (in) {
+                    const unsigned int digit = (key >> shift) & 255u;
+                    const unsigned int same = __match_any_sync(taking, digit);
+                    unsigned long long weight;
+                    if (use_sum) {
+                        const unsigned long long units = mass_units(pv);
+                        const unsigned int low = __reduce_add_sync(same, (unsigned int)(units & 0xFFFFFu));
+                        const unsigned int high = __reduce_add_sync(same, (unsigned int)(units >> 20));
+                        weight = ((unsigned long long)high << 20) + low;
+                    } else {
+                        weight = (unsigned long long)__popc(same);
+                    }
+                    if (lane == __ffs(same) - 1) hist[digit] += weight;
+                }
+                __syncwarp();  // the next turn's leaders may be other lanes
+            }
         }
-        float totals[16];
-        cluster_sum16(cluster, mine, turn, local, s_part, totals);
-        // G(d) = above + sum_{e>d} S[e]; pick the smallest d with G(d) < target.
-        int d = 15;
-        float g = above;  // G(15)
-        while (d > 0) {
-            const float g_next = g + totals[d];  // G(d-1)
-            if (!(g_next < target)) break;
-            g = g_next;
-            --d;
+        __syncthreads();
+        for (int d = threadIdx.x; d < 256; d += blockDim.x) {
+            unsigned long long sum = 0;
+#pragma unroll
+            for (int w = 0; w < STAGE1_WARPS; ++w) sum += warp_hist[w][d];
+            mine->hist[slot][d] = sum;
         }
-        above = g;
-        prefix |= (unsigned int)d << shift;
+        cluster.sync();  // every block's histogram is complete (and the block's own threads have met)
+        for (int d = threadIdx.x; d < 256; d += blockDim.x) {
+            unsigned long long theirs[SAMPLE_CLUSTER];  // the remote loads go out together
+#pragma unroll
+            for (unsigned rank = 0; rank < SAMPLE_CLUSTER; ++rank)
+                theirs[rank] = rank < cluster.num_blocks() ? cluster.map_shared_rank(mine, rank)->hist[slot][d] : 0ull;
+            unsigned long long sum = 0;
+#pragma unroll
+            for (unsigned rank = 0; rank < SAMPLE_CLUSTER; ++rank) sum += theirs[rank];
+            mine->total[d] = sum;
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // G(d) = above + sum_{e>d} total[e]; the smallest d with G(d) < target.  Lane l owns bins 8l..8l+7:
+            // the weight above a lane's bins comes from a scan over the lanes, then the lane in whose bins
+            // G falls below the target for the last time (going down) walks its eight bins.
+            unsigned long long own = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) own += mine->total[8 * lane + e];
+            unsigned long long higher = own;  // inclusive sum over lanes >= this one
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1) {
+                const unsigned long long other = __shfl_down_sync(0xffffffffu, higher, offset);
+                if (lane + offset < 32) higher += other;
+            }
+            const unsigned long long above_lane = mine->above + higher - own;  // G(8l + 7): the weight above this lane's top bin
+            // going down from bin 255, G grows; the walk stops at the first bin d where G(d - 1) >= target
+            const bool stops_here = !(above_lane + own < target);  // G(8l - 1) >= target: the stop lies in this lane's bins or above
+            const unsigned int stopping = __ballot_sync(0xffffffffu, stops_here);
+            const int owner = stopping ? 31 - __clz(stopping) : 0;  // the highest such lane; none: the walk reaches bin 0
+            if (lane == owner) {
+                int d = 8 * lane + 7;
+                unsigned long long g = above_lane;
+                while (d > 0) {
+                    const unsigned long long g_next = g + mine->total[d];  // G(d-1)
+                    if (!(g_next < target)) break;
+                    g = g_next;
+                    --d;
+                    if (d < 8 * lane && stopping) break;  // not reached: the stop lies within the lane's bins
+                }
+                mine->above = g;
+                mine->digit = d;
+            }
+        }
+        __syncthreads();
+        prefix |= (unsigned int)mine->digit << shift;
     }
     return prefix;
 }
@@ -412,8 +499,8 @@ sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work
     __shared__ float scratch[32];
     __shared__ float sv[32];
     __shared__ int si[32];
-    __shared__ float s_part[STAGE1_WARPS][16];
     __shared__ ClusterScratch mine;
+    __shared__ unsigned long long warp_hist[STAGE1_WARPS][256];
     int turn = 0;
 
     const int blocks_per_row = (int)cluster.num_blocks();
@@ -464,19 +551,21 @@ sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work
     unsigned int lo_key = 0;
     // top-k: keep p >= k-th largest (ties kept) (sampler.py:1259-1291)
     const int k = top_k[r];
-    if (k > 0 && k < V) lo_key = select_key(cluster, &mine, turn, p, begin, end, lo_key, (float)k, 0, s_part);
+    if (k > 0 && k < V) lo_key = select_key(cluster, &mine, turn, p, begin, end, lo_key, (unsigned long long)k, 0, warp_hist);
     // top-p: in descending order drop a token once the mass before it reaches
     // top_p * total (sampler.py:1349-1361); tokens tied with the last kept one stay.
     const float tp = top_p[r];
     if (tp < 1.0f) {
-        float total = 0.0f;
+        // the mass that top-k left, in the search's own units
+        unsigned long long units = 0;
         for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
             const float pv = p[i];
-            if (__float_as_uint(pv) >= lo_key) total += pv;
+            if (__float_as_uint(pv) >= lo_key) units += mass_units(pv);
         }
-        total = cluster_sum(cluster, &mine, turn, total, scratch);
-        const float target = tp * fmaxf(total, 1e-12f);
-        const unsigned int u = select_key(cluster, &mine, turn, p, begin, end, lo_key, target, 1, s_part);
+        const unsigned long long total = cluster_sum_units(cluster, &mine, turn, units);
+        unsigned long long target = (unsigned long long)((double)tp * (double)total);
+        if (target < 1) target = 1;
+        const unsigned int u = select_key(cluster, &mine, turn, p, begin, end, lo_key, target, 1, warp_hist);
         lo_key = u > lo_key ? u : lo_key;
     }
     // what is left; its sum renormalises the draw
