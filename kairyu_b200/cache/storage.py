@@ -37,6 +37,13 @@ class CacheStorage:
         self.v: list[torch.Tensor] = []
         for group in layout.groups:
             shape = (len(group.slots), num_pages, page_size, group.spec.num_kv_heads)
+            if group.spec.head_dim == group.spec.value_dim:
+                # one allocation, the values a fixed distance behind the keys: a kernel may then fetch
+                # the keys and the values of a run of positions with one strided copy
+                both = torch.zeros((2, *shape, group.spec.head_dim), dtype=dtype, device=device)
+                self.k.append(both[0])
+                self.v.append(both[1])
+                continue
             self.k.append(torch.zeros((*shape, group.spec.head_dim), dtype=dtype, device=device))
             self.v.append(torch.zeros((*shape, group.spec.value_dim), dtype=dtype, device=device))
         self.states = [

@@ -91,7 +91,11 @@ __device__ __forceinline__ void split_range(int first, int last, int num_splits,
     t1 = min(t0 + per - 1, last);
 }
 
-template <int D>
+// JOINED (head_dim 64 only): the values lie a fixed distance behind the keys in one allocation, and
+// map_k has that distance as its fourth dimension in place of the bands, so that one copy brings a run
+// of rows of the keys AND of the values (twice the bytes a copy; with 2 KB copies the SM's copy rate
+// weighed on the kernel).  In shared memory a stage is then [run][K | V][position][64].
+template <int D, bool JOINED>
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, int q_stride, const int* __restrict__ seq_lens,
@@ -101,6 +105,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
     using S = TmaSmem<D>;
     constexpr int HALVES = S::HALVES;
+    static_assert(!JOINED || HALVES == 1, "keys and values share a copy at head_dim 64 only");
+    constexpr int LAY = JOINED ? 2 : HALVES;  // 64-column blocks side by side in a run of the layout
     constexpr int STAGES = S::STAGES;
     constexpr int STRIDE = Tile<D>::STRIDE;
     constexpr int CH = Tile<D>::CHUNKS;
@@ -166,7 +172,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         // ---------------- producer: one copy per (K or V, 64-column band, run of rows on one page)
         const int box_rows = page_size < TILE_N ? page_size : TILE_N;
         const int runs = TILE_N / box_rows;
-        const int per_tile = 2 * runs;
+        const int per_tile = JOINED ? runs : 2 * runs;
         // The tile that holds the newest position is written by the kernel before this one; the tiles
         // before it are not.  Up to a ring of those go out before the wait (no stage is reused yet,
         // so nothing here waits on the consumers, who are waiting for their queries).
@@ -186,8 +192,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             if (lane == 0) mbar_arrive_expect_tx(full_bar + stage, (uint32_t)(S::STAGE_ELEMS * sizeof(__nv_bfloat16)));
             __syncwarp();
             for (int op = lane; op < per_tile; op += 32) {
-                const int is_v = op / runs;
-                const int run = op % runs;
+                const int is_v = JOINED ? 0 : op / runs;
+                const int run = JOINED ? op : op % runs;
                 const int key = kt * TILE_N + run * box_rows;
                 const int page_index = key >> page_shift;
                 int page = 0, within = 0;  // the reserved page stands in for rows nobody may see
@@ -198,7 +204,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                         within = key - (page_index << page_shift);
                     }
                 }
-                __nv_bfloat16* dst = ring + stage * S::STAGE_ELEMS + is_v * S::TILE_ELEMS + run * HALVES * box_rows * 64;
+                __nv_bfloat16* dst = ring + stage * S::STAGE_ELEMS + is_v * S::TILE_ELEMS + run * LAY * box_rows * 64;
                 tma_load_5d(dst, is_v ? &map_v : &map_k, 0, kvh, within, 0, page, full_bar + stage);
             }
         }
@@ -235,7 +241,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 break;
             }
             __nv_bfloat16* tK = ring + stage * S::STAGE_ELEMS;
-            __nv_bfloat16* tV = tK + S::TILE_ELEMS;
+            __nv_bfloat16* tV = JOINED ? tK : tK + S::TILE_ELEMS;
             const int tile_key0 = kt * TILE_N;
             if (tile_key0 < key_lo || tile_key0 + TILE_N > seq_len) {
                 // Rows nobody may see get probability 0, but 0 * NaN is NaN: clear their values
@@ -245,7 +251,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                     const int c = idx % (HALVES * 8);
                     const int key = tile_key0 + r;
                     if (key < key_lo || key >= seq_len)
-                        *reinterpret_cast<uint4*>(tV + tile_offset<HALVES>(r, c >> 3, c & 7, run_shift)) = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(tV + tile_offset<LAY>(r, JOINED ? 1 : c >> 3, c & 7, run_shift)) = make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();  // these writes stay ordered before the copy that refills the stage
                 __syncwarp();
@@ -259,7 +265,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int m = lane >> 3;
                 const int key = warp * 16 + (m >> 1) * 8 + (lane & 7);
                 const int chunk = (ks * 2 + (m & 1)) & 7;
-                ldmatrix_x4(b, tK + tile_offset<HALVES>(key, ks >> 2, chunk, run_shift));
+                ldmatrix_x4(b, tK + tile_offset<LAY>(key, JOINED ? 0 : ks >> 2, chunk, run_shift));
                 mma_16816(s[0], qf[ks], b[0], b[1]);
                 mma_16816(s[1], qf[ks], b[2], b[3]);
             }
@@ -319,7 +325,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                 const int m = lane >> 3;
                 const int key = warp * 16 + (m & 1) * 8 + (lane & 7);
                 const int chunk = (dp * 2 + (m >> 1)) & 7;
-                ldmatrix_x4_trans(b, tV + tile_offset<HALVES>(key, dp >> 2, chunk, run_shift));
+                ldmatrix_x4_trans(b, tV + tile_offset<LAY>(key, JOINED ? 1 : dp >> 2, chunk, run_shift));
                 mma_16816(o[2 * dp], a, b[0], b[1]);
                 mma_16816(o[2 * dp + 1], a, b[2], b[3]);
             }
@@ -446,11 +452,11 @@ template <int D>
 int resident_blocks() {
     static int cached = -1;
     if (cached >= 0) return cached;
-    if (cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(attention_decode_tma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
     int device = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<D>, TMA_THREADS, TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<D, false>, TMA_THREADS, TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
     cached = sms * per_sm;
     return cached;
 }
@@ -465,18 +471,18 @@ int resident_blocks_for(int D) {
     }
 }
 
-template <int D>
+template <int D, bool JOINED>
 int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q, int q_stride, const int* seq_lens,
            const int* block_table, int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows, int Hq,
            int Hkv, int page_size, int num_pages, float scale, int window, int num_splits, float* part_o, float* part_ml,
            __nv_bfloat16* out, int out_stride, int combine, int* flag, cudaStream_t stream) {
     const size_t smem = TmaSmem<D>::TOTAL;
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, JOINED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
     dim3 grid(num_rows, Hkv, num_splits);
-    kb_launch(attention_decode_tma_kernel<D>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
+    kb_launch(attention_decode_tma_kernel<D, JOINED>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
               block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, shift, num_pages, scale,
               window, num_splits, part_o, part_ml, out, out_stride, combine, flag);
     return kb_launch_result();
@@ -544,16 +550,42 @@ KB_EXPORT int kb_attention_encode_cache_map(void* map_out, const void* base, lon
     return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
 }
 
-// map_k, map_v: host pointers to tensor maps made by kb_attention_encode_cache_map with bands = 1.
+// A map over keys AND values of a cache whose values lie `gap` elements behind its keys, with the same
+// shape and strides (head_dim 64): five dimensions (64 columns, kv_heads, page_size, keys | values, pages),
+// boxes of 1 head x min(page_size, 64) positions of both.  128-byte swizzle.
+KB_EXPORT int kb_attention_encode_joined_map(void* map_out, const void* base_k, long long gap, long long num_pages, int page_size,
+                                             int Hkv, int D, long long stride_page, long long stride_pos, long long stride_head) {
+    if (!map_out || !base_k) return KB_ERR_NULL;
+    if (((uintptr_t)map_out % 64) != 0 || ((uintptr_t)base_k % 16) != 0) return KB_ERR_BAD_ARG;
+    if (D != 64 || !kb_attention_decode_tma_supported(D, page_size) || num_pages < 1 || Hkv < 1) return KB_ERR_UNSUPPORTED_SIZE;
+    if ((stride_page * 2) % 16 != 0 || (stride_pos * 2) % 16 != 0 || (stride_head * 2) % 16 != 0) return KB_ERR_UNSUPPORTED_SIZE;
+    if (gap <= 0 || (gap * 2) % 16 != 0 || gap * 2 >= (1ll << 40)) return KB_ERR_UNSUPPORTED_SIZE;  // a stride has 40 bits
+    const int rc = get_encoder();
+    if (rc != 0) return rc;
+    const cuuint32_t box_rows = (cuuint32_t)(page_size < TILE_N ? page_size : TILE_N);
+    cuuint64_t dims[5] = {64, (cuuint64_t)Hkv, (cuuint64_t)page_size, 2, (cuuint64_t)num_pages};
+    cuuint64_t strides[4] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_pos * 2, (cuuint64_t)gap * 2, (cuuint64_t)stride_page * 2};
+    cuuint32_t box[5] = {64, 1, box_rows, 2, 1};
+    cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    const CUresult r = g_encode((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base_k), dims, strides, box,
+                                elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+// map_k, map_v: host pointers to tensor maps made by kb_attention_encode_cache_map with bands = 1; with
+// `joined` (head_dim 64 only), map_k is a map of kb_attention_encode_joined_map and map_v is not read.
 // num_splits: any value from 1 up (kb_attention_decode_tma_splits gives a good one).
 // part_o: [rows, Hq, splits, D] fp32; part_ml: [rows, Hq, splits, 2] fp32 (scratch; only read
 // and written with more than one split).
 KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, const void* q, int q_stride, void* out, int out_stride,
                                       const int* seq_lens, const int* block_table, int max_pages, const int* decode_rows,
                                       const int* decode_tokens, int num_rows, int Hq, int Hkv, int D, int page_size, int num_pages,
-                                      float scale, int window, int num_splits, float* part_o, float* part_ml, int* flag,
+                                      float scale, int window, int num_splits, float* part_o, float* part_ml, int joined, int* flag,
                                       cudaStream_t stream) {
     if (num_rows == 0) return 0;
+    if (joined && D != 64) return KB_ERR_UNSUPPORTED_SIZE;
+    if (joined) map_v = map_k;
     if (!map_k || !map_v || !q || !out || !seq_lens || !block_table || !decode_rows || !decode_tokens) return KB_ERR_NULL;
     const int combine = num_splits == 1 ? COMBINE_DIRECT : COMBINE_SCRATCH;
     if (combine == COMBINE_SCRATCH && (!part_o || !part_ml)) return KB_ERR_NULL;
@@ -567,10 +599,10 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
 #define ARGS mk, mv, (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, \
              Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, (__nv_bfloat16*)out, out_stride, combine, flag, stream
     switch (D) {
-        case 64: rc = launch<64>(ARGS); break;
-        case 128: rc = launch<128>(ARGS); break;
-        case 192: rc = launch<192>(ARGS); break;
-        default: rc = launch<256>(ARGS); break;
+        case 64: rc = joined ? launch<64, true>(ARGS) : launch<64, false>(ARGS); break;
+        case 128: rc = launch<128, false>(ARGS); break;
+        case 192: rc = launch<192, false>(ARGS); break;
+        default: rc = launch<256, false>(ARGS); break;
     }
 #undef ARGS
     if (rc != 0 || combine != COMBINE_SCRATCH) return rc;

@@ -487,14 +487,17 @@ def attention_decode_mma(
         fn = _fn(
             "attention_decode_tma",
             "kb_attention_decode_tma",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
         )
+        joined = _joined_cache_map(k_cache, v_cache)  # keys and values in one copy where the cache allows
+        map_k = joined or _cache_map(k_cache, bands=True)
+        map_v = joined or _cache_map(v_cache, bands=True)
         _check(
             fn(
-                _cache_map(k_cache, bands=True), _cache_map(v_cache, bands=True), q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
+                map_k, map_v, q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0),
                 seq_lens.data_ptr(), block_table.data_ptr(), block_table.shape[1], decode_rows.data_ptr(),
                 decode_tokens.data_ptr(), int(num_rows), num_q_heads, num_kv_heads, head_dim, page_size, num_pages,
-                float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), _ptr(flag), _stream(),
+                float(scale), int(window), num_splits, part_o.data_ptr(), part_ml.data_ptr(), 1 if joined else 0, _ptr(flag), _stream(),
             ),
             what,
             launches=_fn("attention_decode_tma", "kb_attention_decode_tma_launches", [c_int])(num_splits),
@@ -553,6 +556,33 @@ def _cache_map(cache: torch.Tensor, bands: bool = False) -> int:
         code = fn(address, cache.data_ptr(), num_pages, page_size, num_kv_heads, head_dim, cache.stride(0), cache.stride(1), cache.stride(2), 1 if bands else 0)
         if code != 0:
             raise KernelError(f"tensor map encoding of the cache failed with code {code}")
+        _keep_map(key, held)
+    return (ctypes.addressof(held) + 63) & ~63
+
+
+def _joined_cache_map(k_cache: torch.Tensor, v_cache: torch.Tensor) -> int:
+    """Host address of a cached TMA descriptor over the keys AND the values of one layer's pages, or 0
+    where there is none: head size 64, and values that lie a fixed distance behind the keys with the same
+    shape and strides (the cache storage allocates them so).  One copy then brings a run of key rows and
+    the value rows of the same positions: at 128 bytes a row the decode kernel is bound by how many
+    copies an SM can issue, not by their bytes."""
+    if k_cache.shape[3] != 64 or k_cache.shape != v_cache.shape or k_cache.stride() != v_cache.stride():
+        return 0
+    gap_bytes = v_cache.data_ptr() - k_cache.data_ptr()
+    if gap_bytes <= 0 or gap_bytes % 16 != 0 or gap_bytes >= 1 << 40:
+        return 0
+    key = ("joined", k_cache.data_ptr(), gap_bytes, tuple(k_cache.shape), tuple(k_cache.stride()))
+    held = _held_map(key)
+    if held is None:
+        held = ctypes.create_string_buffer(128 + 64)
+        address = (ctypes.addressof(held) + 63) & ~63
+        ll = ctypes.c_longlong
+        fn = _fn("attention_decode_tma", "kb_attention_encode_joined_map", [c_void_p, c_void_p, ll, ll, c_int, c_int, c_int, ll, ll, ll])
+        num_pages, page_size, num_kv_heads, head_dim = k_cache.shape
+        code = fn(address, k_cache.data_ptr(), gap_bytes // 2, num_pages, page_size, num_kv_heads, head_dim,
+                  k_cache.stride(0), k_cache.stride(1), k_cache.stride(2))
+        if code != 0:
+            raise KernelError(f"tensor map encoding of the cache's keys and values failed with code {code}")
         _keep_map(key, held)
     return (ctypes.addressof(held) + 63) & ~63
 

@@ -613,6 +613,39 @@ def test_decode_attention_streams_many_tiles_through_its_ring(Hq, Hkv, D, page_s
     close(out, expected, 2e-2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,page_size", [(8, 2, 16), (32, 8, 16), (6, 3, 8), (4, 1, 64), (2, 2, 128)])
+@pytest.mark.parametrize("num_splits", [1, 3, 8])
+@pytest.mark.parametrize("window", [0, 333])
+def test_decode_attention_fetches_keys_and_values_in_one_copy(Hq, Hkv, page_size, num_splits, window, workspace):
+    """Head size 64 with the values a fixed distance behind the keys in one allocation (as the cache storage
+    lays them out): one strided copy brings both.  Values that differ from the keys in every element, so
+    that a mix-up of the two halves of a stage shows; the same bits as with two allocations."""
+    D = 64
+    seq_lens = [1000, 700, 257, 64, 1]
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, [1] * len(seq_lens), seed=41)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    both = torch.stack([case["kc"], case["vc"]]).to(DEV)
+    rows = torch.arange(len(seq_lens), dtype=torch.int32, device=DEV)
+    k = kernels()
+    assert k._joined_cache_map(both[0], both[1]) != 0
+    swapped = torch.stack([case["vc"], case["kc"]]).to(DEV)  # the values BEFORE the keys: no such copy, two maps
+    assert k._joined_cache_map(swapped[1], swapped[0]) == 0
+    outs = []
+    for kc, vc in ((both[0], both[1]), (swapped[1], swapped[0])):
+        out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+        flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+        k.attention_decode_mma(
+            case["q"].to(DEV), out, kc, vc, seq_lens=case["seq_lens"].to(DEV), block_table=case["table"].to(DEV),
+            decode_rows=rows, decode_tokens=rows, num_rows=len(seq_lens), max_seq_len=max(seq_lens), num_q_heads=Hq,
+            scale=scale, window=window, workspace=workspace, flag=flag, num_splits=num_splits,
+        )
+        assert int(flag.item()) == 0
+        close(out, expected, 2e-2)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+
+
 def _run_prefill(case, Hq, scale, window, workspace, num_splits, max_seq_len=0, two_tiles=None):
     k = kernels()
     qo = case["qo"].tolist()
