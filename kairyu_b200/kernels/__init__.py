@@ -889,6 +889,14 @@ def _tensor_map(tensor: torch.Tensor, box_rows: int) -> int:
     return (ctypes.addressof(held) + 63) & ~63
 
 
+# The tcgen05 product takes a gated weight from this size on.  Measured at 12 to 64 rows against the library
+# product followed by the gate kernel: 201 to 524 MB (hidden 4,096 and 5,120) it is level or up to 5 % ahead,
+# at 50 to 100 MB (hidden 2,048 to 3,072: 48 to 72 weight rows a block) it takes 18-32 us where the pair
+# takes 12-20: a k step costs it about 600 ns however few rows a block owns, and neither more stages in the
+# same shared memory nor another order of the k steps nor other cache hints changed that.
+TC5_MIN_WEIGHT_BYTES = 160 << 20
+
+
 def _tc5_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
     M, K = x.shape
     return (
@@ -934,8 +942,9 @@ def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: o
     epilogue: the mma.sync skinny kernel up to 8 rows (csrc/gemm_skinny.cu; measured on the
     decode step at 8 rows it is 2 % of the step faster than the tcgen05 kernel, whose fixed
     costs - barrier and tensor-memory set-up, the accumulator read-back - weigh more on a 40 us
-    kernel), the tcgen05 + TMA kernel from 9 to 64 rows (csrc/gemm_tc5.cu); otherwise a product
-    into ``scratch.buffer(...)`` and the gate kernel.
+    kernel), the tcgen05 + TMA kernel from 9 to 64 rows (csrc/gemm_tc5.cu) where the weight is large
+    enough for it (``TC5_MIN_WEIGHT_BYTES``); otherwise a product into ``scratch.buffer(...)`` and the
+    gate kernel.
     """
     if isinstance(x, PreNormed):  # its rows are scaled in the epilogue, before the gate
         _need_cuda("linear_swiglu", x.values, weight_gate_up, out)
@@ -955,7 +964,7 @@ def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: o
         if few_rows(M) and _skinny_ok(x, weight_gate_up, None, out):
             _gemm_skinny(x, weight_gate_up, None, out, gated=True)
             return
-        if _tc5_ok(x, weight_gate_up, None, out):
+        if _tc5_ok(x, weight_gate_up, None, out) and weight_gate_up.numel() * 2 >= TC5_MIN_WEIGHT_BYTES:
             _gemm_tc5(x, weight_gate_up, None, out, gated=True)
             return
     gate_up = scratch.buffer("ffn.gate_up", M, two_i, x.dtype)
