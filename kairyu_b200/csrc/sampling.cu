@@ -103,29 +103,71 @@ KB_EXPORT int kb_argmax(const float* logits, int ld, int n, int V, int* out, cud
 // For report r over row rows[r] of the logits: the log-softmax value of one token, and the k
 // largest log-softmax values with their indices, largest first, ties by the lower index
 // (kairyu/engine/core/sampler.py:1423-1437: taken from the raw logits, before any edit or
-// temperature).  One block per report.  values[r, 0] is the token's, values[r, 1 + i] and
-// indices[r, i] the i-th largest.  Pass i of the top-k finds the best entry that comes after
-// pass i-1's in the order (value down, index up), so nothing has to be remembered but the last.
-constexpr int REPORT_THREADS = 1024;
+// temperature).  values[r, 0] is the token's, values[r, 1 + i] and indices[r, i] the i-th largest.
+//
+// Two launches.  The first cuts a row into chunks (32 of them, or more for a vocabulary beyond
+// 262,144) with a block each: the chunk's part of the log-sum-exp (running maximum, sum) and its own
+// k best entries, found by k passes over the chunk, which the L1 holds after the first.  Pass i finds
+// the best entry that comes after pass i-1's in the order (value down, index up), so nothing has to
+// be remembered but the last.  The second launch, a block a report, adds the chunks' sums in chunk
+// order and finds the k best among the chunks' candidates the same way.  (One block a row, k + 1
+// passes over the whole row, took 250 us at 128,256 entries and k = 5.)
+constexpr int REPORT_THREADS = 256;
+constexpr int REPORT_WARPS = REPORT_THREADS / 32;
+constexpr int REPORT_CHUNKS = 32;
+constexpr int REPORT_MAX_CHUNK = 8192;
+constexpr int REPORT_ABSENT = 0x7fffffff;
 
+__host__ __device__ inline int report_chunk_len(int V) {
+    int len = (V + REPORT_CHUNKS - 1) / REPORT_CHUNKS;
+    if (len > REPORT_MAX_CHUNK) len = REPORT_MAX_CHUNK;
+    return len < 1 ? 1 : len;
+}
+// scratch of (report, chunk): maximum, sum, then k (value, index) pairs
+__host__ __device__ inline size_t report_scratch_floats(int k) { return 2 + 2 * (size_t)k; }
+
+// whether (v, i) comes before (bv, bi) in the order: value down, index up; an absent entry comes last
+__device__ __forceinline__ bool report_before(float v, int i, float bv, int bi) {
+    return i != REPORT_ABSENT && (bi == REPORT_ABSENT || v > bv || (v == bv && i < bi));
+}
+
+// The block's first entry in the order, for every thread.  red_v / red_i: REPORT_WARPS entries.
+__device__ void report_block_best(float& best, int& best_i, float* red_v, int* red_i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (report_before(ov, oi, best, best_i)) { best = ov; best_i = oi; }
+    }
+    __syncthreads();  // the call before has been read
+    if ((threadIdx.x & 31) == 0) { red_v[threadIdx.x >> 5] = best; red_i[threadIdx.x >> 5] = best_i; }
+    __syncthreads();
+    best = red_v[0];
+    best_i = red_i[0];
+#pragma unroll
+    for (int w = 1; w < REPORT_WARPS; ++w)
+        if (report_before(red_v[w], red_i[w], best, best_i)) { best = red_v[w]; best_i = red_i[w]; }
+}
+
+// grid (reports, chunks)
 __global__ void __launch_bounds__(REPORT_THREADS)
-logprob_report_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ rows,
-                      const int* __restrict__ tokens, int tokens_by_row, int k, float* __restrict__ values,
-                      int* __restrict__ indices) {
+logprob_chunk_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ rows, int k, int chunk_len,
+                     float* __restrict__ scratch) {
     pdl_wait();
-    __shared__ float red_m[REPORT_THREADS / 32];
-    __shared__ float red_s[REPORT_THREADS / 32];
-    __shared__ int red_i[REPORT_THREADS / 32];
-    __shared__ float bcast_v;
-    __shared__ int bcast_i;
+    __shared__ float red_m[REPORT_WARPS];
+    __shared__ float red_s[REPORT_WARPS];
+    __shared__ int red_i[REPORT_WARPS];
     const int r = blockIdx.x;
-    const int row = rows[r];
-    const float* x = logits + (size_t)row * ld;
+    const int chunk = blockIdx.y;
+    const float* x = logits + (size_t)rows[r] * ld;
+    const int begin = chunk * chunk_len;
+    const int end = min(V, begin + chunk_len);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* mine = scratch + ((size_t)r * gridDim.y + chunk) * report_scratch_floats(k);
 
-    // log of the sum of exponentials, with the running maximum taken out
+    // the chunk's part of the log of the sum of exponentials, with the running maximum taken out
     float m = -INFINITY, sum = 0.0f;
-    for (int i = threadIdx.x; i < V; i += REPORT_THREADS) {
+    for (int i = begin + threadIdx.x; i < end; i += REPORT_THREADS) {
         const float v = x[i];
         if (v > m) {
             sum = sum * expf(m - v) + 1.0f;  // m = -inf: sum is 0 and stays finite
@@ -146,67 +188,118 @@ logprob_report_kernel(const float* __restrict__ logits, int ld, int V, const int
     __syncthreads();
     if (threadIdx.x == 0) {
         float bm = red_m[0], bs = red_s[0];
-        for (int w = 1; w < REPORT_THREADS / 32; ++w) {
+        for (int w = 1; w < REPORT_WARPS; ++w) {
             const float nm = fmaxf(bm, red_m[w]);
             if (nm > -INFINITY) bs = bs * expf(bm - nm) + red_s[w] * expf(red_m[w] - nm);
             bm = nm;
         }
-        const float lse = bm + logf(bs);
-        bcast_v = lse;
-        int token = tokens[tokens_by_row ? row : r];
-        token = min(max(token, 0), V - 1);
-        values[(size_t)r * (k + 1)] = x[token] - lse;
+        mine[0] = bm;
+        mine[1] = bs;
     }
-    __syncthreads();
-    const float lse = bcast_v;
 
     float prev_v = INFINITY;
     int prev_i = -1;
     for (int pass = 0; pass < k; ++pass) {
         float best = -INFINITY;
-        int best_i = 0x7fffffff;
-        for (int i = threadIdx.x; i < V; i += REPORT_THREADS) {
-            const float v = x[i];
-            const bool after = v < prev_v || (v == prev_v && i > prev_i);
-            if (after && (v > best || (v == best && i < best_i))) { best = v; best_i = i; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (oi != 0x7fffffff && (best_i == 0x7fffffff || ov > best || (ov == best && oi < best_i))) { best = ov; best_i = oi; }
-        }
-        __syncthreads();  // the pass before has read bcast_v / bcast_i
-        if (lane == 0) { red_m[warp] = best; red_i[warp] = best_i; }
-        __syncthreads();
+        int best_i = REPORT_ABSENT;
+        if (prev_i != REPORT_ABSENT)  // else nothing is left: later passes find nothing either
+            for (int i = begin + threadIdx.x; i < end; i += REPORT_THREADS) {
+                const float v = x[i];
+                const bool after = v < prev_v || (v == prev_v && i > prev_i);
+                if (after && report_before(v, i, best, best_i)) { best = v; best_i = i; }
+            }
+        report_block_best(best, best_i, red_m, red_i);
         if (threadIdx.x == 0) {
-            for (int w = 1; w < REPORT_THREADS / 32; ++w)
-                if (red_i[w] != 0x7fffffff && (best_i == 0x7fffffff || red_m[w] > best || (red_m[w] == best && red_i[w] < best_i))) {
-                    best = red_m[w];
-                    best_i = red_i[w];
-                }
-            bcast_v = best;
-            bcast_i = best_i;
-            // fewer than k entries (k > V): the rest are marked absent
-            values[(size_t)r * (k + 1) + 1 + pass] = best_i == 0x7fffffff ? -INFINITY : best - lse;
-            indices[(size_t)r * k + pass] = best_i == 0x7fffffff ? -1 : best_i;
+            mine[2 + 2 * pass] = best;
+            mine[2 + 2 * pass + 1] = __int_as_float(best_i);
         }
-        __syncthreads();
-        prev_v = bcast_v;
-        prev_i = bcast_i;
-        if (prev_i == 0x7fffffff) prev_v = -INFINITY;  // nothing is left: later passes find nothing either
+        prev_v = best;
+        prev_i = best_i;
     }
+}
+
+// grid (reports)
+__global__ void __launch_bounds__(REPORT_THREADS)
+logprob_merge_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ rows, const int* __restrict__ tokens,
+                     int tokens_by_row, int k, int chunks, const float* __restrict__ scratch, float* __restrict__ values,
+                     int* __restrict__ indices) {
+    pdl_wait();
+    __shared__ float red_v[REPORT_WARPS];
+    __shared__ int red_i[REPORT_WARPS];
+    __shared__ float bcast;
+    const int r = blockIdx.x;
+    const int row = rows[r];
+    const float* x = logits + (size_t)row * ld;
+    const size_t per = report_scratch_floats(k);
+    const float* mine = scratch + (size_t)r * chunks * per;
+    if (threadIdx.x == 0) {
+        float bm = mine[0], bs = mine[1];
+        for (int c = 1; c < chunks; ++c) {  // in chunk order
+            const float cm = mine[c * per], cs = mine[c * per + 1];
+            const float nm = fmaxf(bm, cm);
+            if (nm > -INFINITY) bs = bs * expf(bm - nm) + cs * expf(cm - nm);
+            bm = nm;
+        }
+        const float lse = bm + logf(bs);
+        bcast = lse;
+        int token = tokens[tokens_by_row ? row : r];
+        token = min(max(token, 0), V - 1);
+        values[(size_t)r * (k + 1)] = x[token] - lse;
+    }
+    __syncthreads();
+    const float lse = bcast;
+
+    const int candidates = chunks * k;
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int pass = 0; pass < k; ++pass) {
+        float best = -INFINITY;
+        int best_i = REPORT_ABSENT;
+        if (prev_i != REPORT_ABSENT)
+            for (int j = threadIdx.x; j < candidates; j += REPORT_THREADS) {
+                const float* entry = mine + (size_t)(j / k) * per + 2 + 2 * (j % k);
+                const float v = entry[0];
+                const int i = __float_as_int(entry[1]);
+                if (i == REPORT_ABSENT) continue;
+                const bool after = v < prev_v || (v == prev_v && i > prev_i);
+                if (after && report_before(v, i, best, best_i)) { best = v; best_i = i; }
+            }
+        report_block_best(best, best_i, red_v, red_i);
+        if (threadIdx.x == 0) {
+            // fewer than k entries (k > V): the rest are marked absent
+            values[(size_t)r * (k + 1) + 1 + pass] = best_i == REPORT_ABSENT ? -INFINITY : best - lse;
+            indices[(size_t)r * k + pass] = best_i == REPORT_ABSENT ? -1 : best_i;
+        }
+        prev_v = best;
+        prev_i = best_i;
+    }
+}
+
+// Floats of scratch kb_logprob_report needs for this many reports of k entries over a vocabulary of V.
+KB_EXPORT long long kb_logprob_report_scratch_floats(int reports, int V, int k) {
+    if (reports < 1 || V < 1 || k < 0) return 0;
+    const int len = report_chunk_len(V);
+    const int chunks = (V + len - 1) / len;
+    return (long long)reports * chunks * (long long)report_scratch_floats(k);
 }
 
 // values: [reports, k + 1] floats, indices: [reports, k] ints (k may be 0: the token's value only).
 // tokens_by_row: the token of report r is tokens[rows[r]] (a step's sampled ids), else tokens[r].
+// scratch: kb_logprob_report_scratch_floats(reports, V, k) floats.
 KB_EXPORT int kb_logprob_report(const float* logits, int ld, int n_rows, int V, const int* rows, const int* tokens,
-                                int tokens_by_row, int reports, int k, float* values, int* indices, cudaStream_t stream) {
+                                int tokens_by_row, int reports, int k, float* values, int* indices, float* scratch,
+                                cudaStream_t stream) {
     if (reports == 0) return 0;
-    if (!logits || !rows || !tokens || !values || (k > 0 && !indices)) return KB_ERR_NULL;
+    if (!logits || !rows || !tokens || !values || !scratch || (k > 0 && !indices)) return KB_ERR_NULL;
     if (V < 1 || k < 0 || n_rows < 1) return KB_ERR_BAD_ARG;
-    kb_launch(logprob_report_kernel, dim3(reports), dim3(REPORT_THREADS), 0, stream, logits, ld, V, rows, tokens, tokens_by_row, k,
-              values, indices);
+    const int len = report_chunk_len(V);
+    const int chunks = (V + len - 1) / len;
+    if (chunks > 65535) return KB_ERR_UNSUPPORTED_SIZE;
+    kb_launch(logprob_chunk_kernel, dim3(reports, chunks), dim3(REPORT_THREADS), 0, stream, logits, ld, V, rows, k, len, scratch);
+    int rc = kb_launch_result();
+    if (rc != 0) return rc;
+    kb_launch(logprob_merge_kernel, dim3(reports), dim3(REPORT_THREADS), 0, stream, logits, ld, V, rows, tokens, tokens_by_row, k,
+              chunks, (const float*)scratch, values, indices);
     return kb_launch_result();
 }
 

@@ -1032,11 +1032,17 @@ def logprob_report(
         raise KernelError("logprob_report: indices must be contiguous int32 [reports, k]")
     if tokens.numel() < (n if tokens_by_row else reports):
         raise KernelError("logprob_report: too few tokens")
-    fn = _fn("sampling", "kb_logprob_report", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    if reports == 0:
+        return
+    need_fn = _fn("sampling", "kb_logprob_report_scratch_floats", [c_int, c_int, c_int])
+    need_fn.restype = ctypes.c_longlong
+    scratch = torch.empty(max(1, int(need_fn(reports, V, k))), dtype=torch.float32, device=logits.device)  # the chunks' candidates
+    fn = _fn("sampling", "kb_logprob_report", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(
         fn(logits.data_ptr(), logits.stride(0), n, V, rows.data_ptr(), tokens.data_ptr(), 1 if tokens_by_row else 0, reports, k,
-           values.data_ptr(), indices.data_ptr() if k else None, _stream()),
+           values.data_ptr(), indices.data_ptr() if k else None, scratch.data_ptr(), _stream()),
         "logprob_report",
+        launches=2,
     )
 
 

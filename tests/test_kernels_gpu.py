@@ -834,7 +834,7 @@ def test_edit_logits():
     close(dev, expected, 1e-6)
 
 
-@pytest.mark.parametrize("n,V,k", [(3, 331, 5), (6, 128256, 20), (2, 1000, 0), (1, 7, 12)])
+@pytest.mark.parametrize("n,V,k", [(3, 331, 5), (6, 128256, 20), (2, 1000, 0), (1, 7, 12), (2, 300000, 3)])
 def test_logprob_report(n, V, k):
     """Log-softmax of the chosen token and the k largest, against torch.log_softmax / topk in fp32;
     ties go to the lower index; more asked for than the vocabulary holds marks the rest absent."""
@@ -885,7 +885,7 @@ def _sample_both(logits, temperature, top_k, top_p, min_p, seeds):
     return out.cpu().tolist(), expected.tolist()
 
 
-@pytest.mark.parametrize("V", [331, 5000])
+@pytest.mark.parametrize("V", [331, 5000, 151936])
 def test_sample_matches_the_reference_draws(V):
     from kairyu_b200.sampling.rng import as_signed64, mix_seed
 
