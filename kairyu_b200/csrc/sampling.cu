@@ -369,6 +369,7 @@ struct ClusterScratch {
     unsigned long long total[256];    // the cluster's histogram of the round
     unsigned long long above;         // the search's running weight above the prefix
     int digit;                        // the digit the round chose
+    int reached;                      // whether the entries the search looked at weigh as much as the target
 };
 
 // Every block calls this with its partial results in mine->vals[0..count); on return all[k] holds
@@ -460,7 +461,10 @@ __device__ __forceinline__ unsigned long long mass_units(float pv) { return (uns
 // u.  Requires target > 0 and a block of at least 256 threads.
 __device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, const float* __restrict__ p, int begin,
                                    int end, unsigned int lo_key, unsigned long long target, int use_sum,
-                                   unsigned long long (*warp_hist)[256]) {
+                                   unsigned long long (*warp_hist)[256], bool* reached = nullptr) {
+    // `reached` (an attempt over the entries from lo_key up only, which the caller chose above its real
+    // floor): after the first round, which has weighed all of them, the search gives up if they do not
+    // reach the target, and says so; every block of the cluster sees the same totals and decides alike.
     unsigned int prefix = 0;
     if (threadIdx.x == 0) mine->above = 0;
     const int lane = threadIdx.x & 31;
@@ -542,6 +546,7 @@ __device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* m
                 if (lane + offset < 32) higher += other;
             }
             const unsigned long long above_lane = mine->above + higher - own;  // G(8l + 7): the weight above this lane's top bin
+            if (lane == 0) mine->reached = mine->above + higher >= target;  // lane 0's sum runs over every bin
             // going down from bin 255, G grows; the walk stops at the first bin d where G(d - 1) >= target
             const bool stops_here = !(above_lane + own < target);  // G(8l - 1) >= target: the stop lies in this lane's bins or above
             const unsigned int stopping = __ballot_sync(0xffffffffu, stops_here);
@@ -561,6 +566,10 @@ __device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* m
             }
         }
         __syncthreads();
+        if (reached != nullptr && shift == 24) {
+            *reached = mine->reached != 0;
+            if (!*reached) return 0;
+        }
         prefix |= (unsigned int)mine->digit << shift;
     }
     return prefix;
@@ -658,7 +667,15 @@ sample_kernel(const float* __restrict__ logits, int ld, float* __restrict__ work
         const unsigned long long total = cluster_sum_units(cluster, &mine, turn, units);
         unsigned long long target = (unsigned long long)((double)tp * (double)total);
         if (target < 1) target = 1;
-        const unsigned int u = select_key(cluster, &mine, turn, p, begin, end, lo_key, target, 1, warp_hist);
+        // First among the entries of at least 1/65536 of the mass only (a few thousand of a language
+        // model's row, so the rounds' passes over the row find few to weigh): where these reach the
+        // target, the entries below them cannot move the threshold.  A distribution so flat that they do
+        // not is searched again over everything.
+        const unsigned int floor_key = __float_as_uint((float)((double)total * (1.0 / 65536.0) * (1.0 / 1099511627776.0)));
+        bool reached = false;
+        unsigned int u = 0;
+        if (floor_key > lo_key) u = select_key(cluster, &mine, turn, p, begin, end, floor_key, target, 1, warp_hist, &reached);
+        if (!reached) u = select_key(cluster, &mine, turn, p, begin, end, lo_key, target, 1, warp_hist);
         lo_key = u > lo_key ? u : lo_key;
     }
     // what is left; its sum renormalises the draw

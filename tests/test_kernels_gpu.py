@@ -900,6 +900,25 @@ def test_sample_matches_the_reference_draws(V):
     assert got == expected
 
 
+def test_top_p_threshold_with_and_without_the_heavy_entries_reaching_it():
+    """The top-p search looks at the entries of at least 1/65536 of the mass first.  Peaked rows (a few
+    tokens carry the mass: those entries reach the target) and flat rows over a vocabulary of 151,936
+    (no entry is that heavy, or too few: the search runs again over everything) give the reference's draws."""
+    from kairyu_b200.sampling.rng import as_signed64, mix_seed
+
+    V, n = 151936, 12
+    g = torch.Generator().manual_seed(46)
+    logits = torch.randn(n, V, generator=g)
+    logits[0::3] *= 0.01                       # flat: every entry near 1 / V
+    logits[1::3] *= 4.0                        # peaked
+    logits[2::3] = logits[2::3] * 0.3          # flat, with a handful of heavy tokens that hold a third of the mass
+    logits[2::3, :5] += 10.5
+    top_p = [0.9, 0.9, 0.9, 0.5, 0.5, 0.5, 0.99, 0.99, 0.2, 0.05, 0.999, 0.7]
+    seeds = [as_signed64(mix_seed(77 + r, r)) for r in range(n)]
+    got, expected = _sample_both(logits, [1.0] * n, [-1] * n, top_p, [0.0] * n, seeds)
+    assert got == expected
+
+
 def test_sample_respects_the_filters_over_many_seeds():
     from kairyu_b200.sampling.rng import as_signed64, mix_seed
 
