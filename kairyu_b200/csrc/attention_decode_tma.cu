@@ -70,12 +70,22 @@ __device__ __forceinline__ int tile_offset(int key, int band, int chunk, int run
     return row * 64 + ((chunk ^ (key & 7)) << 3);
 }
 
+// Stages of the ring by default.  Head size 64 has a second choice, three stages: four blocks fit an SM
+// then instead of three, which the launcher takes when the grid would not fit the SMs at once otherwise
+// (64 rows x 8 KV heads = 512 blocks against 444 places: the 68 blocks of the second wave ran nearly
+// alone and the kernel took 63 us; with 592 places it takes 45, at 91 % of the copy bandwidth).  Smaller
+// grids keep four stages: a block alone on its SM needs the bytes in flight.
 template <int D>
+struct TmaStages {
+    static constexpr int value = D <= 64 ? 4 : D <= 128 ? 3 : D <= 192 ? 2 : 3;
+};
+
+template <int D, int ST = TmaStages<D>::value>
 struct TmaSmem {
     static constexpr int HALVES = D / 64;
     static constexpr int TILE_ELEMS = HALVES * HALF_ELEMS;  // K (or V) of one tile
     static constexpr int STAGE_ELEMS = 2 * TILE_ELEMS;      // K then V
-    static constexpr int STAGES = D <= 64 ? 4 : D <= 128 ? 3 : D <= 192 ? 2 : 3;
+    static constexpr int STAGES = ST;
     static constexpr size_t RING_BYTES = (size_t)STAGES * STAGE_ELEMS * 2;
     static constexpr size_t Q_BYTES = (size_t)16 * Tile<D>::STRIDE * 2;
     static constexpr size_t MERGE_BYTES = (size_t)(4 * 16 * (D + 8) + 2 * 4 * 16) * sizeof(float);
@@ -95,7 +105,7 @@ __device__ __forceinline__ void split_range(int first, int last, int num_splits,
 // map_k has that distance as its fourth dimension in place of the bands, so that one copy brings a run
 // of rows of the keys AND of the values (twice the bytes a copy; with 2 KB copies the SM's copy rate
 // weighed on the kernel).  In shared memory a stage is then [run][K | V][position][64].
-template <int D, bool JOINED>
+template <int D, bool JOINED, int ST>
 __global__ void __launch_bounds__(TMA_THREADS)
 attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ q, int q_stride, const int* __restrict__ seq_lens,
@@ -103,7 +113,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size, int page_shift,
                             int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,
                             float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
-    using S = TmaSmem<D>;
+    using S = TmaSmem<D, ST>;
     constexpr int HALVES = S::HALVES;
     static_assert(!JOINED || HALVES == 1, "keys and values share a copy at head_dim 64 only");
     constexpr int LAY = JOINED ? 2 : HALVES;  // 64-column blocks side by side in a run of the layout
@@ -447,16 +457,29 @@ int get_encoder() {
     return 0;
 }
 
-// Blocks of the kernel that fit the device at once (0 on error).
+// Blocks of the kernel (with its default number of stages) that fit the device at once (0 on error).
 template <int D>
 int resident_blocks() {
     static int cached = -1;
     if (cached >= 0) return cached;
-    if (cudaFuncSetAttribute(attention_decode_tma_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
+    if (cudaFuncSetAttribute(attention_decode_tma_kernel<D, false, TmaStages<D>::value>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
     int device = 0, sms = 0, per_sm = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<D, false>, TMA_THREADS, TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<D, false, TmaStages<D>::value>, TMA_THREADS, TmaSmem<D>::TOTAL) != cudaSuccess) return 0;
+    cached = sms * per_sm;
+    return cached;
+}
+
+// Blocks that fit the device at once when the grid is crowded (head size 64: the three-stage ring).
+int crowded_blocks_64() {
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    if (cudaFuncSetAttribute(attention_decode_tma_kernel<64, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<64, 3>::TOTAL) != cudaSuccess) return 0;
+    int device = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<64, false, 3>, TMA_THREADS, TmaSmem<64, 3>::TOTAL) != cudaSuccess) return 0;
     cached = sms * per_sm;
     return cached;
 }
@@ -471,18 +494,18 @@ int resident_blocks_for(int D) {
     }
 }
 
-template <int D, bool JOINED>
+template <int D, bool JOINED, int ST = TmaStages<D>::value>
 int launch(const CUtensorMap* mk, const CUtensorMap* mv, const __nv_bfloat16* q, int q_stride, const int* seq_lens,
            const int* block_table, int max_pages, const int* decode_rows, const int* decode_tokens, int num_rows, int Hq,
            int Hkv, int page_size, int num_pages, float scale, int window, int num_splits, float* part_o, float* part_ml,
            __nv_bfloat16* out, int out_stride, int combine, int* flag, cudaStream_t stream) {
-    const size_t smem = TmaSmem<D>::TOTAL;
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, JOINED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = TmaSmem<D, ST>::TOTAL;
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_tma_kernel<D, JOINED, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     int shift = 0;
     while ((1 << shift) < page_size) ++shift;  // page_size is a power of two here
     dim3 grid(num_rows, Hkv, num_splits);
-    kb_launch(attention_decode_tma_kernel<D, JOINED>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
+    kb_launch(attention_decode_tma_kernel<D, JOINED, ST>, dim3(grid), dim3(TMA_THREADS), smem, stream, *mk, *mv, q, q_stride, seq_lens,
               block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, shift, num_pages, scale,
               window, num_splits, part_o, part_ml, out, out_stride, combine, flag);
     return kb_launch_result();
@@ -508,6 +531,19 @@ KB_EXPORT int kb_attention_decode_tma_splits(int num_rows, int Hkv, int D, int m
     long long splits = resident / pairs;
     const int tiles = (max_seq_len + TILE_N - 1) / TILE_N;
     const int worthwhile = (tiles + MIN_TILES_PER_SPLIT - 1) / MIN_TILES_PER_SPLIT;
+    if (pairs > resident) {
+        // More (row, KV head) pairs than places: with one block a pair, the blocks beyond the first wave
+        // run nearly alone (304 pairs on 296 places took 76 us where 288 take 50).  Two splits a pair make
+        // the last wave a smaller share: in units of a whole pair's time the kernel takes about
+        // ceil(2 * pairs / places) / 2, and the merge launch and the second start a tenth.  Taken where
+        // that gains 15 % or more on ceil(pairs / places): measured 8-9 % on the kernel at 38 to 48 rows of
+        // 8 KV heads (head size 128), nothing or a loss outside that range and with more splits.
+        const int places = D == 64 ? crowded_blocks_64() : resident;
+        if (places <= 0) return KB_ERR_UNSUPPORTED_SIZE;
+        const double whole = (double)((pairs + places - 1) / places);
+        const double halves = (double)((pairs * 2 + places - 1) / places) / 2 + 0.1;
+        return (worthwhile >= 2 && halves < 0.85 * whole) ? 2 : 1;
+    }
     if (splits > worthwhile) splits = worthwhile;
     if (splits > MAX_SPLITS) splits = MAX_SPLITS;
     if (splits < 1) splits = 1;
@@ -599,7 +635,13 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
 #define ARGS mk, mv, (const __nv_bfloat16*)q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, num_rows, Hq, \
              Hkv, page_size, num_pages, scale, window, num_splits, part_o, part_ml, (__nv_bfloat16*)out, out_stride, combine, flag, stream
     switch (D) {
-        case 64: rc = joined ? launch<64, true>(ARGS) : launch<64, false>(ARGS); break;
+        case 64: {
+            // a grid that four-stage blocks cannot hold at once runs with three stages, four blocks an SM
+            const bool crowded = (long long)num_rows * Hkv * num_splits > resident_blocks<64>();
+            if (crowded) rc = joined ? launch<64, true, 3>(ARGS) : launch<64, false, 3>(ARGS);
+            else rc = joined ? launch<64, true>(ARGS) : launch<64, false>(ARGS);
+            break;
+        }
         case 128: rc = launch<128, false>(ARGS); break;
         case 192: rc = launch<192, false>(ARGS); break;
         default: rc = launch<256, false>(ARGS); break;

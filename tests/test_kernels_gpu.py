@@ -646,6 +646,36 @@ def test_decode_attention_fetches_keys_and_values_in_one_copy(Hq, Hkv, page_size
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("joined", [True, False])
+@pytest.mark.parametrize("window", [0, 333])
+def test_decode_attention_of_a_grid_too_large_for_one_wave(joined, window, workspace):
+    """Head size 64, 60 rows x 8 KV heads: more blocks than fit the SMs at once with the four-stage ring,
+    so the launcher takes the three-stage one (four blocks an SM); rows of 1 to 900 keys, so that the
+    ring wraps several times in the long ones."""
+    Hq, Hkv, D, page_size = 16, 8, 64, 16
+    seq_lens = [1 + (37 * r) % 900 for r in range(60)]
+    seq_lens[7], seq_lens[8] = 900, 64
+    case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, [1] * len(seq_lens), seed=43)
+    scale = 1.0 / math.sqrt(D)
+    expected = _reference_attention(case, Hq, scale, window)
+    both = torch.stack([case["kc"], case["vc"]] if joined else [case["vc"], case["kc"]]).to(DEV)
+    kc, vc = (both[0], both[1]) if joined else (both[1], both[0])
+    k = kernels()
+    assert (k._joined_cache_map(kc, vc) != 0) == joined
+    resident = k._fn("attention_decode_tma", "kb_attention_decode_tma_splits", [c_int] * 4)
+    assert resident(len(seq_lens), Hkv, D, max(seq_lens)) == 1  # no room for a second split: the grid is crowded
+    rows = torch.arange(len(seq_lens), dtype=torch.int32, device=DEV)
+    out = torch.zeros(case["q"].shape, dtype=torch.bfloat16, device=DEV)
+    flag = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.attention_decode_mma(
+        case["q"].to(DEV), out, kc, vc, seq_lens=case["seq_lens"].to(DEV), block_table=case["table"].to(DEV),
+        decode_rows=rows, decode_tokens=rows, num_rows=len(seq_lens), max_seq_len=max(seq_lens), num_q_heads=Hq,
+        scale=scale, window=window, workspace=workspace, flag=flag,
+    )
+    assert int(flag.item()) == 0
+    close(out, expected, 2e-2)
+
+
 def _run_prefill(case, Hq, scale, window, workspace, num_splits, max_seq_len=0, two_tiles=None):
     k = kernels()
     qo = case["qo"].tolist()
