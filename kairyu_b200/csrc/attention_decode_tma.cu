@@ -106,13 +106,13 @@ __device__ __forceinline__ void split_range(int first, int last, int num_splits,
 // of rows of the keys AND of the values (twice the bytes a copy; with 2 KB copies the SM's copy rate
 // weighed on the kernel).  In shared memory a stage is then [run][K | V][position][64].
 template <int D, bool JOINED, int ST>
-__global__ void __launch_bounds__(TMA_THREADS)
-attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                            const __nv_bfloat16* __restrict__ q, int q_stride, const int* __restrict__ seq_lens,
-                            const int* __restrict__ block_table, int max_pages, const int* __restrict__ decode_rows,
-                            const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size, int page_shift,
-                            int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,
-                            float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
+__device__ __forceinline__ void
+attention_decode_tma_body(const CUtensorMap& map_k, const CUtensorMap& map_v,
+                          const __nv_bfloat16* __restrict__ q, int q_stride, const int* __restrict__ seq_lens,
+                          const int* __restrict__ block_table, int max_pages, const int* __restrict__ decode_rows,
+                          const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size, int page_shift,
+                          int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,
+                          float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag) {
     using S = TmaSmem<D, ST>;
     constexpr int HALVES = S::HALVES;
     static_assert(!JOINED || HALVES == 1, "keys and values share a copy at head_dim 64 only");
@@ -410,6 +410,26 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     }
 }
 
+#define DECODE_TMA_PARAMS                                                                                                 \
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16* __restrict__ q, \
+        int q_stride, const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages,                  \
+        const int* __restrict__ decode_rows, const int* __restrict__ decode_tokens, int Hq, int Hkv, int page_size,          \
+        int page_shift, int num_pages, float scale, int window, int num_splits, float* __restrict__ part_o,                  \
+        float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int out_stride, int combine, int* flag
+#define DECODE_TMA_ARGS                                                                                                     \
+    map_k, map_v, q, q_stride, seq_lens, block_table, max_pages, decode_rows, decode_tokens, Hq, Hkv, page_size, page_shift, \
+        num_pages, scale, window, num_splits, part_o, part_ml, out, out_stride, combine, flag
+
+template <int D, bool JOINED, int ST>
+__global__ void __launch_bounds__(TMA_THREADS) attention_decode_tma_kernel(DECODE_TMA_PARAMS) {
+    attention_decode_tma_body<D, JOINED, ST>(DECODE_TMA_ARGS);
+}
+// head size 128 with two stages: registers held to what lets three blocks share an SM
+template <>
+__global__ void __launch_bounds__(TMA_THREADS, 3) attention_decode_tma_kernel<128, false, 2>(DECODE_TMA_PARAMS) {
+    attention_decode_tma_body<128, false, 2>(DECODE_TMA_ARGS);
+}
+
 // grid (rows, Hq); combines the splits a row has, in split order.
 __global__ void attention_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                   const int* __restrict__ seq_lens, const int* __restrict__ decode_rows,
@@ -484,6 +504,29 @@ int crowded_blocks_64() {
     return cached;
 }
 
+// Head size 128 has a second choice too: two stages, and registers held to what lets three blocks share
+// an SM (444 places instead of 296).  Taken for a grid beyond 296 blocks whose whole waves of 444 hold no
+// more places than its whole waves of 296 (38 to 55 rows of 8 KV heads: one wave, 55-66 us against 76-83;
+// 75 to 111 rows: two waves against three, 115 us against 128 at 80 rows; 56 to 74 rows stay with two
+// waves of 296: 84-98 us against 100-113).
+int crowded_blocks_128() {
+    static int cached = -1;
+    if (cached >= 0) return cached;
+    if (cudaFuncSetAttribute(attention_decode_tma_kernel<128, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TmaSmem<128, 2>::TOTAL) != cudaSuccess) return 0;
+    int device = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_decode_tma_kernel<128, false, 2>, TMA_THREADS, TmaSmem<128, 2>::TOTAL) != cudaSuccess) return 0;
+    cached = sms * per_sm;
+    return cached;
+}
+
+bool dense_128(long long blocks) {
+    const long long usual = resident_blocks<128>(), dense = crowded_blocks_128();
+    if (usual <= 0 || dense <= 0 || blocks <= usual) return false;
+    return (blocks + dense - 1) / dense * dense <= (blocks + usual - 1) / usual * usual;
+}
+
 int resident_blocks_for(int D) {
     switch (D) {
         case 64: return resident_blocks<64>();
@@ -540,6 +583,7 @@ KB_EXPORT int kb_attention_decode_tma_splits(int num_rows, int Hkv, int D, int m
         // 8 KV heads (head size 128), nothing or a loss outside that range and with more splits.
         const int places = D == 64 ? crowded_blocks_64() : resident;
         if (places <= 0) return KB_ERR_UNSUPPORTED_SIZE;
+        if (D == 128 && dense_128(pairs)) return 1;  // whole waves of three blocks an SM
         const double whole = (double)((pairs + places - 1) / places);
         const double halves = (double)((pairs * 2 + places - 1) / places) / 2 + 0.1;
         return (worthwhile >= 2 && halves < 0.85 * whole) ? 2 : 1;
@@ -642,7 +686,12 @@ KB_EXPORT int kb_attention_decode_tma(const void* map_k, const void* map_v, cons
             else rc = joined ? launch<64, true>(ARGS) : launch<64, false>(ARGS);
             break;
         }
-        case 128: rc = launch<128, false>(ARGS); break;
+        case 128: {
+            const long long blocks = (long long)num_rows * Hkv * num_splits;
+            if (dense_128(blocks)) rc = launch<128, false, 2>(ARGS);
+            else rc = launch<128, false>(ARGS);
+            break;
+        }
         case 192: rc = launch<192, false>(ARGS); break;
         default: rc = launch<256, false>(ARGS); break;
     }

@@ -648,12 +648,15 @@ def test_decode_attention_fetches_keys_and_values_in_one_copy(Hq, Hkv, page_size
 
 @pytest.mark.parametrize("joined", [True, False])
 @pytest.mark.parametrize("window", [0, 333])
-def test_decode_attention_of_a_grid_too_large_for_one_wave(joined, window, workspace):
-    """Head size 64, 60 rows x 8 KV heads: more blocks than fit the SMs at once with the four-stage ring,
-    so the launcher takes the three-stage one (four blocks an SM); rows of 1 to 900 keys, so that the
-    ring wraps several times in the long ones."""
-    Hq, Hkv, D, page_size = 16, 8, 64, 16
-    seq_lens = [1 + (37 * r) % 900 for r in range(60)]
+@pytest.mark.parametrize("D,count", [(64, 60), (128, 40)])
+def test_decode_attention_of_a_grid_too_large_for_one_wave(joined, window, D, count, workspace):
+    """60 rows x 8 KV heads at head size 64, 40 at 128: more blocks than fit the SMs at once with the
+    usual ring, so the launcher takes the one with a stage less and a block more an SM; rows of 1 to 900
+    keys, so that the ring wraps several times in the long ones."""
+    Hq, Hkv, page_size = 16, 8, 16
+    if D != 64 and joined:
+        pytest.skip("keys and values share a copy at head size 64 only")
+    seq_lens = [1 + (37 * r) % 900 for r in range(count)]
     seq_lens[7], seq_lens[8] = 900, 64
     case = _attention_case(torch.bfloat16, Hq, Hkv, D, page_size, seq_lens, [1] * len(seq_lens), seed=43)
     scale = 1.0 / math.sqrt(D)
