@@ -189,6 +189,23 @@ class ClockSampler:
         }
 
 
+def layers_that_fit(layers: int, max_batch: int) -> int:
+    """The most layers, up to ``layers``, whose bf16 weights (held twice while random weights are drawn and
+    packed) and whose cache for ``max_batch`` requests fit in nine tenths of the device's free memory."""
+    import torch
+
+    hidden, inter = MODEL["hidden_size"], MODEL["intermediate_size"]
+    head_dim = MODEL.get("head_dim") or hidden // MODEL["num_attention_heads"]
+    q, kv = MODEL["num_attention_heads"] * head_dim, MODEL["num_key_value_heads"] * head_dim
+    layer_weights = 2 * (hidden * (q + 2 * kv) + q * hidden + 3 * hidden * inter)
+    tables = 2 * MODEL["vocab_size"] * hidden * (1 if MODEL.get("tie_word_embeddings") else 2)
+    tokens = max_batch * (-(-(PROMPT_LEN + GEN_LEN + 64) // PAGE_SIZE)) * PAGE_SIZE
+    layer_cache = 2 * 2 * kv * tokens
+    free, _ = torch.cuda.mem_get_info()
+    room = 0.9 * free - 2 * tables - (4 << 30)  # workspace, logits, graphs
+    return max(0, min(layers, int(room // (2 * layer_weights + layer_cache))))
+
+
 def build_engine(layers: int, max_batch: int):
     import torch
 
@@ -641,6 +658,14 @@ def main() -> int:
     torch.cuda.set_device(0)
     peaks, peak_source = load_peaks()
     max_batch = max(args.batch, 1 if args.no_points else 64)
+    fitting = layers_that_fit(args.layers, max_batch)
+    if fitting < 1:
+        print("bench.py: not even one layer of this shape and its cache fit the device's free memory", file=sys.stderr)
+        return 1
+    if fitting < args.layers:
+        print(f"bench.py: {args.layers} layers of this shape do not fit the device beside their cache; running {fitting} "
+              "(the line's config names both numbers)", file=sys.stderr)
+        args.layers = fitting
     engine, config = build_engine(args.layers, max_batch)
     model = engine.model
     weight_bytes = model.bytes_streamed_per_step()
