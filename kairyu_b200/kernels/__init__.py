@@ -637,7 +637,7 @@ def linear(x, weight: torch.Tensor, bias: Optional[torch.Tensor], out: Optional[
         raise KernelError(f"linear: dtypes {x.dtype} / {weight.dtype} are not supported")
     if M == 0:
         return
-    if few_rows(M) and _skinny_ok(x, weight, bias, out):
+    if few_rows(M, max(K, N)) and _skinny_ok(x, weight, bias, out):
         _gemm_skinny(x, weight, bias, out, gated=False)
         return
     if out.dtype == torch.bfloat16:
@@ -659,11 +659,18 @@ SKINNY_MAX_ROWS = 16  # token rows the weight-streaming product takes (csrc/gemm
 # encoding as kernels of their own (measured at 9, 12 and 16 rows; a two-tile variant without
 # register spills, one k step a batch, was no faster).
 SKINNY_FAST_ROWS = 8
+# A narrow model is the exception: at width 2,048 a layer's products are 8 to 67 MB and take 5-15 us each, so
+# the three launches a layer that the fusions save weigh more than the second token tile costs (16 layers of
+# that width, 12 rows: 1.08 -> 0.96 ms a step; 16 rows: 1.14 -> 1.04).
+SKINNY_NARROW_WIDTH = 2048
 
 
-def few_rows(rows: int) -> bool:
-    """Whether a step of this many token rows runs on the weight-streaming product and its fusions."""
-    return 1 <= rows <= SKINNY_FAST_ROWS
+def few_rows(rows: int, width: Optional[int] = None) -> bool:
+    """Whether a step of this many token rows runs on the weight-streaming product and its fusions;
+    ``width``: the larger side of the product, or the residual's width for a layer's chain of products."""
+    if 1 <= rows <= SKINNY_FAST_ROWS:
+        return True
+    return width is not None and 1 <= rows <= SKINNY_MAX_ROWS and width <= SKINNY_NARROW_WIDTH
 
 
 def _skinny_ok(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> bool:
@@ -832,7 +839,7 @@ def fused_norm_shapes_ok(rows: int, hidden: int, *feature_sizes: int) -> bool:
     write) and these other sizes can all take the fused path.  The product that scales adds one
     partial sum per block of the product that folded: a residual so wide that the folding product
     is launched with more blocks than it can add up keeps the norm kernel."""
-    if not few_rows(rows) or hidden % 16 != 0 or any(size % 16 != 0 for size in feature_sizes):
+    if not few_rows(rows, hidden) or hidden % 16 != 0 or any(size % 16 != 0 for size in feature_sizes):
         return False
     fits = _fold_fits.get((rows, hidden))
     if fits is None:
@@ -961,7 +968,7 @@ def linear_swiglu(x, weight_gate_up: torch.Tensor, out: torch.Tensor, scratch: o
     if M == 0:
         return
     if x.dtype == torch.bfloat16 and weight_gate_up.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-        if few_rows(M) and _skinny_ok(x, weight_gate_up, None, out):
+        if few_rows(M, x.shape[1]) and _skinny_ok(x, weight_gate_up, None, out):
             _gemm_skinny(x, weight_gate_up, None, out, gated=True)
             return
         if _tc5_ok(x, weight_gate_up, None, out) and weight_gate_up.numel() * 2 >= TC5_MIN_WEIGHT_BYTES:

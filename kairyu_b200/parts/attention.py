@@ -283,7 +283,7 @@ class GQAAttention(Mixer):
             flag=ctx.error_flag,
         )
         heads = dict(num_q_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim)
-        if not self.qk_norm and kernels.few_rows(tokens) and kernels.linear_rope_ok(x, self.w_qkv, self.b_qkv, qkv, cos=cos, k_cache=placement["k_cache"], **heads):
+        if not self.qk_norm and kernels.few_rows(tokens, self.hidden_size) and kernels.linear_rope_ok(x, self.w_qkv, self.b_qkv, qkv, cos=cos, k_cache=placement["k_cache"], **heads):
             # a few bf16 rows: the rotation and the cache write ride in the product's epilogue
             kernels.linear_rope(x, self.w_qkv, self.b_qkv, qkv, cos=cos, sin=sin, **heads, **placement)
         else:
