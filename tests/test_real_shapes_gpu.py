@@ -149,12 +149,12 @@ def test_every_cut_at_real_layer_sizes(shape, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_decode_steps_of_many_rows_at_real_layer_sizes(shape, dtype):
-    """12, 16, 24 and 64 live requests decoded together: graphs of the batch buckets beyond 8, where
+    """12, 16, 24, 40 and 64 live requests decoded together: graphs of the batch buckets beyond 8, where
     the products, the norms and the position encoding go through other kernels than up to 8 rows."""
     config = shape["config"]
     tail = 5
     runner = make_runner(shape, dtype, num_pages=64 * 6 + 1, max_graph_batch=64)
-    for rows in (12, 16, 24, 64):
+    for rows in (12, 16, 24, 40, 64):
         generator = torch.Generator().manual_seed(rows)
         lengths = torch.randint(tail + 1, 80, (rows,), generator=generator).tolist()
         requests = {f"m{rows}-{i}": t for i, t in enumerate(traces.make_requests(config["vocab_size"], lengths, seed=40 + rows).values())}
