@@ -455,10 +455,10 @@ __device__ __forceinline__ unsigned long long mass_units(float pv) { return (uns
 // Smallest 32-bit key u such that weight{ key_i > u, key_i >= lo_key } < target,
 // where key_i are the bits of the non-negative floats p_i and weight is a count
 // (use_sum = 0) or the sum of p_i in units of 2^-40 (use_sum = 1).  Radix descent, 8 bits a round (four
-// rounds): every block builds the histogram of its slice [begin, end) in shared memory (lanes with the
-// same digit add up in the warp first: most of a row shares a few exponents), thread t adds up bin t
-// of all the cluster's blocks, one thread walks the 256 bins from the top, and all blocks return the same
-// u.  Requires target > 0 and a block of at least 256 threads.
+// rounds): every block builds the histogram of its slice [begin, end) in shared memory (one histogram a
+// warp; lanes with the same digit add up among themselves first: most of a row shares a few exponents),
+// thread t adds up bin t of all the cluster's blocks, a warp walks the 256 bins from the top, and all
+// blocks return the same u.  Requires target > 0 and a block of at least 256 threads.
 __device__ unsigned int select_key(cg::cluster_group& cluster, ClusterScratch* mine, int& turn, const float* __restrict__ p, int begin,
                                    int end, unsigned int lo_key, unsigned long long target, int use_sum,
                                    unsigned long long (*warp_hist)[256], bool* reached = nullptr) {
