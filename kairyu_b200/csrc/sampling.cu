@@ -350,6 +350,27 @@ __device__ __forceinline__ double gumbel_noise(int i, unsigned long long seed) {
     return -log(-log1p(-u));
 }
 
+// The same noise in 32-bit arithmetic, within NOISE_SLACK of the 64-bit value over the whole range of u:
+// below one half, log1pf keeps the relative precision of a small u; above, 1 - u is taken from the integer.
+// It only decides which entries the 64-bit noise is computed for.
+#define NOISE_SLACK 1e-3f
+__device__ __forceinline__ float gumbel_noise_estimate(int i, unsigned long long seed) {
+    const unsigned long long counter = ((unsigned long long)i + 1ull) * 0x9E3779B97F4A7C15ull;
+    const unsigned long long word = splitmix_finalize(counter ^ seed);
+    // u = (k + 0.5) / 2^52 and 1 - u = ((2^52 - 1 - k) + 0.5) / 2^52: whichever is at most one half, from the
+    // integer, so that no 64-bit arithmetic is left in the estimate
+    const unsigned long long k = word & ((1ull << 52) - 1ull);
+    const bool low = k < (1ull << 51);
+    const float t = ((float)(low ? k : (1ull << 52) - 1ull - k) + 0.5f) * 2.220446049250313e-16f;
+    // -log(1 - t) for t in (0, 1/2]: the series where 1 - t would round the small t away (its next term is
+    // below t^3 / 4 of the sum), the fast logarithm elsewhere (absolute error 2^-21 on a value of at least
+    // 1 / 256); then the fast logarithm of that level: together some 1e-4, a tenth of NOISE_SLACK
+    float level;
+    if (low) level = t < 0.00390625f ? t * (1.0f + t * (0.5f + t * 0.33333334f)) : -__logf(1.0f - t);
+    else level = -__logf(t);
+    return -__logf(level);
+}
+
 // ---- stage 1 runs as a thread-block cluster per row: SAMPLE_CLUSTER blocks share the row's passes
 // (each block owns a slice of the vocabulary) and combine their partial results through
 // distributed shared memory, in rank order, so every block holds the same totals.
@@ -713,16 +734,37 @@ sample_noise_kernel(const float* __restrict__ work, int V, const SampleRowState*
     const int begin = blockIdx.y * per;
     const int end = min(begin + per, V);
     const unsigned long long seed = seeds[r];
+    // The 64-bit logarithms are what this kernel's time goes to, and all but the chunk's few best entries
+    // lose by far.  A first pass takes the chunk's largest value in 32-bit arithmetic, which is within
+    // NOISE_SLACK of the 64-bit one for every entry; the second computes the 64-bit value only where the
+    // 32-bit one comes within twice that of the largest, which the winner in 64-bit does by construction.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float fv[SAMPLE_NOISE_THREADS / 32];
+    float near_best = -INFINITY;
+    for (int i = begin + threadIdx.x; i < end; i += SAMPLE_NOISE_THREADS) {
+        const float pv = p[i];
+        if (pv > 0.0f && __float_as_uint(pv) >= st.lo_key) near_best = fmaxf(near_best, __logf(pv) + gumbel_noise_estimate(i, seed));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) near_best = fmaxf(near_best, __shfl_xor_sync(0xffffffffu, near_best, o));
+    if (lane == 0) fv[warp] = near_best;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < SAMPLE_NOISE_THREADS / 32; ++w) near_best = fmaxf(near_best, fv[w]);
+    const float bar = near_best - 2.0f * NOISE_SLACK - 1e-6f * fabsf(near_best);  // and the rounding of the 32-bit sum itself
     double best = -INFINITY;
     int best_index = 0x7fffffff;
     for (int i = begin + threadIdx.x; i < end; i += SAMPLE_NOISE_THREADS) {
         const float pv = p[i];
         if (pv > 0.0f && __float_as_uint(pv) >= st.lo_key) {
+            // (the row's log kept is the same for all: left out of the 32-bit values; keeping the first pass's
+            // values in shared memory instead of computing them again gained 13 us at 64 unfiltered rows and
+            // lost 10 at 64 filtered ones, whose blocks then share an SM with fewer others)
+            if (__logf(pv) + gumbel_noise_estimate(i, seed) < bar) continue;
             const double v = (double)logf(pv / st.kept) + gumbel_noise(i, seed);
             if (v > best || (v == best && i < best_index)) { best = v; best_index = i; }
         }
     }
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const double ov = __shfl_xor_sync(0xffffffffu, best, o);
