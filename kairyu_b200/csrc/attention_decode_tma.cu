@@ -29,6 +29,12 @@
 // 0.5 % slower, because the merge kernel's early trigger lets the output projection fetch its
 // first weights while the merge runs.)  Sizes: head_dim a multiple of 64 up to 256, page_size a power of two from 8 up;
 // anything else goes to the row-copy kernel of attention_mma.cuh.
+//
+// Variants the launcher chooses between.  At head_dim 64 a key row is 128 bytes and a copy of a run 2 KB: where
+// the cache keeps the values a fixed distance behind the keys, one copy brings both (JOINED).  A grid that does
+// not fit the SMs at once leaves a last wave of few blocks that run nearly alone; head_dim 64 and 128 each have a
+// ring with a stage less whose blocks sit one more to an SM (TmaStages, dense_128), taken when that lets the grid
+// run in fewer or fuller waves.
 #include "attention_mma.cuh"
 
 #include <cuda.h>
