@@ -288,13 +288,13 @@ qk_norm_rope_kv_write_many_kernel(T* __restrict__ qkv, int qkv_stride, int Hq, i
     }
 }
 
-// Many bf16 tokens with heads of 128 that rotate whole: eight lanes take one token and walk a slice
-// of its heads, sixteen bytes a lane at a time (eight elements of the first half and their partners
-// of the second), so a token's cos and sin rows are fetched once for all its heads and every access
-// is 16 bytes wide.  All loads of a lane's heads go out before the first result is stored.  Same
-// arithmetic as the kernels above.
-#define ROPE_WIDE_TOKENS 4   // tokens a block of 256 threads takes: eight 8-lane groups a token
-#define ROPE_WIDE_HEADS 8    // heads a group may be dealt: (Hq + 2 Hkv) <= 8 * 8
+// Many bf16 tokens with heads of 128 or 64 that rotate whole: D / 16 lanes take one head at a time and
+// walk a slice of the token's heads, sixteen bytes a lane at a time (eight elements of the first half
+// and their partners of the second), so a token's cos and sin rows are fetched once for all its heads
+// and every access is 16 bytes wide.  All loads of a lane's heads go out before the first result is
+// stored.  Same arithmetic as the kernels above.
+#define ROPE_WIDE_TOKENS 4   // tokens a block of 256 threads takes: 64 threads a token
+#define ROPE_WIDE_HEADS 8    // heads a group of lanes may be dealt: (Hq + 2 Hkv) <= 8 * (64 / (D / 16))
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -313,7 +313,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return v;
 }
 
-template <typename TW>
+template <typename TW, int D>
 __global__ void __launch_bounds__(256)
 qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_stride, int Hq, int Hkv,
                                   const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
@@ -323,11 +323,13 @@ qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_strid
                                   __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, int page_size,
                                   int num_pages, int tokens, int* flag) {
     pdl_trigger();
-    constexpr int D = 128, HALF = 64;
-    const int group = threadIdx.x >> 3;   // 32 groups of eight lanes
-    const int sub = threadIdx.x & 7;      // this lane's 8 elements of each half
-    const int t = blockIdx.x * ROPE_WIDE_TOKENS + (group >> 3);
-    const int slice = group & 7;          // heads slice, slice + 8, ...
+    static_assert(D == 128 || D == 64, "heads of 128 or 64");
+    constexpr int HALF = D / 2;
+    constexpr int LANES = HALF / 8;       // lanes that share a head: 8 elements of each half a lane
+    constexpr int SLICES = 64 / LANES;    // groups of lanes a token has
+    const int sub = threadIdx.x % LANES;  // this lane's 8 elements of each half
+    const int t = blockIdx.x * ROPE_WIDE_TOKENS + (threadIdx.x >> 6);
+    const int slice = (threadIdx.x / LANES) % SLICES;  // heads slice, slice + SLICES, ...
     const int heads = Hq + 2 * Hkv;
     // the step's description comes from the host's copy, not from the kernel before: looked up ahead of the wait
     int pos = 0;
@@ -366,7 +368,7 @@ qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_strid
     uint4 lo_raw[ROPE_WIDE_HEADS], hi_raw[ROPE_WIDE_HEADS];
 #pragma unroll
     for (int n = 0; n < ROPE_WIDE_HEADS; ++n) {
-        const int head = slice + 8 * n;
+        const int head = slice + SLICES * n;
         if (head < heads) {
             lo_raw[n] = *reinterpret_cast<const uint4*>(token + (size_t)head * D + sub * 8);
             hi_raw[n] = *reinterpret_cast<const uint4*>(token + (size_t)head * D + HALF + sub * 8);
@@ -374,7 +376,7 @@ qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_strid
     }
 #pragma unroll
     for (int n = 0; n < ROPE_WIDE_HEADS; ++n) {
-        const int head = slice + 8 * n;
+        const int head = slice + SLICES * n;
         if (head >= heads) break;
         if (head >= Hq + Hkv) {  // a value head: copied as it is
             if (slot >= 0) {
@@ -393,11 +395,10 @@ qk_norm_rope_kv_write_wide_kernel(__nv_bfloat16* __restrict__ qkv, int qkv_strid
             float ss = 0.0f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
-            // the head's eight lanes only: the other groups of the warp may be at other heads, or gone
-            const unsigned mates = 0xffu << ((threadIdx.x & 31) & ~7);
-            ss += __shfl_xor_sync(mates, ss, 1);
-            ss += __shfl_xor_sync(mates, ss, 2);
-            ss += __shfl_xor_sync(mates, ss, 4);
+            // the head's own lanes only: the other groups of the warp may be at other heads, or gone
+            const unsigned mates = ((1u << LANES) - 1u) << ((threadIdx.x & 31) & ~(LANES - 1));
+#pragma unroll
+            for (int step = 1; step < LANES; step <<= 1) ss += __shfl_xor_sync(mates, ss, step);
             const float inv = rsqrtf(ss / (float)D + eps);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -448,17 +449,22 @@ KB_EXPORT int kb_qk_norm_rope_kv_write(void* qkv, int is_bf16, int T, int qkv_st
                         (D * elem) % 16 == 0 && ((size_t)qkv_stride * elem) % 16 == 0 && ((uintptr_t)qkv % 16) == 0 &&
                         ((uintptr_t)k_cache % 16) == 0 && ((uintptr_t)v_cache % 16) == 0 &&
                         ((uintptr_t)cos_table % 8) == 0 && ((uintptr_t)sin_table % 8) == 0;
-    // many bf16 tokens, heads of 128: eight lanes a token, 16 bytes a lane, cos and sin fetched once a token
-    if (paired && is_bf16 && D == 128 && T >= 256 && Hq + 2 * Hkv <= 8 * ROPE_WIDE_HEADS && ((uintptr_t)cos_table % 16) == 0 &&
-        ((uintptr_t)sin_table % 16) == 0) {
+    // many bf16 tokens, heads of 128 or 64: 16 bytes a lane, cos and sin fetched once a token
+    if (paired && is_bf16 && (D == 128 || D == 64) && T >= 256 && Hq + 2 * Hkv <= (64 / (D / 16)) * ROPE_WIDE_HEADS &&
+        ((uintptr_t)cos_table % 16) == 0 && ((uintptr_t)sin_table % 16) == 0) {
         dim3 wide((T + ROPE_WIDE_TOKENS - 1) / ROPE_WIDE_TOKENS);
-#define WIDE(TW_)                                                                                              \
-    kb_launch(qk_norm_rope_kv_write_wide_kernel<TW_>, dim3(wide), dim3(256), 0, stream, (__nv_bfloat16*)qkv,   \
+#define WIDE(TW_, D_)                                                                                          \
+    kb_launch(qk_norm_rope_kv_write_wide_kernel<TW_, D_>, dim3(wide), dim3(256), 0, stream, (__nv_bfloat16*)qkv, \
         qkv_stride, Hq, Hkv, (const TW_*)q_norm_w, (const TW_*)k_norm_w, eps, cos_table, sin_table, max_pos,   \
         positions, row_ids, block_table, max_pages, write_from, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, \
         page_size, num_pages, T, flag)
-        if (norm_w_bf16) WIDE(__nv_bfloat16);
-        else WIDE(float);
+        if (D == 128) {
+            if (norm_w_bf16) WIDE(__nv_bfloat16, 128);
+            else WIDE(float, 128);
+        } else {
+            if (norm_w_bf16) WIDE(__nv_bfloat16, 64);
+            else WIDE(float, 64);
+        }
 #undef WIDE
         return kb_launch_result();
     }
